@@ -1,0 +1,152 @@
+/*
+ * systemds_cla.h -- C ABI of the B200 compressed-linear-algebra (CLA) matrix-multiply library.
+ *
+ * The library owns device-resident copies of the column groups of a SystemDS
+ * CompressedMatrixBlock and runs the compressed matrix products on the GPU. Every entry point
+ * is plain C (pointers and sizes only); the JNI shim in systemds_b200/csrc/cla_jni.cpp maps
+ * 1:1 onto these calls. File:line citations name the reference interface each call replaces,
+ * by path below src/main/java/org/apache/sysds/ of the reference project.
+ *
+ * Conventions (those of the reference's native BLAS bridge, utils/NativeHelper.java:361-418 and
+ * src/main/cpp/systemds.cpp:59-82): dense operands are row-major FP64; product calls return the
+ * number of non-zeros of the result (>= 0) so the caller can setNonZeros(), or a negative
+ * CLA_ERR_* code. There is no CPU fallback: without a usable CUDA device every call fails.
+ *
+ * Threading: calls on one handle are serialised by an internal mutex; different handles may be
+ * used concurrently. The thread budget "k" of the reference's calls has no meaning here.
+ */
+#ifndef SYSTEMDS_CLA_H
+#define SYSTEMDS_CLA_H
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CLA_OK 0
+#define CLA_ERR_BAD_HANDLE (-1)
+#define CLA_ERR_BAD_ARG (-2)
+#define CLA_ERR_UNSUPPORTED (-3)
+#define CLA_ERR_SHAPE (-4)
+#define CLA_ERR_CUDA (-5)
+#define CLA_ERR_STATE (-6)   /* call order violated (e.g. product before finalize) */
+#define CLA_ERR_NOMEM (-7)
+#define CLA_ERR_DEVICE_CHECK (-8) /* a kernel's self-check tripped (index out of range in an index structure) */
+
+/* AMapToData storage classes, in the order of MapToFactory.MAP_TYPE
+ * (runtime/compress/colgroup/mapping/MapToFactory.java:38-40). Arrays are passed in the JVM's
+ * in-memory form: BIT = long[] LSB-first (MapToBit.java:100-103), UBYTE/BYTE = byte[],
+ * CHAR = char[] (u16), CHAR_BYTE = char[] + byte[] (id = c + (b << 16)), INT = int[]. */
+#define CLA_MAP_ZERO 0
+#define CLA_MAP_BIT 1
+#define CLA_MAP_UBYTE 2
+#define CLA_MAP_BYTE 3
+#define CLA_MAP_CHAR 4
+#define CLA_MAP_CHAR_BYTE 5
+#define CLA_MAP_INT 6
+
+/* AOffset storage classes (runtime/compress/colgroup/offset/OffsetFactory.java:105-149).
+ * BYTE covers OffsetByte, OffsetByteNZ and OffsetByteUNZ (same byte stream; the NZ variants
+ * simply contain no zero byte); CHAR covers OffsetChar. */
+#define CLA_OFF_EMPTY 0
+#define CLA_OFF_SINGLE 1
+#define CLA_OFF_TWO 2
+#define CLA_OFF_BYTE 3
+#define CLA_OFF_CHAR 4
+
+/* MapMultChain.ChainType (lops/MapMultChain.java) */
+#define CLA_CHAIN_XtXv 0
+#define CLA_CHAIN_XtwXv 1
+
+typedef int64_t cla_handle;
+
+/* Per-handle counters, the device-side analogue of utils/DMLCompressionStatistics.java:24-125. */
+typedef struct cla_stats {
+  int64_t n_rows, n_cols, n_groups;
+  int64_t device_bytes;      /* bytes held on the device for this matrix */
+  int64_t index_bytes;       /* bytes of index structures + dictionaries (one pass reads these) */
+  int64_t calls_rmm, calls_lmm, calls_tsmm, calls_mmchain, calls_decompress;
+  int64_t kernel_launches;   /* launches issued by this handle since creation */
+  double last_kernel_ms;     /* device time of the last product call (CUDA events) */
+} cla_stats;
+
+/* ---- life cycle ---------------------------------------------------------------------------
+ * Replaces the construction of a CompressedMatrixBlock's group list
+ * (runtime/compress/CompressedMatrixBlock.java:108-132). */
+cla_handle cla_create(int32_t nRows, int32_t nCols, int32_t overlapping);
+int64_t cla_destroy(cla_handle h);
+/* Uploads all groups to CUDA device `device`, builds skip indexes and launch plans.
+ * After this call the host arrays given to cla_add_group_* are no longer referenced. */
+int64_t cla_finalize(cla_handle h, int32_t device);
+/* Copies the message of the calling thread's last failed call into buf; returns its length. */
+int64_t cla_last_error(char* buf, int64_t cap);
+int64_t cla_stats_get(cla_handle h, cla_stats* out);
+
+/* ---- group registration (host arrays are copied) -------------------------------------------
+ * Each returns the index of the new group (>= 0) or a CLA_ERR_* code.
+ * colIdx: the group's IColIndex flattened to int32 (colgroup/indexes/ColIndexFactory.java:38-118).
+ * dict:   Dictionary values, row-major [nVals x gCols] (colgroup/dictionary/Dictionary.java:94-97). */
+
+/* ColGroupDDC {_colIndexes, _dict, _data} (colgroup/ColGroupDDC.java:79-89) */
+int64_t cla_add_group_ddc(cla_handle h, const int32_t* colIdx, int32_t gCols, const double* dict, int32_t nVals,
+                          int32_t mapType, const void* map, const void* mapHi, int64_t mapSize);
+/* ColGroupSDC / SDCZeros / SDCSingle / SDCSingleZeros (colgroup/ColGroupSDC.java:67-99,
+ * ColGroupSDCZeros.java:75-92, ColGroupSDCSingle.java:83-105, ColGroupSDCSingleZeros.java:82-93).
+ * defaultTuple NULL = the *Zeros variants; map NULL = the *Single* variants (one tuple, no map).
+ * offData holds offLen u8 (BYTE) or u16 (CHAR) deltas; nOffsets = AOffset.getSize(). */
+int64_t cla_add_group_sdc(cla_handle h, const int32_t* colIdx, int32_t gCols, const double* dict, int32_t nVals,
+                          const double* defaultTuple, int32_t offType, int32_t offsetToFirst, int32_t offsetToLast,
+                          const void* offData, int64_t offLen, int64_t nOffsets, int32_t mapType, const void* map,
+                          const void* mapHi);
+/* ColGroupRLE {_ptr, _data} (colgroup/AColGroupOffset.java:39-55, ColGroupRLE.java:114-117) */
+int64_t cla_add_group_rle(cla_handle h, const int32_t* colIdx, int32_t gCols, const double* dict, int32_t nVals,
+                          const int32_t* ptr, const uint16_t* data, int64_t dataLen);
+/* ColGroupOLE {_ptr, _data} (colgroup/ColGroupOLE.java:558-599). The reference has no arithmetic for
+ * this group (its product methods throw); here it takes part in every product. */
+int64_t cla_add_group_ole(cla_handle h, const int32_t* colIdx, int32_t gCols, const double* dict, int32_t nVals,
+                          const int32_t* ptr, const uint16_t* data, int64_t dataLen);
+/* ColGroupUncompressed {_data} dense [nRows x gCols] (colgroup/ColGroupUncompressed.java:84) */
+int64_t cla_add_group_uncompressed(cla_handle h, const int32_t* colIdx, int32_t gCols, const double* values);
+/* ColGroupConst (one tuple) and ColGroupEmpty; both fold into the constant row vector that
+ * lib/CLALibUtils.java:188-206 (filterGroups) builds. */
+int64_t cla_add_group_const(cla_handle h, const int32_t* colIdx, int32_t gCols, const double* tuple);
+int64_t cla_add_group_empty(cla_handle h, const int32_t* colIdx, int32_t gCols);
+
+/* ---- products, host buffers (copies to and from the device happen inside the call) ----------
+ * cla_rmm      replaces lib/CLALibRightMultBy.java:57  rightMultByMatrix(m1, m2, ret, k): out[nRows x vCols] = X * V
+ * cla_lmm      replaces lib/CLALibLeftMultBy.java:126  leftMultByMatrix(right, left, ret, k):
+ *              out[yRows x nCols] = Yt * X with Yt [yRows x nRows] (the already transposed left operand)
+ * cla_tsmm     replaces lib/CLALibTSMM.java:59  leftMultByTransposeSelf(cmb, ret, k): out[nCols x nCols] = t(X) X
+ * cla_mmchain  replaces lib/CLALibMMChain.java:92  mmChain(x, v, w, out, ctype, k): out[nCols] = t(X) (w * (X v))
+ * cla_decompress replaces lib/CLALibDecompress.java:56  decompress(cmb, k): out[nRows x nCols] */
+int64_t cla_rmm(cla_handle h, const double* V, int32_t vRows, int32_t vCols, double* out);
+int64_t cla_lmm(cla_handle h, const double* Yt, int32_t yRows, double* out);
+int64_t cla_tsmm(cla_handle h, double* out);
+int64_t cla_mmchain(cla_handle h, const double* v, const double* w, int32_t ctype, double* out);
+int64_t cla_decompress(cla_handle h, double* out);
+
+/* ---- products, device buffers --------------------------------------------------------------
+ * Same semantics; every pointer is a device address on the handle's device, `stream` is a
+ * cudaStream_t (NULL = the legacy default stream). The call enqueues work and returns CLA_OK
+ * without synchronising; no non-zero count is produced. Used for row-sharded multi-GPU runs,
+ * where the caller all-reduces the partial results of cla_lmm_dev / cla_tsmm_dev / cla_mmchain_dev. */
+int64_t cla_rmm_dev(cla_handle h, const double* dV, int32_t vRows, int32_t vCols, double* dOut, void* stream);
+int64_t cla_lmm_dev(cla_handle h, const double* dYt, int32_t yRows, double* dOut, void* stream);
+int64_t cla_tsmm_dev(cla_handle h, double* dOut, void* stream);
+/* dU: caller-provided scratch of nRows doubles for u = X v (may be NULL: the handle then keeps its own) */
+int64_t cla_mmchain_dev(cla_handle h, const double* dV, const double* dW, int32_t ctype, double* dOut, double* dU,
+                        void* stream);
+/* Row sharding needs no special entry point: a handle that holds rows [a, b) of a taller matrix
+ * yields the exact product of those rows (constant columns included), so the partial results of
+ * cla_lmm_dev / cla_tsmm_dev / cla_mmchain_dev over all shards simply add up. */
+
+/* ---- decoded index structures (for bit-exact checks and for f2-style consumers) -------------
+ * ids[nRows]: dictionary id of every row of group g, -1 where the row holds the default (or zero)
+ * tuple; for an uncompressed group the row number. Computed by the device decode kernels.
+ * counts[nVals]: AColGroupValue.getCounts (colgroup/AColGroupValue.java:94-96). */
+int64_t cla_group_decode(cla_handle h, int32_t g, int32_t* ids);
+int64_t cla_group_counts(cla_handle h, int32_t g, int64_t* counts);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

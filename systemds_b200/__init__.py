@@ -1,0 +1,7 @@
+"""B200-native compressed linear algebra for SystemDS column groups (matrix-multiply path)."""
+from .cmb import (CHAIN_XtXv, CHAIN_XtwXv, CLALibDecompress, CLALibLeftMultBy, CLALibMMChain, CLALibRightMultBy,
+                  CLALibTSMM, CompressedMatrixBlock)
+from .native import CLAError
+
+__all__ = ["CompressedMatrixBlock", "CLALibRightMultBy", "CLALibLeftMultBy", "CLALibTSMM", "CLALibMMChain",
+           "CLALibDecompress", "CLAError", "CHAIN_XtXv", "CHAIN_XtwXv"]

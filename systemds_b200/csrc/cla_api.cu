@@ -1,0 +1,505 @@
+// extern "C" entry points declared in include/systemds_cla.h.
+#include "cla_common.cuh"
+#include <cstring>
+#include <memory>
+
+namespace cla {
+std::shared_ptr<Matrix> lookup(cla_handle h);
+cla_handle table_insert(std::shared_ptr<Matrix> m);
+bool table_erase(cla_handle h, std::shared_ptr<Matrix>* out);
+void release(Matrix* m);
+const std::string& last_error();
+}  // namespace cla
+
+using namespace cla;
+
+#define GET_MATRIX(h)                                                       \
+  std::shared_ptr<Matrix> mp = lookup(h);                                   \
+  if (!mp) return fail(CLA_ERR_BAD_HANDLE, "unknown or destroyed handle");  \
+  Matrix* m = mp.get();                                                     \
+  std::lock_guard<std::mutex> lk(m->mu)
+
+#define REQUIRE_OPEN()  \
+  if (m->finalized) return fail(CLA_ERR_STATE, "groups cannot be added after cla_finalize")
+#define REQUIRE_FINAL() \
+  if (!m->finalized) return fail(CLA_ERR_STATE, "cla_finalize has not been called on this handle")
+
+static int64_t check_cols(Matrix* m, const int32_t* colIdx, int32_t gCols) {
+  if (!colIdx || gCols <= 0) return fail(CLA_ERR_BAD_ARG, "group needs at least one column index");
+  for (int j = 0; j < gCols; j++)
+    if (colIdx[j] < 0 || colIdx[j] >= m->nCols) return fail(CLA_ERR_SHAPE, "column index outside the matrix");
+  return CLA_OK;
+}
+
+static size_t map_raw_bytes(int mapType, int64_t size, size_t* hi) {
+  *hi = 0;
+  switch (mapType) {
+    case CLA_MAP_ZERO: return 0;
+    case CLA_MAP_BIT: return (size_t)((size + 63) / 64) * 8;
+    case CLA_MAP_UBYTE:
+    case CLA_MAP_BYTE: return (size_t)size;
+    case CLA_MAP_CHAR: return (size_t)size * 2;
+    case CLA_MAP_CHAR_BYTE: *hi = (size_t)size; return (size_t)size * 2;
+    case CLA_MAP_INT: return (size_t)size * 4;
+    default: return 0;
+  }
+}
+
+// Ids must stay below nVals: the kernels index dictionaries with them unchecked.
+static int64_t check_map(int mapType, const uint8_t* map, const uint8_t* hi, int64_t size, int nVals) {
+  int64_t mx = 0;
+  switch (mapType) {
+    case CLA_MAP_ZERO: mx = 0; break;
+    case CLA_MAP_BIT: {
+      const uint64_t* w = (const uint64_t*)map;
+      uint64_t any = 0;
+      for (int64_t i = 0; i < (size + 63) / 64; i++) any |= w[i];
+      mx = any ? 1 : 0;
+      break;
+    }
+    case CLA_MAP_UBYTE:
+    case CLA_MAP_BYTE:
+      for (int64_t i = 0; i < size; i++) mx = map[i] > mx ? map[i] : mx;
+      break;
+    case CLA_MAP_CHAR: {
+      const uint16_t* c = (const uint16_t*)map;
+      for (int64_t i = 0; i < size; i++) mx = c[i] > mx ? c[i] : mx;
+      break;
+    }
+    case CLA_MAP_CHAR_BYTE: {
+      const uint16_t* c = (const uint16_t*)map;
+      for (int64_t i = 0; i < size; i++) {
+        int64_t v = (int64_t)c[i] + ((int64_t)hi[i] << 16);
+        mx = v > mx ? v : mx;
+      }
+      break;
+    }
+    case CLA_MAP_INT: {
+      const int32_t* c = (const int32_t*)map;
+      for (int64_t i = 0; i < size; i++) {
+        if (c[i] < 0) return fail(CLA_ERR_BAD_ARG, "negative id in map");
+        mx = c[i] > mx ? c[i] : mx;
+      }
+      break;
+    }
+    default: return fail(CLA_ERR_BAD_ARG, "unknown map type");
+  }
+  if (size > 0 && mx >= nVals) return fail(CLA_ERR_BAD_ARG, "map holds an id at or above the number of dictionary tuples");
+  return CLA_OK;
+}
+
+extern "C" {
+
+cla_handle cla_create(int32_t nRows, int32_t nCols, int32_t overlapping) {
+  if (nRows < 0 || nCols < 0) return fail(CLA_ERR_BAD_ARG, "negative matrix dimension");
+  auto m = std::make_shared<Matrix>();
+  m->nRows = nRows;
+  m->nCols = nCols;
+  m->overlapping = overlapping != 0;
+  return table_insert(m);
+}
+
+int64_t cla_destroy(cla_handle h) {
+  std::shared_ptr<Matrix> mp;
+  if (!table_erase(h, &mp)) return fail(CLA_ERR_BAD_HANDLE, "unknown or destroyed handle");
+  std::lock_guard<std::mutex> lk(mp->mu);
+  release(mp.get());
+  return CLA_OK;
+}
+
+int64_t cla_last_error(char* buf, int64_t cap) {
+  const std::string& e = last_error();
+  if (buf && cap > 0) {
+    const size_t n = std::min<size_t>(e.size(), (size_t)cap - 1);
+    std::memcpy(buf, e.data(), n);
+    buf[n] = 0;
+  }
+  return (int64_t)e.size();
+}
+
+int64_t cla_stats_get(cla_handle h, cla_stats* out) {
+  GET_MATRIX(h);
+  if (!out) return fail(CLA_ERR_BAD_ARG, "null stats pointer");
+  *out = m->stats;
+  out->n_rows = m->nRows;
+  out->n_cols = m->nCols;
+  out->n_groups = (int64_t)m->hg.size();
+  return CLA_OK;
+}
+
+static int64_t add_dict_group(Matrix* m, HostGroup& g, int type, const int32_t* colIdx, int32_t gCols,
+                              const double* dict, int32_t nVals) {
+  int64_t rc = check_cols(m, colIdx, gCols);
+  if (rc < 0) return rc;
+  if (nVals < 0 || (nVals > 0 && !dict)) return fail(CLA_ERR_BAD_ARG, "dictionary missing");
+  g.type = type;
+  g.cols.assign(colIdx, colIdx + gCols);
+  g.nVals = nVals;
+  if (nVals) g.dict.assign(dict, dict + (size_t)nVals * gCols);
+  return CLA_OK;
+}
+
+int64_t cla_add_group_ddc(cla_handle h, const int32_t* colIdx, int32_t gCols, const double* dict, int32_t nVals,
+                          int32_t mapType, const void* map, const void* mapHi, int64_t mapSize) {
+  GET_MATRIX(h);
+  REQUIRE_OPEN();
+  HostGroup g;
+  int64_t rc = add_dict_group(m, g, GT_DDC, colIdx, gCols, dict, nVals);
+  if (rc < 0) return rc;
+  if (mapSize != m->nRows) return fail(CLA_ERR_SHAPE, "DDC map must have one cell per row");
+  if (m->nRows > 0 && nVals == 0) return fail(CLA_ERR_BAD_ARG, "DDC group without dictionary tuples");
+  size_t hi;
+  const size_t mb = map_raw_bytes(mapType, mapSize, &hi);
+  if ((mb && !map) || (hi && !mapHi)) return fail(CLA_ERR_BAD_ARG, "map array missing");
+  if ((rc = check_map(mapType, (const uint8_t*)map, (const uint8_t*)mapHi, mapSize, nVals)) < 0) return rc;
+  g.mapType = mapType;
+  g.mapSize = mapSize;
+  if (mb) g.map.assign((const uint8_t*)map, (const uint8_t*)map + mb);
+  if (hi) g.mapHi.assign((const uint8_t*)mapHi, (const uint8_t*)mapHi + hi);
+  m->hg.push_back(std::move(g));
+  return (int64_t)m->hg.size() - 1;
+}
+
+int64_t cla_add_group_sdc(cla_handle h, const int32_t* colIdx, int32_t gCols, const double* dict, int32_t nVals,
+                          const double* defaultTuple, int32_t offType, int32_t offsetToFirst, int32_t offsetToLast,
+                          const void* offData, int64_t offLen, int64_t nOffsets, int32_t mapType, const void* map,
+                          const void* mapHi) {
+  GET_MATRIX(h);
+  REQUIRE_OPEN();
+  HostGroup g;
+  int64_t rc = add_dict_group(m, g, GT_SDC, colIdx, gCols, dict, nVals);
+  if (rc < 0) return rc;
+  if (offType < CLA_OFF_EMPTY || offType > CLA_OFF_CHAR) return fail(CLA_ERR_BAD_ARG, "unknown offset type");
+  if (nOffsets < 0 || nOffsets > m->nRows) return fail(CLA_ERR_SHAPE, "more offsets than rows");
+  if (offType == CLA_OFF_EMPTY && nOffsets != 0) return fail(CLA_ERR_BAD_ARG, "empty offsets with a size");
+  if (offType == CLA_OFF_SINGLE && nOffsets != 1) return fail(CLA_ERR_BAD_ARG, "OffsetSingle holds one row");
+  if (offType == CLA_OFF_TWO && nOffsets != 2) return fail(CLA_ERR_BAD_ARG, "OffsetTwo holds two rows");
+  if (nOffsets > 0 && (offsetToFirst < 0 || offsetToLast >= m->nRows || offsetToFirst > offsetToLast))
+    return fail(CLA_ERR_SHAPE, "offsets outside the matrix");
+  if ((offType == CLA_OFF_BYTE || offType == CLA_OFF_CHAR) && offLen > 0 && !offData)
+    return fail(CLA_ERR_BAD_ARG, "offset array missing");
+  if (nOffsets > 0 && nVals == 0) return fail(CLA_ERR_BAD_ARG, "SDC group without dictionary tuples");
+  if (defaultTuple) g.def.assign(defaultTuple, defaultTuple + gCols);
+  g.offType = offType;
+  g.first = offsetToFirst;
+  g.last = offsetToLast;
+  g.nOff = nOffsets;
+  if (offType == CLA_OFF_BYTE || offType == CLA_OFF_CHAR) {
+    g.offLen = offLen;
+    const size_t ob = (size_t)offLen * (offType == CLA_OFF_BYTE ? 1 : 2);
+    if (ob) g.offData.assign((const uint8_t*)offData, (const uint8_t*)offData + ob);
+  }
+  g.single = (map == nullptr);
+  if (!g.single) {
+    size_t hi;
+    const size_t mb = map_raw_bytes(mapType, nOffsets, &hi);
+    if (hi && !mapHi) return fail(CLA_ERR_BAD_ARG, "map array missing");
+    if ((rc = check_map(mapType, (const uint8_t*)map, (const uint8_t*)mapHi, nOffsets, nVals)) < 0) return rc;
+    g.mapType = mapType;
+    g.mapSize = nOffsets;
+    if (mb) g.map.assign((const uint8_t*)map, (const uint8_t*)map + mb);
+    if (hi) g.mapHi.assign((const uint8_t*)mapHi, (const uint8_t*)mapHi + hi);
+  } else {
+    g.mapType = CLA_MAP_ZERO;
+    g.mapSize = nOffsets;
+  }
+  m->hg.push_back(std::move(g));
+  return (int64_t)m->hg.size() - 1;
+}
+
+static int64_t add_offset_group(cla_handle h, int type, const int32_t* colIdx, int32_t gCols, const double* dict,
+                                int32_t nVals, const int32_t* ptr, const uint16_t* data, int64_t dataLen) {
+  GET_MATRIX(h);
+  REQUIRE_OPEN();
+  HostGroup g;
+  int64_t rc = add_dict_group(m, g, type, colIdx, gCols, dict, nVals);
+  if (rc < 0) return rc;
+  if (!ptr) return fail(CLA_ERR_BAD_ARG, "_ptr array missing");
+  if (dataLen < 0 || (dataLen > 0 && !data)) return fail(CLA_ERR_BAD_ARG, "_data array missing");
+  if (ptr[0] != 0 || ptr[nVals] != dataLen) return fail(CLA_ERR_BAD_ARG, "_ptr does not span _data");
+  for (int k = 0; k < nVals; k++)
+    if (ptr[k + 1] < ptr[k] || (type == GT_RLE && ((ptr[k + 1] - ptr[k]) & 1)))
+      return fail(CLA_ERR_BAD_ARG, "_ptr not monotone (or an RLE list of odd length)");
+  if (type == GT_OLE)
+    for (int k = 0; k < nVals; k++) {  // segment headers must chain exactly to the end of the list
+      int64_t bix = ptr[k];
+      while (bix < ptr[k + 1]) bix += (int64_t)data[bix] + 1;
+      if (bix != ptr[k + 1]) return fail(CLA_ERR_BAD_ARG, "OLE segment headers do not chain to the list end");
+    }
+  g.ptr.assign(ptr, ptr + nVals + 1);
+  if (dataLen) g.data.assign(data, data + dataLen);
+  m->hg.push_back(std::move(g));
+  return (int64_t)m->hg.size() - 1;
+}
+
+int64_t cla_add_group_rle(cla_handle h, const int32_t* colIdx, int32_t gCols, const double* dict, int32_t nVals,
+                          const int32_t* ptr, const uint16_t* data, int64_t dataLen) {
+  return add_offset_group(h, GT_RLE, colIdx, gCols, dict, nVals, ptr, data, dataLen);
+}
+int64_t cla_add_group_ole(cla_handle h, const int32_t* colIdx, int32_t gCols, const double* dict, int32_t nVals,
+                          const int32_t* ptr, const uint16_t* data, int64_t dataLen) {
+  return add_offset_group(h, GT_OLE, colIdx, gCols, dict, nVals, ptr, data, dataLen);
+}
+
+int64_t cla_add_group_uncompressed(cla_handle h, const int32_t* colIdx, int32_t gCols, const double* values) {
+  GET_MATRIX(h);
+  REQUIRE_OPEN();
+  int64_t rc = check_cols(m, colIdx, gCols);
+  if (rc < 0) return rc;
+  if (m->nRows > 0 && !values) return fail(CLA_ERR_BAD_ARG, "dense block missing");
+  HostGroup g;
+  g.type = GT_UNC;
+  g.cols.assign(colIdx, colIdx + gCols);
+  if (m->nRows) g.dense.assign(values, values + (size_t)m->nRows * gCols);
+  m->hg.push_back(std::move(g));
+  return (int64_t)m->hg.size() - 1;
+}
+
+int64_t cla_add_group_const(cla_handle h, const int32_t* colIdx, int32_t gCols, const double* tuple) {
+  GET_MATRIX(h);
+  REQUIRE_OPEN();
+  HostGroup g;
+  int64_t rc = add_dict_group(m, g, GT_CONST, colIdx, gCols, tuple, 1);
+  if (rc < 0) return rc;
+  m->hg.push_back(std::move(g));
+  return (int64_t)m->hg.size() - 1;
+}
+
+int64_t cla_add_group_empty(cla_handle h, const int32_t* colIdx, int32_t gCols) {
+  GET_MATRIX(h);
+  REQUIRE_OPEN();
+  int64_t rc = check_cols(m, colIdx, gCols);
+  if (rc < 0) return rc;
+  HostGroup g;
+  g.type = GT_EMPTY;
+  g.cols.assign(colIdx, colIdx + gCols);
+  m->hg.push_back(std::move(g));
+  return (int64_t)m->hg.size() - 1;
+}
+
+int64_t cla_finalize(cla_handle h, int32_t device) {
+  GET_MATRIX(h);
+  REQUIRE_OPEN();
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0)
+    return fail(CLA_ERR_CUDA, std::string("no usable CUDA device: ") + (e != cudaSuccess ? cudaGetErrorString(e) : "device count is 0"));
+  if (device < 0 || device >= count) return fail(CLA_ERR_BAD_ARG, "device ordinal out of range");
+  m->device = device;
+  int64_t rc = finalize_device(m);
+  if (rc < 0) {
+    release(m);
+    m->device = -1;
+    return rc;
+  }
+  return CLA_OK;
+}
+
+}  // extern "C"
+
+// ---- device-buffer products ---------------------------------------------------------------------
+static int64_t check_errword(Matrix* m) {
+  int32_t herr = 0;
+  CLA_CUDA(cudaMemcpy(&herr, m->dErr, sizeof(herr), cudaMemcpyDeviceToHost));
+  if (herr) {
+    cudaMemset(m->dErr, 0, sizeof(int32_t));
+    return fail(CLA_ERR_DEVICE_CHECK, "a kernel self-check tripped (code " + std::to_string(herr) + ")");
+  }
+  return CLA_OK;
+}
+
+static int64_t rmm_dev(Matrix* m, const double* dV, int32_t vRows, int32_t vCols, double* dOut, cudaStream_t s) {
+  if (vRows != m->nCols) return fail(CLA_ERR_SHAPE, "rmm: V must have nCols rows");
+  if (vCols < 0) return fail(CLA_ERR_SHAPE, "rmm: negative column count");
+  m->stats.calls_rmm++;
+  if (vCols == 1) {
+    int64_t rc = fast_rmm_vec(m, dV, dOut, s);
+    if (rc != 0) return rc < 0 ? rc : CLA_OK;
+  }
+  return launch_rmm(m, dV, vCols, dOut, s);
+}
+
+static int64_t lmm_dev(Matrix* m, const double* dYt, int32_t yRows, double* dOut, cudaStream_t s) {
+  if (yRows < 0) return fail(CLA_ERR_SHAPE, "lmm: negative row count");
+  m->stats.calls_lmm++;
+  if (yRows == 1) {
+    int64_t rc = fast_lmm_vec(m, dYt, dOut, s);
+    if (rc != 0) return rc < 0 ? rc : CLA_OK;
+  }
+  return launch_lmm(m, dYt, yRows, dOut, s);
+}
+
+static int64_t mmchain_dev(Matrix* m, const double* dV, const double* dW, int32_t ctype, double* dOut, double* dU,
+                           cudaStream_t s) {
+  if (ctype != CLA_CHAIN_XtXv && ctype != CLA_CHAIN_XtwXv) return fail(CLA_ERR_UNSUPPORTED, "mmchain: unsupported chain type");
+  if (ctype == CLA_CHAIN_XtwXv && !dW) return fail(CLA_ERR_BAD_ARG, "mmchain: XtwXv needs w");
+  m->stats.calls_mmchain++;
+  if (!dU) {
+    int64_t rc = ensure_scratch2(m, sizeof(double) * (size_t)std::max(m->nRows, 1));
+    if (rc < 0) return rc;
+    dU = (double*)m->scratch2;
+  }
+  int64_t rc = rmm_dev(m, dV, m->nCols, 1, dU, s);
+  if (rc < 0) return rc;
+  if (ctype == CLA_CHAIN_XtwXv)
+    if ((rc = launch_scale_rows(m, dU, dW, m->nRows, s)) < 0) return rc;
+  return lmm_dev(m, dU, 1, dOut, s);
+}
+
+extern "C" {
+
+int64_t cla_rmm_dev(cla_handle h, const double* dV, int32_t vRows, int32_t vCols, double* dOut, void* stream) {
+  GET_MATRIX(h);
+  REQUIRE_FINAL();
+  CLA_CUDA(cudaSetDevice(m->device));
+  return rmm_dev(m, dV, vRows, vCols, dOut, (cudaStream_t)stream);
+}
+int64_t cla_lmm_dev(cla_handle h, const double* dYt, int32_t yRows, double* dOut, void* stream) {
+  GET_MATRIX(h);
+  REQUIRE_FINAL();
+  CLA_CUDA(cudaSetDevice(m->device));
+  return lmm_dev(m, dYt, yRows, dOut, (cudaStream_t)stream);
+}
+int64_t cla_tsmm_dev(cla_handle h, double* dOut, void* stream) {
+  GET_MATRIX(h);
+  REQUIRE_FINAL();
+  CLA_CUDA(cudaSetDevice(m->device));
+  m->stats.calls_tsmm++;
+  return launch_tsmm(m, dOut, (cudaStream_t)stream);
+}
+int64_t cla_mmchain_dev(cla_handle h, const double* dV, const double* dW, int32_t ctype, double* dOut, double* dU,
+                        void* stream) {
+  GET_MATRIX(h);
+  REQUIRE_FINAL();
+  CLA_CUDA(cudaSetDevice(m->device));
+  return mmchain_dev(m, dV, dW, ctype, dOut, dU, (cudaStream_t)stream);
+}
+
+}  // extern "C"
+
+// ---- host-buffer products -------------------------------------------------------------------------
+// Staging layout in m->io: [inputs ... | output | nnz counter]
+template <class F>
+static int64_t host_call(Matrix* m, const double* in1, size_t n1, const double* in2, size_t n2, double* out, size_t nOut,
+                         F&& run) {
+  CLA_CUDA(cudaSetDevice(m->device));
+  auto al = [](size_t b) { return (b + 255) & ~(size_t)255; };
+  const size_t o1 = 0, o2 = al(n1 * 8), oOut = o2 + al(n2 * 8), oCnt = oOut + al(nOut * 8);
+  int64_t rc = ensure_io(m, oCnt + 256);
+  if (rc < 0) return rc;
+  char* base = (char*)m->io;
+  double* d1 = (double*)(base + o1);
+  double* d2 = (double*)(base + o2);
+  double* dOut = (double*)(base + oOut);
+  unsigned long long* dCnt = (unsigned long long*)(base + oCnt);
+  cudaStream_t s = m->stream;
+  if (n1) CLA_CUDA(cudaMemcpyAsync(d1, in1, n1 * 8, cudaMemcpyHostToDevice, s));
+  if (n2) CLA_CUDA(cudaMemcpyAsync(d2, in2, n2 * 8, cudaMemcpyHostToDevice, s));
+  CLA_CUDA(cudaEventRecord(m->ev0, s));
+  if ((rc = run(d1, n2 ? d2 : nullptr, dOut, s)) < 0) return rc;
+  CLA_CUDA(cudaEventRecord(m->ev1, s));
+  if ((rc = launch_count_nnz(m, dOut, (int64_t)nOut, dCnt, s)) < 0) return rc;
+  if (nOut) CLA_CUDA(cudaMemcpyAsync(out, dOut, nOut * 8, cudaMemcpyDeviceToHost, s));
+  unsigned long long nnz = 0;
+  CLA_CUDA(cudaMemcpyAsync(&nnz, dCnt, sizeof(nnz), cudaMemcpyDeviceToHost, s));
+  CLA_CUDA(cudaStreamSynchronize(s));
+  float ms = 0;
+  if (cudaEventElapsedTime(&ms, m->ev0, m->ev1) == cudaSuccess) m->stats.last_kernel_ms = ms;
+  if ((rc = check_errword(m)) < 0) return rc;
+  return (int64_t)nnz;
+}
+
+extern "C" {
+
+int64_t cla_rmm(cla_handle h, const double* V, int32_t vRows, int32_t vCols, double* out) {
+  GET_MATRIX(h);
+  REQUIRE_FINAL();
+  if (vRows != m->nCols || vCols < 0) return fail(CLA_ERR_SHAPE, "rmm: V must be [nCols x vCols]");
+  if ((!V && (size_t)vRows * vCols) || (!out && (size_t)m->nRows * vCols)) return fail(CLA_ERR_BAD_ARG, "rmm: null buffer");
+  return host_call(m, V, (size_t)vRows * vCols, nullptr, 0, out, (size_t)m->nRows * vCols,
+                   [&](double* dV, double*, double* dOut, cudaStream_t s) { return rmm_dev(m, dV, vRows, vCols, dOut, s); });
+}
+
+int64_t cla_lmm(cla_handle h, const double* Yt, int32_t yRows, double* out) {
+  GET_MATRIX(h);
+  REQUIRE_FINAL();
+  if (yRows < 0) return fail(CLA_ERR_SHAPE, "lmm: negative row count");
+  if ((!Yt && (size_t)yRows * m->nRows) || (!out && (size_t)yRows * m->nCols)) return fail(CLA_ERR_BAD_ARG, "lmm: null buffer");
+  return host_call(m, Yt, (size_t)yRows * m->nRows, nullptr, 0, out, (size_t)yRows * m->nCols,
+                   [&](double* dY, double*, double* dOut, cudaStream_t s) { return lmm_dev(m, dY, yRows, dOut, s); });
+}
+
+int64_t cla_tsmm(cla_handle h, double* out) {
+  GET_MATRIX(h);
+  REQUIRE_FINAL();
+  if (!out && m->nCols) return fail(CLA_ERR_BAD_ARG, "tsmm: null buffer");
+  m->stats.calls_tsmm++;
+  return host_call(m, nullptr, 0, nullptr, 0, out, (size_t)m->nCols * m->nCols,
+                   [&](double*, double*, double* dOut, cudaStream_t s) { return launch_tsmm(m, dOut, s); });
+}
+
+int64_t cla_mmchain(cla_handle h, const double* v, const double* w, int32_t ctype, double* out) {
+  GET_MATRIX(h);
+  REQUIRE_FINAL();
+  if ((!v || !out) && m->nCols) return fail(CLA_ERR_BAD_ARG, "mmchain: null buffer");
+  if (ctype == CLA_CHAIN_XtwXv && !w && m->nRows) return fail(CLA_ERR_BAD_ARG, "mmchain: XtwXv needs w");
+  const size_t nW = ctype == CLA_CHAIN_XtwXv ? (size_t)m->nRows : 0;
+  return host_call(m, v, (size_t)m->nCols, w, nW, out, (size_t)m->nCols,
+                   [&](double* dV, double* dW, double* dOut, cudaStream_t s) {
+                     return mmchain_dev(m, dV, dW, ctype, dOut, nullptr, s);
+                   });
+}
+
+int64_t cla_decompress(cla_handle h, double* out) {
+  GET_MATRIX(h);
+  REQUIRE_FINAL();
+  if (!out && (size_t)m->nRows * m->nCols) return fail(CLA_ERR_BAD_ARG, "decompress: null buffer");
+  m->stats.calls_decompress++;
+  return host_call(m, nullptr, 0, nullptr, 0, out, (size_t)m->nRows * m->nCols,
+                   [&](double*, double*, double* dOut, cudaStream_t s) { return launch_decompress(m, dOut, s); });
+}
+
+// ---- decoded index structures -----------------------------------------------------------------------
+int64_t cla_group_decode(cla_handle h, int32_t g, int32_t* ids) {
+  GET_MATRIX(h);
+  REQUIRE_FINAL();
+  if (g < 0 || g >= (int)m->regToDev.size()) return fail(CLA_ERR_BAD_ARG, "group index out of range");
+  if (!ids && m->nRows) return fail(CLA_ERR_BAD_ARG, "null buffer");
+  if (m->nRows == 0) return CLA_OK;
+  CLA_CUDA(cudaSetDevice(m->device));
+  const int dg = m->regToDev[g];
+  if (dg < 0) {  // const: tuple 0 everywhere; empty: no tuple
+    const int v = m->hg[g].type == GT_CONST ? 0 : -1;
+    for (int r = 0; r < m->nRows; r++) ids[r] = v;
+    return CLA_OK;
+  }
+  int64_t rc = ensure_io(m, sizeof(int32_t) * (size_t)m->nRows);
+  if (rc < 0) return rc;
+  if ((rc = launch_group_decode(m, dg, (int32_t*)m->io, m->stream)) < 0) return rc;
+  CLA_CUDA(cudaMemcpyAsync(ids, m->io, sizeof(int32_t) * (size_t)m->nRows, cudaMemcpyDeviceToHost, m->stream));
+  CLA_CUDA(cudaStreamSynchronize(m->stream));
+  return CLA_OK;
+}
+
+int64_t cla_group_counts(cla_handle h, int32_t g, int64_t* counts) {
+  GET_MATRIX(h);
+  REQUIRE_FINAL();
+  if (g < 0 || g >= (int)m->regToDev.size()) return fail(CLA_ERR_BAD_ARG, "group index out of range");
+  if (!counts) return fail(CLA_ERR_BAD_ARG, "null buffer");
+  CLA_CUDA(cudaSetDevice(m->device));
+  const int dg = m->regToDev[g];
+  if (dg < 0) {
+    if (m->hg[g].type == GT_CONST) counts[0] = m->nRows;
+    return CLA_OK;
+  }
+  const int nv = m->hg[g].nVals;
+  if (m->groups[dg].type == GT_UNC) return fail(CLA_ERR_UNSUPPORTED, "counts: uncompressed group has no dictionary");
+  int64_t rc = ensure_io(m, sizeof(unsigned long long) * (size_t)std::max(nv + 1, 1));
+  if (rc < 0) return rc;
+  if ((rc = launch_group_counts(m, dg, (unsigned long long*)m->io, m->stream)) < 0) return rc;
+  CLA_CUDA(cudaMemcpyAsync(counts, m->io, sizeof(int64_t) * (size_t)nv, cudaMemcpyDeviceToHost, m->stream));
+  CLA_CUDA(cudaStreamSynchronize(m->stream));
+  return CLA_OK;
+}
+
+}  // extern "C"

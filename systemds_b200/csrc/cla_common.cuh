@@ -1,0 +1,202 @@
+// Shared declarations of the CLA device library: device-side group records, the host-side
+// matrix object behind a cla_handle, and helpers used by every translation unit.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <mutex>
+#include <string>
+#include <vector>
+#include "../../include/systemds_cla.h"
+
+namespace cla {
+
+constexpr int SKIP_ROWS = 1024;  // granularity of the SDC / RLE skip indexes (AOffset's skip list uses ~1000)
+constexpr int BITMAP_BLOCK_SZ = 65535;
+
+enum GroupType : int { GT_DDC = 0, GT_SDC = 1, GT_RLE = 2, GT_OLE = 3, GT_UNC = 4, GT_CONST = 5, GT_EMPTY = 6 };
+
+// Start state for decoding an offset stream at a row-block boundary: the first listed row at or
+// after the boundary, its position in the map (AIterator.getDataIndex), and the stream position
+// right behind it.
+struct SdcSkip {
+  int32_t elem;  // index of that element (== nOff when there is none)
+  int32_t row;   // its row
+  int64_t pos;   // index of the next delta to read
+};
+
+// One run of a value, in absolute rows (decoded from the (gap, len) pairs and merged over values).
+struct RleRun {
+  int32_t start;
+  uint16_t len;
+  uint16_t k;
+};
+
+// Device-visible record of one column group. All pointers are device addresses.
+struct DevGroup {
+  int32_t type;      // how products treat it: GT_DDC (also transcoded OLE), GT_SDC, GT_RLE, GT_UNC
+  int32_t origType;  // the registered type
+  int32_t gCols, nVals;
+  int32_t mapType;
+  int32_t single;  // SDCSingle*: every listed row holds tuple 0
+  int32_t offType, first, last;
+  int32_t pad_;
+  int64_t mapSize, offLen, nOff, nRuns, dataLen;
+  int64_t valOff;  // first row of this group's table in the per-call value arenas (sum of nVals before it)
+  const int32_t* cols;
+  const double* dict;  // effective dictionary (default tuple subtracted), [nVals x gCols]
+  const void* map;
+  const void* mapHi;
+  const void* offData;
+  const SdcSkip* skip;
+  const RleRun* runs;
+  const int32_t* runSkip;  // per SKIP_ROWS block: first run whose end lies behind the block start
+  const int32_t* ptr;      // RLE / OLE as registered
+  const uint16_t* data;
+  const double* dense;  // UNC [nRows x gCols]
+};
+
+// Read one cell of a map in the reference's storage layout.
+__device__ __forceinline__ int map_get(int mapType, const void* __restrict__ map, const void* __restrict__ mapHi,
+                                       int64_t r) {
+  switch (mapType) {
+    case CLA_MAP_ZERO: return 0;
+    case CLA_MAP_BIT: return (int)((((const unsigned long long*)map)[r >> 6] >> (r & 63)) & 1ULL);
+    case CLA_MAP_UBYTE:
+    case CLA_MAP_BYTE: return ((const uint8_t*)map)[r];
+    case CLA_MAP_CHAR: return ((const uint16_t*)map)[r];
+    case CLA_MAP_CHAR_BYTE: return (int)((const uint16_t*)map)[r] + ((int)((const uint8_t*)mapHi)[r] << 16);
+    default: return ((const int32_t*)map)[r];
+  }
+}
+
+// Warp-level decode of one SKIP_ROWS block of an offset stream: deltas are read 32 at a time,
+// a warp scan turns them into rows, a ballot numbers the elements (continuation deltas carry none).
+// f(row, elemIndex) is called for every listed row in [rowBegin, rowEnd).
+template <class F>
+__device__ __forceinline__ void sdc_walk_block(const DevGroup& g, int rowBegin, int rowEnd, F&& f) {
+  const int lane = threadIdx.x & 31;
+  if (g.nOff == 0) return;
+  if (g.offType == CLA_OFF_SINGLE || g.offType == CLA_OFF_TWO) {
+    if (lane == 0) {
+      if (g.first >= rowBegin && g.first < rowEnd) f(g.first, 0);
+      if (g.offType == CLA_OFF_TWO && g.last >= rowBegin && g.last < rowEnd) f(g.last, 1);
+    }
+    return;
+  }
+  const SdcSkip sk = g.skip[rowBegin / SKIP_ROWS];
+  int row = sk.row;
+  int elem = sk.elem;
+  int64_t pos = sk.pos;
+  if (elem >= g.nOff || row >= rowEnd) return;
+  if (lane == 0 && row >= rowBegin) f(row, elem);
+  const int maxV = g.offType == CLA_OFF_BYTE ? 255 : 65535;
+  while (pos < g.offLen) {
+    const int64_t i = pos + lane;
+    int d = 0;
+    if (i < g.offLen) d = g.offType == CLA_OFF_BYTE ? (int)((const uint8_t*)g.offData)[i] : (int)((const uint16_t*)g.offData)[i];
+    const bool inb = i < g.offLen;
+    int inc = inb ? (d == 0 ? maxV : d) : 0;
+#pragma unroll
+    for (int s = 1; s < 32; s <<= 1) {
+      int t = __shfl_up_sync(0xffffffffu, inc, s);
+      if (lane >= s) inc += t;
+    }
+    const bool isElem = inb && d != 0;
+    const unsigned bal = __ballot_sync(0xffffffffu, isElem);
+    const int myRow = row + inc;
+    const int myElem = elem + __popc(bal & ((2u << lane) - 1u));
+    if (isElem && myRow >= rowBegin && myRow < rowEnd) f(myRow, myElem);
+    row += __shfl_sync(0xffffffffu, inc, 31);
+    elem += __popc(bal);
+    pos += 32;
+    if (row >= rowEnd) break;
+  }
+}
+
+// Host-side group as registered (arrays copied from the caller).
+struct HostGroup {
+  int type = GT_DDC;
+  std::vector<int32_t> cols;
+  int nVals = 0;
+  std::vector<double> dict;
+  std::vector<double> def;  // default tuple (empty = zeros)
+  int mapType = CLA_MAP_ZERO;
+  int64_t mapSize = 0;
+  std::vector<uint8_t> map, mapHi;  // raw bytes
+  bool single = false;
+  int offType = CLA_OFF_EMPTY, first = 0, last = 0;
+  int64_t offLen = 0, nOff = 0;
+  std::vector<uint8_t> offData;
+  std::vector<int32_t> ptr;
+  std::vector<uint16_t> data;
+  std::vector<double> dense;
+};
+
+struct FastPlan;  // plans of the specialised DDC kernels (cla_fast.cu)
+
+struct Matrix {
+  int32_t nRows = 0, nCols = 0;
+  bool overlapping = false;
+  bool finalized = false;
+  int device = -1;
+  std::mutex mu;
+  std::vector<HostGroup> hg;   // cleared after finalize (records kept, arrays dropped)
+  std::vector<DevGroup> groups;  // host copy of the device records (product groups only)
+  std::vector<int> regToDev;     // registered group index -> index in groups (-1: const / empty)
+  DevGroup* dGroups = nullptr;
+  int nDev = 0;
+  int64_t totalVals = 0;         // sum of nVals over dictionary groups
+  std::vector<double> constV;    // host copy
+  double* dConstV = nullptr;     // [nCols]
+  bool hasConst = false;
+  std::vector<void*> allocs;     // everything cudaMalloc'ed for the groups
+  int64_t deviceBytes = 0, indexBytes = 0;
+  // growable scratch (value arenas, partial results, host staging)
+  void* scratch = nullptr;
+  size_t scratchBytes = 0;
+  void* scratch2 = nullptr;
+  size_t scratch2Bytes = 0;
+  void* io = nullptr;  // device staging for host-buffer calls
+  size_t ioBytes = 0;
+  int32_t* dErr = nullptr;  // device self-check word
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  FastPlan* fast = nullptr;
+  cla_stats stats{};
+  int smCount = 148;
+};
+
+// error plumbing --------------------------------------------------------------------------------
+void set_error(const std::string& msg);
+int64_t fail(int64_t code, const std::string& msg);
+#define CLA_CUDA(expr)                                                                              \
+  do {                                                                                              \
+    cudaError_t e_ = (expr);                                                                        \
+    if (e_ != cudaSuccess)                                                                          \
+      return ::cla::fail(CLA_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(e_));         \
+  } while (0)
+
+int64_t ensure_scratch(Matrix* m, size_t bytes);
+int64_t ensure_scratch2(Matrix* m, size_t bytes);
+int64_t ensure_io(Matrix* m, size_t bytes);
+
+// launchers implemented in the kernel translation units; all enqueue on `s` and return CLA_OK or an error.
+int64_t launch_rmm(Matrix* m, const double* dV, int vCols, double* dOut, cudaStream_t s);
+int64_t launch_lmm(Matrix* m, const double* dYt, int q, double* dOut, cudaStream_t s);
+int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s);
+int64_t launch_decompress(Matrix* m, double* dOut, cudaStream_t s);
+int64_t launch_decompress_range(Matrix* m, int r0, int r1, double* dOut, cudaStream_t s);
+int64_t launch_group_decode(Matrix* m, int devGroup, int32_t* dIds, cudaStream_t s);
+int64_t launch_group_counts(Matrix* m, int devGroup, unsigned long long* dCounts, cudaStream_t s);
+int64_t launch_count_nnz(Matrix* m, const double* d, int64_t n, unsigned long long* dCount, cudaStream_t s);
+int64_t launch_scale_rows(Matrix* m, double* dU, const double* dW, int64_t n, cudaStream_t s);
+
+// finalize-time device work (cla_finalize.cu)
+int64_t finalize_device(Matrix* m);
+// fast paths (cla_fast.cu): return 1 if they handled the call, 0 if not applicable, <0 on error
+int64_t fast_plan_build(Matrix* m);
+void fast_plan_free(Matrix* m);
+int64_t fast_rmm_vec(Matrix* m, const double* dV, double* dOut, cudaStream_t s);
+int64_t fast_lmm_vec(Matrix* m, const double* dY, double* dOut, cudaStream_t s);
+
+}  // namespace cla

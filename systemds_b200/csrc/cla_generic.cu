@@ -1,0 +1,427 @@
+// General product kernels: they accept every group type, any number of right-hand columns / left
+// rows, and overlapping groups. The specialised kernels in cla_fast.cu take over for the shapes
+// they cover; everything else runs here.
+//
+//   RMM  (CLALibRightMultBy.RMM, lib/CLALibRightMultBy.java:208-258)
+//        1. k_dict_times_v : P_g = D_g * V[cols_g, :] for every dictionary group
+//                            (ADictBasedColGroup.rightMultByMatrix, colgroup/ADictBasedColGroup.java:246-275)
+//        2. k_rmm_tile     : a CTA owns a tile of output rows and sums P_g[id_g(r), :] over all groups,
+//                            then adds constV * V (the decompress-and-sum of lib/CLALibDecompress.java:310-357)
+//   LMM  (CLALibLeftMultBy.LMM, lib/CLALibLeftMultBy.java:286-346)
+//        1. k_lmm_preagg   : A_g[i, k] = sum of Yt[i, r] over rows r holding tuple k
+//                            (APreAgg.preAggregateDense, colgroup/APreAgg.java:137)
+//        2. k_lmm_post     : out[i, cols_g] += A_g[i, :] * D_g  (APreAgg.mmWithDictionary, :312-322)
+//        3. k_lmm_unc      : uncompressed groups, direct product (ColGroupUncompressed.java:429-539)
+//        4. k_lmm_const    : out += rowSums(Yt) (x) constV  (lib/CLALibLeftMultBy.java:530-629)
+#include "cla_common.cuh"
+#include <algorithm>
+
+namespace cla {
+
+static inline int grid_for(int64_t n, int block, int cap = 148 * 16) {
+  int64_t g = (n + block - 1) / block;
+  return (int)std::max<int64_t>(1, std::min<int64_t>(g, cap));
+}
+
+// --------------------------------------------------------------------------------------------------
+// P arena: [totalVals x vCols]
+// --------------------------------------------------------------------------------------------------
+__global__ void k_dict_times_v(const DevGroup* __restrict__ groups, const double* __restrict__ V, int vCols,
+                               double* __restrict__ P) {
+  const DevGroup g = groups[blockIdx.x];
+  if (g.type == GT_UNC) return;
+  const int64_t n = (int64_t)g.nVals * vCols;
+  for (int64_t e = blockIdx.y * (int64_t)blockDim.x + threadIdx.x; e < n; e += (int64_t)gridDim.y * blockDim.x) {
+    const int k = (int)(e / vCols), j = (int)(e - (int64_t)k * vCols);
+    double s = 0;
+    for (int h = 0; h < g.gCols; h++) s += g.dict[(size_t)k * g.gCols + h] * V[(size_t)g.cols[h] * vCols + j];
+    P[(g.valOff + k) * vCols + j] = s;
+  }
+}
+
+// constRow[j] = sum_c constV[c] * V[c, j]
+__global__ void k_const_times_v(const double* __restrict__ constV, int nCols, const double* __restrict__ V, int vCols,
+                                double* __restrict__ constRow) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= vCols) return;
+  double s = 0;
+  for (int c = 0; c < nCols; c++) s += constV[c] * V[(size_t)c * vCols + j];
+  constRow[j] = s;
+}
+
+// --------------------------------------------------------------------------------------------------
+// RMM tile kernel. Tile = TR rows x vc columns, TR * vc <= TILE_ELEMS, 256 threads; each thread owns
+// fixed elements of the tile, so dense-map and uncompressed groups accumulate in registers without
+// synchronisation. Sparse groups (SDC) scatter into the shared tile with shared-memory atomics, one
+// group per warp. RLE groups are staged eight at a time as per-row ids in shared memory.
+// --------------------------------------------------------------------------------------------------
+constexpr int RMM_THREADS = 256;
+constexpr int RMM_E = 16;
+constexpr int TILE_ELEMS = RMM_THREADS * RMM_E;  // 4096 doubles = 32 KB
+constexpr int RLE_BATCH = 8;
+constexpr int MAX_TR = 1024;
+
+__global__ void __launch_bounds__(RMM_THREADS)
+k_rmm_tile(const DevGroup* __restrict__ groups, int nGroups, int nRows, const double* __restrict__ P,
+           const double* __restrict__ V, int vCols, const double* __restrict__ constRow, double* __restrict__ out,
+           int TR, int vcTile, int hasSparse) {
+  extern __shared__ double smem[];
+  double* acc = smem;                                         // [TR * vc]
+  uint16_t* ids = (uint16_t*)(smem + TILE_ELEMS);             // [RLE_BATCH][MAX_TR]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int r0 = blockIdx.x * TR, r1 = min(nRows, r0 + TR);
+  const int j0 = blockIdx.y * vcTile, vc = min(vcTile, vCols - j0);
+  const int nElem = (r1 - r0) * vc;
+
+  double racc[RMM_E];
+  int er[RMM_E], ej[RMM_E];
+#pragma unroll
+  for (int i = 0; i < RMM_E; i++) {
+    const int e = tid + i * RMM_THREADS;
+    er[i] = e / vc;
+    ej[i] = e - er[i] * vc;
+    racc[i] = (constRow != nullptr && e < nElem) ? constRow[j0 + ej[i]] : 0.0;
+  }
+  // phase A: dense-map and uncompressed groups, registers
+  for (int gi = 0; gi < nGroups; gi++) {
+    const DevGroup& g = groups[gi];
+    if (g.type == GT_DDC) {
+      const double* Pg = P + g.valOff * vCols + j0;
+#pragma unroll
+      for (int i = 0; i < RMM_E; i++) {
+        if (tid + i * RMM_THREADS < nElem) {
+          const int id = map_get(g.mapType, g.map, g.mapHi, r0 + er[i]);
+          racc[i] += Pg[(size_t)id * vCols + ej[i]];
+        }
+      }
+    } else if (g.type == GT_UNC) {
+#pragma unroll
+      for (int i = 0; i < RMM_E; i++) {
+        if (tid + i * RMM_THREADS < nElem) {
+          const double* x = g.dense + (size_t)(r0 + er[i]) * g.gCols;
+          double s = 0;
+          for (int c = 0; c < g.gCols; c++) s += x[c] * V[(size_t)g.cols[c] * vCols + j0 + ej[i]];
+          racc[i] += s;
+        }
+      }
+    }
+  }
+  if (!hasSparse) {
+#pragma unroll
+    for (int i = 0; i < RMM_E; i++)
+      if (tid + i * RMM_THREADS < nElem) out[(size_t)(r0 + er[i]) * vCols + j0 + ej[i]] = racc[i];
+    return;
+  }
+#pragma unroll
+  for (int i = 0; i < RMM_E; i++)
+    if (tid + i * RMM_THREADS < nElem) acc[tid + i * RMM_THREADS] = racc[i];
+  __syncthreads();
+  // phase B: SDC groups, one per warp at a time, shared atomics (listed rows are sparse)
+  for (int gi = warp; gi < nGroups; gi += RMM_THREADS / 32) {
+    const DevGroup& g = groups[gi];
+    if (g.type != GT_SDC) continue;
+    const double* Pg = P + g.valOff * vCols + j0;
+    sdc_walk_block(g, r0, r1, [&](int row, int e) {
+      const int id = g.single ? 0 : map_get(g.mapType, g.map, g.mapHi, e);
+      double* a = acc + (row - r0) * vc;
+      const double* p = Pg + (size_t)id * vCols;
+      for (int j = 0; j < vc; j++) atomicAdd(&a[j], p[j]);
+    });
+  }
+  __syncthreads();
+  // phase C: RLE groups in batches: stage per-row ids, then every thread adds to its own elements
+  int batch[RLE_BATCH];
+  int nb = 0;
+  for (int gi = 0; gi <= nGroups; gi++) {
+    if (gi < nGroups && groups[gi].type == GT_RLE) batch[nb++] = gi;
+    if (nb == RLE_BATCH || (gi == nGroups && nb > 0)) {
+      for (int e = tid; e < nb * MAX_TR; e += RMM_THREADS) ids[e] = 0xFFFF;
+      __syncthreads();
+      if (warp < nb) {
+        const DevGroup& g = groups[batch[warp]];
+        for (int64_t ri = g.runSkip[r0 / SKIP_ROWS]; ri < g.nRuns; ri++) {
+          const RleRun run = g.runs[ri];
+          if (run.start >= r1) break;
+          const int a = max(run.start, r0), b = min(run.start + (int)run.len, r1);
+          for (int r = a + lane; r < b; r += 32) ids[warp * MAX_TR + (r - r0)] = run.k;
+        }
+      }
+      __syncthreads();
+      for (int bi = 0; bi < nb; bi++) {
+        const DevGroup& g = groups[batch[bi]];
+        const double* Pg = P + g.valOff * vCols + j0;
+#pragma unroll
+        for (int i = 0; i < RMM_E; i++) {
+          const int e = tid + i * RMM_THREADS;
+          if (e < nElem) {
+            const int id = ids[bi * MAX_TR + er[i]];
+            if (id != 0xFFFF) acc[e] += Pg[(size_t)id * vCols + ej[i]];
+          }
+        }
+      }
+      __syncthreads();
+      nb = 0;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < RMM_E; i++) {
+    const int e = tid + i * RMM_THREADS;
+    if (e < nElem) out[(size_t)(r0 + er[i]) * vCols + j0 + ej[i]] = acc[e];
+  }
+}
+
+int64_t launch_rmm(Matrix* m, const double* dV, int vCols, double* dOut, cudaStream_t s) {
+  if (m->nRows == 0 || vCols == 0) return CLA_OK;
+  int64_t rc;
+  const size_t pBytes = (size_t)std::max<int64_t>(m->totalVals, 1) * vCols * sizeof(double);
+  const size_t cOff = (pBytes + 255) & ~(size_t)255;
+  if ((rc = ensure_scratch(m, cOff + (size_t)vCols * sizeof(double))) < 0) return rc;
+  double* P = (double*)m->scratch;
+  double* constRow = nullptr;
+  if (m->nDev > 0) {
+    int maxE = 1;
+    for (auto& g : m->groups) maxE = std::max<int64_t>(maxE, (int64_t)g.nVals * vCols);
+    dim3 grid(m->nDev, std::max(1, std::min(64, (maxE + 255) / 256)));
+    k_dict_times_v<<<grid, 256, 0, s>>>(m->dGroups, dV, vCols, P);
+    m->stats.kernel_launches++;
+  }
+  if (m->hasConst) {
+    constRow = (double*)((char*)m->scratch + cOff);
+    k_const_times_v<<<(vCols + 127) / 128, 128, 0, s>>>(m->dConstV, m->nCols, dV, vCols, constRow);
+    m->stats.kernel_launches++;
+  }
+  const int vcTile = std::min(vCols, 64);
+  int TR = std::min(MAX_TR, std::max(32, TILE_ELEMS / vcTile));
+  int hasSparse = 0;
+  for (auto& g : m->groups) hasSparse |= (g.type == GT_SDC || g.type == GT_RLE);
+  const size_t smem = TILE_ELEMS * sizeof(double) + (size_t)RLE_BATCH * MAX_TR * sizeof(uint16_t);
+  static bool attr = false;
+  if (!attr) {
+    CLA_CUDA(cudaFuncSetAttribute(k_rmm_tile, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr = true;
+  }
+  dim3 grid((m->nRows + TR - 1) / TR, (vCols + vcTile - 1) / vcTile);
+  k_rmm_tile<<<grid, RMM_THREADS, smem, s>>>(m->dGroups, m->nDev, m->nRows, P, dV, vCols, constRow, dOut, TR, vcTile,
+                                             hasSparse);
+  m->stats.kernel_launches++;
+  CLA_CUDA(cudaGetLastError());
+  return CLA_OK;
+}
+
+// --------------------------------------------------------------------------------------------------
+// decompress = RMM with V = I restricted to the group's own columns: out[r, cols_g] += D_g[id_g(r), :]
+// One launch per group keeps the reference's "groups in list order" summation
+// (lib/CLALibDecompress.java:427-434) without atomics.
+// --------------------------------------------------------------------------------------------------
+__global__ void k_decomp_init(double* __restrict__ out, const double* __restrict__ constV, int64_t nRows, int nCols) {
+  const int64_t n = nRows * nCols;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    out[i] = constV ? constV[i % nCols] : 0.0;
+}
+// rows [r0, r1); out points at row r0
+__global__ void k_decomp_dense(DevGroup g, double* __restrict__ out, int r0, int r1, int nCols) {
+  const int64_t n = (int64_t)(r1 - r0) * g.gCols;
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < n; e += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = e / g.gCols;
+    const int c = (int)(e - r * g.gCols);
+    double v;
+    if (g.type == GT_UNC) v = g.dense[(size_t)(r0 + r) * g.gCols + c];
+    else v = g.dict[(size_t)map_get(g.mapType, g.map, g.mapHi, r0 + r) * g.gCols + c];
+    out[r * nCols + g.cols[c]] += v;
+  }
+}
+__global__ void k_decomp_sdc(DevGroup g, double* __restrict__ out, int r0, int r1, int nCols) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int rb = r0 + warp * SKIP_ROWS;
+  if (rb >= r1) return;
+  const int re = min(r1, rb + SKIP_ROWS);
+  sdc_walk_block(g, rb, re, [&](int row, int e) {
+    const int id = g.single ? 0 : map_get(g.mapType, g.map, g.mapHi, e);
+    for (int c = 0; c < g.gCols; c++) out[(size_t)(row - r0) * nCols + g.cols[c]] += g.dict[(size_t)id * g.gCols + c];
+  });
+}
+__global__ void k_decomp_rle(DevGroup g, double* __restrict__ out, int r0, int r1, int nCols) {
+  const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  const int64_t nWarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int64_t ri = g.runSkip[r0 / SKIP_ROWS] + warp; ri < g.nRuns; ri += nWarps) {
+    const RleRun r = g.runs[ri];
+    if (r.start >= r1) break;
+    const int a = max(r.start, r0), b = min(r.start + (int)r.len, r1);
+    for (int i = a + lane; i < b; i += 32)
+      for (int c = 0; c < g.gCols; c++) out[(size_t)(i - r0) * nCols + g.cols[c]] += g.dict[(size_t)r.k * g.gCols + c];
+  }
+}
+
+// r0 must be a multiple of SKIP_ROWS
+int64_t launch_decompress_range(Matrix* m, int r0, int r1, double* dOut, cudaStream_t s) {
+  const int64_t n = (int64_t)(r1 - r0) * m->nCols;
+  if (n <= 0) return CLA_OK;
+  k_decomp_init<<<grid_for(n, 256), 256, 0, s>>>(dOut, m->hasConst ? m->dConstV : nullptr, r1 - r0, m->nCols);
+  for (auto& g : m->groups) {
+    if (g.type == GT_DDC || g.type == GT_UNC)
+      k_decomp_dense<<<grid_for((int64_t)(r1 - r0) * g.gCols, 256), 256, 0, s>>>(g, dOut, r0, r1, m->nCols);
+    else if (g.type == GT_SDC) {
+      const int nb = (r1 - r0 + SKIP_ROWS - 1) / SKIP_ROWS;
+      k_decomp_sdc<<<(nb * 32 + 255) / 256, 256, 0, s>>>(g, dOut, r0, r1, m->nCols);
+    } else if (g.type == GT_RLE && g.nRuns)
+      k_decomp_rle<<<64, 256, 0, s>>>(g, dOut, r0, r1, m->nCols);
+    m->stats.kernel_launches++;
+  }
+  CLA_CUDA(cudaGetLastError());
+  return CLA_OK;
+}
+
+int64_t launch_decompress(Matrix* m, double* dOut, cudaStream_t s) {
+  return launch_decompress_range(m, 0, m->nRows, dOut, s);
+}
+
+// --------------------------------------------------------------------------------------------------
+// LMM
+// --------------------------------------------------------------------------------------------------
+constexpr int LMM_THREADS = 256;
+constexpr int LMM_QT = 4;                 // left rows per pass (the reference's rowBlockSize)
+constexpr int LMM_HIST_MAX = 6144;        // doubles of shared histogram (48 KB)
+
+// grid: (row chunks, dictionary groups, q tiles). A: [totalVals x q]
+__global__ void __launch_bounds__(LMM_THREADS)
+k_lmm_preagg(const DevGroup* __restrict__ groups, int nRows, int rowsPerChunk, const double* __restrict__ Yt, int q,
+             double* __restrict__ A) {
+  __shared__ double hist[LMM_HIST_MAX];
+  const DevGroup& g = groups[blockIdx.y];
+  if (g.type == GT_UNC) return;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int ra = blockIdx.x * rowsPerChunk, rb = min(nRows, ra + rowsPerChunk);
+  if (ra >= rb) return;
+  const int q0 = blockIdx.z * LMM_QT, qt = min(LMM_QT, q - q0);
+  const int nv = g.nVals;
+  const bool useShared = (int64_t)nv * qt <= LMM_HIST_MAX;
+  double* Ag = A + g.valOff * q;
+  if (useShared) {
+    for (int e = tid; e < nv * qt; e += LMM_THREADS) hist[e] = 0.0;
+    __syncthreads();
+  }
+  auto add = [&](int id, int i, double v) {
+    if (useShared) atomicAdd(&hist[i * nv + id], v);
+    else atomicAdd(&Ag[(size_t)id * q + q0 + i], v);
+  };
+  if (g.type == GT_DDC) {
+    for (int r = ra + tid; r < rb; r += LMM_THREADS) {
+      const int id = map_get(g.mapType, g.map, g.mapHi, r);
+      for (int i = 0; i < qt; i++) add(id, i, Yt[(size_t)(q0 + i) * nRows + r]);
+    }
+  } else if (g.type == GT_SDC) {
+    for (int b = ra + warp * SKIP_ROWS; b < rb; b += (LMM_THREADS / 32) * SKIP_ROWS) {
+      sdc_walk_block(g, b, min(rb, b + SKIP_ROWS), [&](int row, int e) {
+        const int id = g.single ? 0 : map_get(g.mapType, g.map, g.mapHi, e);
+        for (int i = 0; i < qt; i++) add(id, i, Yt[(size_t)(q0 + i) * nRows + row]);
+      });
+    }
+  } else if (g.type == GT_RLE) {
+    // one warp per run: sum the left values over the run, then one add per left row
+    for (int64_t ri = g.runSkip[ra / SKIP_ROWS] + warp; ri < g.nRuns; ri += LMM_THREADS / 32) {
+      const RleRun run = g.runs[ri];
+      if (run.start >= rb) break;
+      const int a = max(run.start, ra), b = min(run.start + (int)run.len, rb);
+      for (int i = 0; i < qt; i++) {
+        double sum = 0;
+        for (int r = a + lane; r < b; r += 32) sum += Yt[(size_t)(q0 + i) * nRows + r];
+        for (int d = 16; d; d >>= 1) sum += __shfl_down_sync(0xffffffffu, sum, d);
+        if (lane == 0 && a < b) add(run.k, i, sum);
+      }
+    }
+  }
+  if (useShared) {
+    __syncthreads();
+    for (int e = tid; e < nv * qt; e += LMM_THREADS) {
+      const double v = hist[e];
+      if (v != 0.0) {
+        const int i = e / nv, id = e - i * nv;
+        atomicAdd(&Ag[(size_t)id * q + q0 + i], v);
+      }
+    }
+  }
+}
+
+// out[i, cols_g[c]] += sum_k A_g[k, i] * D_g[k, c]; one block per group
+__global__ void k_lmm_post(const DevGroup* __restrict__ groups, const double* __restrict__ A, int q, int nCols,
+                           double* __restrict__ out) {
+  const DevGroup& g = groups[blockIdx.x];
+  if (g.type == GT_UNC) return;
+  const double* Ag = A + g.valOff * q;
+  for (int e = threadIdx.x; e < q * g.gCols; e += blockDim.x) {
+    const int i = e / g.gCols, c = e - i * g.gCols;
+    double s = 0;
+    for (int k = 0; k < g.nVals; k++) s += Ag[(size_t)k * q + i] * g.dict[(size_t)k * g.gCols + c];
+    atomicAdd(&out[(size_t)i * nCols + g.cols[c]], s);
+  }
+}
+
+// uncompressed group: out[i, cols[c]] += sum_r Yt[i, r] * dense[r, c]; block = (row chunk), threads over (i, c)
+__global__ void k_lmm_unc(DevGroup g, int nRows, int rowsPerChunk, const double* __restrict__ Yt, int q, int nCols,
+                          double* __restrict__ out) {
+  const int ra = blockIdx.x * rowsPerChunk, rb = min(nRows, ra + rowsPerChunk);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nWarps = blockDim.x >> 5;
+  // each warp owns output cells (i, c) round robin; lanes stride over rows
+  for (int e = warp; e < q * g.gCols; e += nWarps) {
+    const int i = e / g.gCols, c = e - i * g.gCols;
+    double s = 0;
+    for (int r = ra + lane; r < rb; r += 32) s += Yt[(size_t)i * nRows + r] * g.dense[(size_t)r * g.gCols + c];
+    for (int d = 16; d; d >>= 1) s += __shfl_down_sync(0xffffffffu, s, d);
+    if (lane == 0) atomicAdd(&out[(size_t)i * nCols + g.cols[c]], s);
+  }
+}
+
+__global__ void k_row_sums(const double* __restrict__ Yt, int nRows, int q, double* __restrict__ sums) {
+  const int i = blockIdx.y;
+  double s = 0;
+  for (int64_t r = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; r < nRows; r += (int64_t)gridDim.x * blockDim.x)
+    s += Yt[(size_t)i * nRows + r];
+  for (int d = 16; d; d >>= 1) s += __shfl_down_sync(0xffffffffu, s, d);
+  if ((threadIdx.x & 31) == 0) atomicAdd(&sums[i], s);
+}
+__global__ void k_lmm_const(const double* __restrict__ sums, const double* __restrict__ constV, int q, int nCols,
+                            double* __restrict__ out) {
+  const int64_t n = (int64_t)q * nCols;
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < n; e += (int64_t)gridDim.x * blockDim.x)
+    out[e] += sums[e / nCols] * constV[e % nCols];
+}
+
+int64_t launch_lmm(Matrix* m, const double* dYt, int q, double* dOut, cudaStream_t s) {
+  if (q == 0 || m->nCols == 0) return CLA_OK;
+  CLA_CUDA(cudaMemsetAsync(dOut, 0, sizeof(double) * (size_t)q * m->nCols, s));
+  if (m->nRows == 0) return CLA_OK;
+  int64_t rc;
+  const size_t aBytes = (size_t)std::max<int64_t>(m->totalVals, 1) * q * sizeof(double);
+  const size_t sOff = (aBytes + 255) & ~(size_t)255;
+  if ((rc = ensure_scratch(m, sOff + (size_t)q * sizeof(double))) < 0) return rc;
+  double* A = (double*)m->scratch;
+  double* sums = (double*)((char*)m->scratch + sOff);
+  CLA_CUDA(cudaMemsetAsync(A, 0, sOff + (size_t)q * sizeof(double), s));
+  if (m->nDev > 0) {
+    const int target = std::max(1, (8 * m->smCount) / std::max(1, m->nDev));
+    int rowsPerChunk = (int)(((int64_t)m->nRows + target - 1) / target);
+    rowsPerChunk = std::max(SKIP_ROWS * 4, ((rowsPerChunk + SKIP_ROWS - 1) / SKIP_ROWS) * SKIP_ROWS);
+    const int chunks = (m->nRows + rowsPerChunk - 1) / rowsPerChunk;
+    dim3 grid(chunks, m->nDev, (q + LMM_QT - 1) / LMM_QT);
+    k_lmm_preagg<<<grid, LMM_THREADS, 0, s>>>(m->dGroups, m->nRows, rowsPerChunk, dYt, q, A);
+    k_lmm_post<<<m->nDev, 128, 0, s>>>(m->dGroups, A, q, m->nCols, dOut);
+    m->stats.kernel_launches += 2;
+    for (auto& g : m->groups)
+      if (g.type == GT_UNC) {
+        const int rpc = std::max(4096, (int)(((int64_t)m->nRows + 4 * m->smCount - 1) / (4 * m->smCount)));
+        k_lmm_unc<<<(m->nRows + rpc - 1) / rpc, 256, 0, s>>>(g, m->nRows, rpc, dYt, q, m->nCols, dOut);
+        m->stats.kernel_launches++;
+      }
+  }
+  if (m->hasConst) {
+    dim3 grid(grid_for(m->nRows, 256, 4 * m->smCount), q);
+    k_row_sums<<<grid, 256, 0, s>>>(dYt, m->nRows, q, sums);
+    k_lmm_const<<<grid_for((int64_t)q * m->nCols, 256), 256, 0, s>>>(sums, m->dConstV, q, m->nCols, dOut);
+    m->stats.kernel_launches += 2;
+  }
+  CLA_CUDA(cudaGetLastError());
+  return CLA_OK;
+}
+
+}  // namespace cla
