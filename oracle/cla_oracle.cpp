@@ -428,10 +428,25 @@ void lmm(const ocl_matrix* m, const double* left, int q, double* out, int k) {
   const int rowBlockSize = std::max(q / k, 1);
   // pre-agg groups: strided subsets, one task each (writes to disjoint output columns unless overlapping)
   // the reference writes directly into ret when groups do not overlap; disjoint columns make this race free.
+  // overlapping groups share output columns: private results per task, summed afterwards
+  // (LMMParallelTempOut, CLALibLeftMultBy.java:442-493)
+  std::vector<int> cover(nCols, 0);
+  bool overlapping = false;
+  for (auto& v : pa)
+    for (int c : v.g->cols) overlapping |= (++cover[c] > 1);
+  std::vector<std::vector<double>> tmpOut(overlapping ? s : 0);
 #pragma omp parallel for schedule(dynamic, 1) num_threads(k)
-  for (int off = 0; off < s; off++)
+  for (int off = 0; off < s; off++) {
+    double* dst = out;
+    if (overlapping) {
+      tmpOut[off].assign((size_t)q * nCols, 0.0);
+      dst = tmpOut[off].data();
+    }
     for (int blo = 0; blo < q; blo += rowBlockSize)
-      lmm_with_preagg(pa, left, nRows, out, nCols, blo, std::min(blo + rowBlockSize, q), 0, nRows, off, s, nullptr);
+      lmm_with_preagg(pa, left, nRows, dst, nCols, blo, std::min(blo + rowBlockSize, q), 0, nRows, off, s, nullptr);
+  }
+  for (auto& t : tmpOut)
+    for (size_t i = 0; i < (size_t)q * nCols; i++) out[i] += t[i];
   if (filtered)  // separate rowSum task in the parallel variants (CLALibLeftMultBy.java:399-400)
     for (int i = 0; i < q; i++)
       for (int r = 0; r < nRows; r++) rowSums[i] += left[(size_t)i * nRows + r];

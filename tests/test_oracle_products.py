@@ -24,7 +24,7 @@ def test_oracle_vs_dense(oracle, name, kinds, overlap, nRows):
     cmb = datagen.random_cmb(sum(map(ord, name)) + nRows, nRows, kinds, overlap)
     X = dense_of(cmb)
     om = oracle.OracleMatrix(cmb, threads=3)
-    assert np.array_equal(om.decompress(), X) or rel_err(om.decompress(), X) < 1e-15
+    assert rel_err(om.decompress(), X) < 1e-14  # default + (dict - default) rounds once
     rng = np.random.default_rng(nRows)
     for vc in (1, 5):
         V = rng.standard_normal((cmb.clen, vc))
