@@ -66,7 +66,9 @@ typedef struct cla_stats {
   int64_t index_bytes;       /* bytes of index structures + dictionaries (one pass reads these) */
   int64_t calls_rmm, calls_lmm, calls_tsmm, calls_mmchain, calls_decompress;
   int64_t kernel_launches;   /* launches issued by this handle since creation */
-  double last_kernel_ms;     /* device time of the last product call (CUDA events) */
+  double last_kernel_ms;     /* device time of the last host-buffer product call (CUDA events) */
+  double main_kernel_ms;     /* with profiling on: summed device time of the dominant kernel of each product call */
+  int64_t main_kernel_count; /* ... and how many launches that sum covers */
 } cla_stats;
 
 /* ---- life cycle ---------------------------------------------------------------------------
@@ -80,6 +82,10 @@ int64_t cla_finalize(cla_handle h, int32_t device);
 /* Copies the message of the calling thread's last failed call into buf; returns its length. */
 int64_t cla_last_error(char* buf, int64_t cap);
 int64_t cla_stats_get(cla_handle h, cla_stats* out);
+/* Profiling switch (the analogue of the reference's -stats timers, utils/Statistics.java): when on, every
+ * product call brackets its dominant kernel with CUDA events on the launching stream; cla_stats_get
+ * synchronises those events and adds them to main_kernel_ms / main_kernel_count. */
+int64_t cla_set_profile(cla_handle h, int32_t on);
 
 /* ---- group registration (host arrays are copied) -------------------------------------------
  * Each returns the index of the new group (>= 0) or a CLA_ERR_* code.

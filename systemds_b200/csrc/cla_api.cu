@@ -120,10 +120,18 @@ int64_t cla_last_error(char* buf, int64_t cap) {
 int64_t cla_stats_get(cla_handle h, cla_stats* out) {
   GET_MATRIX(h);
   if (!out) return fail(CLA_ERR_BAD_ARG, "null stats pointer");
+  if (m->device >= 0) cudaSetDevice(m->device);
+  prof_collect(m);
   *out = m->stats;
   out->n_rows = m->nRows;
   out->n_cols = m->nCols;
   out->n_groups = (int64_t)m->hg.size();
+  return CLA_OK;
+}
+
+int64_t cla_set_profile(cla_handle h, int32_t on) {
+  GET_MATRIX(h);
+  m->profile = on != 0;
   return CLA_OK;
 }
 

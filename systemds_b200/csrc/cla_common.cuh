@@ -162,6 +162,9 @@ struct Matrix {
   cudaStream_t stream = nullptr;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   FastPlan* fast = nullptr;
+  bool profile = false;
+  std::vector<std::pair<cudaEvent_t, cudaEvent_t>> profEvents;  // ring of event pairs
+  size_t profUsed = 0;
   cla_stats stats{};
   int smCount = 148;
 };
@@ -175,6 +178,11 @@ int64_t fail(int64_t code, const std::string& msg);
     if (e_ != cudaSuccess)                                                                          \
       return ::cla::fail(CLA_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(e_));         \
   } while (0)
+
+// profiling brackets around the dominant kernel of a product call (no-ops unless m->profile)
+void prof_begin(Matrix* m, cudaStream_t s);
+void prof_end(Matrix* m, cudaStream_t s);
+void prof_collect(Matrix* m);
 
 int64_t ensure_scratch(Matrix* m, size_t bytes);
 int64_t ensure_scratch2(Matrix* m, size_t bytes);

@@ -1,8 +1,597 @@
-// placeholder, replaced below
+// Specialised vector products for matrices whose product groups are all dense-map (DDC) groups with
+// at most 256 dictionary tuples and one byte per map cell -- the shape of the headline workloads
+// (X %*% v, t(y) %*% X and the two passes of t(X) %*% (X %*% v)).
+//
+// Both kernels are bound by shared-memory lookups (one 8-byte dictionary read per map cell), so the
+// layouts are chosen to make those reads bank-conflict free:
+//
+//  * k_rmm_vec_u8: a thread owns 16 consecutive rows (one 128-bit map load per group) and keeps their
+//    16 partial sums in registers; the tables P_g = D_g * v[cols_g] (built per call by k_fast_ptable)
+//    sit in shared memory back to back. A table of <= 16 entries spans each 8-byte bank once, so random
+//    ids never conflict; larger tables conflict in proportion to their size.
+//
+//  * k_lmm_vec_u8: a lane owns *columns*, not rows. Tables are interleaved 32 columns wide
+//    (entry k of slot s at byte k*256 + s*8), so lane s only ever touches bank pair s mod 16 whatever the
+//    ids are: conflict free for any cardinality, without replicating tables. The two half-warps of a warp
+//    work on different rows of the same 2 x 16 column slots. The left vector is read with warp-uniform
+//    128-bit loads and kept in registers for all columns of the CTA.
+//
+// Tables are staged into shared memory with TMA bulk copies (cp.async.bulk + mbarrier, no multicast).
 #include "cla_common.cuh"
+#include <algorithm>
+#include <numeric>
+
 namespace cla {
-int64_t fast_plan_build(Matrix*) { return CLA_OK; }
-void fast_plan_free(Matrix*) {}
-int64_t fast_rmm_vec(Matrix*, const double*, double*, cudaStream_t) { return 0; }
-int64_t fast_lmm_vec(Matrix*, const double*, double*, cudaStream_t) { return 0; }
+
+int64_t launch_lmm_const(Matrix* m, const double* dYt, int q, double* dOut, cudaStream_t s);  // cla_generic.cu
+
+constexpr int FAST_MIN_ROWS = 4096;
+constexpr int SMEM_MAX = 227 * 1024;
+
+// ---- RMM plan ----
+constexpr int RMM_T = 256;            // threads
+constexpr int RMM_ROWS_PT = 16;       // rows per thread
+constexpr int RMM_TILE = RMM_T * RMM_ROWS_PT;
+
+// ---- LMM plan ----
+constexpr int LMM_W = 12;             // warps per CTA
+constexpr int LMM_T = LMM_W * 32;
+constexpr int LMM_MAX_PAIRS = 3;      // 32-column table slabs per CTA (3 x 64 KB at 256 tuples)
+constexpr int LMM_STEP = 64;          // rows per warp step (32 per half-warp)
+
+struct RmmChunk {
+  int g0, g1;          // range in plan order
+  int tblDoubles;      // table doubles of the chunk (even)
+  int64_t tblOff;      // offset of the chunk's tables in the P image (doubles, even)
+};
+struct LmmChunk {
+  int pair0, nPairs;     // slabs of 32 column slots
+  int nk[LMM_MAX_PAIRS]; // table depth (max tuples) of each slab
+  int64_t tblOff;        // offset in the table image (doubles)
+  int tblDoubles;
+  int cta0, nCta;        // CTA range of the launch that works on this chunk
+};
+
+struct FastPlan {
+  bool ok = false;
+  int nG = 0;
+  // RMM
+  std::vector<RmmChunk> rchunks;
+  const uint8_t** dMaps = nullptr;  // [nG] plan order
+  int* dTblOff = nullptr;           // [nG] offset of each group's table inside its chunk (doubles)
+  int* dGroupOf = nullptr;          // [nG] plan order -> device group index
+  int64_t* dImgOff = nullptr;       // [nG] offset of each group's table in the P image (doubles)
+  int64_t pImgDoubles = 0;
+  // LMM
+  int nUnits = 0, nSlots = 0;
+  std::vector<LmmChunk> lchunks;
+  LmmChunk* dLChunks = nullptr;
+  const uint8_t** dSlotMap = nullptr;  // [nSlots]
+  int* dSlotCol = nullptr;             // [nSlots] output column or -1
+  double* dLmmTables = nullptr;        // image of all chunk tables
+  int lmmGrid = 0;
+  std::vector<void*> allocs;
+};
+
+// --------------------------------------------------------------------------------------------------
+// TMA bulk copy global -> shared, completion on an mbarrier; bounded wait.
+// --------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// Copies `bytes` (multiple of 16, both addresses 16-byte aligned) and waits. Returns false on timeout.
+__device__ __forceinline__ bool tma_load_to_smem(void* dst, const void* src, uint32_t bytes, uint64_t* mbar) {
+  const uint32_t bar = smem_u32(mbar);
+  if (threadIdx.x == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+    const uint32_t CH = 32768;
+    for (uint32_t off = 0; off < bytes; off += CH) {
+      const uint32_t sz = min(CH, bytes - off);
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                       smem_u32((char*)dst + off)),
+                   "l"((const char*)src + off), "r"(sz), "r"(bar)
+                   : "memory");
+    }
+  }
+  uint32_t done = 0;
+  for (int it = 0; it < (1 << 22) && !done; it++) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(0u)
+        : "memory");
+  }
+  // one verdict for the whole CTA (also the barrier that publishes the data to every thread)
+  return __syncthreads_and(done != 0) != 0;
 }
+
+// --------------------------------------------------------------------------------------------------
+// RMM: P image (padded per-group tables), then the row kernel
+// --------------------------------------------------------------------------------------------------
+__global__ void k_fast_ptable(const DevGroup* __restrict__ groups, const int* __restrict__ groupOf,
+                              const int64_t* __restrict__ imgOff, int nG, const double* __restrict__ v,
+                              double* __restrict__ P) {
+  const int gi = blockIdx.x;
+  if (gi >= nG) return;
+  const DevGroup& g = groups[groupOf[gi]];
+  for (int k = threadIdx.x; k < g.nVals; k += blockDim.x) {
+    double s = 0;
+    for (int h = 0; h < g.gCols; h++) s += g.dict[(size_t)k * g.gCols + h] * v[g.cols[h]];
+    P[imgOff[gi] + k] = s;
+  }
+}
+
+__device__ __forceinline__ uint32_t byte_x8(uint32_t w, int i) {  // (byte i of w) * 8
+  return i == 0 ? (w << 3) & 0x7F8u : (w >> (8 * i - 3)) & 0x7F8u;
+}
+
+__global__ void __launch_bounds__(RMM_T)
+k_rmm_vec_u8(const uint8_t* const* __restrict__ maps, const int* __restrict__ tblOff, int g0, int g1,
+             const double* __restrict__ Pchunk, int tblDoubles, int nRows, const double* __restrict__ constRow,
+             double* __restrict__ out, int accumulate, int32_t* err) {
+  extern __shared__ __align__(128) unsigned char smraw[];
+  double* tables = (double*)smraw;
+  const int nG = g1 - g0;
+  const uint8_t** sMaps = (const uint8_t**)(smraw + (size_t)tblDoubles * 8);
+  int* sOff = (int*)(sMaps + nG);
+  __shared__ __align__(8) uint64_t mbar;
+  const int tid = threadIdx.x;
+  for (int i = tid; i < nG; i += RMM_T) {
+    sMaps[i] = maps[g0 + i];
+    sOff[i] = tblOff[g0 + i] * 8;  // byte offset
+  }
+  if (!tma_load_to_smem(tables, Pchunk, (uint32_t)tblDoubles * 8u, &mbar)) {
+    if (tid == 0) atomicExch(err, 100);
+    return;
+  }
+  const double c0 = (constRow != nullptr && !accumulate) ? constRow[0] : 0.0;
+  const int nTiles = (nRows + RMM_TILE - 1) / RMM_TILE;
+  const unsigned char* tb = (const unsigned char*)tables;
+  for (int tile = blockIdx.x; tile < nTiles; tile += gridDim.x) {
+    const int row = tile * RMM_TILE + tid * RMM_ROWS_PT;
+    if (row >= nRows) continue;
+    if (row + RMM_ROWS_PT <= nRows) {
+      double acc[16];
+#pragma unroll
+      for (int i = 0; i < 16; i++) acc[i] = c0;
+#pragma unroll 4
+      for (int g = 0; g < nG; g++) {
+        const uint4 w = __ldg((const uint4*)(sMaps[g] + row));
+        const unsigned char* T = tb + sOff[g];
+        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int i = 0; i < 16; i++) acc[i] += *(const double*)(T + byte_x8(ww[i >> 2], i & 3));
+      }
+      if (accumulate) {
+#pragma unroll
+        for (int i = 0; i < 16; i++) atomicAdd(out + row + i, acc[i]);
+      } else {
+        double2* o = (double2*)(out + row);
+#pragma unroll
+        for (int i = 0; i < 8; i++) o[i] = make_double2(acc[2 * i], acc[2 * i + 1]);
+      }
+    } else {  // ragged last rows
+      for (int r = row; r < nRows; r++) {
+        double a = c0;
+        for (int g = 0; g < nG; g++) a += *(const double*)(tb + sOff[g] + 8 * (int)sMaps[g][r]);
+        if (accumulate) atomicAdd(out + r, a);
+        else out[r] = a;
+      }
+    }
+  }
+}
+
+// --------------------------------------------------------------------------------------------------
+// LMM: column-per-lane kernel
+// --------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t byte_x256(uint32_t w, int i) {  // (byte i of w) << 8, one PRMT
+  // selector nibbles (low to high): result byte0 = 0 (take byte 4 of {w, 0} pair = zero operand), byte1 = byte i
+  return __byte_perm(w, 0u, 0x4404u | ((uint32_t)i << 4));
+}
+
+template <int NP>
+__device__ __forceinline__ void lmm_cells(const uint4 (&m)[NP][2][2], int sub, const double (&yv)[16],
+                                          const unsigned char* const (&tbase)[NP], double (&acc)[NP][2]) {
+#pragma unroll
+  for (int p = 0; p < NP; p++) {
+#pragma unroll
+    for (int ab = 0; ab < 2; ab++) {
+      const uint4 w = m[p][ab][sub];
+      const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+      const unsigned char* T = tbase[p] + ab * 128;
+#pragma unroll
+      for (int i = 0; i < 16; i++) {
+        const double t = *(const double*)(T + byte_x256(ww[i >> 2], i & 3));
+        acc[p][ab] = fma(yv[i], t, acc[p][ab]);
+      }
+    }
+  }
+}
+
+// partial: [gridDim.x][LMM_MAX_PAIRS * 32]
+template <int NP>
+__device__ __forceinline__ void lmm_vec_body(const LmmChunk& ch, const uint8_t* const* __restrict__ slotMap,
+                                             const double* __restrict__ tablesImg, const double* __restrict__ y,
+                                             int nRows, double* __restrict__ partial, unsigned char* smraw,
+                                             uint64_t* mbar, int32_t* err) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int slot = lane & 15, half = lane >> 4;
+  if (!tma_load_to_smem(smraw, tablesImg + ch.tblOff, (uint32_t)ch.tblDoubles * 8u, mbar)) {
+    if (tid == 0) atomicExch(err, 101);
+    return;
+  }
+  // table base of each slab for this lane (slot offset folded in), and this lane's map pointers
+  const unsigned char* tbase[NP];
+  const uint8_t* mp[NP][2];
+  {
+    size_t off = 0;
+#pragma unroll
+    for (int p = 0; p < NP; p++) {
+      tbase[p] = smraw + off + slot * 8;
+      off += (size_t)ch.nk[p] * 256;
+      mp[p][0] = slotMap[(ch.pair0 + p) * 32 + slot];
+      mp[p][1] = slotMap[(ch.pair0 + p) * 32 + 16 + slot];
+    }
+  }
+  double acc[NP][2];
+#pragma unroll
+  for (int p = 0; p < NP; p++) acc[p][0] = acc[p][1] = 0.0;
+
+  // rows of this CTA: contiguous range of 64-row steps
+  const int ctaInChunk = blockIdx.x - ch.cta0;
+  const int64_t nSteps = ((int64_t)nRows + LMM_STEP - 1) / LMM_STEP;
+  const int64_t s0 = nSteps * ctaInChunk / ch.nCta, s1 = nSteps * (ctaInChunk + 1) / ch.nCta;
+  for (int64_t st = s0 + warp; st < s1; st += LMM_W) {
+    const int64_t r0 = st * LMM_STEP + half * 32;
+    if (st * LMM_STEP + LMM_STEP <= nRows) {
+      uint4 m[NP][2][2];
+#pragma unroll
+      for (int p = 0; p < NP; p++)
+#pragma unroll
+        for (int ab = 0; ab < 2; ab++) {
+          const uint4* src = (const uint4*)(mp[p][ab] + r0);
+          m[p][ab][0] = __ldg(src);
+          m[p][ab][1] = __ldg(src + 1);
+        }
+#pragma unroll
+      for (int sub = 0; sub < 2; sub++) {
+        double yv[16];
+        const double2* ys = (const double2*)(y + r0 + sub * 16);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          const double2 t = __ldg(ys + i);
+          yv[2 * i] = t.x;
+          yv[2 * i + 1] = t.y;
+        }
+        lmm_cells<NP>(m, sub, yv, tbase, acc);
+      }
+    } else {  // ragged last step
+      for (int64_t r = r0; r < min((int64_t)nRows, r0 + 32); r++) {
+        const double yy = y[r];
+#pragma unroll
+        for (int p = 0; p < NP; p++)
+#pragma unroll
+          for (int ab = 0; ab < 2; ab++)
+            acc[p][ab] = fma(yy, *(const double*)(tbase[p] + ab * 128 + 256 * (int)mp[p][ab][r]), acc[p][ab]);
+      }
+    }
+  }
+  // combine the two half-warps (same column slots, different rows), then the warps through shared memory
+  __syncthreads();  // tables no longer needed
+  double* red = (double*)smraw;  // [LMM_W][NP*32]
+#pragma unroll
+  for (int p = 0; p < NP; p++)
+#pragma unroll
+    for (int ab = 0; ab < 2; ab++) {
+      double a = acc[p][ab];
+      a += __shfl_xor_sync(0xffffffffu, a, 16);
+      if (half == 0) red[warp * (NP * 32) + p * 32 + ab * 16 + slot] = a;
+    }
+  __syncthreads();
+  for (int u = tid; u < NP * 32; u += LMM_T) {
+    double s = 0;
+    for (int w = 0; w < LMM_W; w++) s += red[w * (NP * 32) + u];
+    partial[(size_t)blockIdx.x * (LMM_MAX_PAIRS * 32) + u] = s;
+  }
+}
+
+__global__ void __launch_bounds__(LMM_T, 1)
+k_lmm_vec_u8(const LmmChunk* __restrict__ chunks, int nChunks, const uint8_t* const* __restrict__ slotMap,
+             const double* __restrict__ tablesImg, const double* __restrict__ y, int nRows,
+             double* __restrict__ partial, int32_t* err) {
+  extern __shared__ __align__(128) unsigned char smraw[];
+  __shared__ __align__(8) uint64_t mbar;
+  __shared__ LmmChunk ch;
+  if (threadIdx.x == 0) {
+    int c = 0;
+    while (c + 1 < nChunks && (int)blockIdx.x >= chunks[c].cta0 + chunks[c].nCta) c++;
+    ch = chunks[c];
+  }
+  __syncthreads();
+  switch (ch.nPairs) {
+    case 1: lmm_vec_body<1>(ch, slotMap, tablesImg, y, nRows, partial, smraw, &mbar, err); break;
+    case 2: lmm_vec_body<2>(ch, slotMap, tablesImg, y, nRows, partial, smraw, &mbar, err); break;
+    default: lmm_vec_body<3>(ch, slotMap, tablesImg, y, nRows, partial, smraw, &mbar, err); break;
+  }
+}
+
+// out[col] += sum over the chunk's CTAs of partial[cta][slot], in CTA order (deterministic per column)
+__global__ void k_lmm_vec_final(const LmmChunk* __restrict__ chunks, int nChunks, const int* __restrict__ slotCol,
+                                const double* __restrict__ partial, double* __restrict__ out) {
+  const int c = blockIdx.x;
+  if (c >= nChunks) return;
+  const LmmChunk ch = chunks[c];
+  for (int u = threadIdx.x; u < ch.nPairs * 32; u += blockDim.x) {
+    const int col = slotCol[ch.pair0 * 32 + u];
+    if (col < 0) continue;
+    double s = 0;
+    for (int b = 0; b < ch.nCta; b++) s += partial[(size_t)(ch.cta0 + b) * (LMM_MAX_PAIRS * 32) + u];
+    atomicAdd(&out[col], s);
+  }
+}
+
+// bit map -> byte map (one id per byte), used once at plan time
+__global__ void k_bits_to_bytes(const unsigned long long* __restrict__ bits, uint8_t* __restrict__ out, int64_t n) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    out[i] = (uint8_t)((bits[i >> 6] >> (i & 63)) & 1ULL);
+}
+
+// --------------------------------------------------------------------------------------------------
+// plan
+// --------------------------------------------------------------------------------------------------
+template <typename T>
+static int64_t plan_upload(FastPlan* fp, const std::vector<T>& h, T** d) {
+  *d = nullptr;
+  if (h.empty()) return CLA_OK;
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, h.size() * sizeof(T));
+  if (e != cudaSuccess) return fail(CLA_ERR_NOMEM, std::string("cudaMalloc plan: ") + cudaGetErrorString(e));
+  fp->allocs.push_back(p);
+  CLA_CUDA(cudaMemcpy(p, h.data(), h.size() * sizeof(T), cudaMemcpyHostToDevice));
+  *d = (T*)p;
+  return CLA_OK;
+}
+
+void fast_plan_free(Matrix* m) {
+  if (!m->fast) return;
+  for (void* p : m->fast->allocs) cudaFree(p);
+  delete m->fast;
+  m->fast = nullptr;
+}
+
+int64_t fast_plan_build(Matrix* m) {
+  FastPlan* fp = new FastPlan();
+  m->fast = fp;
+  if (m->nRows < FAST_MIN_ROWS || m->nDev == 0) return CLA_OK;
+  for (auto& g : m->groups) {
+    if (g.type != GT_DDC || g.nVals > 256 || g.nVals < 1) return CLA_OK;
+    if (g.mapType != CLA_MAP_UBYTE && g.mapType != CLA_MAP_BYTE && g.mapType != CLA_MAP_BIT) return CLA_OK;
+  }
+  const int nG = m->nDev;
+  fp->nG = nG;
+  int64_t rc;
+  // byte maps for every group (bit maps are expanded once)
+  std::vector<const uint8_t*> gmap(nG);
+  for (int gi = 0; gi < nG; gi++) {
+    const DevGroup& g = m->groups[gi];
+    if (g.mapType == CLA_MAP_BIT) {
+      void* p = nullptr;
+      CLA_CUDA(cudaMalloc(&p, (size_t)m->nRows + 64));
+      fp->allocs.push_back(p);
+      m->deviceBytes += m->nRows;
+      k_bits_to_bytes<<<std::min(4096, (m->nRows + 255) / 256), 256, 0, m->stream>>>((const unsigned long long*)g.map,
+                                                                                   (uint8_t*)p, m->nRows);
+      gmap[gi] = (const uint8_t*)p;
+    } else
+      gmap[gi] = (const uint8_t*)g.map;
+  }
+  CLA_CUDA(cudaStreamSynchronize(m->stream));
+
+  // ---- RMM: groups ordered by table size so the small (conflict-free) tables pack together ----
+  std::vector<int> order(nG);
+  std::iota(order.begin(), order.end(), 0);
+  std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return m->groups[a].nVals < m->groups[b].nVals; });
+  int64_t total = 0;
+  for (int gi : order) total += (m->groups[gi].nVals + 1) & ~1;
+  const int budget = total * 8 <= 40 * 1024 ? 40 * 1024 : 96 * 1024;  // small: many CTAs per SM; else two per SM
+  std::vector<const uint8_t*> maps(nG);
+  std::vector<int> tblOff(nG), groupOf(nG);
+  std::vector<int64_t> imgOff(nG);
+  int64_t img = 0;
+  RmmChunk cur{0, 0, 0, 0};
+  for (int i = 0; i < nG; i++) {
+    const int gi = order[i];
+    const int pad = (m->groups[gi].nVals + 1) & ~1;
+    const int perGroup = 8 + 4;  // map pointer + offset kept in shared memory
+    if (cur.g1 > cur.g0 && (cur.tblDoubles + pad) * 8 + (cur.g1 - cur.g0 + 1) * perGroup > budget) {
+      fp->rchunks.push_back(cur);
+      cur = RmmChunk{i, i, 0, img};
+    }
+    maps[i] = gmap[gi];
+    groupOf[i] = gi;
+    tblOff[i] = cur.tblDoubles;
+    imgOff[i] = img;
+    cur.tblDoubles += pad;
+    cur.g1 = i + 1;
+    img += pad;
+  }
+  fp->rchunks.push_back(cur);
+  fp->pImgDoubles = img;
+  if ((rc = plan_upload(fp, maps, &fp->dMaps)) < 0) return rc;
+  if ((rc = plan_upload(fp, tblOff, &fp->dTblOff)) < 0) return rc;
+  if ((rc = plan_upload(fp, groupOf, &fp->dGroupOf)) < 0) return rc;
+  if ((rc = plan_upload(fp, imgOff, &fp->dImgOff)) < 0) return rc;
+
+  // ---- LMM: one unit per (group, column); units ordered by table depth; 32 per slab ----
+  struct Unit { int g, j, nv; };
+  std::vector<Unit> units;
+  for (int gi = 0; gi < nG; gi++)
+    for (int j = 0; j < m->groups[gi].gCols; j++) units.push_back({gi, j, m->groups[gi].nVals});
+  std::stable_sort(units.begin(), units.end(), [](const Unit& a, const Unit& b) { return a.nv > b.nv; });
+  fp->nUnits = (int)units.size();
+  const int nPairs = (fp->nUnits + 31) / 32;
+  fp->nSlots = nPairs * 32;
+  // unused slots of the last slab read the map of the last unit (its ids stay inside the slab's table depth)
+  std::vector<const uint8_t*> slotMap(fp->nSlots, gmap[units.back().g]);
+  std::vector<int> slotCol(fp->nSlots, -1);
+  std::vector<int> pairNk(nPairs, 1);
+  // host copies of the dictionaries
+  std::vector<std::vector<double>> dicts(nG);
+  for (int gi = 0; gi < nG; gi++) {
+    dicts[gi].resize((size_t)m->groups[gi].nVals * m->groups[gi].gCols);
+    CLA_CUDA(cudaMemcpy(dicts[gi].data(), m->groups[gi].dict, dicts[gi].size() * 8, cudaMemcpyDeviceToHost));
+  }
+  for (int u = 0; u < fp->nUnits; u++) pairNk[u / 32] = std::max(pairNk[u / 32], units[u].nv);
+  // chunks: greedily pack slabs up to the shared-memory budget and LMM_MAX_PAIRS
+  const size_t redBytes = (size_t)LMM_W * LMM_MAX_PAIRS * 32 * 8;
+  const size_t lmmBudget = SMEM_MAX - 2048;
+  std::vector<double> image;
+  LmmChunk lc{};
+  lc.pair0 = 0;
+  auto flush = [&]() {
+    lc.tblDoubles = 0;
+    for (int p = 0; p < lc.nPairs; p++) lc.tblDoubles += lc.nk[p] * 32;
+    lc.tblOff = (int64_t)image.size();
+    image.resize(image.size() + lc.tblDoubles, 0.0);
+    size_t off = lc.tblOff;
+    for (int p = 0; p < lc.nPairs; p++) {
+      for (int s = 0; s < 32; s++) {
+        const int u = (lc.pair0 + p) * 32 + s;
+        if (u >= fp->nUnits) continue;
+        const Unit& un = units[u];
+        const int gc = m->groups[un.g].gCols;
+        for (int k = 0; k < un.nv; k++) image[off + (size_t)k * 32 + s] = dicts[un.g][(size_t)k * gc + un.j];
+      }
+      off += (size_t)lc.nk[p] * 32;
+    }
+    fp->lchunks.push_back(lc);
+  };
+  size_t curBytes = 0;
+  lc.nPairs = 0;
+  for (int p = 0; p < nPairs; p++) {
+    const size_t b = (size_t)pairNk[p] * 256;
+    if (lc.nPairs == LMM_MAX_PAIRS || (lc.nPairs > 0 && std::max(curBytes + b, redBytes) > lmmBudget)) {
+      flush();
+      lc = LmmChunk{};
+      lc.pair0 = p;
+      lc.nPairs = 0;
+      curBytes = 0;
+    }
+    lc.nk[lc.nPairs++] = pairNk[p];
+    curBytes += b;
+  }
+  flush();
+  for (int u = 0; u < fp->nUnits; u++) {
+    slotMap[u] = gmap[units[u].g];
+    slotCol[u] = 0;  // filled below from the device column lists
+  }
+  {  // output column of every unit
+    for (int gi = 0; gi < nG; gi++) {
+      std::vector<int32_t> cols(m->groups[gi].gCols);
+      CLA_CUDA(cudaMemcpy(cols.data(), m->groups[gi].cols, cols.size() * 4, cudaMemcpyDeviceToHost));
+      for (int u = 0; u < fp->nUnits; u++)
+        if (units[u].g == gi) slotCol[u] = cols[units[u].j];
+    }
+  }
+  // CTAs per chunk in proportion to its work (slabs), one CTA per SM in total
+  const int totalCta = std::max(m->smCount, (int)fp->lchunks.size());
+  int totalPairs = 0;
+  for (auto& c : fp->lchunks) totalPairs += c.nPairs;
+  int cta = 0;
+  const int64_t nSteps = ((int64_t)m->nRows + LMM_STEP - 1) / LMM_STEP;
+  for (size_t i = 0; i < fp->lchunks.size(); i++) {
+    auto& c = fp->lchunks[i];
+    int n = std::max(1, (int)((int64_t)totalCta * c.nPairs / totalPairs));
+    n = (int)std::min<int64_t>(n, nSteps);
+    c.cta0 = cta;
+    c.nCta = n;
+    cta += n;
+  }
+  fp->lmmGrid = cta;
+  if ((rc = plan_upload(fp, fp->lchunks, &fp->dLChunks)) < 0) return rc;
+  if ((rc = plan_upload(fp, slotMap, &fp->dSlotMap)) < 0) return rc;
+  if ((rc = plan_upload(fp, slotCol, &fp->dSlotCol)) < 0) return rc;
+  if ((rc = plan_upload(fp, image, &fp->dLmmTables)) < 0) return rc;
+  m->deviceBytes += (int64_t)image.size() * 8;
+  CLA_CUDA(cudaFuncSetAttribute(k_lmm_vec_u8, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_MAX - 1024));
+  CLA_CUDA(cudaFuncSetAttribute(k_rmm_vec_u8, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+  fp->ok = true;
+  return CLA_OK;
+}
+
+// --------------------------------------------------------------------------------------------------
+// launchers
+// --------------------------------------------------------------------------------------------------
+__global__ void k_const_dot(const double* __restrict__ constV, const double* __restrict__ v, int n, double* out) {
+  double s = 0;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) s += constV[i] * v[i];
+  __shared__ double sh[256];
+  sh[threadIdx.x] = s;
+  __syncthreads();
+  for (int d = 128; d; d >>= 1) {
+    if ((int)threadIdx.x < d) sh[threadIdx.x] += sh[threadIdx.x + d];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) out[0] = sh[0];
+}
+
+int64_t fast_rmm_vec(Matrix* m, const double* dV, double* dOut, cudaStream_t s) {
+  FastPlan* fp = m->fast;
+  if (!fp || !fp->ok || ((uintptr_t)dOut & 15)) return 0;  // 128-bit stores need an aligned output
+  int64_t rc;
+  const size_t pBytes = ((size_t)fp->pImgDoubles * 8 + 255) & ~(size_t)255;
+  if ((rc = ensure_scratch(m, pBytes + 256)) < 0) return rc;
+  double* P = (double*)m->scratch;
+  double* constRow = nullptr;
+  k_fast_ptable<<<fp->nG, 128, 0, s>>>(m->dGroups, fp->dGroupOf, fp->dImgOff, fp->nG, dV, P);
+  m->stats.kernel_launches++;
+  if (m->hasConst) {
+    constRow = (double*)((char*)m->scratch + pBytes);
+    k_const_dot<<<1, 256, 0, s>>>(m->dConstV, dV, m->nCols, constRow);
+    m->stats.kernel_launches++;
+  }
+  const int nTiles = (m->nRows + RMM_TILE - 1) / RMM_TILE;
+  for (size_t c = 0; c < fp->rchunks.size(); c++) {
+    const RmmChunk& ch = fp->rchunks[c];
+    const size_t smem = (size_t)ch.tblDoubles * 8 + (size_t)(ch.g1 - ch.g0) * 12 + 16;
+    const int perSm = std::max(1, std::min(8, (int)((200 * 1024) / std::max<size_t>(smem, 1))));
+    const int grid = std::min(nTiles, m->smCount * perSm);
+    if (c == 0) prof_begin(m, s);
+    k_rmm_vec_u8<<<grid, RMM_T, smem, s>>>(fp->dMaps, fp->dTblOff, ch.g0, ch.g1, P + ch.tblOff, ch.tblDoubles, m->nRows,
+                                           constRow, dOut, c > 0 ? 1 : 0, m->dErr);
+    if (c + 1 == fp->rchunks.size()) prof_end(m, s);
+    m->stats.kernel_launches++;
+  }
+  CLA_CUDA(cudaGetLastError());
+  return 1;
+}
+
+int64_t fast_lmm_vec(Matrix* m, const double* dY, double* dOut, cudaStream_t s) {
+  FastPlan* fp = m->fast;
+  if (!fp || !fp->ok || ((uintptr_t)dY & 15)) return 0;  // 128-bit loads of the left vector need alignment
+  int64_t rc;
+  const size_t partBytes = (size_t)fp->lmmGrid * LMM_MAX_PAIRS * 32 * 8;
+  if ((rc = ensure_scratch(m, partBytes + 256)) < 0) return rc;
+  double* partial = (double*)m->scratch;
+  CLA_CUDA(cudaMemsetAsync(dOut, 0, sizeof(double) * (size_t)m->nCols, s));
+  size_t smem = (size_t)LMM_W * LMM_MAX_PAIRS * 32 * 8;
+  for (auto& c : fp->lchunks) smem = std::max(smem, (size_t)c.tblDoubles * 8);
+  prof_begin(m, s);
+  k_lmm_vec_u8<<<fp->lmmGrid, LMM_T, smem, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dSlotMap, fp->dLmmTables, dY,
+                                               m->nRows, partial, m->dErr);
+  prof_end(m, s);
+  k_lmm_vec_final<<<(unsigned)fp->lchunks.size(), 128, 0, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dSlotCol,
+                                                              partial, dOut);
+  m->stats.kernel_launches += 2;
+  if (m->hasConst)
+    if ((rc = launch_lmm_const(m, dY, 1, dOut, s)) < 0) return rc;
+  CLA_CUDA(cudaGetLastError());
+  return 1;
+}
+
+}  // namespace cla

@@ -43,6 +43,33 @@ int64_t ensure_scratch(Matrix* m, size_t bytes) { return grow(&m->scratch, &m->s
 int64_t ensure_scratch2(Matrix* m, size_t bytes) { return grow(&m->scratch2, &m->scratch2Bytes, bytes); }
 int64_t ensure_io(Matrix* m, size_t bytes) { return grow(&m->io, &m->ioBytes, bytes); }
 
+constexpr size_t PROF_MAX = 512;
+void prof_begin(Matrix* m, cudaStream_t s) {
+  if (!m->profile || m->profUsed >= PROF_MAX) return;
+  if (m->profUsed == m->profEvents.size()) {
+    cudaEvent_t a, b;
+    if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) return;
+    m->profEvents.push_back({a, b});
+  }
+  cudaEventRecord(m->profEvents[m->profUsed].first, s);
+}
+void prof_end(Matrix* m, cudaStream_t s) {
+  if (!m->profile || m->profUsed >= m->profEvents.size()) return;
+  cudaEventRecord(m->profEvents[m->profUsed].second, s);
+  m->profUsed++;
+}
+void prof_collect(Matrix* m) {
+  for (size_t i = 0; i < m->profUsed; i++) {
+    float ms = 0;
+    if (cudaEventSynchronize(m->profEvents[i].second) == cudaSuccess &&
+        cudaEventElapsedTime(&ms, m->profEvents[i].first, m->profEvents[i].second) == cudaSuccess) {
+      m->stats.main_kernel_ms += ms;
+      m->stats.main_kernel_count++;
+    }
+  }
+  m->profUsed = 0;
+}
+
 // ------------------------------------------------------------------------------------------------
 // device kernels used at upload and for decode checks
 // ------------------------------------------------------------------------------------------------
@@ -555,6 +582,11 @@ void release(Matrix* m) {
   if (m->scratch2) cudaFree(m->scratch2);
   if (m->io) cudaFree(m->io);
   if (m->dErr) cudaFree(m->dErr);
+  for (auto& pr : m->profEvents) {
+    cudaEventDestroy(pr.first);
+    cudaEventDestroy(pr.second);
+  }
+  m->profEvents.clear();
   if (m->ev0) cudaEventDestroy(m->ev0);
   if (m->ev1) cudaEventDestroy(m->ev1);
   if (m->stream) cudaStreamDestroy(m->stream);

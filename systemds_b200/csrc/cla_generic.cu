@@ -201,8 +201,10 @@ int64_t launch_rmm(Matrix* m, const double* dV, int vCols, double* dOut, cudaStr
     attr = true;
   }
   dim3 grid((m->nRows + TR - 1) / TR, (vCols + vcTile - 1) / vcTile);
+  prof_begin(m, s);
   k_rmm_tile<<<grid, RMM_THREADS, smem, s>>>(m->dGroups, m->nDev, m->nRows, P, dV, vCols, constRow, dOut, TR, vcTile,
                                              hasSparse);
+  prof_end(m, s);
   m->stats.kernel_launches++;
   CLA_CUDA(cudaGetLastError());
   return CLA_OK;
@@ -404,7 +406,9 @@ int64_t launch_lmm(Matrix* m, const double* dYt, int q, double* dOut, cudaStream
     rowsPerChunk = std::max(SKIP_ROWS * 4, ((rowsPerChunk + SKIP_ROWS - 1) / SKIP_ROWS) * SKIP_ROWS);
     const int chunks = (m->nRows + rowsPerChunk - 1) / rowsPerChunk;
     dim3 grid(chunks, m->nDev, (q + LMM_QT - 1) / LMM_QT);
+    prof_begin(m, s);
     k_lmm_preagg<<<grid, LMM_THREADS, 0, s>>>(m->dGroups, m->nRows, rowsPerChunk, dYt, q, A);
+    prof_end(m, s);
     k_lmm_post<<<m->nDev, 128, 0, s>>>(m->dGroups, A, q, m->nCols, dOut);
     m->stats.kernel_launches += 2;
     for (auto& g : m->groups)
@@ -420,6 +424,21 @@ int64_t launch_lmm(Matrix* m, const double* dYt, int q, double* dOut, cudaStream
     k_lmm_const<<<grid_for((int64_t)q * m->nCols, 256), 256, 0, s>>>(sums, m->dConstV, q, m->nCols, dOut);
     m->stats.kernel_launches += 2;
   }
+  CLA_CUDA(cudaGetLastError());
+  return CLA_OK;
+}
+
+// out += rowSums(Yt) (x) constV, for callers that computed the group part themselves
+int64_t launch_lmm_const(Matrix* m, const double* dYt, int q, double* dOut, cudaStream_t s) {
+  if (!m->hasConst || q == 0 || m->nRows == 0) return CLA_OK;
+  int64_t rc;
+  if ((rc = ensure_scratch2(m, (size_t)q * sizeof(double) + 256)) < 0) return rc;
+  double* sums = (double*)m->scratch2;
+  CLA_CUDA(cudaMemsetAsync(sums, 0, (size_t)q * sizeof(double), s));
+  dim3 grid(grid_for(m->nRows, 256, 4 * m->smCount), q);
+  k_row_sums<<<grid, 256, 0, s>>>(dYt, m->nRows, q, sums);
+  k_lmm_const<<<grid_for((int64_t)q * m->nCols, 256), 256, 0, s>>>(sums, m->dConstV, q, m->nCols, dOut);
+  m->stats.kernel_launches += 2;
   CLA_CUDA(cudaGetLastError());
   return CLA_OK;
 }

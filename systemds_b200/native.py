@@ -25,7 +25,9 @@ class CLAError(RuntimeError):
 class cla_stats(C.Structure):
     _fields_ = [(n, C.c_int64) for n in ("n_rows", "n_cols", "n_groups", "device_bytes", "index_bytes", "calls_rmm",
                                          "calls_lmm", "calls_tsmm", "calls_mmchain", "calls_decompress",
-                                         "kernel_launches")] + [("last_kernel_ms", C.c_double)]
+                                         "kernel_launches")] + [("last_kernel_ms", C.c_double),
+                                                                 ("main_kernel_ms", C.c_double),
+                                                                 ("main_kernel_count", C.c_int64)]
 
 
 _P, _I32, _I64 = C.c_void_p, C.c_int32, C.c_int64
@@ -36,6 +38,7 @@ SIGNATURES = {
     "cla_finalize": [_I64, _I32],
     "cla_last_error": [C.c_char_p, _I64],
     "cla_stats_get": [_I64, C.POINTER(cla_stats)],
+    "cla_set_profile": [_I64, _I32],
     "cla_add_group_ddc": [_I64, _P, _I32, _P, _I32, _I32, _P, _P, _I64],
     "cla_add_group_sdc": [_I64, _P, _I32, _P, _I32, _P, _I32, _I32, _I32, _P, _I64, _I64, _I32, _P, _P],
     "cla_add_group_rle": [_I64, _P, _I32, _P, _I32, _P, _P, _I64],

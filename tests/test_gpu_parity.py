@@ -1,0 +1,173 @@
+"""GPU parity: every product and every decoded index structure through the C ABI against the CPU oracle."""
+import numpy as np
+import pytest
+
+from systemds_b200 import CLAError, CompressedMatrixBlock, datagen
+from systemds_b200 import colgroup as cg
+from systemds_b200.cmb import (CHAIN_XtwXv, CLALibDecompress, CLALibLeftMultBy, CLALibMMChain, CLALibRightMultBy,
+                               CLALibTSMM)
+from systemds_b200.mapping import MapToFactory
+from tests.util import TOL, dense_of, rel_err
+
+pytestmark = pytest.mark.gpu
+
+CASES = [
+    ("all", datagen.KINDS, False),
+    ("ddc_only", ("ddc", "ddc", "ddc2", "ddc_bit", "ddc_char"), False),
+    ("ddc_u8", ("ddc", "ddc", "ddc2", "ddc_bit", "const"), False),
+    ("sparse", ("sdc", "sdcz", "sdcs", "sdcsz", "const", "empty"), False),
+    ("runs", ("rle", "rle", "ole", "ddc"), False),
+    ("overlap", ("ddc", "sdc", "rle", "ddc2", "const", "sdcz"), True),
+]
+
+
+def seed_of(name, n):
+    return sum(map(ord, name)) + n
+
+
+@pytest.mark.parametrize("name,kinds,overlap", CASES)
+@pytest.mark.parametrize("nRows", [1, 37, 1024, 5000, 70001])
+def test_decode_bit_exact(oracle, name, kinds, overlap, nRows):
+    """Decoded maps, offsets, run boundaries and counts are bit-exact (device decode kernels vs oracle vs host)."""
+    cmb = datagen.random_cmb(seed_of(name, nRows), nRows, kinds, overlap).to_device()
+    om = oracle.OracleMatrix(cmb)
+    for gi, g in enumerate(cmb.getColGroups()):
+        want = om.group_row_ids(gi)
+        got = cmb.group_row_ids(gi)
+        assert np.array_equal(got, want), f"group {gi} ({type(g).__name__}) decodes differently"
+        if hasattr(g, "row_ids"):
+            assert np.array_equal(got, g.row_ids(nRows))
+        if g.getNumValues() and not isinstance(g, cg.ColGroupConst):
+            assert np.array_equal(cmb.group_counts(gi), om.group_counts(gi))
+    cmb.free()
+
+
+@pytest.mark.parametrize("name,kinds,overlap", CASES)
+@pytest.mark.parametrize("nRows", [1, 37, 1024, 5000, 70001])
+def test_products_vs_oracle(oracle, name, kinds, overlap, nRows):
+    cmb = datagen.random_cmb(seed_of(name, nRows), nRows, kinds, overlap).to_device()
+    X = dense_of(cmb)
+    aX = np.abs(X)
+    om = oracle.OracleMatrix(cmb)
+    rng = np.random.default_rng(nRows)
+    assert rel_err(CLALibDecompress.decompress(cmb), om.decompress()) < 1e-14
+    for vc in (1, 5, 64):
+        V = rng.standard_normal((cmb.clen, vc))
+        got = CLALibRightMultBy.rightMultByMatrix(cmb, V)
+        assert got.shape == (nRows, vc)
+        assert rel_err(got, om.rmm(V), aX @ np.abs(V) + 1e-300) < TOL
+        assert got.nnz == int(np.count_nonzero(got))
+    for q in (1, 6):
+        Yt = rng.standard_normal((q, nRows))
+        got = CLALibLeftMultBy.leftMultByMatrix(cmb, Yt)
+        assert rel_err(got, om.lmm(Yt), np.abs(Yt) @ aX + 1e-300) < TOL
+    if not overlap:
+        got = CLALibTSMM.leftMultByTransposeSelf(cmb)
+        assert rel_err(got, om.tsmm(), aX.T @ aX + 1e-300) < TOL
+        assert np.array_equal(got, got.T)
+    v = rng.standard_normal(cmb.clen)
+    w = rng.standard_normal(nRows)
+    s = aX.T @ (aX @ np.abs(v)) + 1e-300
+    assert rel_err(CLALibMMChain.mmChain(cmb, v).ravel(), om.mmchain(v).ravel(), s) < 10 * TOL
+    sw = aX.T @ (np.abs(w) * (aX @ np.abs(v))) + 1e-300
+    assert rel_err(CLALibMMChain.mmChain(cmb, v, w, CHAIN_XtwXv).ravel(), om.mmchain(v, w, 1).ravel(), sw) < 10 * TOL
+    cmb.free()
+
+
+def _ddc_matrix(nRows, cards, seed, const_col=False, pair=False):
+    rng = np.random.default_rng(seed)
+    groups, c = [], 0
+    for k in cards:
+        w = 2 if (pair and c % 3 == 0) else 1
+        groups.append(cg.ColGroupDDC(list(range(c, c + w)), rng.standard_normal((k, w)),
+                                     MapToFactory.create_from(rng.integers(0, k, nRows), k)))
+        c += w
+    if const_col:
+        groups.append(cg.ColGroupConst([c], [[0.75]]))
+        c += 1
+    return CompressedMatrixBlock(nRows, c, groups)
+
+
+@pytest.mark.parametrize("nRows", [4096, 70001, 262144 + 17])
+@pytest.mark.parametrize("shape", ["card16", "card256", "mixed", "mixed_const_pairs"])
+def test_fast_vector_paths(oracle, nRows, shape):
+    """The specialised DDC kernels (X v, t(y) X, t(X)(X v)) on the shapes of the headline workloads."""
+    rng = np.random.default_rng(nRows)
+    if shape == "card16":
+        cmb = _ddc_matrix(nRows, [16] * 100, 1)
+    elif shape == "card256":
+        cmb = _ddc_matrix(nRows, [256] * 200, 2)
+    elif shape == "mixed":
+        cmb = _ddc_matrix(nRows, list(rng.integers(2, 256, 150)) + [2, 2, 255, 129], 3)
+    else:
+        cmb = _ddc_matrix(nRows, list(rng.integers(2, 256, 70)), 4, const_col=True, pair=True)
+    cmb.to_device()
+    om = oracle.OracleMatrix(cmb)
+    X = dense_of(cmb)
+    aX = np.abs(X)
+    v = rng.standard_normal(cmb.clen)
+    y = rng.standard_normal((1, nRows))
+    assert rel_err(CLALibRightMultBy.rightMultByMatrix(cmb, v), om.rmm(v), aX @ np.abs(v).reshape(-1, 1) + 1e-300) < TOL
+    assert rel_err(CLALibLeftMultBy.leftMultByMatrix(cmb, y), om.lmm(y), np.abs(y) @ aX + 1e-300) < TOL
+    s = aX.T @ (aX @ np.abs(v)) + 1e-300
+    assert rel_err(CLALibMMChain.mmChain(cmb, v).ravel(), om.mmchain(v).ravel(), s) < 10 * TOL
+    st = cmb.stats()
+    assert st["kernel_launches"] > 0 and st["calls_rmm"] >= 2 and st["calls_lmm"] >= 2
+    cmb.free()
+
+
+def test_tsmm_integer_exact(oracle):
+    """Integer-valued dictionaries: the self product is exact (CLALibMMChainTest.java:159-171 asks for 0 ULP)."""
+    cmb = datagen.random_cmb(11, 3000, ("ddc", "ddc2", "sdcz", "rle", "ddc_bit"), integer=True).to_device()
+    X = dense_of(cmb)
+    assert np.array_equal(CLALibTSMM.leftMultByTransposeSelf(cmb), X.T @ X)
+    cmb.free()
+
+
+def test_tsmm_wide(oracle):
+    """More than one 64-column block, ragged edge."""
+    cmb = _ddc_matrix(9000, [7] * 150, 5).to_device()
+    X = dense_of(cmb)
+    got = CLALibTSMM.leftMultByTransposeSelf(cmb)
+    assert rel_err(got, oracle.dense_tsmm_ld(X), np.abs(X).T @ np.abs(X)) < TOL
+    cmb.free()
+
+
+def test_empty_and_errors():
+    e = datagen.random_cmb(1, 0, ("ddc", "sdcz")).to_device()
+    assert CLALibRightMultBy.rightMultByMatrix(e, np.ones((2, 3))).shape == (0, 3)
+    assert np.array_equal(CLALibLeftMultBy.leftMultByMatrix(e, np.zeros((2, 0))), np.zeros((2, 2)))
+    assert np.array_equal(CLALibTSMM.leftMultByTransposeSelf(e), np.zeros((2, 2)))
+    e.free()
+    cmb = datagen.random_cmb(2, 100, ("ddc", "sdcz")).to_device()
+    with pytest.raises(CLAError) as ex:
+        CLALibRightMultBy.rightMultByMatrix(cmb, np.ones((3, 1)))
+    assert ex.value.code == -4
+    with pytest.raises(CLAError):
+        CLALibLeftMultBy.leftMultByMatrix(cmb, np.ones((1, 99)))
+    cmb.free()
+    with pytest.raises(RuntimeError):
+        cmb.handle()
+
+
+def test_full_size_checksum_config2(oracle):
+    """BASELINE-size t(y) %*% X (10M x 200): with y = 1 the product equals counts . dictionary, a checksum built
+    from the bit-exact device histograms; linearity ties a random y to it."""
+    cmb, y = datagen.config2(nRows=10_000_000, nCols=200)
+    cmb.to_device()
+    ones = np.ones((1, cmb.rlen))
+    got = CLALibLeftMultBy.leftMultByMatrix(cmb, ones).ravel()
+    want = np.array([float(cmb.group_counts(g).astype(np.float64) @ cmb.getColGroups()[g]._dict[:, 0]) for g in range(200)])
+    scale = np.array([float(cmb.group_counts(g).astype(np.float64) @ np.abs(cmb.getColGroups()[g]._dict[:, 0])) for g in range(200)])
+    assert rel_err(got, want, scale) < TOL
+    a = CLALibLeftMultBy.leftMultByMatrix(cmb, y).ravel()
+    b = CLALibLeftMultBy.leftMultByMatrix(cmb, 2.0 * y + ones).ravel()
+    assert rel_err(b, 2.0 * a + got, 2 * np.sqrt(cmb.rlen) + scale) < 1e-11
+    # sampled rows of X %*% v against the host records
+    v = np.random.default_rng(0).standard_normal(200)
+    u = CLALibRightMultBy.rightMultByMatrix(cmb, v).ravel()
+    rows = np.random.default_rng(1).integers(0, cmb.rlen, 50)
+    for r in rows:
+        ref = sum(g._dict[g._data.getIndex(int(r)), 0] * v[c] for c, g in enumerate(cmb.getColGroups()))
+        assert abs(u[r] - ref) <= 1e-12 * 200 * 4
+    cmb.free()
