@@ -156,6 +156,8 @@ struct Matrix {
   size_t scratchBytes = 0;
   void* scratch2 = nullptr;
   size_t scratch2Bytes = 0;
+  void* small_ = nullptr;  // small per-call vectors (row sums of the left operand)
+  size_t smallBytes = 0;
   void* io = nullptr;  // device staging for host-buffer calls
   size_t ioBytes = 0;
   int32_t* dErr = nullptr;  // device self-check word
@@ -187,6 +189,7 @@ void prof_collect(Matrix* m);
 int64_t ensure_scratch(Matrix* m, size_t bytes);
 int64_t ensure_scratch2(Matrix* m, size_t bytes);
 int64_t ensure_io(Matrix* m, size_t bytes);
+int64_t ensure_small(Matrix* m, size_t bytes);
 
 // launchers implemented in the kernel translation units; all enqueue on `s` and return CLA_OK or an error.
 int64_t launch_rmm(Matrix* m, const double* dV, int vCols, double* dOut, cudaStream_t s);

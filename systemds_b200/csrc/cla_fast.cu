@@ -66,7 +66,9 @@ struct FastPlan {
   int nUnits = 0, nSlots = 0;
   std::vector<LmmChunk> lchunks;
   LmmChunk* dLChunks = nullptr;
-  const uint8_t** dSlotMap = nullptr;  // [nSlots]
+  const uint8_t** dSlotMap = nullptr;  // [nSlots] column-major byte maps (plan order)
+  uint8_t* dLmmMaps = nullptr;         // the same maps interleaved for the column-per-lane kernel (see k_lmm_interleave)
+  int64_t nRB = 0;                     // 16-row blocks per column in that layout (padded to whole 64-row steps)
   int* dSlotCol = nullptr;             // [nSlots] output column or -1
   double* dLmmTables = nullptr;        // image of all chunk tables
   int lmmGrid = 0;
@@ -130,6 +132,14 @@ __device__ __forceinline__ uint32_t byte_x8(uint32_t w, int i) {  // (byte i of 
   return i == 0 ? (w << 3) & 0x7F8u : (w >> (8 * i - 3)) & 0x7F8u;
 }
 
+template <int R>
+struct MapWord;
+template <> struct MapWord<16> { typedef uint4 T; };
+template <> struct MapWord<8> { typedef uint2 T; };
+template <> struct MapWord<4> { typedef uint32_t T; };
+
+// R = rows per thread (16, 8 or 4): fewer rows per thread means more threads for short matrices.
+template <int R>
 __global__ void __launch_bounds__(RMM_T)
 k_rmm_vec_u8(const uint8_t* const* __restrict__ maps, const int* __restrict__ tblOff, int g0, int g1,
              const double* __restrict__ Pchunk, int tblDoubles, int nRows, const double* __restrict__ constRow,
@@ -150,30 +160,35 @@ k_rmm_vec_u8(const uint8_t* const* __restrict__ maps, const int* __restrict__ tb
     return;
   }
   const double c0 = (constRow != nullptr && !accumulate) ? constRow[0] : 0.0;
-  const int nTiles = (nRows + RMM_TILE - 1) / RMM_TILE;
+  constexpr int TILE = RMM_T * R;
+  const int nTiles = (nRows + TILE - 1) / TILE;
   const unsigned char* tb = (const unsigned char*)tables;
+  typedef typename MapWord<R>::T W;
   for (int tile = blockIdx.x; tile < nTiles; tile += gridDim.x) {
-    const int row = tile * RMM_TILE + tid * RMM_ROWS_PT;
+    const int row = tile * TILE + tid * R;
     if (row >= nRows) continue;
-    if (row + RMM_ROWS_PT <= nRows) {
-      double acc[16];
+    if (row + R <= nRows) {
+      double acc[R];
 #pragma unroll
-      for (int i = 0; i < 16; i++) acc[i] = c0;
-#pragma unroll 4
+      for (int i = 0; i < R; i++) acc[i] = c0;
+#pragma unroll 8
       for (int g = 0; g < nG; g++) {
-        const uint4 w = __ldg((const uint4*)(sMaps[g] + row));
+        const W w = __ldg((const W*)(sMaps[g] + row));
         const unsigned char* T = tb + sOff[g];
-        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+        uint32_t ww[4];
+        if constexpr (R == 16) { ww[0] = w.x; ww[1] = w.y; ww[2] = w.z; ww[3] = w.w; }
+        else if constexpr (R == 8) { ww[0] = w.x; ww[1] = w.y; }
+        else { ww[0] = w; }
 #pragma unroll
-        for (int i = 0; i < 16; i++) acc[i] += *(const double*)(T + byte_x8(ww[i >> 2], i & 3));
+        for (int i = 0; i < R; i++) acc[i] += *(const double*)(T + byte_x8(ww[i >> 2], i & 3));
       }
       if (accumulate) {
 #pragma unroll
-        for (int i = 0; i < 16; i++) atomicAdd(out + row + i, acc[i]);
+        for (int i = 0; i < R; i++) atomicAdd(out + row + i, acc[i]);
       } else {
         double2* o = (double2*)(out + row);
 #pragma unroll
-        for (int i = 0; i < 8; i++) o[i] = make_double2(acc[2 * i], acc[2 * i + 1]);
+        for (int i = 0; i < R / 2; i++) o[i] = make_double2(acc[2 * i], acc[2 * i + 1]);
       }
     } else {  // ragged last rows
       for (int r = row; r < nRows; r++) {
@@ -215,7 +230,7 @@ __device__ __forceinline__ void lmm_cells(const uint4 (&m)[NP][2][2], int sub, c
 
 // partial: [gridDim.x][LMM_MAX_PAIRS * 32]
 template <int NP>
-__device__ __forceinline__ void lmm_vec_body(const LmmChunk& ch, const uint8_t* const* __restrict__ slotMap,
+__device__ __forceinline__ void lmm_vec_body(const LmmChunk& ch, const uint8_t* __restrict__ imaps, int64_t nRB,
                                              const double* __restrict__ tablesImg, const double* __restrict__ y,
                                              int nRows, double* __restrict__ partial, unsigned char* smraw,
                                              uint64_t* mbar, int32_t* err) {
@@ -234,8 +249,8 @@ __device__ __forceinline__ void lmm_vec_body(const LmmChunk& ch, const uint8_t* 
     for (int p = 0; p < NP; p++) {
       tbase[p] = smraw + off + slot * 8;
       off += (size_t)ch.nk[p] * 256;
-      mp[p][0] = slotMap[(ch.pair0 + p) * 32 + slot];
-      mp[p][1] = slotMap[(ch.pair0 + p) * 32 + 16 + slot];
+      mp[p][0] = imaps + (size_t)((ch.pair0 + p) * 2 + 0) * nRB * 256 + slot * 16;
+      mp[p][1] = imaps + (size_t)((ch.pair0 + p) * 2 + 1) * nRB * 256 + slot * 16;
     }
   }
   double acc[NP][2];
@@ -254,9 +269,9 @@ __device__ __forceinline__ void lmm_vec_body(const LmmChunk& ch, const uint8_t* 
       for (int p = 0; p < NP; p++)
 #pragma unroll
         for (int ab = 0; ab < 2; ab++) {
-          const uint4* src = (const uint4*)(mp[p][ab] + r0);
-          m[p][ab][0] = __ldg(src);
-          m[p][ab][1] = __ldg(src + 1);
+          const uint8_t* src = mp[p][ab] + (r0 >> 4) * 256;
+          m[p][ab][0] = __ldg((const uint4*)src);
+          m[p][ab][1] = __ldg((const uint4*)(src + 256));
         }
 #pragma unroll
       for (int sub = 0; sub < 2; sub++) {
@@ -277,7 +292,8 @@ __device__ __forceinline__ void lmm_vec_body(const LmmChunk& ch, const uint8_t* 
         for (int p = 0; p < NP; p++)
 #pragma unroll
           for (int ab = 0; ab < 2; ab++)
-            acc[p][ab] = fma(yy, *(const double*)(tbase[p] + ab * 128 + 256 * (int)mp[p][ab][r]), acc[p][ab]);
+            acc[p][ab] = fma(yy, *(const double*)(tbase[p] + ab * 128 + 256 * (int)mp[p][ab][(r >> 4) * 256 + (r & 15)]),
+                             acc[p][ab]);
       }
     }
   }
@@ -301,7 +317,7 @@ __device__ __forceinline__ void lmm_vec_body(const LmmChunk& ch, const uint8_t* 
 }
 
 __global__ void __launch_bounds__(LMM_T, 1)
-k_lmm_vec_u8(const LmmChunk* __restrict__ chunks, int nChunks, const uint8_t* const* __restrict__ slotMap,
+k_lmm_vec_u8(const LmmChunk* __restrict__ chunks, int nChunks, const uint8_t* __restrict__ imaps, int64_t nRB,
              const double* __restrict__ tablesImg, const double* __restrict__ y, int nRows,
              double* __restrict__ partial, int32_t* err) {
   extern __shared__ __align__(128) unsigned char smraw[];
@@ -314,9 +330,9 @@ k_lmm_vec_u8(const LmmChunk* __restrict__ chunks, int nChunks, const uint8_t* co
   }
   __syncthreads();
   switch (ch.nPairs) {
-    case 1: lmm_vec_body<1>(ch, slotMap, tablesImg, y, nRows, partial, smraw, &mbar, err); break;
-    case 2: lmm_vec_body<2>(ch, slotMap, tablesImg, y, nRows, partial, smraw, &mbar, err); break;
-    default: lmm_vec_body<3>(ch, slotMap, tablesImg, y, nRows, partial, smraw, &mbar, err); break;
+    case 1: lmm_vec_body<1>(ch, imaps, nRB, tablesImg, y, nRows, partial, smraw, &mbar, err); break;
+    case 2: lmm_vec_body<2>(ch, imaps, nRB, tablesImg, y, nRows, partial, smraw, &mbar, err); break;
+    default: lmm_vec_body<3>(ch, imaps, nRB, tablesImg, y, nRows, partial, smraw, &mbar, err); break;
   }
 }
 
@@ -332,6 +348,32 @@ __global__ void k_lmm_vec_final(const LmmChunk* __restrict__ chunks, int nChunks
     double s = 0;
     for (int b = 0; b < ch.nCta; b++) s += partial[(size_t)(ch.cta0 + b) * (LMM_MAX_PAIRS * 32) + u];
     atomicAdd(&out[col], s);
+  }
+}
+
+// Device layout of the maps for k_lmm_vec_u8: [slab of 16 column slots][16-row block][slot][16 ids].
+// A half-warp (one lane per slot) then reads 256 contiguous bytes per 128-bit load instead of 16 scattered
+// lines. Built once at plan time; unused slots and rows past the end hold id 0.
+__global__ void k_lmm_interleave(const uint8_t* const* __restrict__ slotMap, int nSlots, int nUnits, int nRows,
+                                 int64_t nRB, uint8_t* __restrict__ out) {
+  const int64_t total = (int64_t)nSlots * nRB;
+  for (int64_t g = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; g < total; g += (int64_t)gridDim.x * blockDim.x) {
+    const int slot = (int)(g & 15);
+    const int64_t rb = (g >> 4) % nRB;
+    const int64_t slab = (g >> 4) / nRB;
+    const int unit = (int)slab * 16 + slot;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    const int64_t r = rb * 16;
+    if (unit < nUnits && r < nRows) {
+      const uint8_t* src = slotMap[unit] + r;
+      if (r + 16 <= nRows) v = *(const uint4*)src;
+      else {
+        __align__(16) uint8_t tmp[16];
+        for (int i = 0; i < 16; i++) tmp[i] = (r + i < nRows) ? src[i] : 0;
+        v = *(const uint4*)tmp;
+      }
+    }
+    ((uint4*)out)[g] = v;
   }
 }
 
@@ -516,10 +558,25 @@ int64_t fast_plan_build(Matrix* m) {
   if ((rc = plan_upload(fp, fp->lchunks, &fp->dLChunks)) < 0) return rc;
   if ((rc = plan_upload(fp, slotMap, &fp->dSlotMap)) < 0) return rc;
   if ((rc = plan_upload(fp, slotCol, &fp->dSlotCol)) < 0) return rc;
+  {
+    fp->nRB = (((int64_t)m->nRows + LMM_STEP - 1) / LMM_STEP) * (LMM_STEP / 16);
+    const size_t bytes = (size_t)fp->nSlots * fp->nRB * 16;
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e != cudaSuccess) return fail(CLA_ERR_NOMEM, std::string("cudaMalloc interleaved maps: ") + cudaGetErrorString(e));
+    fp->allocs.push_back(p);
+    fp->dLmmMaps = (uint8_t*)p;
+    m->deviceBytes += (int64_t)bytes;
+    k_lmm_interleave<<<m->smCount * 8, 256, 0, m->stream>>>(fp->dSlotMap, fp->nSlots, fp->nUnits, m->nRows, fp->nRB,
+                                                           fp->dLmmMaps);
+    CLA_CUDA(cudaStreamSynchronize(m->stream));
+  }
   if ((rc = plan_upload(fp, image, &fp->dLmmTables)) < 0) return rc;
   m->deviceBytes += (int64_t)image.size() * 8;
   CLA_CUDA(cudaFuncSetAttribute(k_lmm_vec_u8, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_MAX - 1024));
-  CLA_CUDA(cudaFuncSetAttribute(k_rmm_vec_u8, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+  CLA_CUDA(cudaFuncSetAttribute(k_rmm_vec_u8<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+  CLA_CUDA(cudaFuncSetAttribute(k_rmm_vec_u8<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+  CLA_CUDA(cudaFuncSetAttribute(k_rmm_vec_u8<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
   fp->ok = true;
   return CLA_OK;
 }
@@ -555,15 +612,19 @@ int64_t fast_rmm_vec(Matrix* m, const double* dV, double* dOut, cudaStream_t s) 
     k_const_dot<<<1, 256, 0, s>>>(m->dConstV, dV, m->nCols, constRow);
     m->stats.kernel_launches++;
   }
-  const int nTiles = (m->nRows + RMM_TILE - 1) / RMM_TILE;
+  // rows per thread: the widest map load that still leaves >= 32 resident warps per SM
+  const double warpsPerSm16 = (double)m->nRows / (16.0 * 32.0 * m->smCount);
+  const int R = warpsPerSm16 >= 32 ? 16 : (warpsPerSm16 * 2 >= 32 ? 8 : 4);
+  const int nTiles = (m->nRows + RMM_T * R - 1) / (RMM_T * R);
   for (size_t c = 0; c < fp->rchunks.size(); c++) {
     const RmmChunk& ch = fp->rchunks[c];
     const size_t smem = (size_t)ch.tblDoubles * 8 + (size_t)(ch.g1 - ch.g0) * 12 + 16;
     const int perSm = std::max(1, std::min(8, (int)((200 * 1024) / std::max<size_t>(smem, 1))));
     const int grid = std::min(nTiles, m->smCount * perSm);
     if (c == 0) prof_begin(m, s);
-    k_rmm_vec_u8<<<grid, RMM_T, smem, s>>>(fp->dMaps, fp->dTblOff, ch.g0, ch.g1, P + ch.tblOff, ch.tblDoubles, m->nRows,
-                                           constRow, dOut, c > 0 ? 1 : 0, m->dErr);
+    auto kern = R == 16 ? k_rmm_vec_u8<16> : (R == 8 ? k_rmm_vec_u8<8> : k_rmm_vec_u8<4>);
+    kern<<<grid, RMM_T, smem, s>>>(fp->dMaps, fp->dTblOff, ch.g0, ch.g1, P + ch.tblOff, ch.tblDoubles, m->nRows, constRow,
+                                   dOut, c > 0 ? 1 : 0, m->dErr);
     if (c + 1 == fp->rchunks.size()) prof_end(m, s);
     m->stats.kernel_launches++;
   }
@@ -582,7 +643,7 @@ int64_t fast_lmm_vec(Matrix* m, const double* dY, double* dOut, cudaStream_t s) 
   size_t smem = (size_t)LMM_W * LMM_MAX_PAIRS * 32 * 8;
   for (auto& c : fp->lchunks) smem = std::max(smem, (size_t)c.tblDoubles * 8);
   prof_begin(m, s);
-  k_lmm_vec_u8<<<fp->lmmGrid, LMM_T, smem, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dSlotMap, fp->dLmmTables, dY,
+  k_lmm_vec_u8<<<fp->lmmGrid, LMM_T, smem, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dLmmMaps, fp->nRB, fp->dLmmTables, dY,
                                                m->nRows, partial, m->dErr);
   prof_end(m, s);
   k_lmm_vec_final<<<(unsigned)fp->lchunks.size(), 128, 0, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dSlotCol,

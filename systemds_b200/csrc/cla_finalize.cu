@@ -42,6 +42,7 @@ static int64_t grow(void** p, size_t* cur, size_t bytes) {
 int64_t ensure_scratch(Matrix* m, size_t bytes) { return grow(&m->scratch, &m->scratchBytes, bytes); }
 int64_t ensure_scratch2(Matrix* m, size_t bytes) { return grow(&m->scratch2, &m->scratch2Bytes, bytes); }
 int64_t ensure_io(Matrix* m, size_t bytes) { return grow(&m->io, &m->ioBytes, bytes); }
+int64_t ensure_small(Matrix* m, size_t bytes) { return grow(&m->small_, &m->smallBytes, bytes); }
 
 constexpr size_t PROF_MAX = 512;
 void prof_begin(Matrix* m, cudaStream_t s) {
@@ -581,6 +582,8 @@ void release(Matrix* m) {
   if (m->scratch) cudaFree(m->scratch);
   if (m->scratch2) cudaFree(m->scratch2);
   if (m->io) cudaFree(m->io);
+  if (m->small_) cudaFree(m->small_);
+  m->small_ = nullptr;
   if (m->dErr) cudaFree(m->dErr);
   for (auto& pr : m->profEvents) {
     cudaEventDestroy(pr.first);

@@ -432,8 +432,8 @@ int64_t launch_lmm(Matrix* m, const double* dYt, int q, double* dOut, cudaStream
 int64_t launch_lmm_const(Matrix* m, const double* dYt, int q, double* dOut, cudaStream_t s) {
   if (!m->hasConst || q == 0 || m->nRows == 0) return CLA_OK;
   int64_t rc;
-  if ((rc = ensure_scratch2(m, (size_t)q * sizeof(double) + 256)) < 0) return rc;
-  double* sums = (double*)m->scratch2;
+  if ((rc = ensure_small(m, (size_t)q * sizeof(double) + 256)) < 0) return rc;
+  double* sums = (double*)m->small_;
   CLA_CUDA(cudaMemsetAsync(sums, 0, (size_t)q * sizeof(double), s));
   dim3 grid(grid_for(m->nRows, 256, 4 * m->smCount), q);
   k_row_sums<<<grid, 256, 0, s>>>(dYt, m->nRows, q, sums);
