@@ -171,7 +171,7 @@ k_rmm_vec_u8(const uint8_t* const* __restrict__ maps, const int* __restrict__ tb
       double acc[R];
 #pragma unroll
       for (int i = 0; i < R; i++) acc[i] = c0;
-#pragma unroll 8
+#pragma unroll(R == 16 ? 8 : 16)
       for (int g = 0; g < nG; g++) {
         const W w = __ldg((const W*)(sMaps[g] + row));
         const unsigned char* T = tb + sOff[g];
@@ -540,16 +540,24 @@ int64_t fast_plan_build(Matrix* m) {
         if (units[u].g == gi) slotCol[u] = cols[units[u].j];
     }
   }
-  // CTAs per chunk in proportion to its work (slabs), one CTA per SM in total
+  // CTAs per chunk in proportion to its cost, one CTA per SM in total. Cost per 64-row warp step in
+  // L1 data-pipe wavefronts: 128 per slab for the dictionary reads, 16 per slab for the map loads and
+  // 64 for the left vector (which does not depend on the number of slabs).
   const int totalCta = std::max(m->smCount, (int)fp->lchunks.size());
-  int totalPairs = 0;
-  for (auto& c : fp->lchunks) totalPairs += c.nPairs;
+  double totalCost = 0;
+  for (auto& c : fp->lchunks) totalCost += 144.0 * c.nPairs + 64.0;
   int cta = 0;
   const int64_t nSteps = ((int64_t)m->nRows + LMM_STEP - 1) / LMM_STEP;
+  std::vector<int> share(fp->lchunks.size());
+  int used = 0;
+  for (size_t i = 0; i < fp->lchunks.size(); i++) {
+    share[i] = std::max(1, (int)(totalCta * (144.0 * fp->lchunks[i].nPairs + 64.0) / totalCost));
+    used += share[i];
+  }
+  for (size_t i = 0; used < totalCta; i = (i + 1) % fp->lchunks.size(), used++) share[i]++;  // hand out the remainder
   for (size_t i = 0; i < fp->lchunks.size(); i++) {
     auto& c = fp->lchunks[i];
-    int n = std::max(1, (int)((int64_t)totalCta * c.nPairs / totalPairs));
-    n = (int)std::min<int64_t>(n, nSteps);
+    const int n = (int)std::min<int64_t>(share[i], nSteps);
     c.cta0 = cta;
     c.nCta = n;
     cta += n;
