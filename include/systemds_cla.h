@@ -145,6 +145,20 @@ int64_t cla_mmchain_dev(cla_handle h, const double* dV, const double* dW, int32_
  * yields the exact product of those rows (constant columns included), so the partial results of
  * cla_lmm_dev / cla_tsmm_dev / cla_mmchain_dev over all shards simply add up. */
 
+/* t(y) %*% X (one left row) that performs no device allocation. It has no counterpart in the reference.
+ * For hosts that must not allocate when they call in -- a runtime whose own pool owns all device memory, or a loop
+ * that cannot afford the device-wide synchronisation inside cudaMalloc -- the kernel's scratch (per-CTA partial
+ * sums, the row sum of dY) is a fixed array inside the library, about 385 KB, held by every GPU that loads the
+ * library until the process exits. Inputs and output are still the caller's: dY [nRows] and dOut [nCols] are
+ * device addresses, dY 16-byte aligned. Same result as cla_lmm_dev with yRows = 1.
+ * Limits: the matrix must consist of dense-map (DDC) groups with at most 256 tuples and 1-byte (or 1-bit) maps,
+ * and need at most 512 partial-sum rows (one per launched CTA: the SM count, or the number of 96-column chunks if
+ * that is larger); otherwise CLA_ERR_UNSUPPORTED is returned and nothing runs.
+ * The first call on a device looks up the array's device address; make that call outside any stream capture.
+ * All calls share the array and it keeps the previous call's contents (what must start at zero is cleared on the
+ * stream first), so two calls whose kernels overlap on the GPU -- different streams or handles -- race. */
+int64_t cla_lmm_vec_noalloc_dev(cla_handle h, const double* dY, double* dOut, void* stream);
+
 /* ---- decoded index structures (for bit-exact checks and for f2-style consumers) -------------
  * ids[nRows]: dictionary id of every row of group g, -1 where the row holds the default (or zero)
  * tuple; for an uncompressed group the row number. Computed by the device decode kernels.

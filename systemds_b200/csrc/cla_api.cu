@@ -368,6 +368,14 @@ int64_t cla_lmm_dev(cla_handle h, const double* dYt, int32_t yRows, double* dOut
   CLA_CUDA(cudaSetDevice(m->device));
   return lmm_dev(m, dYt, yRows, dOut, (cudaStream_t)stream);
 }
+int64_t cla_lmm_vec_noalloc_dev(cla_handle h, const double* dY, double* dOut, void* stream) {
+  GET_MATRIX(h);
+  REQUIRE_FINAL();
+  CLA_CUDA(cudaSetDevice(m->device));
+  if (!dY || !dOut) return fail(CLA_ERR_BAD_ARG, "no-allocation product: null buffer");
+  m->stats.calls_lmm++;
+  return fast_lmm_vec_noalloc(m, dY, dOut, (cudaStream_t)stream);
+}
 int64_t cla_tsmm_dev(cla_handle h, double* dOut, void* stream) {
   GET_MATRIX(h);
   REQUIRE_FINAL();

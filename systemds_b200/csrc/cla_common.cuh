@@ -209,5 +209,6 @@ int64_t fast_plan_build(Matrix* m);
 void fast_plan_free(Matrix* m);
 int64_t fast_rmm_vec(Matrix* m, const double* dV, double* dOut, cudaStream_t s);
 int64_t fast_lmm_vec(Matrix* m, const double* dY, double* dOut, cudaStream_t s);
+int64_t fast_lmm_vec_noalloc(Matrix* m, const double* dY, double* dOut, cudaStream_t s);
 
 }  // namespace cla

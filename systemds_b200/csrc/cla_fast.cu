@@ -24,6 +24,7 @@
 namespace cla {
 
 int64_t launch_lmm_const(Matrix* m, const double* dYt, int q, double* dOut, cudaStream_t s);  // cla_generic.cu
+int64_t launch_lmm_const_with(Matrix* m, const double* dYt, int q, double* dOut, double* sums, cudaStream_t s);
 
 constexpr int FAST_MIN_ROWS = 4096;
 constexpr int SMEM_MAX = 227 * 1024;
@@ -661,6 +662,66 @@ int64_t fast_lmm_vec(Matrix* m, const double* dY, double* dOut, cudaStream_t s) 
     if ((rc = launch_lmm_const(m, dY, 1, dOut, s)) < 0) return rc;
   CLA_CUDA(cudaGetLastError());
   return 1;
+}
+
+
+// --------------------------------------------------------------------------------------------------
+// t(y) %*% X without any device allocation.
+//
+// Some hosts may not allocate device memory when they call in: a runtime that has handed the whole GPU to
+// its own memory pool (SystemDS's GPU memory manager works that way), or a service loop that must not hit
+// cudaMalloc because the driver synchronises the device inside it. For them the per-CTA partial sums and the
+// row sum of the left vector live in this fixed array instead of the handle's growable scratch. Every GPU
+// whose context loads the library holds the array (about 385 KB) until the process exits.
+// --------------------------------------------------------------------------------------------------
+constexpr int NOALLOC_MAX_CTAS = 512;  // partial-sum rows available; one CTA per SM is launched, more only with > 148 column chunks
+constexpr size_t NOALLOC_PARTIAL_DOUBLES = (size_t)NOALLOC_MAX_CTAS * LMM_MAX_PAIRS * 32;
+static __device__ __align__(256) double g_noalloc_scratch[NOALLOC_PARTIAL_DOUBLES + 32];
+
+static std::mutex g_noallocMu;
+static double* g_noallocAddr[64] = {};  // device address of the array, per device ordinal
+
+// The name g_noalloc_scratch is only a handle on the host; kernels need the address the device sees.
+// Looked up once per device, with that device current.
+static int64_t noalloc_address(int device, double** out) {
+  if (device < 0 || device >= 64) return fail(CLA_ERR_BAD_ARG, "device ordinal out of range");
+  std::lock_guard<std::mutex> lk(g_noallocMu);
+  if (!g_noallocAddr[device]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || !p)
+      return fail(CLA_ERR_CUDA, std::string("cudaGetSymbolAddress(g_noalloc_scratch): ") + cudaGetErrorString(e));
+    g_noallocAddr[device] = (double*)p;
+  }
+  *out = g_noallocAddr[device];
+  return CLA_OK;
+}
+
+int64_t fast_lmm_vec_noalloc(Matrix* m, const double* dY, double* dOut, cudaStream_t s) {
+  FastPlan* fp = m->fast;
+  if (!fp || !fp->ok)
+    return fail(CLA_ERR_UNSUPPORTED, "no-allocation product: needs dense-map groups with at most 256 tuples and byte maps");
+  if ((uintptr_t)dY & 15) return fail(CLA_ERR_BAD_ARG, "no-allocation product: the left vector must be 16-byte aligned");
+  if (fp->lmmGrid > NOALLOC_MAX_CTAS)
+    return fail(CLA_ERR_UNSUPPORTED, "no-allocation product: the matrix needs " + std::to_string(fp->lmmGrid) +
+                                         " partial-sum rows, the fixed scratch holds " + std::to_string(NOALLOC_MAX_CTAS));
+  double* scratch = nullptr;
+  int64_t rc = noalloc_address(m->device, &scratch);
+  if (rc < 0) return rc;
+  double* partial = scratch;                           // fully rewritten by every launch
+  double* rowSum = scratch + NOALLOC_PARTIAL_DOUBLES;  // accumulated with atomics: cleared below before use
+  CLA_CUDA(cudaMemsetAsync(dOut, 0, sizeof(double) * (size_t)m->nCols, s));
+  size_t smem = (size_t)LMM_W * LMM_MAX_PAIRS * 32 * 8;
+  for (auto& c : fp->lchunks) smem = std::max(smem, (size_t)c.tblDoubles * 8);
+  k_lmm_vec_u8<<<fp->lmmGrid, LMM_T, smem, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dLmmMaps, fp->nRB, fp->dLmmTables,
+                                               dY, m->nRows, partial, m->dErr);
+  k_lmm_vec_final<<<(unsigned)fp->lchunks.size(), 128, 0, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dSlotCol,
+                                                              partial, dOut);
+  m->stats.kernel_launches += 2;
+  if (m->hasConst)
+    if ((rc = launch_lmm_const_with(m, dY, 1, dOut, rowSum, s)) < 0) return rc;
+  CLA_CUDA(cudaGetLastError());
+  return CLA_OK;
 }
 
 }  // namespace cla

@@ -428,12 +428,9 @@ int64_t launch_lmm(Matrix* m, const double* dYt, int q, double* dOut, cudaStream
   return CLA_OK;
 }
 
-// out += rowSums(Yt) (x) constV, for callers that computed the group part themselves
-int64_t launch_lmm_const(Matrix* m, const double* dYt, int q, double* dOut, cudaStream_t s) {
+// out += rowSums(Yt) (x) constV into a caller-provided vector of q sums
+int64_t launch_lmm_const_with(Matrix* m, const double* dYt, int q, double* dOut, double* sums, cudaStream_t s) {
   if (!m->hasConst || q == 0 || m->nRows == 0) return CLA_OK;
-  int64_t rc;
-  if ((rc = ensure_small(m, (size_t)q * sizeof(double) + 256)) < 0) return rc;
-  double* sums = (double*)m->small_;
   CLA_CUDA(cudaMemsetAsync(sums, 0, (size_t)q * sizeof(double), s));
   dim3 grid(grid_for(m->nRows, 256, 4 * m->smCount), q);
   k_row_sums<<<grid, 256, 0, s>>>(dYt, m->nRows, q, sums);
@@ -441,6 +438,14 @@ int64_t launch_lmm_const(Matrix* m, const double* dYt, int q, double* dOut, cuda
   m->stats.kernel_launches += 2;
   CLA_CUDA(cudaGetLastError());
   return CLA_OK;
+}
+
+// out += rowSums(Yt) (x) constV, for callers that computed the group part themselves
+int64_t launch_lmm_const(Matrix* m, const double* dYt, int q, double* dOut, cudaStream_t s) {
+  if (!m->hasConst || q == 0 || m->nRows == 0) return CLA_OK;
+  int64_t rc;
+  if ((rc = ensure_small(m, (size_t)q * sizeof(double) + 256)) < 0) return rc;
+  return launch_lmm_const_with(m, dYt, q, dOut, (double*)m->small_, s);
 }
 
 }  // namespace cla
