@@ -234,7 +234,10 @@ def main():
     achieved = alg_bytes / (k_ms * 1e-3) / 1e9 if k_ms > 0 else None
     roofline = {"bound": "hbm", "kernel": "k_lmm_vec_u8", "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": (achieved / peak) if achieved else None, "peak_source": f"of {peak_kind}",
-                "kernel_ms": k_ms, "algorithmic_bytes": alg_bytes, "traffic": None}
+                "kernel_ms": k_ms, "algorithmic_bytes": alg_bytes,
+                # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture of a 2,000,000-row
+                # case scaled by rows (traffic grows in proportion to rows); see profiles/k_lmm_vec_u8_config2.md
+                "traffic": 485.1e6 * (n / 2_000_000.0)}
 
     result = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,

@@ -140,13 +140,11 @@ class CompressedMatrixBlock:
         return {n: getattr(st, n) for n, _ in st._fields_}
 
     # --- the MatrixBlock operator API of the reference (CompressedMatrixBlock.java:587-627) -----
-    def aggregateBinaryOperations(self, m1, m2):
+    def aggregateBinaryOperations(self, m1, m2, transposeLeft: bool = False, transposeRight: bool = False):
         """``m1 %*% m2`` where one side is this block (CLALibMatrixMult.matrixMultiply picks right / left)."""
-        if m1 is self:
-            return CLALibRightMultBy.rightMultByMatrix(self, m2)
-        if m2 is self:
-            return CLALibLeftMultBy.leftMultByMatrix(self, m1)
-        raise ValueError("one operand must be this CompressedMatrixBlock")
+        if m1 is not self and m2 is not self:
+            raise ValueError("one operand must be this CompressedMatrixBlock")
+        return CLALibMatrixMult.matrixMultiply(m1, m2, transposeLeft, transposeRight)
 
     def transposeSelfMatrixMultOperations(self):
         return CLALibTSMM.leftMultByTransposeSelf(self)
@@ -181,6 +179,28 @@ def _wrap(a: np.ndarray, nnz: int) -> np.ndarray:
     r = a.view(_Result)
     r.nnz = nnz
     return r
+
+
+class CLALibMatrixMult:
+    """``CLALibMatrixMult.matrixMultiply`` (runtime/compress/lib/CLALibMatrixMult.java:42-94): resolves the
+    transpose flags so that the compressed side is multiplied as it is stored, then picks right or left."""
+
+    @staticmethod
+    def matrixMultiply(m1, m2, transposeLeft: bool = False, transposeRight: bool = False) -> np.ndarray:
+        c1, c2 = isinstance(m1, CompressedMatrixBlock), isinstance(m2, CompressedMatrixBlock)
+        if c1 == c2:
+            raise native.CLAError(-3, "matrixMultiply: exactly one operand must be compressed")
+        if (c1 and transposeLeft) or (c2 and transposeRight):
+            # t(X) %*% B = t(t(B) %*% X) and A %*% t(X) = t(X %*% t(A)): swap sides (:50-59), transpose the result
+            r = CLALibMatrixMult.matrixMultiply(m2, m1, not transposeRight, not transposeLeft)
+            return _wrap(np.ascontiguousarray(np.asarray(r).T), r.nnz)
+        if c1:
+            B = _f64(m2)
+            B = B.reshape(-1, 1) if B.ndim == 1 else B
+            return CLALibRightMultBy.rightMultByMatrix(m1, np.ascontiguousarray(B.T) if transposeRight else B)
+        A = _f64(m1)
+        A = A.reshape(1, -1) if A.ndim == 1 else A
+        return CLALibLeftMultBy.leftMultByMatrix(m2, np.ascontiguousarray(A.T) if transposeLeft else A)
 
 
 class CLALibRightMultBy:

@@ -175,3 +175,70 @@ def test_full_size_checksum_config2(oracle):
         ref = sum(g._dict[g._data.getIndex(int(r)), 0] * v[c] for c, g in enumerate(cmb.getColGroups()))
         assert abs(u[r] - ref) <= 1e-12 * 200 * 4
     cmb.free()
+
+
+@pytest.mark.parametrize("force", ["CHAR_BYTE", "INT", "BYTE", "CHAR"])
+def test_wide_map_types(oracle, force):
+    """MapToCharPByte / MapToInt (and forced wider storage of small ids, MappingTestUtil.getAllHigherVersions)."""
+    from systemds_b200 import mapping
+    rng = np.random.default_rng(9)
+    nRows, card = 30000, {"CHAR_BYTE": 70000, "INT": 70000, "BYTE": 100, "CHAR": 100}[force]
+    ids = rng.integers(0, card, nRows)
+    ids[:3] = [0, card - 1, card // 2]
+    m = mapping.MapToFactory.create_from(ids, card, force_type=getattr(mapping, "MAP_" + force))
+    off_rows = np.sort(rng.choice(nRows, 2000, replace=False))
+    from systemds_b200.offset import OffsetFactory
+    ms = mapping.MapToFactory.create_from(rng.integers(0, card, 2000), card, force_type=getattr(mapping, "MAP_" + force))
+    groups = [cg.ColGroupDDC([0], rng.standard_normal((card, 1)), m),
+              cg.ColGroupSDCZeros([1], nRows, rng.standard_normal((card, 1)), OffsetFactory.createOffset(off_rows), ms)]
+    cmb = CompressedMatrixBlock(nRows, 2, groups).to_device()
+    om = oracle.OracleMatrix(cmb)
+    for gi in range(2):
+        assert np.array_equal(cmb.group_row_ids(gi), om.group_row_ids(gi))
+        assert np.array_equal(cmb.group_counts(gi), om.group_counts(gi))
+    X = dense_of(cmb)
+    V = rng.standard_normal((2, 3))
+    y = rng.standard_normal((2, nRows))
+    assert rel_err(CLALibRightMultBy.rightMultByMatrix(cmb, V), om.rmm(V), np.abs(X) @ np.abs(V) + 1e-300) < TOL
+    assert rel_err(CLALibLeftMultBy.leftMultByMatrix(cmb, y), om.lmm(y), np.abs(y) @ np.abs(X) + 1e-300) < TOL
+    cmb.free()
+
+
+def test_matrix_multiply_transposes(oracle):
+    """CLALibMatrixMult.matrixMultiply: the four transpose combinations against numpy on the decompressed matrix."""
+    from systemds_b200 import CLALibMatrixMult
+    cmb = datagen.random_cmb(4, 3000, ("ddc", "sdc", "rle", "unc")).to_device()
+    X = dense_of(cmb)
+    rng = np.random.default_rng(2)
+    A = rng.standard_normal((3, 3000))
+    B = rng.standard_normal((cmb.clen, 4))
+    assert rel_err(CLALibMatrixMult.matrixMultiply(cmb, B), X @ B, np.abs(X) @ np.abs(B)) < TOL
+    assert rel_err(CLALibMatrixMult.matrixMultiply(cmb, B.T.copy(), False, True), X @ B, np.abs(X) @ np.abs(B)) < TOL
+    assert rel_err(CLALibMatrixMult.matrixMultiply(A, cmb), A @ X, np.abs(A) @ np.abs(X)) < TOL
+    assert rel_err(CLALibMatrixMult.matrixMultiply(A.T.copy(), cmb, True, False), A @ X, np.abs(A) @ np.abs(X)) < TOL
+    assert rel_err(CLALibMatrixMult.matrixMultiply(cmb, A.T.copy(), True, False), X.T @ A.T, np.abs(X).T @ np.abs(A).T) < TOL
+    assert rel_err(cmb.aggregateBinaryOperations(A, cmb), A @ X, np.abs(A) @ np.abs(X)) < TOL
+    cmb.free()
+
+
+def test_sharded_partials_add_up(oracle):
+    """Two row shards as two handles on one GPU: partial t(Y)X, t(X)X and mmchain results sum to the full product."""
+    from systemds_b200 import shard
+    cmb = datagen.random_cmb(33, 20000, ("ddc", "ddc2", "sdc", "rle", "ole", "unc", "const", "sdcsz"))
+    X = dense_of(cmb)
+    aX = np.abs(X)
+    rng = np.random.default_rng(1)
+    y = rng.standard_normal((2, cmb.rlen))
+    v = rng.standard_normal(cmb.clen)
+    lmm = np.zeros((2, cmb.clen))
+    tsmm = np.zeros((cmb.clen, cmb.clen))
+    chain = np.zeros((cmb.clen, 1))
+    for (a, b), s in zip(shard.shard_bounds(cmb.rlen, 2), shard.shard(cmb, 2)):
+        s.to_device()
+        lmm += CLALibLeftMultBy.leftMultByMatrix(s, y[:, a:b])
+        tsmm += CLALibTSMM.leftMultByTransposeSelf(s)
+        chain += CLALibMMChain.mmChain(s, v)
+        s.free()
+    assert rel_err(lmm, oracle.dense_lmm_ld(X, y), np.abs(y) @ aX) < TOL
+    assert rel_err(tsmm, oracle.dense_tsmm_ld(X), aX.T @ aX) < TOL
+    assert rel_err(chain.ravel(), X.T @ (X @ v), aX.T @ (aX @ np.abs(v))) < 10 * TOL
