@@ -148,6 +148,8 @@ struct Matrix {
   int64_t totalVals = 0;         // sum of nVals over dictionary groups
   std::vector<double> constV;    // host copy
   double* dConstV = nullptr;     // [nCols]
+  int32_t* dColSrc = nullptr;    // [nCols][2]: dense-map / uncompressed group holding the column and the position in it (-1: none)
+  bool colSrcValid = false;      // false when some column is held by more than one such group (overlapping input)
   bool hasConst = false;
   std::vector<void*> allocs;     // everything cudaMalloc'ed for the groups
   int64_t deviceBytes = 0, indexBytes = 0;

@@ -73,6 +73,8 @@ struct FastPlan {
   int* dSlotCol = nullptr;             // [nSlots] output column or -1
   double* dLmmTables = nullptr;        // image of all chunk tables
   int lmmGrid = 0;
+  int maxNVals = 0;                    // deepest table: <= 16 keeps the row-per-thread kernel conflict free
+  size_t imageDoubles = 0;
   std::vector<void*> allocs;
 };
 
@@ -110,6 +112,42 @@ __device__ __forceinline__ bool tma_load_to_smem(void* dst, const void* src, uin
         : "memory");
   }
   // one verdict for the whole CTA (also the barrier that publishes the data to every thread)
+  return __syncthreads_and(done != 0) != 0;
+}
+
+// The same copy for kernels that reload the buffer several times: the barrier is initialised once and each use
+// waits on the next phase parity. The caller must have synchronised the CTA (all reads of the old contents done)
+// before calling; the issuing thread then orders those generic-proxy reads before the async-proxy writes.
+__device__ __forceinline__ void tma_barrier_init(uint64_t* mbar) {
+  if (threadIdx.x == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(mbar)));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+}
+__device__ __forceinline__ bool tma_reload(void* dst, const void* src, uint32_t bytes, uint64_t* mbar, uint32_t parity) {
+  const uint32_t bar = smem_u32(mbar);
+  if (threadIdx.x == 0) {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+    const uint32_t CH = 32768;
+    for (uint32_t off = 0; off < bytes; off += CH) {
+      const uint32_t sz = min(CH, bytes - off);
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                       smem_u32((char*)dst + off)),
+                   "l"((const char*)src + off), "r"(sz), "r"(bar)
+                   : "memory");
+    }
+  }
+  uint32_t done = 0;
+  for (int it = 0; it < (1 << 22) && !done; it++) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+  }
   return __syncthreads_and(done != 0) != 0;
 }
 
@@ -352,6 +390,118 @@ __global__ void k_lmm_vec_final(const LmmChunk* __restrict__ chunks, int nChunks
   }
 }
 
+// --------------------------------------------------------------------------------------------------
+// RMM, column-per-lane variant (tables of any depth up to 256 without bank conflicts).
+// Same slabs, interleaved maps and table layout as k_lmm_vec_u8; the table of slot s holds
+// D[:, j] * v[col] (k_rmm_b_tables), so summing a row's lookups over all slots gives the row of X v.
+// A CTA owns a contiguous range of rows and walks the column chunks one after the other, reloading the tables;
+// the first chunk stores its partial sums, later chunks add to them (the CTA owns the rows: no atomics, and the
+// summation order is fixed). Within a chunk each lane accumulates 16 rows x its column slots, then a
+// reduce-scatter over the 16 lanes of the half-warp (15 shuffles) leaves lane s with the sum of row s.
+// --------------------------------------------------------------------------------------------------
+__global__ void k_rmm_b_tables(const LmmChunk* __restrict__ chunks, const int* __restrict__ slotCol,
+                               const double* __restrict__ T, const double* __restrict__ v, double* __restrict__ P) {
+  const LmmChunk ch = chunks[blockIdx.x];
+  int base = 0;
+  for (int p = 0; p < ch.nPairs; p++) {
+    const int n = ch.nk[p] * 32;
+    for (int e = threadIdx.x; e < n; e += blockDim.x) {
+      const int col = slotCol[(ch.pair0 + p) * 32 + (e & 31)];
+      P[ch.tblOff + base + e] = col >= 0 ? T[ch.tblOff + base + e] * v[col] : 0.0;
+    }
+    base += n;
+  }
+}
+
+template <int NP>
+__device__ __forceinline__ void rmm_b_chunk(const LmmChunk& ch, const uint8_t* __restrict__ imaps, int64_t nRB,
+                                            int64_t s0, int64_t s1, int nRows, double init, bool first,
+                                            double* __restrict__ out, const unsigned char* smraw) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int slot = lane & 15, half = lane >> 4;
+  const unsigned char* tbase[NP];
+  const uint8_t* mp[NP][2];
+  {
+    size_t off = 0;
+#pragma unroll
+    for (int p = 0; p < NP; p++) {
+      tbase[p] = smraw + off + slot * 8;
+      off += (size_t)ch.nk[p] * 256;
+      mp[p][0] = imaps + (size_t)((ch.pair0 + p) * 2 + 0) * nRB * 256 + slot * 16;
+      mp[p][1] = imaps + (size_t)((ch.pair0 + p) * 2 + 1) * nRB * 256 + slot * 16;
+    }
+  }
+  for (int64_t st = s0 + warp; st < s1; st += LMM_W) {
+    const int64_t r0 = st * LMM_STEP + half * 32;
+    uint4 m[NP][2][2];
+#pragma unroll
+    for (int p = 0; p < NP; p++)
+#pragma unroll
+      for (int ab = 0; ab < 2; ab++) {
+        const uint8_t* src = mp[p][ab] + (r0 >> 4) * 256;
+        m[p][ab][0] = __ldg((const uint4*)src);
+        m[p][ab][1] = __ldg((const uint4*)(src + 256));
+      }
+#pragma unroll
+    for (int sub = 0; sub < 2; sub++) {
+      double acc[16];
+#pragma unroll
+      for (int i = 0; i < 16; i++) acc[i] = 0.0;
+#pragma unroll
+      for (int p = 0; p < NP; p++)
+#pragma unroll
+        for (int ab = 0; ab < 2; ab++) {
+          const uint4 w = m[p][ab][sub];
+          const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+          const unsigned char* T = tbase[p] + ab * 128;
+#pragma unroll
+          for (int i = 0; i < 16; i++) acc[i] += *(const double*)(T + byte_x256(ww[i >> 2], i & 3));
+        }
+      // reduce-scatter over the half-warp: after the stage with distance d, a lane keeps the rows whose bit d
+      // equals its own slot bit
+#pragma unroll
+      for (int d = 8; d >= 1; d >>= 1) {
+        const bool up = (slot & d) != 0;
+#pragma unroll
+        for (int i = 0; i < d; i++) {
+          const double lo = acc[i], hi = acc[i + d];
+          const double recv = __shfl_xor_sync(0xffffffffu, up ? lo : hi, d);
+          acc[i] = (up ? hi : lo) + recv;
+        }
+      }
+      const int64_t row = r0 + sub * 16 + slot;
+      if (row < nRows) out[row] = first ? acc[0] + init : out[row] + acc[0];
+    }
+  }
+}
+
+__global__ void __launch_bounds__(LMM_T, 1)
+k_rmm_vec_b(const LmmChunk* __restrict__ chunks, int nChunks, const uint8_t* __restrict__ imaps, int64_t nRB,
+            const double* __restrict__ P, int nRows, const double* __restrict__ constRow, double* __restrict__ out,
+            int32_t* err) {
+  extern __shared__ __align__(128) unsigned char smraw[];
+  __shared__ __align__(8) uint64_t mbar;
+  __shared__ LmmChunk ch;
+  const int64_t nSteps = ((int64_t)nRows + LMM_STEP - 1) / LMM_STEP;
+  const int64_t s0 = nSteps * blockIdx.x / gridDim.x, s1 = nSteps * (blockIdx.x + 1) / gridDim.x;
+  const double init = constRow ? constRow[0] : 0.0;
+  tma_barrier_init(&mbar);
+  for (int c = 0; c < nChunks; c++) {
+    __syncthreads();  // everyone is done with the previous chunk's tables and with `ch`
+    if (threadIdx.x == 0) ch = chunks[c];
+    __syncthreads();
+    if (!tma_reload(smraw, P + ch.tblOff, (uint32_t)ch.tblDoubles * 8u, &mbar, (uint32_t)(c & 1))) {
+      if (threadIdx.x == 0) atomicExch(err, 102);
+      return;
+    }
+    switch (ch.nPairs) {
+      case 1: rmm_b_chunk<1>(ch, imaps, nRB, s0, s1, nRows, init, c == 0, out, smraw); break;
+      case 2: rmm_b_chunk<2>(ch, imaps, nRB, s0, s1, nRows, init, c == 0, out, smraw); break;
+      default: rmm_b_chunk<3>(ch, imaps, nRB, s0, s1, nRows, init, c == 0, out, smraw); break;
+    }
+  }
+}
+
 // Device layout of the maps for k_lmm_vec_u8: [slab of 16 column slots][16-row block][slot][16 ids].
 // A half-warp (one lane per slot) then reads 256 contiguous bytes per 128-bit load instead of 16 scattered
 // lines. Built once at plan time; unused slots and rows past the end hold id 0.
@@ -581,8 +731,11 @@ int64_t fast_plan_build(Matrix* m) {
     CLA_CUDA(cudaStreamSynchronize(m->stream));
   }
   if ((rc = plan_upload(fp, image, &fp->dLmmTables)) < 0) return rc;
+  fp->imageDoubles = image.size();
+  for (auto& g : m->groups) fp->maxNVals = std::max(fp->maxNVals, g.nVals);
   m->deviceBytes += (int64_t)image.size() * 8;
   CLA_CUDA(cudaFuncSetAttribute(k_lmm_vec_u8, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_MAX - 1024));
+  CLA_CUDA(cudaFuncSetAttribute(k_rmm_vec_b, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_MAX - 1024));
   CLA_CUDA(cudaFuncSetAttribute(k_rmm_vec_u8<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
   CLA_CUDA(cudaFuncSetAttribute(k_rmm_vec_u8<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
   CLA_CUDA(cudaFuncSetAttribute(k_rmm_vec_u8<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
@@ -606,9 +759,36 @@ __global__ void k_const_dot(const double* __restrict__ constV, const double* __r
   if (threadIdx.x == 0) out[0] = sh[0];
 }
 
+static int64_t fast_rmm_vec_b(Matrix* m, FastPlan* fp, const double* dV, double* dOut, cudaStream_t s) {
+  int64_t rc;
+  const size_t pBytes = ((size_t)fp->imageDoubles * 8 + 255) & ~(size_t)255;
+  if ((rc = ensure_scratch(m, pBytes + 256)) < 0) return rc;
+  double* P = (double*)m->scratch;
+  double* constRow = nullptr;
+  k_rmm_b_tables<<<(unsigned)fp->lchunks.size(), 256, 0, s>>>(fp->dLChunks, fp->dSlotCol, fp->dLmmTables, dV, P);
+  m->stats.kernel_launches++;
+  if (m->hasConst) {
+    constRow = (double*)((char*)m->scratch + pBytes);
+    k_const_dot<<<1, 256, 0, s>>>(m->dConstV, dV, m->nCols, constRow);
+    m->stats.kernel_launches++;
+  }
+  size_t smem = 1024;
+  for (auto& c : fp->lchunks) smem = std::max(smem, (size_t)c.tblDoubles * 8);
+  const int64_t nSteps = ((int64_t)m->nRows + LMM_STEP - 1) / LMM_STEP;
+  const int grid = (int)std::min<int64_t>(m->smCount, nSteps);
+  prof_begin(m, s);
+  k_rmm_vec_b<<<grid, LMM_T, smem, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dLmmMaps, fp->nRB, P, m->nRows, constRow,
+                                        dOut, m->dErr);
+  prof_end(m, s);
+  m->stats.kernel_launches++;
+  CLA_CUDA(cudaGetLastError());
+  return 1;
+}
+
 int64_t fast_rmm_vec(Matrix* m, const double* dV, double* dOut, cudaStream_t s) {
   FastPlan* fp = m->fast;
   if (!fp || !fp->ok || ((uintptr_t)dOut & 15)) return 0;  // 128-bit stores need an aligned output
+  if (fp->maxNVals > 16) return fast_rmm_vec_b(m, fp, dV, dOut, s);  // deep tables: the conflict-free layout
   int64_t rc;
   const size_t pBytes = ((size_t)fp->pImgDoubles * 8 + 255) & ~(size_t)255;
   if ((rc = ensure_scratch(m, pBytes + 256)) < 0) return rc;

@@ -255,14 +255,42 @@ __global__ void k_decomp_rle(DevGroup g, double* __restrict__ out, int r0, int r
   }
 }
 
+// All dense-map and uncompressed groups in one pass: every output cell is written once, from constV plus the
+// value of the one such group that holds its column (colSrc). Sparse groups are added afterwards.
+__global__ void k_decomp_fused(const DevGroup* __restrict__ groups, const int32_t* __restrict__ colSrc,
+                               const double* __restrict__ constV, double* __restrict__ out, int r0, int r1, int nCols) {
+  const int64_t n = (int64_t)(r1 - r0) * nCols;
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < n; e += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = e / nCols;
+    const int c = (int)(e - r * nCols);
+    double v = constV ? constV[c] : 0.0;
+    const int gi = colSrc[2 * c];
+    if (gi >= 0) {
+      const DevGroup& g = groups[gi];
+      const int j = colSrc[2 * c + 1];
+      if (g.type == GT_UNC) v += g.dense[(size_t)(r0 + r) * g.gCols + j];
+      else v += g.dict[(size_t)map_get(g.mapType, g.map, g.mapHi, r0 + r) * g.gCols + j];
+    }
+    out[e] = v;
+  }
+}
+
 // r0 must be a multiple of SKIP_ROWS
 int64_t launch_decompress_range(Matrix* m, int r0, int r1, double* dOut, cudaStream_t s) {
   const int64_t n = (int64_t)(r1 - r0) * m->nCols;
   if (n <= 0) return CLA_OK;
-  k_decomp_init<<<grid_for(n, 256), 256, 0, s>>>(dOut, m->hasConst ? m->dConstV : nullptr, r1 - r0, m->nCols);
+  const bool fused = m->colSrcValid;
+  if (fused) {
+    k_decomp_fused<<<grid_for(n, 256, 148 * 32), 256, 0, s>>>(m->dGroups, m->dColSrc, m->hasConst ? m->dConstV : nullptr,
+                                                             dOut, r0, r1, m->nCols);
+    m->stats.kernel_launches++;
+  } else
+    k_decomp_init<<<grid_for(n, 256), 256, 0, s>>>(dOut, m->hasConst ? m->dConstV : nullptr, r1 - r0, m->nCols);
   for (auto& g : m->groups) {
-    if (g.type == GT_DDC || g.type == GT_UNC)
+    if (g.type == GT_DDC || g.type == GT_UNC) {
+      if (fused) continue;
       k_decomp_dense<<<grid_for((int64_t)(r1 - r0) * g.gCols, 256), 256, 0, s>>>(g, dOut, r0, r1, m->nCols);
+    }
     else if (g.type == GT_SDC) {
       const int nb = (r1 - r0 + SKIP_ROWS - 1) / SKIP_ROWS;
       k_decomp_sdc<<<(nb * 32 + 255) / 256, 256, 0, s>>>(g, dOut, r0, r1, m->nCols);
