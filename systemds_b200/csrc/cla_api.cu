@@ -322,7 +322,9 @@ static int64_t rmm_dev(Matrix* m, const double* dV, int32_t vRows, int32_t vCols
   m->stats.calls_rmm++;
   if (vCols == 1) {
     int64_t rc = fast_rmm_vec(m, dV, dOut, s);
-    if (rc != 0) return rc < 0 ? rc : CLA_OK;
+    if (rc < 0) return rc;
+    if (rc == 1) return CLA_OK;
+    if (rc == 2) return launch_rmm(m, dV, vCols, dOut, s, true);
   }
   return launch_rmm(m, dV, vCols, dOut, s);
 }
@@ -332,7 +334,9 @@ static int64_t lmm_dev(Matrix* m, const double* dYt, int32_t yRows, double* dOut
   m->stats.calls_lmm++;
   if (yRows == 1) {
     int64_t rc = fast_lmm_vec(m, dYt, dOut, s);
-    if (rc != 0) return rc < 0 ? rc : CLA_OK;
+    if (rc < 0) return rc;
+    if (rc == 1) return CLA_OK;
+    if (rc == 2) return launch_lmm(m, dYt, yRows, dOut, s, true);
   }
   return launch_lmm(m, dYt, yRows, dOut, s);
 }

@@ -39,7 +39,7 @@ struct DevGroup {
   int32_t mapType;
   int32_t single;  // SDCSingle*: every listed row holds tuple 0
   int32_t offType, first, last;
-  int32_t pad_;
+  int32_t inFast;  // 1: the specialised vector kernels cover this group (general kernels skip it on their request)
   int64_t mapSize, offLen, nOff, nRuns, dataLen;
   int64_t valOff;  // first row of this group's table in the per-call value arenas (sum of nVals before it)
   const int32_t* cols;
@@ -194,8 +194,8 @@ int64_t ensure_io(Matrix* m, size_t bytes);
 int64_t ensure_small(Matrix* m, size_t bytes);
 
 // launchers implemented in the kernel translation units; all enqueue on `s` and return CLA_OK or an error.
-int64_t launch_rmm(Matrix* m, const double* dV, int vCols, double* dOut, cudaStream_t s);
-int64_t launch_lmm(Matrix* m, const double* dYt, int q, double* dOut, cudaStream_t s);
+int64_t launch_rmm(Matrix* m, const double* dV, int vCols, double* dOut, cudaStream_t s, bool afterFast = false);
+int64_t launch_lmm(Matrix* m, const double* dYt, int q, double* dOut, cudaStream_t s, bool afterFast = false);
 int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s);
 int64_t launch_decompress(Matrix* m, double* dOut, cudaStream_t s);
 int64_t launch_decompress_range(Matrix* m, int r0, int r1, double* dOut, cudaStream_t s);
@@ -206,7 +206,8 @@ int64_t launch_scale_rows(Matrix* m, double* dU, const double* dW, int64_t n, cu
 
 // finalize-time device work (cla_finalize.cu)
 int64_t finalize_device(Matrix* m);
-// fast paths (cla_fast.cu): return 1 if they handled the call, 0 if not applicable, <0 on error
+// fast paths (cla_fast.cu): return 1 if they handled the whole product, 2 if they handled the groups marked inFast
+// (the caller then runs the general launcher with afterFast = true), 0 if not applicable, <0 on error
 int64_t fast_plan_build(Matrix* m);
 void fast_plan_free(Matrix* m);
 int64_t fast_rmm_vec(Matrix* m, const double* dV, double* dOut, cudaStream_t s);

@@ -55,6 +55,7 @@ struct LmmChunk {
 
 struct FastPlan {
   bool ok = false;
+  bool partial = false;  // only some groups are covered; the general kernels add the rest
   int nG = 0;
   // RMM
   std::vector<RmmChunk> rchunks;
@@ -561,17 +562,28 @@ int64_t fast_plan_build(Matrix* m) {
   FastPlan* fp = new FastPlan();
   m->fast = fp;
   if (m->nRows < FAST_MIN_ROWS || m->nDev == 0) return CLA_OK;
-  for (auto& g : m->groups) {
-    if (g.type != GT_DDC || g.nVals > 256 || g.nVals < 1) return CLA_OK;
-    if (g.mapType != CLA_MAP_UBYTE && g.mapType != CLA_MAP_BYTE && g.mapType != CLA_MAP_BIT) return CLA_OK;
+  // the groups these kernels cover: dense maps, at most 256 tuples, one byte (or bit) per cell
+  std::vector<DevGroup> G;
+  std::vector<int> selIdx;
+  for (int gi = 0; gi < m->nDev; gi++) {
+    const DevGroup& g = m->groups[gi];
+    if (g.type != GT_DDC || g.nVals > 256 || g.nVals < 1) continue;
+    if (g.mapType != CLA_MAP_UBYTE && g.mapType != CLA_MAP_BYTE && g.mapType != CLA_MAP_BIT) continue;
+    G.push_back(g);
+    selIdx.push_back(gi);
   }
-  const int nG = m->nDev;
+  const bool all = (int)G.size() == m->nDev;
+  int nUnitsSel = 0;
+  for (auto& g : G) nUnitsSel += g.gCols;
+  if (G.empty() || (!all && nUnitsSel < 16)) return CLA_OK;  // too few columns to be worth a separate pass
+  fp->partial = !all;
+  const int nG = (int)G.size();
   fp->nG = nG;
   int64_t rc;
   // byte maps for every group (bit maps are expanded once)
   std::vector<const uint8_t*> gmap(nG);
   for (int gi = 0; gi < nG; gi++) {
-    const DevGroup& g = m->groups[gi];
+    const DevGroup& g = G[gi];
     if (g.mapType == CLA_MAP_BIT) {
       void* p = nullptr;
       CLA_CUDA(cudaMalloc(&p, (size_t)m->nRows + 64));
@@ -588,9 +600,9 @@ int64_t fast_plan_build(Matrix* m) {
   // ---- RMM: groups ordered by table size so the small (conflict-free) tables pack together ----
   std::vector<int> order(nG);
   std::iota(order.begin(), order.end(), 0);
-  std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return m->groups[a].nVals < m->groups[b].nVals; });
+  std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return G[a].nVals < G[b].nVals; });
   int64_t total = 0;
-  for (int gi : order) total += (m->groups[gi].nVals + 1) & ~1;
+  for (int gi : order) total += (G[gi].nVals + 1) & ~1;
   const int budget = total * 8 <= 40 * 1024 ? 40 * 1024 : 96 * 1024;  // small: many CTAs per SM; else two per SM
   std::vector<const uint8_t*> maps(nG);
   std::vector<int> tblOff(nG), groupOf(nG);
@@ -599,14 +611,14 @@ int64_t fast_plan_build(Matrix* m) {
   RmmChunk cur{0, 0, 0, 0};
   for (int i = 0; i < nG; i++) {
     const int gi = order[i];
-    const int pad = (m->groups[gi].nVals + 1) & ~1;
+    const int pad = (G[gi].nVals + 1) & ~1;
     const int perGroup = 8 + 4;  // map pointer + offset kept in shared memory
     if (cur.g1 > cur.g0 && (cur.tblDoubles + pad) * 8 + (cur.g1 - cur.g0 + 1) * perGroup > budget) {
       fp->rchunks.push_back(cur);
       cur = RmmChunk{i, i, 0, img};
     }
     maps[i] = gmap[gi];
-    groupOf[i] = gi;
+    groupOf[i] = selIdx[gi];
     tblOff[i] = cur.tblDoubles;
     imgOff[i] = img;
     cur.tblDoubles += pad;
@@ -624,7 +636,7 @@ int64_t fast_plan_build(Matrix* m) {
   struct Unit { int g, j, nv; };
   std::vector<Unit> units;
   for (int gi = 0; gi < nG; gi++)
-    for (int j = 0; j < m->groups[gi].gCols; j++) units.push_back({gi, j, m->groups[gi].nVals});
+    for (int j = 0; j < G[gi].gCols; j++) units.push_back({gi, j, G[gi].nVals});
   std::stable_sort(units.begin(), units.end(), [](const Unit& a, const Unit& b) { return a.nv > b.nv; });
   fp->nUnits = (int)units.size();
   const int nPairs = (fp->nUnits + 31) / 32;
@@ -636,8 +648,8 @@ int64_t fast_plan_build(Matrix* m) {
   // host copies of the dictionaries
   std::vector<std::vector<double>> dicts(nG);
   for (int gi = 0; gi < nG; gi++) {
-    dicts[gi].resize((size_t)m->groups[gi].nVals * m->groups[gi].gCols);
-    CLA_CUDA(cudaMemcpy(dicts[gi].data(), m->groups[gi].dict, dicts[gi].size() * 8, cudaMemcpyDeviceToHost));
+    dicts[gi].resize((size_t)G[gi].nVals * G[gi].gCols);
+    CLA_CUDA(cudaMemcpy(dicts[gi].data(), G[gi].dict, dicts[gi].size() * 8, cudaMemcpyDeviceToHost));
   }
   for (int u = 0; u < fp->nUnits; u++) pairNk[u / 32] = std::max(pairNk[u / 32], units[u].nv);
   // chunks: greedily pack slabs up to the shared-memory budget and LMM_MAX_PAIRS
@@ -657,7 +669,7 @@ int64_t fast_plan_build(Matrix* m) {
         const int u = (lc.pair0 + p) * 32 + s;
         if (u >= fp->nUnits) continue;
         const Unit& un = units[u];
-        const int gc = m->groups[un.g].gCols;
+        const int gc = G[un.g].gCols;
         for (int k = 0; k < un.nv; k++) image[off + (size_t)k * 32 + s] = dicts[un.g][(size_t)k * gc + un.j];
       }
       off += (size_t)lc.nk[p] * 32;
@@ -685,8 +697,8 @@ int64_t fast_plan_build(Matrix* m) {
   }
   {  // output column of every unit
     for (int gi = 0; gi < nG; gi++) {
-      std::vector<int32_t> cols(m->groups[gi].gCols);
-      CLA_CUDA(cudaMemcpy(cols.data(), m->groups[gi].cols, cols.size() * 4, cudaMemcpyDeviceToHost));
+      std::vector<int32_t> cols(G[gi].gCols);
+      CLA_CUDA(cudaMemcpy(cols.data(), G[gi].cols, cols.size() * 4, cudaMemcpyDeviceToHost));
       for (int u = 0; u < fp->nUnits; u++)
         if (units[u].g == gi) slotCol[u] = cols[units[u].j];
     }
@@ -732,13 +744,17 @@ int64_t fast_plan_build(Matrix* m) {
   }
   if ((rc = plan_upload(fp, image, &fp->dLmmTables)) < 0) return rc;
   fp->imageDoubles = image.size();
-  for (auto& g : m->groups) fp->maxNVals = std::max(fp->maxNVals, g.nVals);
+  for (auto& g : G) fp->maxNVals = std::max(fp->maxNVals, g.nVals);
   m->deviceBytes += (int64_t)image.size() * 8;
   CLA_CUDA(cudaFuncSetAttribute(k_lmm_vec_u8, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_MAX - 1024));
   CLA_CUDA(cudaFuncSetAttribute(k_rmm_vec_b, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_MAX - 1024));
   CLA_CUDA(cudaFuncSetAttribute(k_rmm_vec_u8<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
   CLA_CUDA(cudaFuncSetAttribute(k_rmm_vec_u8<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
   CLA_CUDA(cudaFuncSetAttribute(k_rmm_vec_u8<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+  if (fp->partial) {  // tell the general kernels which groups are taken care of
+    for (int gi : selIdx) m->groups[gi].inFast = 1;
+    CLA_CUDA(cudaMemcpy(m->dGroups, m->groups.data(), sizeof(DevGroup) * m->groups.size(), cudaMemcpyHostToDevice));
+  }
   fp->ok = true;
   return CLA_OK;
 }
@@ -782,7 +798,7 @@ static int64_t fast_rmm_vec_b(Matrix* m, FastPlan* fp, const double* dV, double*
   prof_end(m, s);
   m->stats.kernel_launches++;
   CLA_CUDA(cudaGetLastError());
-  return 1;
+  return fp->partial ? 2 : 1;
 }
 
 int64_t fast_rmm_vec(Matrix* m, const double* dV, double* dOut, cudaStream_t s) {
@@ -818,7 +834,7 @@ int64_t fast_rmm_vec(Matrix* m, const double* dV, double* dOut, cudaStream_t s) 
     m->stats.kernel_launches++;
   }
   CLA_CUDA(cudaGetLastError());
-  return 1;
+  return fp->partial ? 2 : 1;
 }
 
 int64_t fast_lmm_vec(Matrix* m, const double* dY, double* dOut, cudaStream_t s) {
@@ -841,7 +857,7 @@ int64_t fast_lmm_vec(Matrix* m, const double* dY, double* dOut, cudaStream_t s) 
   if (m->hasConst)
     if ((rc = launch_lmm_const(m, dY, 1, dOut, s)) < 0) return rc;
   CLA_CUDA(cudaGetLastError());
-  return 1;
+  return fp->partial ? 2 : 1;
 }
 
 
@@ -879,7 +895,7 @@ static int64_t noalloc_address(int device, double** out) {
 
 int64_t fast_lmm_vec_noalloc(Matrix* m, const double* dY, double* dOut, cudaStream_t s) {
   FastPlan* fp = m->fast;
-  if (!fp || !fp->ok)
+  if (!fp || !fp->ok || fp->partial)
     return fail(CLA_ERR_UNSUPPORTED, "no-allocation product: needs dense-map groups with at most 256 tuples and byte maps");
   if ((uintptr_t)dY & 15) return fail(CLA_ERR_BAD_ARG, "no-allocation product: the left vector must be 16-byte aligned");
   if (fp->lmmGrid > NOALLOC_MAX_CTAS)

@@ -27,9 +27,9 @@ static inline int grid_for(int64_t n, int block, int cap = 148 * 16) {
 // P arena: [totalVals x vCols]
 // --------------------------------------------------------------------------------------------------
 __global__ void k_dict_times_v(const DevGroup* __restrict__ groups, const double* __restrict__ V, int vCols,
-                               double* __restrict__ P) {
+                               double* __restrict__ P, int skipFast) {
   const DevGroup g = groups[blockIdx.x];
-  if (g.type == GT_UNC) return;
+  if (g.type == GT_UNC || (skipFast && g.inFast)) return;
   const int64_t n = (int64_t)g.nVals * vCols;
   for (int64_t e = blockIdx.y * (int64_t)blockDim.x + threadIdx.x; e < n; e += (int64_t)gridDim.y * blockDim.x) {
     const int k = (int)(e / vCols), j = (int)(e - (int64_t)k * vCols);
@@ -64,7 +64,7 @@ constexpr int MAX_TR = 1024;
 __global__ void __launch_bounds__(RMM_THREADS)
 k_rmm_tile(const DevGroup* __restrict__ groups, int nGroups, int nRows, const double* __restrict__ P,
            const double* __restrict__ V, int vCols, const double* __restrict__ constRow, double* __restrict__ out,
-           int TR, int vcTile, int hasSparse) {
+           int TR, int vcTile, int hasSparse, int afterFast) {
   extern __shared__ double smem[];
   double* acc = smem;                                         // [TR * vc]
   uint16_t* ids = (uint16_t*)(smem + TILE_ELEMS);             // [RLE_BATCH][MAX_TR]
@@ -80,11 +80,14 @@ k_rmm_tile(const DevGroup* __restrict__ groups, int nGroups, int nRows, const do
     const int e = tid + i * RMM_THREADS;
     er[i] = e / vc;
     ej[i] = e - er[i] * vc;
-    racc[i] = (constRow != nullptr && e < nElem) ? constRow[j0 + ej[i]] : 0.0;
+    // after the specialised kernels ran, `out` already holds their groups' sums and the constant part
+    if (afterFast) racc[i] = e < nElem ? out[(size_t)(r0 + er[i]) * vCols + j0 + ej[i]] : 0.0;
+    else racc[i] = (constRow != nullptr && e < nElem) ? constRow[j0 + ej[i]] : 0.0;
   }
   // phase A: dense-map and uncompressed groups, registers
   for (int gi = 0; gi < nGroups; gi++) {
     const DevGroup& g = groups[gi];
+    if (afterFast && g.inFast) continue;
     if (g.type == GT_DDC) {
       const double* Pg = P + g.valOff * vCols + j0;
 #pragma unroll
@@ -170,7 +173,7 @@ k_rmm_tile(const DevGroup* __restrict__ groups, int nGroups, int nRows, const do
   }
 }
 
-int64_t launch_rmm(Matrix* m, const double* dV, int vCols, double* dOut, cudaStream_t s) {
+int64_t launch_rmm(Matrix* m, const double* dV, int vCols, double* dOut, cudaStream_t s, bool afterFast) {
   if (m->nRows == 0 || vCols == 0) return CLA_OK;
   int64_t rc;
   const size_t pBytes = (size_t)std::max<int64_t>(m->totalVals, 1) * vCols * sizeof(double);
@@ -182,10 +185,10 @@ int64_t launch_rmm(Matrix* m, const double* dV, int vCols, double* dOut, cudaStr
     int maxE = 1;
     for (auto& g : m->groups) maxE = std::max<int64_t>(maxE, (int64_t)g.nVals * vCols);
     dim3 grid(m->nDev, std::max(1, std::min(64, (maxE + 255) / 256)));
-    k_dict_times_v<<<grid, 256, 0, s>>>(m->dGroups, dV, vCols, P);
+    k_dict_times_v<<<grid, 256, 0, s>>>(m->dGroups, dV, vCols, P, afterFast ? 1 : 0);
     m->stats.kernel_launches++;
   }
-  if (m->hasConst) {
+  if (m->hasConst && !afterFast) {
     constRow = (double*)((char*)m->scratch + cOff);
     k_const_times_v<<<(vCols + 127) / 128, 128, 0, s>>>(m->dConstV, m->nCols, dV, vCols, constRow);
     m->stats.kernel_launches++;
@@ -194,6 +197,11 @@ int64_t launch_rmm(Matrix* m, const double* dV, int vCols, double* dOut, cudaStr
   int TR = std::min(MAX_TR, std::max(32, TILE_ELEMS / vcTile));
   int hasSparse = 0;
   for (auto& g : m->groups) hasSparse |= (g.type == GT_SDC || g.type == GT_RLE);
+  if (afterFast) {  // nothing left for this pass if the remaining groups are all covered
+    bool rest = false;
+    for (auto& g : m->groups) rest |= !g.inFast;
+    if (!rest) return CLA_OK;
+  }
   const size_t smem = TILE_ELEMS * sizeof(double) + (size_t)RLE_BATCH * MAX_TR * sizeof(uint16_t);
   static bool attr = false;
   if (!attr) {
@@ -203,7 +211,7 @@ int64_t launch_rmm(Matrix* m, const double* dV, int vCols, double* dOut, cudaStr
   dim3 grid((m->nRows + TR - 1) / TR, (vCols + vcTile - 1) / vcTile);
   prof_begin(m, s);
   k_rmm_tile<<<grid, RMM_THREADS, smem, s>>>(m->dGroups, m->nDev, m->nRows, P, dV, vCols, constRow, dOut, TR, vcTile,
-                                             hasSparse);
+                                             hasSparse, afterFast ? 1 : 0);
   prof_end(m, s);
   m->stats.kernel_launches++;
   CLA_CUDA(cudaGetLastError());
@@ -316,10 +324,10 @@ constexpr int LMM_HIST_MAX = 6144;        // doubles of shared histogram (48 KB)
 // grid: (row chunks, dictionary groups, q tiles). A: [totalVals x q]
 __global__ void __launch_bounds__(LMM_THREADS)
 k_lmm_preagg(const DevGroup* __restrict__ groups, int nRows, int rowsPerChunk, const double* __restrict__ Yt, int q,
-             double* __restrict__ A) {
+             double* __restrict__ A, int skipFast) {
   __shared__ double hist[LMM_HIST_MAX];
   const DevGroup& g = groups[blockIdx.y];
-  if (g.type == GT_UNC) return;
+  if (g.type == GT_UNC || (skipFast && g.inFast)) return;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int ra = blockIdx.x * rowsPerChunk, rb = min(nRows, ra + rowsPerChunk);
   if (ra >= rb) return;
@@ -375,9 +383,9 @@ k_lmm_preagg(const DevGroup* __restrict__ groups, int nRows, int rowsPerChunk, c
 
 // out[i, cols_g[c]] += sum_k A_g[k, i] * D_g[k, c]; one block per group
 __global__ void k_lmm_post(const DevGroup* __restrict__ groups, const double* __restrict__ A, int q, int nCols,
-                           double* __restrict__ out) {
+                           double* __restrict__ out, int skipFast) {
   const DevGroup& g = groups[blockIdx.x];
-  if (g.type == GT_UNC) return;
+  if (g.type == GT_UNC || (skipFast && g.inFast)) return;
   const double* Ag = A + g.valOff * q;
   for (int e = threadIdx.x; e < q * g.gCols; e += blockDim.x) {
     const int i = e / g.gCols, c = e - i * g.gCols;
@@ -417,9 +425,9 @@ __global__ void k_lmm_const(const double* __restrict__ sums, const double* __res
     out[e] += sums[e / nCols] * constV[e % nCols];
 }
 
-int64_t launch_lmm(Matrix* m, const double* dYt, int q, double* dOut, cudaStream_t s) {
+int64_t launch_lmm(Matrix* m, const double* dYt, int q, double* dOut, cudaStream_t s, bool afterFast) {
   if (q == 0 || m->nCols == 0) return CLA_OK;
-  CLA_CUDA(cudaMemsetAsync(dOut, 0, sizeof(double) * (size_t)q * m->nCols, s));
+  if (!afterFast) CLA_CUDA(cudaMemsetAsync(dOut, 0, sizeof(double) * (size_t)q * m->nCols, s));
   if (m->nRows == 0) return CLA_OK;
   int64_t rc;
   const size_t aBytes = (size_t)std::max<int64_t>(m->totalVals, 1) * q * sizeof(double);
@@ -435,9 +443,9 @@ int64_t launch_lmm(Matrix* m, const double* dYt, int q, double* dOut, cudaStream
     const int chunks = (m->nRows + rowsPerChunk - 1) / rowsPerChunk;
     dim3 grid(chunks, m->nDev, (q + LMM_QT - 1) / LMM_QT);
     prof_begin(m, s);
-    k_lmm_preagg<<<grid, LMM_THREADS, 0, s>>>(m->dGroups, m->nRows, rowsPerChunk, dYt, q, A);
+    k_lmm_preagg<<<grid, LMM_THREADS, 0, s>>>(m->dGroups, m->nRows, rowsPerChunk, dYt, q, A, afterFast ? 1 : 0);
     prof_end(m, s);
-    k_lmm_post<<<m->nDev, 128, 0, s>>>(m->dGroups, A, q, m->nCols, dOut);
+    k_lmm_post<<<m->nDev, 128, 0, s>>>(m->dGroups, A, q, m->nCols, dOut, afterFast ? 1 : 0);
     m->stats.kernel_launches += 2;
     for (auto& g : m->groups)
       if (g.type == GT_UNC) {
@@ -446,7 +454,7 @@ int64_t launch_lmm(Matrix* m, const double* dYt, int q, double* dOut, cudaStream
         m->stats.kernel_launches++;
       }
   }
-  if (m->hasConst) {
+  if (m->hasConst && !afterFast) {
     dim3 grid(grid_for(m->nRows, 256, 4 * m->smCount), q);
     k_row_sums<<<grid, 256, 0, s>>>(dYt, m->nRows, q, sums);
     k_lmm_const<<<grid_for((int64_t)q * m->nCols, 256), 256, 0, s>>>(sums, m->dConstV, q, m->nCols, dOut);

@@ -242,3 +242,26 @@ def test_sharded_partials_add_up(oracle):
     assert rel_err(lmm, oracle.dense_lmm_ld(X, y), np.abs(y) @ aX) < TOL
     assert rel_err(tsmm, oracle.dense_tsmm_ld(X), aX.T @ aX) < TOL
     assert rel_err(chain.ravel(), X.T @ (X @ v), aX.T @ (aX @ np.abs(v))) < 10 * TOL
+
+
+@pytest.mark.parametrize("nRows", [5000, 70001])
+def test_mixed_fast_and_general(oracle, nRows):
+    """Vector products on a mixed matrix: the specialised kernels take the byte-map DDC groups, the general
+    kernels add the SDC / RLE / uncompressed / wide-map groups and the constant part exactly once."""
+    kinds = ("ddc",) * 14 + ("ddc2",) * 3 + ("ddc_bit", "sdc", "sdcz", "rle", "ole", "unc", "const", "ddc_char", "sdcs")
+    cmb = datagen.random_cmb(77 + nRows, nRows, kinds).to_device()
+    om = oracle.OracleMatrix(cmb)
+    X = dense_of(cmb)
+    aX = np.abs(X)
+    rng = np.random.default_rng(nRows)
+    v = rng.standard_normal(cmb.clen)
+    y = rng.standard_normal((1, nRows))
+    w = rng.standard_normal(nRows)
+    assert rel_err(CLALibRightMultBy.rightMultByMatrix(cmb, v), om.rmm(v), aX @ np.abs(v).reshape(-1, 1) + 1e-300) < TOL
+    assert rel_err(CLALibLeftMultBy.leftMultByMatrix(cmb, y), om.lmm(y), np.abs(y) @ aX + 1e-300) < TOL
+    s = aX.T @ (np.abs(w) * (aX @ np.abs(v))) + 1e-300
+    assert rel_err(CLALibMMChain.mmChain(cmb, v, w, CHAIN_XtwXv).ravel(), om.mmchain(v, w, 1).ravel(), s) < 10 * TOL
+    # multi-column operands still take the general kernels for every group
+    V = rng.standard_normal((cmb.clen, 3))
+    assert rel_err(CLALibRightMultBy.rightMultByMatrix(cmb, V), om.rmm(V), aX @ np.abs(V) + 1e-300) < TOL
+    cmb.free()
