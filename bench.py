@@ -136,6 +136,9 @@ def main():
     ap.add_argument("--rows", type=int, default=10_000_000, help="rows per GPU (default: the benchmark configuration)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-also", action="store_true", help="skip the secondary X%%*%%v measurement")
+    ap.add_argument("--extras", action="store_true",
+                    help="also time scaled-down versions of the other benchmark configurations (mixed-group X%%*%%V, "
+                         "t(X)%%*%%X, the lmCG step); adds about a minute of host-side data generation")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -258,6 +261,8 @@ def main():
     # ---- secondary: X %*% v on configs[0] (1,000,000 x 100, 16 values/column), L2 flushed between iterations ----
     if rank == 0 and not args.no_also:
         result["also"] = {"rmm_config0": bench_rmm_config0(L, dev, sptr, peak)}
+    if rank == 0 and args.extras:
+        result["also"] = dict(result.get("also", {}), **bench_extras(L, dev, sptr, peak))
     # ---- CPU baseline (rank 0 only) ----
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         rate, ms, cores = cpu_reference_rate(CPU_SAMPLE_ROWS, 3, 1)
@@ -302,6 +307,81 @@ def bench_rmm_config0(L, dev, sptr, peak):
            "l2": "256 MB buffer written between iterations (inputs are 100 MB, below L2)"}
     cmb.free()
     return res
+
+
+def _time_dev(fn, iters=5):
+    import torch
+    fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def bench_extras(L, dev, sptr, peak):
+    """Scaled-down versions of configs[2..4] (same shapes per row, fewer rows), device-resident operands."""
+    import torch
+    from systemds_b200 import datagen
+    from systemds_b200.native import check
+    P = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
+    out = {}
+    # configs[2]: mixed groups, X %*% V with 64 columns
+    n = 1_000_000
+    cmb, V = datagen.config3(nRows=n)
+    cmb.to_device(dev.index)
+    h = cmb.handle()
+    Vd = torch.from_numpy(V).to(dev)
+    Od = torch.empty((n, 64), dtype=torch.float64, device=dev)
+    ms = _time_dev(lambda: check(L.cla_rmm_dev(h, P(Vd), 500, 64, P(Od), sptr)))
+    alg = cmb.index_bytes() + n * 64 * 8 + V.nbytes
+    out["rmm_mixed_config2"] = {"workload": f"configs[2] at {n} rows: 500 columns (40% DDC, 30% SDCZeros, 20% RLE, 10% dense), V 500x64",
+                                "ms": ms, "rows_per_s": n / (ms * 1e-3), "algorithmic_GBps": alg / (ms * 1e-3) / 1e9,
+                                "hbm_frac": alg / (ms * 1e-3) / 1e9 / peak}
+    yd = torch.randn(n, dtype=torch.float64, device=dev)
+    od = torch.empty(500, dtype=torch.float64, device=dev)
+    ms = _time_dev(lambda: check(L.cla_lmm_dev(h, P(yd), 1, P(od), sptr)))
+    algl = cmb.index_bytes() + n * 8
+    out["lmm_mixed_config2"] = {"workload": "t(y) %*% X on the same matrix", "ms": ms, "rows_per_s": n / (ms * 1e-3),
+                                "algorithmic_GBps": algl / (ms * 1e-3) / 1e9, "hbm_frac": algl / (ms * 1e-3) / 1e9 / peak}
+    cmb.free()
+    del Vd, Od
+    # configs[3]: t(X) %*% X, 100 DDC columns with 1000 values (MapToChar), Zipf ids
+    n = 2_000_000
+    cmb = datagen.config4(nRows=n)
+    cmb.to_device(dev.index)
+    h = cmb.handle()
+    Cd = torch.empty((100, 100), dtype=torch.float64, device=dev)
+    ms = _time_dev(lambda: check(L.cla_tsmm_dev(h, P(Cd), sptr)))
+    flops = 2.0 * n * 100 * 101 / 2
+    out["tsmm_config3"] = {"workload": f"configs[3] at {n} rows: 100 DDC columns, 1000 values, MapToChar, Zipf(1.1)",
+                           "ms": ms, "rows_per_s": n / (ms * 1e-3), "algorithmic_TFLOPs": flops / (ms * 1e-3) / 1e12,
+                           "dmma_peak_TFLOPs": 148 * 64 * 2 * 1.965e9 / 1e12,
+                           "note": "peak = 148 SMs x one m8n8k4 DMMA per 4 clocks (ncu: tensor pipe 100 % = that rate) x 1965 MHz"}
+    cmb.free()
+    # configs[4]: lmCG step w = t(X) (X v) + 1e-3 v on one shard
+    n = 2_000_000
+    cmb, v = datagen.config5(nRows=n)
+    cmb.to_device(dev.index)
+    h = cmb.handle()
+    vd = torch.from_numpy(v.reshape(-1)).to(dev)
+    wd = torch.empty(1000, dtype=torch.float64, device=dev)
+    ud = torch.empty(n, dtype=torch.float64, device=dev)
+
+    def step():
+        check(L.cla_mmchain_dev(h, P(vd), None, 0, P(wd), P(ud), sptr))
+        wd.add_(vd, alpha=1e-3)
+
+    ms = _time_dev(step)
+    alg5 = 2 * cmb.index_bytes() + 2 * n * 8
+    out["lmcg_step_config4"] = {"workload": f"configs[4] shard at {n} rows x 1000 columns (cardinality 2..255): w = t(X)(Xv) + 1e-3 v",
+                                "ms": ms, "rows_per_s": n / (ms * 1e-3), "algorithmic_GBps": alg5 / (ms * 1e-3) / 1e9,
+                                "hbm_frac": alg5 / (ms * 1e-3) / 1e9 / peak}
+    cmb.free()
+    return out
 
 
 if __name__ == "__main__":

@@ -326,6 +326,7 @@ static int64_t rmm_dev(Matrix* m, const double* dV, int32_t vRows, int32_t vCols
     if (rc == 1) return CLA_OK;
     if (rc == 2) return launch_rmm(m, dV, vCols, dOut, s, true);
   }
+  if (vCols >= 8) return launch_rmm_dmma(m, dV, vCols, dOut, s);  // wide V: FP64 tensor cores
   return launch_rmm(m, dV, vCols, dOut, s);
 }
 

@@ -148,6 +148,9 @@ struct Matrix {
   int64_t totalVals = 0;         // sum of nVals over dictionary groups
   std::vector<double> constV;    // host copy
   double* dConstV = nullptr;     // [nCols]
+  void* dDenseCols = nullptr;    // list of dense-operand columns for the tensor-core RMM (built on first use)
+  int nDenseCols = 0;
+  bool denseColsBuilt = false;
   int32_t* dColSrc = nullptr;    // [nCols][2]: dense-map / uncompressed group holding the column and the position in it (-1: none)
   bool colSrcValid = false;      // false when some column is held by more than one such group (overlapping input)
   bool hasConst = false;
@@ -195,6 +198,7 @@ int64_t ensure_small(Matrix* m, size_t bytes);
 
 // launchers implemented in the kernel translation units; all enqueue on `s` and return CLA_OK or an error.
 int64_t launch_rmm(Matrix* m, const double* dV, int vCols, double* dOut, cudaStream_t s, bool afterFast = false);
+int64_t launch_rmm_dmma(Matrix* m, const double* dV, int vCols, double* dOut, cudaStream_t s);
 int64_t launch_lmm(Matrix* m, const double* dYt, int q, double* dOut, cudaStream_t s, bool afterFast = false);
 int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s);
 int64_t launch_decompress(Matrix* m, double* dOut, cudaStream_t s);

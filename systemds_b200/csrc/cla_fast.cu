@@ -51,6 +51,7 @@ struct LmmChunk {
   int64_t tblOff;        // offset in the table image (doubles)
   int tblDoubles;
   int cta0, nCta;        // CTA range of the launch that works on this chunk
+  int halfLast;          // the chunk's last slab only uses its first 16 column slots
 };
 
 struct FastPlan {
@@ -249,13 +250,14 @@ __device__ __forceinline__ uint32_t byte_x256(uint32_t w, int i) {  // (byte i o
   return __byte_perm(w, 0u, 0x4404u | ((uint32_t)i << 4));
 }
 
-template <int NP>
+template <int NP, bool HALF>
 __device__ __forceinline__ void lmm_cells(const uint4 (&m)[NP][2][2], int sub, const double (&yv)[16],
                                           const unsigned char* const (&tbase)[NP], double (&acc)[NP][2]) {
 #pragma unroll
   for (int p = 0; p < NP; p++) {
 #pragma unroll
     for (int ab = 0; ab < 2; ab++) {
+      if (HALF && p == NP - 1 && ab == 1) continue;
       const uint4 w = m[p][ab][sub];
       const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
       const unsigned char* T = tbase[p] + ab * 128;
@@ -269,7 +271,7 @@ __device__ __forceinline__ void lmm_cells(const uint4 (&m)[NP][2][2], int sub, c
 }
 
 // partial: [gridDim.x][LMM_MAX_PAIRS * 32]
-template <int NP>
+template <int NP, bool HALF>
 __device__ __forceinline__ void lmm_vec_body(const LmmChunk& ch, const uint8_t* __restrict__ imaps, int64_t nRB,
                                              const double* __restrict__ tablesImg, const double* __restrict__ y,
                                              int nRows, double* __restrict__ partial, unsigned char* smraw,
@@ -309,6 +311,7 @@ __device__ __forceinline__ void lmm_vec_body(const LmmChunk& ch, const uint8_t* 
       for (int p = 0; p < NP; p++)
 #pragma unroll
         for (int ab = 0; ab < 2; ab++) {
+          if (HALF && p == NP - 1 && ab == 1) continue;
           const uint8_t* src = mp[p][ab] + (r0 >> 4) * 256;
           m[p][ab][0] = __ldg((const uint4*)src);
           m[p][ab][1] = __ldg((const uint4*)(src + 256));
@@ -323,7 +326,7 @@ __device__ __forceinline__ void lmm_vec_body(const LmmChunk& ch, const uint8_t* 
           yv[2 * i] = t.x;
           yv[2 * i + 1] = t.y;
         }
-        lmm_cells<NP>(m, sub, yv, tbase, acc);
+        lmm_cells<NP, HALF>(m, sub, yv, tbase, acc);
       }
     } else {  // ragged last step
       for (int64_t r = r0; r < min((int64_t)nRows, r0 + 32); r++) {
@@ -331,9 +334,11 @@ __device__ __forceinline__ void lmm_vec_body(const LmmChunk& ch, const uint8_t* 
 #pragma unroll
         for (int p = 0; p < NP; p++)
 #pragma unroll
-          for (int ab = 0; ab < 2; ab++)
+          for (int ab = 0; ab < 2; ab++) {
+            if (HALF && p == NP - 1 && ab == 1) continue;
             acc[p][ab] = fma(yy, *(const double*)(tbase[p] + ab * 128 + 256 * (int)mp[p][ab][(r >> 4) * 256 + (r & 15)]),
                              acc[p][ab]);
+          }
       }
     }
   }
@@ -369,10 +374,13 @@ k_lmm_vec_u8(const LmmChunk* __restrict__ chunks, int nChunks, const uint8_t* __
     ch = chunks[c];
   }
   __syncthreads();
-  switch (ch.nPairs) {
-    case 1: lmm_vec_body<1>(ch, imaps, nRB, tablesImg, y, nRows, partial, smraw, &mbar, err); break;
-    case 2: lmm_vec_body<2>(ch, imaps, nRB, tablesImg, y, nRows, partial, smraw, &mbar, err); break;
-    default: lmm_vec_body<3>(ch, imaps, nRB, tablesImg, y, nRows, partial, smraw, &mbar, err); break;
+  switch (ch.nPairs * 2 + (ch.halfLast ? 1 : 0)) {
+    case 2: lmm_vec_body<1, false>(ch, imaps, nRB, tablesImg, y, nRows, partial, smraw, &mbar, err); break;
+    case 3: lmm_vec_body<1, true>(ch, imaps, nRB, tablesImg, y, nRows, partial, smraw, &mbar, err); break;
+    case 4: lmm_vec_body<2, false>(ch, imaps, nRB, tablesImg, y, nRows, partial, smraw, &mbar, err); break;
+    case 5: lmm_vec_body<2, true>(ch, imaps, nRB, tablesImg, y, nRows, partial, smraw, &mbar, err); break;
+    case 6: lmm_vec_body<3, false>(ch, imaps, nRB, tablesImg, y, nRows, partial, smraw, &mbar, err); break;
+    default: lmm_vec_body<3, true>(ch, imaps, nRB, tablesImg, y, nRows, partial, smraw, &mbar, err); break;
   }
 }
 
@@ -674,6 +682,7 @@ int64_t fast_plan_build(Matrix* m) {
       }
       off += (size_t)lc.nk[p] * 32;
     }
+    lc.halfLast = ((lc.pair0 + lc.nPairs) * 32 - fp->nUnits >= 16) ? 1 : 0;  // only the very last slab can be half empty
     fp->lchunks.push_back(lc);
   };
   size_t curBytes = 0;
@@ -708,13 +717,14 @@ int64_t fast_plan_build(Matrix* m) {
   // 64 for the left vector (which does not depend on the number of slabs).
   const int totalCta = std::max(m->smCount, (int)fp->lchunks.size());
   double totalCost = 0;
-  for (auto& c : fp->lchunks) totalCost += 144.0 * c.nPairs + 64.0;
+  auto chunkCost = [](const LmmChunk& c) { return 144.0 * (c.nPairs - 0.5 * c.halfLast) + 64.0; };
+  for (auto& c : fp->lchunks) totalCost += chunkCost(c);
   int cta = 0;
   const int64_t nSteps = ((int64_t)m->nRows + LMM_STEP - 1) / LMM_STEP;
   std::vector<int> share(fp->lchunks.size());
   int used = 0;
   for (size_t i = 0; i < fp->lchunks.size(); i++) {
-    share[i] = std::max(1, (int)(totalCta * (144.0 * fp->lchunks[i].nPairs + 64.0) / totalCost));
+    share[i] = std::max(1, (int)(totalCta * chunkCost(fp->lchunks[i]) / totalCost));
     used += share[i];
   }
   for (size_t i = 0; used < totalCta; i = (i + 1) % fp->lchunks.size(), used++) share[i]++;  // hand out the remainder

@@ -73,6 +73,179 @@ k_syrk_dmma(const double* __restrict__ X, int rows, int nCols, int nBlk, double*
   }
 }
 
+// --------------------------------------------------------------------------------------------------
+// Up to 128 columns: one CTA holds the whole upper triangle of the result (8x8 DMMA tiles, split over the 8
+// warps in row-major order so a warp's tiles share their A fragment), so nothing of the product is computed
+// twice and only the triangle's tiles are computed at all. Rows are split across CTAs; each adds its partial
+// triangle to the result with atomics at the end.
+// FUSED: the 32-row stage is decoded straight from the maps and dictionaries (dense-map and uncompressed groups
+// only), so the dense form of X never exists, not even in L2. Otherwise the stage is read from a decompressed chunk.
+// --------------------------------------------------------------------------------------------------
+constexpr int TT_KT = 32;             // rows per stage
+constexpr int TT_LD = TT_KT + 4;      // stride of the transposed stage Xt[col][row]: = 4 mod 16
+constexpr int TT_MAXJ = 16;           // tile columns at 128 matrix columns
+constexpr int TT_CONS = 8;            // warps issuing DMMA
+constexpr int TT_PROD = 0;            // extra warps that only decode (0: every warp decodes, then multiplies)
+constexpr int TT_THREADS = (TT_CONS + TT_PROD) * 32;
+
+// What the staging loop needs to know about one matrix column, kept in shared memory.
+struct TsmmCol {
+  const void* map;     // null: no dense-map / uncompressed group holds the column
+  const void* mapHi;
+  const double* src;   // dictionary (or the dense block) already offset to the column inside the group
+  double cst;          // constant part of the column
+  int32_t mapType;     // -1: uncompressed (src is the dense block + j)
+  int32_t gCols;
+};
+
+// Warp w owns tile rows I1 = w and I2 = NT-1-w of the upper triangle (NT+1 tiles together, for every w), so the
+// B fragment of tile column J serves both rows and every fragment address is the warp's base plus a constant.
+template <bool FUSED>
+__global__ void __launch_bounds__(TT_THREADS, 2)
+k_tsmm_tri(const DevGroup* __restrict__ groups, const int32_t* __restrict__ colSrc, const double* __restrict__ constV,
+           const double* __restrict__ X, int rowBegin, int rowEnd, int nCols, double* __restrict__ C) {
+  extern __shared__ __align__(16) double XtAll[];  // two stages of [NT * 8][TT_LD], then the column records
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int NT = (nCols + 7) >> 3;
+  const int nColsPad = NT * 8;
+  const int stageDoubles = nColsPad * TT_LD;
+  TsmmCol* cols = (TsmmCol*)(XtAll + 2 * stageDoubles);
+  if (FUSED) {
+    for (int cc = tid; cc < nColsPad; cc += TT_THREADS) {
+      TsmmCol d;
+      d.map = nullptr;
+      d.mapHi = nullptr;
+      d.src = nullptr;
+      d.cst = (constV && cc < nCols) ? constV[cc] : 0.0;
+      d.mapType = 0;
+      d.gCols = 1;
+      if (cc < nCols && colSrc[2 * cc] >= 0) {
+        const DevGroup& g = groups[colSrc[2 * cc]];
+        const int j = colSrc[2 * cc + 1];
+        d.gCols = g.gCols;
+        if (g.type == GT_UNC) {
+          d.mapType = -1;
+          d.src = g.dense + j;
+          d.map = g.dense;  // non-null marker
+        } else {
+          d.mapType = g.mapType;
+          d.map = g.mapType == CLA_MAP_ZERO ? (const void*)g.dict : g.map;
+          d.mapHi = g.mapHi;
+          d.src = g.dict + j;
+        }
+      }
+      cols[cc] = d;
+    }
+    __syncthreads();
+  }
+  // this warp's two tile rows; len = number of tiles of each (counted from the last tile column backwards)
+  const int half = NT >> 1;
+  const int I1 = warp, I2 = NT - 1 - warp;
+  int len1 = 0, len2 = 0;
+  if (warp < half) {
+    len1 = NT - I1;
+    len2 = NT - I2;  // = I1 + 1
+  } else if ((NT & 1) && warp == half)
+    len1 = NT - I1;
+  double c1[TT_MAXJ][2], c2[TT_MAXJ / 2][2];  // the second row of a pair has at most NT / 2 tiles
+#pragma unroll
+  for (int i = 0; i < TT_MAXJ; i++) c1[i][0] = c1[i][1] = 0.0;
+#pragma unroll
+  for (int i = 0; i < TT_MAXJ / 2; i++) c2[i][0] = c2[i][1] = 0.0;
+  const int am = lane >> 2, ak = lane & 3;
+  const int a1o = (min(I1, NT - 1) * 8 + am) * TT_LD + ak;
+  const int a2o = (min(max(I2, 0), NT - 1) * 8 + am) * TT_LD + ak;
+  const int bo = ((NT - 1) * 8 + am) * TT_LD + ak;  // tile column NT-1; column NT-1-jr is 8*TT_LD*jr below
+
+  const int64_t nStages = ((int64_t)(rowEnd - rowBegin) + TT_KT - 1) / TT_KT;
+  const int64_t sa = nStages * blockIdx.x / gridDim.x, sb = nStages * (blockIdx.x + 1) / gridDim.x;
+  // Decode one 32-row stage; a warp takes every nw-th column, four at a time so that the map loads of a batch
+  // are all in flight before the first dictionary load that depends on one of them.
+  constexpr int NB = 4;
+  auto stage = [&](int64_t st, double* Xt, int w, int nw) {
+    const int row = rowBegin + (int)st * TT_KT + lane;  // lanes run along rows
+    const bool inRange = row < rowEnd;
+    for (int c0 = w; c0 < nColsPad; c0 += nw * NB) {
+      double v[NB];
+      if (FUSED) {
+        const double* src[NB];
+        size_t off[NB];
+#pragma unroll
+        for (int b = 0; b < NB; b++) {
+          const int cc = c0 + b * nw;
+          v[b] = 0.0;
+          src[b] = nullptr;
+          off[b] = 0;
+          if (cc < nColsPad && inRange) {
+            const TsmmCol d = cols[cc];
+            v[b] = d.cst;
+            if (d.map) {
+              src[b] = d.src;
+              off[b] = (d.mapType < 0 ? (size_t)row : (size_t)map_get(d.mapType, d.map, d.mapHi, row)) * d.gCols;
+            }
+          }
+        }
+#pragma unroll
+        for (int b = 0; b < NB; b++)
+          if (src[b]) v[b] += src[b][off[b]];
+      } else {
+#pragma unroll
+        for (int b = 0; b < NB; b++) {
+          const int cc = c0 + b * nw;
+          v[b] = (inRange && cc < nCols) ? X[(size_t)(row - rowBegin) * nCols + cc] : 0.0;
+        }
+      }
+#pragma unroll
+      for (int b = 0; b < NB; b++) {
+        const int cc = c0 + b * nw;
+        if (cc < nColsPad) Xt[cc * TT_LD + lane] = v[b];
+      }
+    }
+  };
+  if (sa < sb) stage(sa, XtAll, warp, TT_CONS);
+  __syncthreads();
+  for (int64_t st = sa; st < sb; st++) {
+    const int cur = (int)(st - sa) & 1;
+    // issue the next stage's decode first: its loads overlap the DMMAs below (other buffer, no hazard)
+    if (st + 1 < sb) stage(st + 1, XtAll + (cur ^ 1) * stageDoubles, warp, TT_CONS);
+    {
+      const double* Xt = XtAll + cur * stageDoubles;
+#pragma unroll
+      for (int ks = 0; ks < TT_KT; ks += 4) {
+        const double a1 = Xt[a1o + ks], a2 = Xt[a2o + ks];
+#pragma unroll
+        for (int jr = 0; jr < TT_MAXJ; jr++) {
+          if (jr < len1) {
+            const double b = Xt[bo + ks - jr * 8 * TT_LD];
+            dmma884(c1[jr][0], c1[jr][1], a1, b);
+            if (jr < TT_MAXJ / 2) {
+              if (jr < len2) dmma884(c2[jr][0], c2[jr][1], a2, b);
+            }
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int jr = 0; jr < TT_MAXJ; jr++) {
+    const int J = NT - 1 - jr;
+#pragma unroll
+    for (int u = 0; u < 2; u++) {
+      const int gj = J * 8 + (lane & 3) * 2 + u;
+      if (jr < len1) {
+        const int gi = I1 * 8 + (lane >> 2);
+        if (gi < nCols && gj < nCols && gi <= gj && c1[jr][u] != 0.0) atomicAdd(&C[(size_t)gi * nCols + gj], c1[jr][u]);
+      }
+      if (jr < TT_MAXJ / 2 && jr < len2) {
+        const int gi = I2 * 8 + (lane >> 2);
+        if (gi < nCols && gj < nCols && gi <= gj && c2[jr < TT_MAXJ / 2 ? jr : 0][u] != 0.0)
+          atomicAdd(&C[(size_t)gi * nCols + gj], c2[jr < TT_MAXJ / 2 ? jr : 0][u]);
+      }
+    }
+  }
+}
+
 // LibMatrixMult.copyUpperToLowerTriangle (runtime/matrix/data/LibMatrixMult.java:4769-4799)
 __global__ void k_mirror(double* __restrict__ C, int n) {
   const int64_t total = (int64_t)n * n;
@@ -87,25 +260,51 @@ int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s) {
   if (n == 0) return CLA_OK;
   CLA_CUDA(cudaMemsetAsync(dOut, 0, sizeof(double) * (size_t)n * n, s));
   if (m->nRows == 0) return CLA_OK;
-  // chunk of rows whose dense form stays well inside L2 (48 MB)
-  int64_t chunk = (48ll << 20) / ((int64_t)n * 8);
-  chunk = std::max<int64_t>(SKIP_ROWS, (chunk / SKIP_ROWS) * SKIP_ROWS);
-  chunk = std::min<int64_t>(chunk, ((int64_t)m->nRows + SKIP_ROWS - 1) / SKIP_ROWS * SKIP_ROWS);
   int64_t rc;
-  if ((rc = ensure_scratch2(m, (size_t)chunk * n * sizeof(double))) < 0) return rc;
-  double* X = (double*)m->scratch2;
-  const int nBlk = (n + TS_BLK - 1) / TS_BLK;
-  const int nPairs = nBlk * (nBlk + 1) / 2;
-  for (int64_t r0 = 0; r0 < m->nRows; r0 += chunk) {
-    const int r1 = (int)std::min<int64_t>(m->nRows, r0 + chunk);
-    if ((rc = launch_decompress_range(m, (int)r0, r1, X, s)) < 0) return rc;
-    const int rows = r1 - (int)r0;
-    int splits = std::max(1, std::min((rows + TS_KT * 8 - 1) / (TS_KT * 8), (4 * m->smCount + nPairs - 1) / nPairs));
-    int rowsPerSplit = ((rows + splits - 1) / splits + TS_KT - 1) / TS_KT * TS_KT;
-    splits = (rows + rowsPerSplit - 1) / rowsPerSplit;
-    dim3 grid(nPairs, splits);
-    k_syrk_dmma<<<grid, TS_THREADS, 0, s>>>(X, rows, n, nBlk, dOut, rowsPerSplit);
+  const bool tri = n <= 128;
+  bool denseOnly = m->colSrcValid;
+  for (auto& g : m->groups) denseOnly &= (g.type == GT_DDC || g.type == GT_UNC);
+  const size_t triSmem = (size_t)((n + 7) / 8 * 8) * (2 * TT_LD * sizeof(double) + sizeof(TsmmCol));
+  static bool attr = false;
+  if (!attr) {
+    CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * (2 * TT_LD * 8 + (int)sizeof(TsmmCol))));
+    CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * (2 * TT_LD * 8 + (int)sizeof(TsmmCol))));
+    attr = true;
+  }
+  if (tri && denseOnly) {  // one launch over all rows, decoding as it goes
+    const int64_t nStages = ((int64_t)m->nRows + TT_KT - 1) / TT_KT;
+    const int grid = (int)std::min<int64_t>(2 * m->smCount, nStages);
+    prof_begin(m, s);
+    k_tsmm_tri<true><<<grid, TT_THREADS, triSmem, s>>>(m->dGroups, m->dColSrc, m->hasConst ? m->dConstV : nullptr, nullptr, 0,
+                                                      m->nRows, n, dOut);
+    prof_end(m, s);
     m->stats.kernel_launches++;
+  } else {
+    // chunk of rows whose dense form stays well inside L2 (48 MB)
+    int64_t chunk = (48ll << 20) / ((int64_t)n * 8);
+    chunk = std::max<int64_t>(SKIP_ROWS, (chunk / SKIP_ROWS) * SKIP_ROWS);
+    chunk = std::min<int64_t>(chunk, ((int64_t)m->nRows + SKIP_ROWS - 1) / SKIP_ROWS * SKIP_ROWS);
+    if ((rc = ensure_scratch2(m, (size_t)chunk * n * sizeof(double))) < 0) return rc;
+    double* X = (double*)m->scratch2;
+    const int nBlk = (n + TS_BLK - 1) / TS_BLK;
+    const int nPairs = nBlk * (nBlk + 1) / 2;
+    for (int64_t r0 = 0; r0 < m->nRows; r0 += chunk) {
+      const int r1 = (int)std::min<int64_t>(m->nRows, r0 + chunk);
+      if ((rc = launch_decompress_range(m, (int)r0, r1, X, s)) < 0) return rc;
+      const int rows = r1 - (int)r0;
+      if (tri) {
+        const int64_t nStages = ((int64_t)rows + TT_KT - 1) / TT_KT;
+        const int grid = (int)std::min<int64_t>(2 * m->smCount, nStages);
+        k_tsmm_tri<false><<<grid, TT_THREADS, triSmem, s>>>(nullptr, nullptr, nullptr, X, 0, rows, n, dOut);
+      } else {
+        int splits = std::max(1, std::min((rows + TS_KT * 8 - 1) / (TS_KT * 8), (4 * m->smCount + nPairs - 1) / nPairs));
+        int rowsPerSplit = ((rows + splits - 1) / splits + TS_KT - 1) / TS_KT * TS_KT;
+        splits = (rows + rowsPerSplit - 1) / rowsPerSplit;
+        dim3 grid(nPairs, splits);
+        k_syrk_dmma<<<grid, TS_THREADS, 0, s>>>(X, rows, n, nBlk, dOut, rowsPerSplit);
+      }
+      m->stats.kernel_launches++;
+    }
   }
   k_mirror<<<std::max(1, std::min(1024, (int)(((int64_t)n * n + 255) / 256))), 256, 0, s>>>(dOut, n);
   m->stats.kernel_launches++;

@@ -51,7 +51,7 @@ def test_products_vs_oracle(oracle, name, kinds, overlap, nRows):
     om = oracle.OracleMatrix(cmb)
     rng = np.random.default_rng(nRows)
     assert rel_err(CLALibDecompress.decompress(cmb), om.decompress()) < 1e-14
-    for vc in (1, 5, 64):
+    for vc in (1, 5, 13, 64, 70):
         V = rng.standard_normal((cmb.clen, vc))
         got = CLALibRightMultBy.rightMultByMatrix(cmb, V)
         assert got.shape == (nRows, vc)
