@@ -150,6 +150,10 @@ struct Matrix {
   double* dConstV = nullptr;     // [nCols]
   void* dDenseCols = nullptr;    // list of dense-operand columns for the tensor-core RMM (built on first use)
   int nDenseCols = 0;
+  void* dDenseDesc = nullptr;    // the same columns as flat records (map, dictionary column, V row)
+  void* dSdcIdx = nullptr;       // device group indices of the SDC / RLE groups
+  void* dRleIdx = nullptr;
+  int nSdcGroups = 0, nRleGroups = 0;
   bool denseColsBuilt = false;
   int32_t* dColSrc = nullptr;    // [nCols][2]: dense-map / uncompressed group holding the column and the position in it (-1: none)
   bool colSrcValid = false;      // false when some column is held by more than one such group (overlapping input)

@@ -395,12 +395,33 @@ __global__ void k_lmm_post(const DevGroup* __restrict__ groups, const double* __
   }
 }
 
-// uncompressed group: out[i, cols[c]] += sum_r Yt[i, r] * dense[r, c]; block = (row chunk), threads over (i, c)
+// uncompressed group: out[i, cols[c]] += sum_r Yt[i, r] * dense[r, c]. A thread owns one column c (threads along
+// the columns read a dense row contiguously) and one of `ry` row phases; the block covers a chunk of rows.
 __global__ void k_lmm_unc(DevGroup g, int nRows, int rowsPerChunk, const double* __restrict__ Yt, int q, int nCols,
                           double* __restrict__ out) {
+  extern __shared__ double red[];  // [ry][gCols]
+  const int ra = blockIdx.x * rowsPerChunk, rb = min(nRows, ra + rowsPerChunk);
+  const int gc = g.gCols;
+  const int cx = threadIdx.x % gc, ry = threadIdx.x / gc, nry = blockDim.x / gc;
+  for (int i = 0; i < q; i++) {
+    double s = 0;
+    if (ry < nry)
+      for (int r = ra + ry; r < rb; r += nry) s += Yt[(size_t)i * nRows + r] * g.dense[(size_t)r * gc + cx];
+    if (ry < nry) red[ry * gc + cx] = s;
+    __syncthreads();
+    if (ry == 0) {
+      for (int k = 1; k < nry; k++) s += red[k * gc + cx];
+      atomicAdd(&out[(size_t)i * nCols + g.cols[cx]], s);
+    }
+    __syncthreads();
+  }
+}
+
+__global__ void k_lmm_unc_wide(DevGroup g, int nRows, int rowsPerChunk, const double* __restrict__ Yt, int q, int nCols,
+                               double* __restrict__ out) {
   const int ra = blockIdx.x * rowsPerChunk, rb = min(nRows, ra + rowsPerChunk);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nWarps = blockDim.x >> 5;
-  // each warp owns output cells (i, c) round robin; lanes stride over rows
+  // more columns than a block has threads: each warp owns output cells (i, c) round robin; lanes stride over rows
   for (int e = warp; e < q * g.gCols; e += nWarps) {
     const int i = e / g.gCols, c = e - i * g.gCols;
     double s = 0;
@@ -449,8 +470,13 @@ int64_t launch_lmm(Matrix* m, const double* dYt, int q, double* dOut, cudaStream
     m->stats.kernel_launches += 2;
     for (auto& g : m->groups)
       if (g.type == GT_UNC) {
-        const int rpc = std::max(4096, (int)(((int64_t)m->nRows + 4 * m->smCount - 1) / (4 * m->smCount)));
-        k_lmm_unc<<<(m->nRows + rpc - 1) / rpc, 256, 0, s>>>(g, m->nRows, rpc, dYt, q, m->nCols, dOut);
+        const int rpc = std::max(2048, (int)(((int64_t)m->nRows + 8 * m->smCount - 1) / (8 * m->smCount)));
+        if (g.gCols <= 512) {
+          const int threads = std::max(g.gCols, (512 / g.gCols) * g.gCols);  // whole multiples of the column count
+          k_lmm_unc<<<(m->nRows + rpc - 1) / rpc, threads, (size_t)threads * sizeof(double), s>>>(g, m->nRows, rpc, dYt, q,
+                                                                                              m->nCols, dOut);
+        } else
+          k_lmm_unc_wide<<<(m->nRows + rpc - 1) / rpc, 256, 0, s>>>(g, m->nRows, rpc, dYt, q, m->nCols, dOut);
         m->stats.kernel_launches++;
       }
   }

@@ -13,6 +13,7 @@
 //   4. adds constV * V and stores.
 #include "cla_common.cuh"
 #include <algorithm>
+#include <climits>
 
 namespace cla {
 
@@ -165,6 +166,296 @@ k_rmm_dmma(const DevGroup* __restrict__ groups, int nGroups, const DenseCol* __r
   }
 }
 
+// --------------------------------------------------------------------------------------------------
+// Second generation of the same kernel. Differences:
+//  * a CTA owns a block of 1024 rows (the granularity of the skip indexes) and walks it as eight 128-row tiles,
+//    so the decode state of every sparse group survives from tile to tile: one lane per SDC group keeps
+//    (next listed row, its element index, stream position), one lane per RLE group keeps its current run;
+//  * the lanes do not add anything themselves: they push work items {first row, last row, table row} into one
+//    queue per warp (a warp owns 16 rows of the tile), and each warp then applies its own queue to its own rows
+//    with plain read-modify-writes (no atomics on doubles), eight items in flight at a time;
+//  * runs that cover a whole tile go to a base queue that every warp folds into two registers per lane;
+//  * dense-operand columns come from a flat descriptor array (map, dictionary column, V row).
+// Limits: at most 256 SDC and 256 RLE groups (8 warps x 32 lanes); larger inputs use k_rmm_dmma.
+// --------------------------------------------------------------------------------------------------
+struct DenseDesc {
+  const void* map;     // map (dense-map groups) or null
+  const void* mapHi;
+  const double* src;   // dictionary + j, or dense block + j
+  int32_t mapType;     // -1: uncompressed
+  int32_t gCols;
+  int32_t vrow;        // row of V (= matrix column)
+  int32_t pad;
+};
+
+constexpr int Q_CAP = 448;            // items per warp queue
+constexpr int QB_CAP = 512;           // base queue
+constexpr int GM_SUB = SKIP_ROWS / GM_TR;  // tiles per block
+
+struct WorkItem {
+  uint16_t ra, rb;   // rows [ra, rb) of the tile
+  uint32_t prow;     // row of the table arena P
+};
+
+__device__ __forceinline__ void push_item(WorkItem* q, int* qn, int w, int ra, int rb, uint32_t prow, double* Cs,
+                                          const double* __restrict__ P, int vCols, int j0, int vc) {
+  const int slot = atomicAdd(&qn[w], 1);
+  if (slot < Q_CAP) {
+    WorkItem it;
+    it.ra = (uint16_t)ra;
+    it.rb = (uint16_t)rb;
+    it.prow = prow;
+    q[w * Q_CAP + slot] = it;
+  } else {  // queue full: add directly (atomics, since the owning warp may be working on the same rows)
+    const double* p = P + (size_t)prow * vCols + j0;
+    for (int r = ra; r < rb; r++)
+      for (int n = 0; n < vc; n++) atomicAdd(&Cs[r * GM_LDC + n], p[n]);
+  }
+}
+
+__global__ void __launch_bounds__(GM_THREADS, 2)
+k_rmm_dmma2(const DevGroup* __restrict__ groups, const DenseDesc* __restrict__ dd, int nDense,
+            const int32_t* __restrict__ sdcIdx, int nSdc, const int32_t* __restrict__ rleIdx, int nRle, int nRows,
+            const double* __restrict__ V, int vCols, const double* __restrict__ P, const double* __restrict__ constRow,
+            double* __restrict__ out) {
+  extern __shared__ __align__(16) double sm[];
+  double* At = sm;                      // [GM_KC][GM_LDA]
+  double* Bs = sm + GM_KC * GM_LDA;     // [GM_KC][GM_LDB]
+  double* Cs = sm;                      // [GM_TR][GM_LDC] (aliases the stage)
+  WorkItem* q = (WorkItem*)(sm + GM_TR * GM_LDC);      // [8][Q_CAP]
+  uint32_t* qb = (uint32_t*)(q + 8 * Q_CAP);           // [QB_CAP] table rows of tile-covering runs
+  int* qn = (int*)(qb + QB_CAP);                       // [8] queue lengths, [8] = base queue length
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int blk0 = blockIdx.x * SKIP_ROWS;
+  const int j0 = blockIdx.y * GM_TN, vc = min(GM_TN, vCols - j0);
+  const int am = lane >> 2, ak = lane & 3;
+  const bool sparse = (nSdc + nRle) > 0;
+
+  // ---- per-lane decode state for the whole block ----
+  const int sgi = warp * 32 + lane;
+  const bool hasS = sgi < nSdc, hasR = sgi < nRle;
+  int sRow = INT_MAX, sElem = 0;
+  int64_t sPos = 0;
+  int64_t rRun = 0;
+  DevGroup gs, gr;  // copies of this lane's groups (registers / local)
+  if (hasS) {
+    gs = groups[sdcIdx[sgi]];
+    if (gs.nOff > 0) {
+      if (gs.offType == CLA_OFF_BYTE || gs.offType == CLA_OFF_CHAR) {
+        const SdcSkip sk = gs.skip[blockIdx.x];
+        if (sk.elem < gs.nOff) {
+          sRow = sk.row;
+          sElem = sk.elem;
+          sPos = sk.pos;
+        }
+      } else {  // OffsetSingle / OffsetTwo
+        if (gs.first >= blk0) sRow = gs.first;
+        else if (gs.offType == CLA_OFF_TWO && gs.last >= blk0) {
+          sRow = gs.last;
+          sElem = 1;
+        }
+      }
+    }
+  }
+  if (hasR) {
+    gr = groups[rleIdx[sgi]];
+    rRun = gr.runSkip[blockIdx.x];
+  }
+
+  for (int sub = 0; sub < GM_SUB; sub++) {
+    const int r0 = blk0 + sub * GM_TR;
+    if (r0 >= nRows) break;
+    const int r1 = min(nRows, r0 + GM_TR);
+    double c[2][8][2];
+#pragma unroll
+    for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+      for (int nt = 0; nt < 8; nt++) c[mt][nt][0] = c[mt][nt][1] = 0.0;
+
+    for (int k0 = 0; k0 < nDense; k0 += GM_KC) {
+      {  // stage: thread = (row, half of the 32 columns); lanes along rows; eight columns in flight at a time
+        const int r = tid & (GM_TR - 1), kh = tid >> 7;
+        const int row = r0 + r;
+#pragma unroll
+        for (int kb = 0; kb < 16; kb += 8) {
+          double v[8];
+          const double* src[8];
+          size_t off[8];
+#pragma unroll
+          for (int kk = 0; kk < 8; kk++) {
+            const int kc = k0 + kh * 16 + kb + kk;
+            v[kk] = 0.0;
+            src[kk] = nullptr;
+            off[kk] = 0;
+            if (kc < nDense && row < nRows) {
+              const DenseDesc d = dd[kc];
+              src[kk] = d.src;
+              off[kk] = (d.mapType < 0 ? (size_t)row : (size_t)map_get(d.mapType, d.map, d.mapHi, row)) * d.gCols;
+            }
+          }
+#pragma unroll
+          for (int kk = 0; kk < 8; kk++)
+            if (src[kk]) v[kk] = src[kk][off[kk]];
+#pragma unroll
+          for (int kk = 0; kk < 8; kk++) At[(kh * 16 + kb + kk) * GM_LDA + r] = v[kk];
+        }
+        for (int e = tid; e < GM_KC * GM_TN; e += GM_THREADS) {
+          const int kc = e >> 6, n = e & 63;
+          double v = 0.0;
+          if (k0 + kc < nDense && n < vc) v = V[(size_t)dd[k0 + kc].vrow * vCols + j0 + n];
+          Bs[kc * GM_LDB + n] = v;
+        }
+      }
+      __syncthreads();
+#pragma unroll
+      for (int ks = 0; ks < GM_KC; ks += 4) {
+        double a[2];
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++) a[mt] = At[(ks + ak) * GM_LDA + warp * 16 + mt * 8 + am];
+#pragma unroll
+        for (int nt = 0; nt < 8; nt++) {
+          const double b = Bs[(ks + ak) * GM_LDB + nt * 8 + am];
+#pragma unroll
+          for (int mt = 0; mt < 2; mt++) dmma884(c[mt][nt][0], c[mt][nt][1], a[mt], b);
+        }
+      }
+      __syncthreads();
+    }
+
+    if (!sparse) {  // straight from the fragments
+#pragma unroll
+      for (int mt = 0; mt < 2; mt++) {
+        const int row = r0 + warp * 16 + mt * 8 + (lane >> 2);
+        if (row >= r1) continue;
+#pragma unroll
+        for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+          for (int u = 0; u < 2; u++) {
+            const int n = nt * 8 + (lane & 3) * 2 + u;
+            if (n < vc) out[(size_t)row * vCols + j0 + n] = c[mt][nt][u] + (constRow ? constRow[j0 + n] : 0.0);
+          }
+      }
+      continue;
+    }
+#pragma unroll
+    for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+      for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+        for (int u = 0; u < 2; u++)
+          Cs[(warp * 16 + mt * 8 + (lane >> 2)) * GM_LDC + nt * 8 + (lane & 3) * 2 + u] = c[mt][nt][u];
+    if (tid < 9) qn[tid] = 0;
+    __syncthreads();
+
+    // ---- decode: every lane advances its groups through [r0, r1) and queues the work ----
+    if (hasS) {
+      const int maxV = gs.offType == CLA_OFF_BYTE ? 255 : 65535;
+      while (sRow < r1) {
+        if (sRow >= r0) {
+          const int id = gs.single ? 0 : map_get(gs.mapType, gs.map, gs.mapHi, sElem);
+          const int rl = sRow - r0;
+          push_item(q, qn, rl >> 4, rl, rl + 1, (uint32_t)(gs.valOff + id), Cs, P, vCols, j0, vc);
+        }
+        if (sElem + 1 >= gs.nOff) {
+          sRow = INT_MAX;
+          break;
+        }
+        if (gs.offType == CLA_OFF_BYTE) {
+          const uint8_t* dp = (const uint8_t*)gs.offData;
+          int d = dp[sPos++];
+          while (d == 0) {
+            sRow += maxV;
+            d = dp[sPos++];
+          }
+          sRow += d;
+        } else if (gs.offType == CLA_OFF_CHAR) {
+          const uint16_t* dp = (const uint16_t*)gs.offData;
+          int d = dp[sPos++];
+          while (d == 0) {
+            sRow += maxV;
+            d = dp[sPos++];
+          }
+          sRow += d;
+        } else
+          sRow = gs.last;  // OffsetTwo
+        sElem++;
+      }
+    }
+    if (hasR) {
+      while (rRun < gr.nRuns) {
+        const RleRun run = gr.runs[rRun];
+        if (run.start >= r1) break;
+        const int end = run.start + (int)run.len;
+        const int a = max(run.start, r0), b = min(end, r1);
+        if (a < b) {
+          const uint32_t prow = (uint32_t)(gr.valOff + run.k);
+          if (a == r0 && b == r0 + GM_TR) {
+            const int slot = atomicAdd(&qn[8], 1);
+            if (slot < QB_CAP) qb[slot] = prow;
+            else
+              for (int w = 0; w < 8; w++) push_item(q, qn, w, w * 16, w * 16 + 16, prow, Cs, P, vCols, j0, vc);
+          } else {
+            for (int w = (a - r0) >> 4; w <= (b - 1 - r0) >> 4; w++)
+              push_item(q, qn, w, max(a - r0, w * 16), min(b - r0, w * 16 + 16), prow, Cs, P, vCols, j0, vc);
+          }
+        }
+        if (end <= r1) rRun++;
+        else break;
+      }
+    }
+    __syncthreads();
+
+    // ---- apply: warp w owns rows [16 w, 16 w + 16); lane owns columns lane and lane + 32 ----
+    {
+      const bool c0ok = lane < vc, c1ok = lane + 32 < vc;
+      double b0 = (constRow && c0ok) ? constRow[j0 + lane] : 0.0, b1 = (constRow && c1ok) ? constRow[j0 + lane + 32] : 0.0;
+      const int nb = min(qn[8], QB_CAP);
+      for (int i0 = 0; i0 < nb; i0 += 8) {
+        double t0[8], t1[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          const double* p = P + (size_t)qb[min(i0 + i, nb - 1)] * vCols + j0;
+          t0[i] = (i0 + i < nb && c0ok) ? p[lane] : 0.0;
+          t1[i] = (i0 + i < nb && c1ok) ? p[lane + 32] : 0.0;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          b0 += t0[i];
+          b1 += t1[i];
+        }
+      }
+      const int nq = min(qn[warp], Q_CAP);
+      const WorkItem* myq = q + warp * Q_CAP;
+      for (int i0 = 0; i0 < nq; i0 += 8) {
+        double t0[8], t1[8];
+        WorkItem it[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          it[i] = myq[min(i0 + i, nq - 1)];
+          const double* p = P + (size_t)it[i].prow * vCols + j0;
+          t0[i] = (i0 + i < nq && c0ok) ? p[lane] : 0.0;
+          t1[i] = (i0 + i < nq && c1ok) ? p[lane + 32] : 0.0;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          if (i0 + i < nq)
+            for (int r = it[i].ra; r < it[i].rb; r++) {
+              Cs[r * GM_LDC + lane] += t0[i];
+              Cs[r * GM_LDC + lane + 32] += t1[i];
+            }
+        }
+      }
+      __syncwarp();
+      for (int r = warp * 16; r < warp * 16 + 16; r++) {
+        if (r0 + r >= r1) break;
+        if (c0ok) out[(size_t)(r0 + r) * vCols + j0 + lane] = Cs[r * GM_LDC + lane] + b0;
+        if (c1ok) out[(size_t)(r0 + r) * vCols + j0 + lane + 32] = Cs[r * GM_LDC + lane + 32] + b1;
+      }
+    }
+    __syncthreads();  // the stage of the next tile overwrites Cs
+  }
+}
+
 // dictionary pre-aggregation for the groups that are added from tables (SDC, RLE)
 __global__ void k_dict_times_v_sparse(const DevGroup* __restrict__ groups, const double* __restrict__ V, int vCols,
                                       double* __restrict__ P) {
@@ -188,26 +479,50 @@ __global__ void k_const_times_v2(const double* __restrict__ constV, int nCols, c
   constRow[j] = s;
 }
 
-// Builds (once per handle) the list of dense-operand columns.
+// Builds (once per handle) the lists the kernels walk: dense-operand columns, SDC groups, RLE groups.
 static int64_t ensure_dense_cols(Matrix* m) {
-  if (m->dDenseCols || m->denseColsBuilt) return CLA_OK;
+  if (m->denseColsBuilt) return CLA_OK;
   std::vector<DenseCol> dc;
+  std::vector<DenseDesc> dd;
+  std::vector<int32_t> sdc, rle;
   for (int gi = 0; gi < m->nDev; gi++) {
     const DevGroup& g = m->groups[gi];
+    if (g.type == GT_SDC) sdc.push_back(gi);
+    if (g.type == GT_RLE) rle.push_back(gi);
     if (g.type != GT_DDC && g.type != GT_UNC) continue;
     std::vector<int32_t> cols(g.gCols);
     CLA_CUDA(cudaMemcpy(cols.data(), g.cols, cols.size() * 4, cudaMemcpyDeviceToHost));
-    for (int j = 0; j < g.gCols; j++) dc.push_back(DenseCol{gi, j, cols[j], 0});
+    for (int j = 0; j < g.gCols; j++) {
+      dc.push_back(DenseCol{gi, j, cols[j], 0});
+      DenseDesc d;
+      d.map = g.type == GT_UNC ? nullptr : g.map;
+      d.mapHi = g.mapHi;
+      d.src = (g.type == GT_UNC ? g.dense : g.dict) + j;
+      d.mapType = g.type == GT_UNC ? -1 : g.mapType;
+      d.gCols = g.gCols;
+      d.vrow = cols[j];
+      d.pad = 0;
+      dd.push_back(d);
+    }
   }
+  auto up = [&](const void* src, size_t bytes, void** dst) -> int64_t {
+    *dst = nullptr;
+    if (!bytes) return CLA_OK;
+    cudaError_t e = cudaMalloc(dst, bytes);
+    if (e != cudaSuccess) return fail(CLA_ERR_NOMEM, std::string("cudaMalloc column lists: ") + cudaGetErrorString(e));
+    m->allocs.push_back(*dst);
+    CLA_CUDA(cudaMemcpy(*dst, src, bytes, cudaMemcpyHostToDevice));
+    return CLA_OK;
+  };
+  int64_t rc;
+  if ((rc = up(dc.data(), dc.size() * sizeof(DenseCol), &m->dDenseCols)) < 0) return rc;
+  if ((rc = up(dd.data(), dd.size() * sizeof(DenseDesc), &m->dDenseDesc)) < 0) return rc;
+  if ((rc = up(sdc.data(), sdc.size() * 4, &m->dSdcIdx)) < 0) return rc;
+  if ((rc = up(rle.data(), rle.size() * 4, &m->dRleIdx)) < 0) return rc;
   m->nDenseCols = (int)dc.size();
+  m->nSdcGroups = (int)sdc.size();
+  m->nRleGroups = (int)rle.size();
   m->denseColsBuilt = true;
-  if (dc.empty()) return CLA_OK;
-  void* p = nullptr;
-  cudaError_t e = cudaMalloc(&p, dc.size() * sizeof(DenseCol));
-  if (e != cudaSuccess) return fail(CLA_ERR_NOMEM, std::string("cudaMalloc dense column list: ") + cudaGetErrorString(e));
-  m->allocs.push_back(p);
-  CLA_CUDA(cudaMemcpy(p, dc.data(), dc.size() * sizeof(DenseCol), cudaMemcpyHostToDevice));
-  m->dDenseCols = p;
   return CLA_OK;
 }
 
@@ -237,15 +552,24 @@ int64_t launch_rmm_dmma(Matrix* m, const double* dV, int vCols, double* dOut, cu
     m->stats.kernel_launches++;
   }
   const size_t smem = std::max((size_t)(GM_KC * GM_LDA + GM_KC * GM_LDB), (size_t)(GM_TR * GM_LDC + GM_TN)) * sizeof(double);
+  const size_t smem2 = (size_t)GM_TR * GM_LDC * sizeof(double) + 8 * Q_CAP * sizeof(WorkItem) + QB_CAP * 4 + 16 * 4;
   static bool attr = false;
   if (!attr) {
     CLA_CUDA(cudaFuncSetAttribute(k_rmm_dmma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CLA_CUDA(cudaFuncSetAttribute(k_rmm_dmma2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2));
     attr = true;
   }
-  dim3 grid((m->nRows + GM_TR - 1) / GM_TR, (vCols + GM_TN - 1) / GM_TN);
   prof_begin(m, s);
-  k_rmm_dmma<<<grid, GM_THREADS, smem, s>>>(m->dGroups, m->nDev, (const DenseCol*)m->dDenseCols, m->nDenseCols, m->nRows,
-                                           dV, vCols, P, constRow, dOut, hasSparse);
+  if (m->nSdcGroups <= 256 && m->nRleGroups <= 256 && m->totalVals < (1ll << 32)) {
+    dim3 grid((m->nRows + SKIP_ROWS - 1) / SKIP_ROWS, (vCols + GM_TN - 1) / GM_TN);
+    k_rmm_dmma2<<<grid, GM_THREADS, smem2, s>>>(m->dGroups, (const DenseDesc*)m->dDenseDesc, m->nDenseCols,
+                                               (const int32_t*)m->dSdcIdx, m->nSdcGroups, (const int32_t*)m->dRleIdx,
+                                               m->nRleGroups, m->nRows, dV, vCols, P, constRow, dOut);
+  } else {
+    dim3 grid((m->nRows + GM_TR - 1) / GM_TR, (vCols + GM_TN - 1) / GM_TN);
+    k_rmm_dmma<<<grid, GM_THREADS, smem, s>>>(m->dGroups, m->nDev, (const DenseCol*)m->dDenseCols, m->nDenseCols, m->nRows,
+                                             dV, vCols, P, constRow, dOut, hasSparse);
+  }
   prof_end(m, s);
   m->stats.kernel_launches++;
   CLA_CUDA(cudaGetLastError());
