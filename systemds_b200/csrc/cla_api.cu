@@ -402,7 +402,7 @@ int64_t cla_mmchain_dev(cla_handle h, const double* dV, const double* dW, int32_
 // Staging layout in m->io: [inputs ... | output | nnz counter]
 template <class F>
 static int64_t host_call(Matrix* m, const double* in1, size_t n1, const double* in2, size_t n2, double* out, size_t nOut,
-                         F&& run) {
+                         F&& run, bool deferIn1 = false) {
   CLA_CUDA(cudaSetDevice(m->device));
   auto al = [](size_t b) { return (b + 255) & ~(size_t)255; };
   const size_t o1 = 0, o2 = al(n1 * 8), oOut = o2 + al(n2 * 8), oCnt = oOut + al(nOut * 8);
@@ -414,7 +414,7 @@ static int64_t host_call(Matrix* m, const double* in1, size_t n1, const double* 
   double* dOut = (double*)(base + oOut);
   unsigned long long* dCnt = (unsigned long long*)(base + oCnt);
   cudaStream_t s = m->stream;
-  if (n1) CLA_CUDA(cudaMemcpyAsync(d1, in1, n1 * 8, cudaMemcpyHostToDevice, s));
+  if (n1 && !deferIn1) CLA_CUDA(cudaMemcpyAsync(d1, in1, n1 * 8, cudaMemcpyHostToDevice, s));  // deferred: run() uploads it
   if (n2) CLA_CUDA(cudaMemcpyAsync(d2, in2, n2 * 8, cudaMemcpyHostToDevice, s));
   CLA_CUDA(cudaEventRecord(m->ev0, s));
   if ((rc = run(d1, n2 ? d2 : nullptr, dOut, s)) < 0) return rc;
@@ -446,6 +446,18 @@ int64_t cla_lmm(cla_handle h, const double* Yt, int32_t yRows, double* out) {
   REQUIRE_FINAL();
   if (yRows < 0) return fail(CLA_ERR_SHAPE, "lmm: negative row count");
   if ((!Yt && (size_t)yRows * m->nRows) || (!out && (size_t)yRows * m->nCols)) return fail(CLA_ERR_BAD_ARG, "lmm: null buffer");
+  if (yRows == 1)  // one left row: upload it in slices that overlap with the product where the kernel allows
+    return host_call(
+        m, Yt, (size_t)m->nRows, nullptr, 0, out, (size_t)m->nCols,
+        [&](double* dY, double*, double* dOut, cudaStream_t s) -> int64_t {
+          m->stats.calls_lmm++;
+          int64_t rc = fast_lmm_vec_host(m, Yt, dY, dOut, s);
+          if (rc != 0) return rc < 0 ? rc : CLA_OK;
+          m->stats.calls_lmm--;
+          if (m->nRows) CLA_CUDA(cudaMemcpyAsync(dY, Yt, (size_t)m->nRows * 8, cudaMemcpyHostToDevice, s));
+          return lmm_dev(m, dY, 1, dOut, s);
+        },
+        true);
   return host_call(m, Yt, (size_t)yRows * m->nRows, nullptr, 0, out, (size_t)yRows * m->nCols,
                    [&](double* dY, double*, double* dOut, cudaStream_t s) { return lmm_dev(m, dY, yRows, dOut, s); });
 }

@@ -171,6 +171,8 @@ struct Matrix {
   size_t ioBytes = 0;
   int32_t* dErr = nullptr;  // device self-check word
   cudaStream_t stream = nullptr;
+  cudaStream_t copyStream = nullptr;  // uploads overlapped with kernels in the host-buffer left product
+  cudaEvent_t copyDone[4] = {nullptr, nullptr, nullptr, nullptr};
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   FastPlan* fast = nullptr;
   bool profile = false;
@@ -220,6 +222,7 @@ int64_t fast_plan_build(Matrix* m);
 void fast_plan_free(Matrix* m);
 int64_t fast_rmm_vec(Matrix* m, const double* dV, double* dOut, cudaStream_t s);
 int64_t fast_lmm_vec(Matrix* m, const double* dY, double* dOut, cudaStream_t s);
+int64_t fast_lmm_vec_host(Matrix* m, const double* hostY, double* dY, double* dOut, cudaStream_t s);
 int64_t fast_lmm_vec_noalloc(Matrix* m, const double* dY, double* dOut, cudaStream_t s);
 
 }  // namespace cla

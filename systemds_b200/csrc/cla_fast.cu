@@ -19,6 +19,7 @@
 // Tables are staged into shared memory with TMA bulk copies (cp.async.bulk + mbarrier, no multicast).
 #include "cla_common.cuh"
 #include <algorithm>
+#include <cstdlib>
 #include <numeric>
 
 namespace cla {
@@ -274,8 +275,9 @@ __device__ __forceinline__ void lmm_cells(const uint4 (&m)[NP][2][2], int sub, c
 template <int NP, bool HALF>
 __device__ __forceinline__ void lmm_vec_body(const LmmChunk& ch, const uint8_t* __restrict__ imaps, int64_t nRB,
                                              const double* __restrict__ tablesImg, const double* __restrict__ y,
-                                             int nRows, double* __restrict__ partial, unsigned char* smraw,
-                                             uint64_t* mbar, int32_t* err) {
+                                             int nRows, int64_t stepBegin, int64_t stepEnd,
+                                             double* __restrict__ partial, unsigned char* smraw, uint64_t* mbar,
+                                             int32_t* err) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int slot = lane & 15, half = lane >> 4;
   if (!tma_load_to_smem(smraw, tablesImg + ch.tblOff, (uint32_t)ch.tblDoubles * 8u, mbar)) {
@@ -301,8 +303,8 @@ __device__ __forceinline__ void lmm_vec_body(const LmmChunk& ch, const uint8_t* 
 
   // rows of this CTA: contiguous range of 64-row steps
   const int ctaInChunk = blockIdx.x - ch.cta0;
-  const int64_t nSteps = ((int64_t)nRows + LMM_STEP - 1) / LMM_STEP;
-  const int64_t s0 = nSteps * ctaInChunk / ch.nCta, s1 = nSteps * (ctaInChunk + 1) / ch.nCta;
+  const int64_t nSteps = stepEnd - stepBegin;  // this launch covers the 64-row steps [stepBegin, stepEnd)
+  const int64_t s0 = stepBegin + nSteps * ctaInChunk / ch.nCta, s1 = stepBegin + nSteps * (ctaInChunk + 1) / ch.nCta;
   for (int64_t st = s0 + warp; st < s1; st += LMM_W) {
     const int64_t r0 = st * LMM_STEP + half * 32;
     if (st * LMM_STEP + LMM_STEP <= nRows) {
@@ -363,8 +365,8 @@ __device__ __forceinline__ void lmm_vec_body(const LmmChunk& ch, const uint8_t* 
 
 __global__ void __launch_bounds__(LMM_T, 1)
 k_lmm_vec_u8(const LmmChunk* __restrict__ chunks, int nChunks, const uint8_t* __restrict__ imaps, int64_t nRB,
-             const double* __restrict__ tablesImg, const double* __restrict__ y, int nRows,
-             double* __restrict__ partial, int32_t* err) {
+             const double* __restrict__ tablesImg, const double* __restrict__ y, int nRows, int64_t stepBegin,
+             int64_t stepEnd, double* __restrict__ partial, int32_t* err) {
   extern __shared__ __align__(128) unsigned char smraw[];
   __shared__ __align__(8) uint64_t mbar;
   __shared__ LmmChunk ch;
@@ -375,18 +377,18 @@ k_lmm_vec_u8(const LmmChunk* __restrict__ chunks, int nChunks, const uint8_t* __
   }
   __syncthreads();
   switch (ch.nPairs * 2 + (ch.halfLast ? 1 : 0)) {
-    case 2: lmm_vec_body<1, false>(ch, imaps, nRB, tablesImg, y, nRows, partial, smraw, &mbar, err); break;
-    case 3: lmm_vec_body<1, true>(ch, imaps, nRB, tablesImg, y, nRows, partial, smraw, &mbar, err); break;
-    case 4: lmm_vec_body<2, false>(ch, imaps, nRB, tablesImg, y, nRows, partial, smraw, &mbar, err); break;
-    case 5: lmm_vec_body<2, true>(ch, imaps, nRB, tablesImg, y, nRows, partial, smraw, &mbar, err); break;
-    case 6: lmm_vec_body<3, false>(ch, imaps, nRB, tablesImg, y, nRows, partial, smraw, &mbar, err); break;
-    default: lmm_vec_body<3, true>(ch, imaps, nRB, tablesImg, y, nRows, partial, smraw, &mbar, err); break;
+    case 2: lmm_vec_body<1, false>(ch, imaps, nRB, tablesImg, y, nRows, stepBegin, stepEnd, partial, smraw, &mbar, err); break;
+    case 3: lmm_vec_body<1, true>(ch, imaps, nRB, tablesImg, y, nRows, stepBegin, stepEnd, partial, smraw, &mbar, err); break;
+    case 4: lmm_vec_body<2, false>(ch, imaps, nRB, tablesImg, y, nRows, stepBegin, stepEnd, partial, smraw, &mbar, err); break;
+    case 5: lmm_vec_body<2, true>(ch, imaps, nRB, tablesImg, y, nRows, stepBegin, stepEnd, partial, smraw, &mbar, err); break;
+    case 6: lmm_vec_body<3, false>(ch, imaps, nRB, tablesImg, y, nRows, stepBegin, stepEnd, partial, smraw, &mbar, err); break;
+    default: lmm_vec_body<3, true>(ch, imaps, nRB, tablesImg, y, nRows, stepBegin, stepEnd, partial, smraw, &mbar, err); break;
   }
 }
 
 // out[col] += sum over the chunk's CTAs of partial[cta][slot], in CTA order (deterministic per column)
 __global__ void k_lmm_vec_final(const LmmChunk* __restrict__ chunks, int nChunks, const int* __restrict__ slotCol,
-                                const double* __restrict__ partial, double* __restrict__ out) {
+                                const double* __restrict__ partial, double* __restrict__ out, int nParts, int gridPerPart) {
   const int c = blockIdx.x;
   if (c >= nChunks) return;
   const LmmChunk ch = chunks[c];
@@ -394,7 +396,9 @@ __global__ void k_lmm_vec_final(const LmmChunk* __restrict__ chunks, int nChunks
     const int col = slotCol[ch.pair0 * 32 + u];
     if (col < 0) continue;
     double s = 0;
-    for (int b = 0; b < ch.nCta; b++) s += partial[(size_t)(ch.cta0 + b) * (LMM_MAX_PAIRS * 32) + u];
+    for (int part = 0; part < nParts; part++)  // row ranges that were launched separately, in row order
+      for (int b = 0; b < ch.nCta; b++)
+        s += partial[((size_t)part * gridPerPart + ch.cta0 + b) * (LMM_MAX_PAIRS * 32) + u];
     atomicAdd(&out[col], s);
   }
 }
@@ -829,7 +833,11 @@ int64_t fast_rmm_vec(Matrix* m, const double* dV, double* dOut, cudaStream_t s) 
   }
   // rows per thread: the widest map load that still leaves >= 32 resident warps per SM
   const double warpsPerSm16 = (double)m->nRows / (16.0 * 32.0 * m->smCount);
-  const int R = warpsPerSm16 >= 32 ? 16 : (warpsPerSm16 * 2 >= 32 ? 8 : 4);
+  int R = warpsPerSm16 >= 32 ? 16 : (warpsPerSm16 * 2 >= 32 ? 8 : 4);
+  if (const char* e = getenv("CLA_RMM_ROWS_PER_THREAD")) {  // tuning aid
+    const int v = atoi(e);
+    if (v == 4 || v == 8 || v == 16) R = v;
+  }
   const int nTiles = (m->nRows + RMM_T * R - 1) / (RMM_T * R);
   for (size_t c = 0; c < fp->rchunks.size(); c++) {
     const RmmChunk& ch = fp->rchunks[c];
@@ -858,11 +866,12 @@ int64_t fast_lmm_vec(Matrix* m, const double* dY, double* dOut, cudaStream_t s) 
   size_t smem = (size_t)LMM_W * LMM_MAX_PAIRS * 32 * 8;
   for (auto& c : fp->lchunks) smem = std::max(smem, (size_t)c.tblDoubles * 8);
   prof_begin(m, s);
+  const int64_t nSteps = ((int64_t)m->nRows + LMM_STEP - 1) / LMM_STEP;
   k_lmm_vec_u8<<<fp->lmmGrid, LMM_T, smem, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dLmmMaps, fp->nRB, fp->dLmmTables, dY,
-                                               m->nRows, partial, m->dErr);
+                                               m->nRows, 0, nSteps, partial, m->dErr);
   prof_end(m, s);
   k_lmm_vec_final<<<(unsigned)fp->lchunks.size(), 128, 0, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dSlotCol,
-                                                              partial, dOut);
+                                                              partial, dOut, 1, fp->lmmGrid);
   m->stats.kernel_launches += 2;
   if (m->hasConst)
     if ((rc = launch_lmm_const(m, dY, 1, dOut, s)) < 0) return rc;
@@ -870,6 +879,50 @@ int64_t fast_lmm_vec(Matrix* m, const double* dY, double* dOut, cudaStream_t s) 
   return fp->partial ? 2 : 1;
 }
 
+
+// Host-buffer t(y) %*% X with the upload of y overlapped with the product: y is copied in LMM_PIPE row ranges
+// on a second stream, and the kernel for a range starts as soon as its slice has arrived. Returns 0 if the
+// specialised kernel does not cover the matrix (the caller then copies y whole and takes the normal path).
+constexpr int LMM_PIPE = 4;
+int64_t fast_lmm_vec_host(Matrix* m, const double* hostY, double* dY, double* dOut, cudaStream_t s) {
+  FastPlan* fp = m->fast;
+  if (!fp || !fp->ok || fp->partial || ((uintptr_t)dY & 15) || m->nRows < (1 << 20)) return 0;
+  int64_t rc;
+  const size_t partBytes = (size_t)LMM_PIPE * fp->lmmGrid * LMM_MAX_PAIRS * 32 * 8;
+  if ((rc = ensure_scratch(m, partBytes + 256)) < 0) return rc;
+  if (!m->copyStream) {
+    CLA_CUDA(cudaStreamCreateWithFlags(&m->copyStream, cudaStreamNonBlocking));
+    for (int i = 0; i < LMM_PIPE; i++) CLA_CUDA(cudaEventCreateWithFlags(&m->copyDone[i], cudaEventDisableTiming));
+  }
+  double* partial = (double*)m->scratch;
+  CLA_CUDA(cudaMemsetAsync(dOut, 0, sizeof(double) * (size_t)m->nCols, s));
+  size_t smem = (size_t)LMM_W * LMM_MAX_PAIRS * 32 * 8;
+  for (auto& c : fp->lchunks) smem = std::max(smem, (size_t)c.tblDoubles * 8);
+  const int64_t nSteps = ((int64_t)m->nRows + LMM_STEP - 1) / LMM_STEP;
+  // the copy stream must not run ahead of work already queued on s that still reads dY
+  CLA_CUDA(cudaEventRecord(m->ev1, s));
+  CLA_CUDA(cudaStreamWaitEvent(m->copyStream, m->ev1, 0));
+  for (int i = 0; i < LMM_PIPE; i++) {
+    const int64_t sb = nSteps * i / LMM_PIPE, se = nSteps * (i + 1) / LMM_PIPE;
+    const int64_t rb = sb * LMM_STEP, re = std::min<int64_t>(m->nRows, se * LMM_STEP);
+    if (re > rb) CLA_CUDA(cudaMemcpyAsync(dY + rb, hostY + rb, (size_t)(re - rb) * 8, cudaMemcpyHostToDevice, m->copyStream));
+    CLA_CUDA(cudaEventRecord(m->copyDone[i], m->copyStream));
+    CLA_CUDA(cudaStreamWaitEvent(s, m->copyDone[i], 0));
+    if (i == 0) prof_begin(m, s);
+    k_lmm_vec_u8<<<fp->lmmGrid, LMM_T, smem, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dLmmMaps, fp->nRB, fp->dLmmTables,
+                                                 dY, m->nRows, sb, se, partial + (size_t)i * fp->lmmGrid * LMM_MAX_PAIRS * 32,
+                                                 m->dErr);
+    if (i == LMM_PIPE - 1) prof_end(m, s);
+    m->stats.kernel_launches++;
+  }
+  k_lmm_vec_final<<<(unsigned)fp->lchunks.size(), 128, 0, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dSlotCol, partial,
+                                                              dOut, LMM_PIPE, fp->lmmGrid);
+  m->stats.kernel_launches++;
+  if (m->hasConst)
+    if ((rc = launch_lmm_const(m, dY, 1, dOut, s)) < 0) return rc;
+  CLA_CUDA(cudaGetLastError());
+  return 1;
+}
 
 // --------------------------------------------------------------------------------------------------
 // t(y) %*% X without any device allocation.
@@ -919,10 +972,11 @@ int64_t fast_lmm_vec_noalloc(Matrix* m, const double* dY, double* dOut, cudaStre
   CLA_CUDA(cudaMemsetAsync(dOut, 0, sizeof(double) * (size_t)m->nCols, s));
   size_t smem = (size_t)LMM_W * LMM_MAX_PAIRS * 32 * 8;
   for (auto& c : fp->lchunks) smem = std::max(smem, (size_t)c.tblDoubles * 8);
+  const int64_t nSteps = ((int64_t)m->nRows + LMM_STEP - 1) / LMM_STEP;
   k_lmm_vec_u8<<<fp->lmmGrid, LMM_T, smem, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dLmmMaps, fp->nRB, fp->dLmmTables,
-                                               dY, m->nRows, partial, m->dErr);
+                                               dY, m->nRows, 0, nSteps, partial, m->dErr);
   k_lmm_vec_final<<<(unsigned)fp->lchunks.size(), 128, 0, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dSlotCol,
-                                                              partial, dOut);
+                                                              partial, dOut, 1, fp->lmmGrid);
   m->stats.kernel_launches += 2;
   if (m->hasConst)
     if ((rc = launch_lmm_const_with(m, dY, 1, dOut, rowSum, s)) < 0) return rc;

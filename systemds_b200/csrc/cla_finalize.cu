@@ -612,6 +612,13 @@ void release(Matrix* m) {
   m->profEvents.clear();
   if (m->ev0) cudaEventDestroy(m->ev0);
   if (m->ev1) cudaEventDestroy(m->ev1);
+  for (auto& e : m->copyDone)
+    if (e) {
+      cudaEventDestroy(e);
+      e = nullptr;
+    }
+  if (m->copyStream) cudaStreamDestroy(m->copyStream);
+  m->copyStream = nullptr;
   if (m->stream) cudaStreamDestroy(m->stream);
   m->scratch = m->scratch2 = m->io = nullptr;
   m->dErr = nullptr;

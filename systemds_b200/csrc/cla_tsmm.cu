@@ -100,7 +100,8 @@ struct TsmmCol {
 
 // Warp w owns tile rows I1 = w and I2 = NT-1-w of the upper triangle (NT+1 tiles together, for every w), so the
 // B fragment of tile column J serves both rows and every fragment address is the warp's base plus a constant.
-template <bool FUSED>
+// MT: map type shared by every column (CLA_MAP_BYTE for 1-byte, CLA_MAP_CHAR for 2-byte cells), or -2 = mixed.
+template <bool FUSED, int MT>
 __global__ void __launch_bounds__(TT_THREADS, 2)
 k_tsmm_tri(const DevGroup* __restrict__ groups, const int32_t* __restrict__ colSrc, const double* __restrict__ constV,
            const double* __restrict__ X, int rowBegin, int rowEnd, int nCols, double* __restrict__ C) {
@@ -177,11 +178,20 @@ k_tsmm_tri(const DevGroup* __restrict__ groups, const int32_t* __restrict__ colS
           src[b] = nullptr;
           off[b] = 0;
           if (cc < nColsPad && inRange) {
-            const TsmmCol d = cols[cc];
-            v[b] = d.cst;
-            if (d.map) {
+            if (MT == CLA_MAP_BYTE || MT == CLA_MAP_CHAR) {  // every column is a dense-map column of this width
+              const TsmmCol& d = cols[cc];
+              v[b] = d.cst;
               src[b] = d.src;
-              off[b] = (d.mapType < 0 ? (size_t)row : (size_t)map_get(d.mapType, d.map, d.mapHi, row)) * d.gCols;
+              if (src[b])
+                off[b] = (size_t)(MT == CLA_MAP_BYTE ? (int)((const uint8_t*)d.map)[row] : (int)((const uint16_t*)d.map)[row]) *
+                         d.gCols;
+            } else {
+              const TsmmCol d = cols[cc];
+              v[b] = d.cst;
+              if (d.map) {
+                src[b] = d.src;
+                off[b] = (d.mapType < 0 ? (size_t)row : (size_t)map_get(d.mapType, d.map, d.mapHi, row)) * d.gCols;
+              }
             }
           }
         }
@@ -267,16 +277,28 @@ int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s) {
   const size_t triSmem = (size_t)((n + 7) / 8 * 8) * (2 * TT_LD * sizeof(double) + sizeof(TsmmCol));
   static bool attr = false;
   if (!attr) {
-    CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * (2 * TT_LD * 8 + (int)sizeof(TsmmCol))));
-    CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * (2 * TT_LD * 8 + (int)sizeof(TsmmCol))));
+    const int maxSmem = 128 * (2 * TT_LD * 8 + (int)sizeof(TsmmCol));
+    CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri<true, -2>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxSmem));
+    CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri<true, CLA_MAP_BYTE>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxSmem));
+    CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri<true, CLA_MAP_CHAR>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxSmem));
+    CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri<false, -2>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxSmem));
     attr = true;
   }
   if (tri && denseOnly) {  // one launch over all rows, decoding as it goes
     const int64_t nStages = ((int64_t)m->nRows + TT_KT - 1) / TT_KT;
     const int grid = (int)std::min<int64_t>(2 * m->smCount, nStages);
+    // one map width for every column (and every column held by a dense-map group): the specialised decode
+    int mt = -1;
+    for (auto& g : m->groups) {
+      const int w = (g.type != GT_DDC) ? -2
+                    : (g.mapType == CLA_MAP_UBYTE || g.mapType == CLA_MAP_BYTE) ? CLA_MAP_BYTE
+                    : (g.mapType == CLA_MAP_CHAR ? CLA_MAP_CHAR : -2);
+      mt = (mt == -1 || mt == w) ? w : -2;
+    }
+    auto kern = mt == CLA_MAP_BYTE ? k_tsmm_tri<true, CLA_MAP_BYTE> : (mt == CLA_MAP_CHAR ? k_tsmm_tri<true, CLA_MAP_CHAR> : k_tsmm_tri<true, -2>);
     prof_begin(m, s);
-    k_tsmm_tri<true><<<grid, TT_THREADS, triSmem, s>>>(m->dGroups, m->dColSrc, m->hasConst ? m->dConstV : nullptr, nullptr, 0,
-                                                      m->nRows, n, dOut);
+    kern<<<grid, TT_THREADS, triSmem, s>>>(m->dGroups, m->dColSrc, m->hasConst ? m->dConstV : nullptr, nullptr, 0, m->nRows, n,
+                                          dOut);
     prof_end(m, s);
     m->stats.kernel_launches++;
   } else {
@@ -295,7 +317,7 @@ int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s) {
       if (tri) {
         const int64_t nStages = ((int64_t)rows + TT_KT - 1) / TT_KT;
         const int grid = (int)std::min<int64_t>(2 * m->smCount, nStages);
-        k_tsmm_tri<false><<<grid, TT_THREADS, triSmem, s>>>(nullptr, nullptr, nullptr, X, 0, rows, n, dOut);
+        k_tsmm_tri<false, -2><<<grid, TT_THREADS, triSmem, s>>>(nullptr, nullptr, nullptr, X, 0, rows, n, dOut);
       } else {
         int splits = std::max(1, std::min((rows + TS_KT * 8 - 1) / (TS_KT * 8), (4 * m->smCount + nPairs - 1) / nPairs));
         int rowsPerSplit = ((rows + splits - 1) / splits + TS_KT - 1) / TS_KT * TS_KT;
