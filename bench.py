@@ -329,6 +329,20 @@ def bench_extras(L, dev, sptr, peak):
     from systemds_b200.native import check
     P = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
     out = {}
+    # configs[0] with ten times the rows: the steady state of the X %*% v kernel (configs[0] itself is 17 us of HBM time)
+    n = 10_000_000
+    cmb, v = datagen.config1(nRows=n)
+    cmb.to_device(dev.index)
+    h = cmb.handle()
+    vd = torch.from_numpy(v.reshape(-1)).to(dev)
+    od = torch.empty(n, dtype=torch.float64, device=dev)
+    ms = _time_dev(lambda: check(L.cla_rmm_dev(h, P(vd), 100, 1, P(od), sptr)))
+    alg0 = cmb.index_bytes() + n * 8
+    out["rmm_config0_x10"] = {"workload": f"configs[0] shape at {n} rows (100 DDC columns, 16 values, MapToUByte)", "ms": ms,
+                              "rows_per_s": n / (ms * 1e-3), "algorithmic_GBps": alg0 / (ms * 1e-3) / 1e9,
+                              "hbm_frac": alg0 / (ms * 1e-3) / 1e9 / peak}
+    cmb.free()
+    del vd, od
     # configs[2]: mixed groups, X %*% V with 64 columns
     n = 1_000_000
     cmb, V = datagen.config3(nRows=n)
