@@ -81,6 +81,8 @@ int64_t cla_destroy(cla_handle h);
 int64_t cla_finalize(cla_handle h, int32_t device);
 /* Copies the message of the calling thread's last failed call into buf; returns its length. */
 int64_t cla_last_error(char* buf, int64_t cap);
+/* Also reports (as CLA_ERR_DEVICE_CHECK) a self-check that tripped in a kernel of an earlier device-buffer call:
+ * those calls return before their kernels ran. Synchronises the handle's profiling events. */
 int64_t cla_stats_get(cla_handle h, cla_stats* out);
 /* Profiling switch (the analogue of the reference's -stats timers, utils/Statistics.java): when on, every
  * product call brackets its dominant kernel with CUDA events on the launching stream; cla_stats_get
@@ -129,6 +131,14 @@ int64_t cla_lmm(cla_handle h, const double* Yt, int32_t yRows, double* out);
 int64_t cla_tsmm(cla_handle h, double* out);
 int64_t cla_mmchain(cla_handle h, const double* v, const double* w, int32_t ctype, double* out);
 int64_t cla_decompress(cla_handle h, double* out);
+
+/* Sum aggregates on the compressed block, the uak+ / uark+ / uack+ cases of lib/CLALibCompAgg.java
+ * (colgroup/AColGroupCompressed.java:140-205 computeSum / computeRowSums / computeColSums):
+ * CLA_AGG_COL_SUMS -> out[nCols], CLA_AGG_ROW_SUMS -> out[nRows], CLA_AGG_SUM -> out[1]. Host buffer. */
+#define CLA_AGG_COL_SUMS 0
+#define CLA_AGG_ROW_SUMS 1
+#define CLA_AGG_SUM 2
+int64_t cla_unary_agg(cla_handle h, int32_t op, double* out);
 
 /* ---- products, device buffers --------------------------------------------------------------
  * Same semantics; every pointer is a device address on the handle's device, `stream` is a

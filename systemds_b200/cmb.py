@@ -264,6 +264,28 @@ class CLALibMMChain:
         return _wrap(out, nnz)
 
 
+class CLALibCompAgg:
+    """Sum aggregates of ``CLALibCompAgg.aggregateUnary`` (runtime/compress/lib/CLALibCompAgg.java): uack+, uark+, uak+."""
+
+    @staticmethod
+    def colSums(cmb: CompressedMatrixBlock) -> np.ndarray:
+        out = np.empty((1, cmb.clen), np.float64)
+        check(native.lib().cla_unary_agg(cmb.handle(), 0, ptr(out)))
+        return out
+
+    @staticmethod
+    def rowSums(cmb: CompressedMatrixBlock) -> np.ndarray:
+        out = np.empty((cmb.rlen, 1), np.float64)
+        check(native.lib().cla_unary_agg(cmb.handle(), 1, ptr(out)))
+        return out
+
+    @staticmethod
+    def sum(cmb: CompressedMatrixBlock) -> float:
+        out = np.empty(1, np.float64)
+        check(native.lib().cla_unary_agg(cmb.handle(), 2, ptr(out)))
+        return float(out[0])
+
+
 class CLALibDecompress:
     @staticmethod
     def decompress(cmb: CompressedMatrixBlock) -> np.ndarray:

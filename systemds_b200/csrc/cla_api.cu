@@ -2,6 +2,7 @@
 #include "cla_common.cuh"
 #include <cstring>
 #include <memory>
+#include <vector>
 
 namespace cla {
 std::shared_ptr<Matrix> lookup(cla_handle h);
@@ -88,6 +89,8 @@ static int64_t check_map(int mapType, const uint8_t* map, const uint8_t* hi, int
   return CLA_OK;
 }
 
+static int64_t check_errword(Matrix* m);
+
 extern "C" {
 
 cla_handle cla_create(int32_t nRows, int32_t nCols, int32_t overlapping) {
@@ -122,6 +125,10 @@ int64_t cla_stats_get(cla_handle h, cla_stats* out) {
   if (!out) return fail(CLA_ERR_BAD_ARG, "null stats pointer");
   if (m->device >= 0) cudaSetDevice(m->device);
   prof_collect(m);
+  if (m->finalized) {  // device-buffer calls do not synchronise: this is where their kernels' self-checks surface
+    int64_t rc = check_errword(m);
+    if (rc < 0) return rc;
+  }
   *out = m->stats;
   out->n_rows = m->nRows;
   out->n_cols = m->nCols;
@@ -481,6 +488,27 @@ int64_t cla_mmchain(cla_handle h, const double* v, const double* w, int32_t ctyp
                    [&](double* dV, double* dW, double* dOut, cudaStream_t s) {
                      return mmchain_dev(m, dV, dW, ctype, dOut, nullptr, s);
                    });
+}
+
+// Column sums are t(1) %*% X and row sums X %*% 1, so both run on the product kernels.
+int64_t cla_unary_agg(cla_handle h, int32_t op, double* out) {
+  GET_MATRIX(h);
+  REQUIRE_FINAL();
+  if (op < CLA_AGG_COL_SUMS || op > CLA_AGG_SUM) return fail(CLA_ERR_BAD_ARG, "unary aggregate: unknown operation");
+  if (!out) return fail(CLA_ERR_BAD_ARG, "unary aggregate: null buffer");
+  if (op == CLA_AGG_ROW_SUMS) {
+    std::vector<double> ones((size_t)m->nCols, 1.0);
+    return host_call(m, ones.data(), ones.size(), nullptr, 0, out, (size_t)m->nRows,
+                     [&](double* dV, double*, double* dOut, cudaStream_t s) { return rmm_dev(m, dV, m->nCols, 1, dOut, s); });
+  }
+  std::vector<double> ones((size_t)m->nRows, 1.0), cs((size_t)m->nCols, 0.0);
+  int64_t rc = host_call(m, ones.data(), ones.size(), nullptr, 0, op == CLA_AGG_SUM ? cs.data() : out, (size_t)m->nCols,
+                         [&](double* dY, double*, double* dOut, cudaStream_t s) { return lmm_dev(m, dY, 1, dOut, s); });
+  if (rc < 0 || op == CLA_AGG_COL_SUMS) return rc;
+  double total = 0;
+  for (double x : cs) total += x;
+  out[0] = total;
+  return total != 0.0 ? 1 : 0;
 }
 
 int64_t cla_decompress(cla_handle h, double* out) {

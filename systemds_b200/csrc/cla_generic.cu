@@ -203,7 +203,8 @@ int64_t launch_rmm(Matrix* m, const double* dV, int vCols, double* dOut, cudaStr
     if (!rest) return CLA_OK;
   }
   const size_t smem = TILE_ELEMS * sizeof(double) + (size_t)RLE_BATCH * MAX_TR * sizeof(uint16_t);
-  static bool attr = false;
+  static bool attrSet[64] = {};  // per device: function attributes belong to the device's context
+  bool& attr = attrSet[m->device & 63];
   if (!attr) {
     CLA_CUDA(cudaFuncSetAttribute(k_rmm_tile, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attr = true;

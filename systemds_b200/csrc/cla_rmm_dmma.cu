@@ -553,7 +553,8 @@ int64_t launch_rmm_dmma(Matrix* m, const double* dV, int vCols, double* dOut, cu
   }
   const size_t smem = std::max((size_t)(GM_KC * GM_LDA + GM_KC * GM_LDB), (size_t)(GM_TR * GM_LDC + GM_TN)) * sizeof(double);
   const size_t smem2 = (size_t)GM_TR * GM_LDC * sizeof(double) + 8 * Q_CAP * sizeof(WorkItem) + QB_CAP * 4 + 16 * 4;
-  static bool attr = false;
+  static bool attrSet[64] = {};  // per device: function attributes belong to the device's context
+  bool& attr = attrSet[m->device & 63];
   if (!attr) {
     CLA_CUDA(cudaFuncSetAttribute(k_rmm_dmma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     CLA_CUDA(cudaFuncSetAttribute(k_rmm_dmma2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2));

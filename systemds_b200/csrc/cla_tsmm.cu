@@ -220,16 +220,30 @@ k_tsmm_tri(const DevGroup* __restrict__ groups, const int32_t* __restrict__ colS
     if (st + 1 < sb) stage(st + 1, XtAll + (cur ^ 1) * stageDoubles, warp, TT_CONS);
     {
       const double* Xt = XtAll + cur * stageDoubles;
+      // four k-steps at a time: the A fragments of both tile rows stay in registers while the warp walks its tile
+      // columns, so the "does this warp own tile column jr" tests run once per four DMMAs instead of once per DMMA
 #pragma unroll
-      for (int ks = 0; ks < TT_KT; ks += 4) {
-        const double a1 = Xt[a1o + ks], a2 = Xt[a2o + ks];
+      for (int kh = 0; kh < TT_KT; kh += 16) {
+        double a1[4], a2[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          a1[q] = Xt[a1o + kh + 4 * q];
+          a2[q] = Xt[a2o + kh + 4 * q];
+        }
 #pragma unroll
         for (int jr = 0; jr < TT_MAXJ; jr++) {
-          if (jr < len1) {
-            const double b = Xt[bo + ks - jr * 8 * TT_LD];
-            dmma884(c1[jr][0], c1[jr][1], a1, b);
-            if (jr < TT_MAXJ / 2) {
-              if (jr < len2) dmma884(c2[jr][0], c2[jr][1], a2, b);
+          if (jr < TT_MAXJ / 2 && jr < len2) {
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+              const double b = Xt[bo + kh + 4 * q - jr * 8 * TT_LD];
+              dmma884(c1[jr][0], c1[jr][1], a1[q], b);
+              dmma884(c2[jr < TT_MAXJ / 2 ? jr : 0][0], c2[jr < TT_MAXJ / 2 ? jr : 0][1], a2[q], b);
+            }
+          } else if (jr < len1) {
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+              const double b = Xt[bo + kh + 4 * q - jr * 8 * TT_LD];
+              dmma884(c1[jr][0], c1[jr][1], a1[q], b);
             }
           }
         }
@@ -275,7 +289,8 @@ int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s) {
   bool denseOnly = m->colSrcValid;
   for (auto& g : m->groups) denseOnly &= (g.type == GT_DDC || g.type == GT_UNC);
   const size_t triSmem = (size_t)((n + 7) / 8 * 8) * (2 * TT_LD * sizeof(double) + sizeof(TsmmCol));
-  static bool attr = false;
+  static bool attrSet[64] = {};  // per device: function attributes belong to the device's context
+  bool& attr = attrSet[m->device & 63];
   if (!attr) {
     const int maxSmem = 128 * (2 * TT_LD * 8 + (int)sizeof(TsmmCol));
     CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri<true, -2>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxSmem));

@@ -51,6 +51,7 @@ SIGNATURES = {
     "cla_tsmm": [_I64, _P],
     "cla_mmchain": [_I64, _P, _P, _I32, _P],
     "cla_decompress": [_I64, _P],
+    "cla_unary_agg": [_I64, _I32, _P],
     "cla_rmm_dev": [_I64, _P, _I32, _I32, _P, _P],
     "cla_lmm_dev": [_I64, _P, _I32, _P, _P],
     "cla_lmm_vec_noalloc_dev": [_I64, _P, _P, _P],

@@ -265,3 +265,61 @@ def test_mixed_fast_and_general(oracle, nRows):
     V = rng.standard_normal((cmb.clen, 3))
     assert rel_err(CLALibRightMultBy.rightMultByMatrix(cmb, V), om.rmm(V), aX @ np.abs(V) + 1e-300) < TOL
     cmb.free()
+
+
+def test_offset_and_run_edge_cases(oracle):
+    """Listed-row counts 0 / 1 / 2 (OffsetEmpty / Single / Two), byte and char delta streams with continuation
+    zeros, and RLE / OLE runs and gaps across the 65535 boundaries: decode bit-exact, products within tolerance."""
+    from systemds_b200.offset import OFF_BYTE, OFF_CHAR, OFF_EMPTY, OFF_SINGLE, OFF_TWO
+    nRows = 300_000
+    rng = np.random.default_rng(3)
+    d1 = np.array([[1.5], [-2.0]])
+    cases = {
+        "empty": np.array([], int), "single": np.array([123_456]), "two": np.array([5, 299_999]),
+        "byte_cont": np.sort(np.concatenate([np.arange(0, 200_000, 7), [200_000 + 255, 200_000 + 255 * 2, 200_000 + 255 * 5 + 1]])),
+        "char": np.sort(rng.choice(nRows, 300, replace=False)),
+        "char_cont": np.array([0, 10, 65_545, 65_545 + 65_535 * 2, 299_000]),
+    }
+    want_type = {"empty": OFF_EMPTY, "single": OFF_SINGLE, "two": OFF_TWO, "byte_cont": OFF_BYTE, "char": OFF_CHAR,
+                 "char_cont": OFF_CHAR}
+    groups, c = [], 0
+    for name, rows in cases.items():
+        ids = np.full(nRows, -1, np.int32)
+        ids[rows] = rng.integers(0, 2, rows.shape[0])
+        g = cg.sdc_from_row_ids([c], d1, ids, None if c % 2 else [0.25])
+        assert g._indexes.type == want_type[name], name
+        groups.append(g)
+        c += 1
+    # runs: one run of 150000 rows (split at 65535), a gap above 2 * 65535, single-row runs around the boundaries
+    ids = np.full(nRows, -1, np.int32)
+    ids[100:150_100] = 0
+    ids[290_000:290_001] = 1
+    ids[65_534:65_537] = 1
+    for cls in (cg.ColGroupRLE, cg.ColGroupOLE):
+        groups.append(cls.from_row_ids([c], np.array([[0.5], [3.0]]), ids))
+        c += 1
+    cmb = CompressedMatrixBlock(nRows, c, groups).to_device()
+    om = oracle.OracleMatrix(cmb)
+    for gi, g in enumerate(groups):
+        assert np.array_equal(cmb.group_row_ids(gi), g.row_ids(nRows)), f"group {gi}"
+        assert np.array_equal(cmb.group_row_ids(gi), om.group_row_ids(gi))
+        assert np.array_equal(cmb.group_counts(gi), om.group_counts(gi))
+    X = dense_of(cmb)
+    V = rng.standard_normal((c, 9))
+    y = rng.standard_normal((2, nRows))
+    assert rel_err(CLALibRightMultBy.rightMultByMatrix(cmb, V), om.rmm(V), np.abs(X) @ np.abs(V) + 1e-300) < TOL
+    assert rel_err(CLALibRightMultBy.rightMultByMatrix(cmb, V[:, 0]), om.rmm(V[:, 0]), np.abs(X) @ np.abs(V[:, :1]) + 1e-300) < TOL
+    assert rel_err(CLALibLeftMultBy.leftMultByMatrix(cmb, y), om.lmm(y), np.abs(y) @ np.abs(X) + 1e-300) < TOL
+    assert rel_err(CLALibTSMM.leftMultByTransposeSelf(cmb), oracle.dense_tsmm_ld(X), np.abs(X).T @ np.abs(X) + 1e-300) < TOL
+    assert rel_err(CLALibDecompress.decompress(cmb), X) < 1e-14
+    cmb.free()
+
+
+def test_sum_aggregates():
+    from systemds_b200.cmb import CLALibCompAgg
+    cmb = datagen.random_cmb(8, 20000, datagen.KINDS).to_device()
+    X = dense_of(cmb)
+    assert rel_err(CLALibCompAgg.colSums(cmb), X.sum(axis=0, keepdims=True), np.abs(X).sum(axis=0, keepdims=True) + 1e-300) < TOL
+    assert rel_err(CLALibCompAgg.rowSums(cmb), X.sum(axis=1, keepdims=True), np.abs(X).sum(axis=1, keepdims=True) + 1e-300) < TOL
+    assert abs(CLALibCompAgg.sum(cmb) - X.sum()) <= TOL * np.abs(X).sum()
+    cmb.free()
