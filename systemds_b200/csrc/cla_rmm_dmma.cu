@@ -21,6 +21,7 @@ constexpr int GM_TR = 128;     // rows per CTA
 constexpr int GM_TN = 64;      // output columns per CTA
 constexpr int GM_KC = 32;      // dense columns per stage
 constexpr int GM_LDA = 132;    // A^T row stride (doubles), = 4 mod 16: conflict-free fragment loads
+constexpr int GM_LDAR = 36;    // row-major stage stride (second-generation kernel), = 4 mod 16
 constexpr int GM_LDB = 68;     // V tile row stride, = 4 mod 16
 constexpr int GM_LDC = 66;     // C tile row stride
 constexpr int GM_THREADS = 256;
@@ -219,8 +220,8 @@ k_rmm_dmma2(const DevGroup* __restrict__ groups, const DenseDesc* __restrict__ d
             const double* __restrict__ V, int vCols, const double* __restrict__ P, const double* __restrict__ constRow,
             double* __restrict__ out) {
   extern __shared__ __align__(16) double sm[];
-  double* At = sm;                      // [GM_KC][GM_LDA]
-  double* Bs = sm + GM_KC * GM_LDA;     // [GM_KC][GM_LDB]
+  double* As = sm;                      // [GM_TR][GM_LDAR] row-major stage of the dense operand
+  double* Bs = sm + GM_TR * GM_LDAR;    // [GM_KC][GM_LDB]
   double* Cs = sm;                      // [GM_TR][GM_LDC] (aliases the stage)
   WorkItem* q = (WorkItem*)(sm + GM_TR * GM_LDC);      // [8][Q_CAP]
   uint32_t* qb = (uint32_t*)(q + 8 * Q_CAP);           // [QB_CAP] table rows of tile-covering runs
@@ -273,37 +274,39 @@ k_rmm_dmma2(const DevGroup* __restrict__ groups, const DenseDesc* __restrict__ d
       for (int nt = 0; nt < 8; nt++) c[mt][nt][0] = c[mt][nt][1] = 0.0;
 
     for (int k0 = 0; k0 < nDense; k0 += GM_KC) {
-      {  // stage: thread = (row, half of the 32 columns); lanes along rows; eight columns in flight at a time
-        const int r = tid & (GM_TR - 1), kh = tid >> 7;
-        const int row = r0 + r;
+      {  // stage: warp = 16 rows of the tile, lane = one of the 32 dense columns. A dense-map column costs its lane
+         // one 128-bit map load (16 ids) and 16 dictionary reads; an uncompressed column is read row by row, the
+         // warp covering 32 consecutive values of a dense row. A warp-wide store is one row of the stage.
+        const int kc = k0 + lane;
+        const int rbase = warp * 16;
+        double v[16];
 #pragma unroll
-        for (int kb = 0; kb < 16; kb += 8) {
-          double v[8];
-          const double* src[8];
-          size_t off[8];
+        for (int i = 0; i < 16; i++) v[i] = 0.0;
+        if (kc < nDense) {
+          const DenseDesc d = dd[kc];
+          const int row0 = r0 + rbase;
+          if (d.mapType < 0) {
 #pragma unroll
-          for (int kk = 0; kk < 8; kk++) {
-            const int kc = k0 + kh * 16 + kb + kk;
-            v[kk] = 0.0;
-            src[kk] = nullptr;
-            off[kk] = 0;
-            if (kc < nDense && row < nRows) {
-              const DenseDesc d = dd[kc];
-              src[kk] = d.src;
-              off[kk] = (d.mapType < 0 ? (size_t)row : (size_t)map_get(d.mapType, d.map, d.mapHi, row)) * d.gCols;
-            }
+            for (int i = 0; i < 16; i++)
+              if (row0 + i < nRows) v[i] = d.src[(size_t)(row0 + i) * d.gCols];
+          } else if ((d.mapType == CLA_MAP_UBYTE || d.mapType == CLA_MAP_BYTE) && row0 + 16 <= nRows) {
+            const uint4 w = __ldg((const uint4*)((const uint8_t*)d.map + row0));  // row0 is a multiple of 16
+            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int i = 0; i < 16; i++) v[i] = d.src[(size_t)((ww[i >> 2] >> (8 * (i & 3))) & 0xFF) * d.gCols];
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; i++)
+              if (row0 + i < nRows) v[i] = d.src[(size_t)map_get(d.mapType, d.map, d.mapHi, row0 + i) * d.gCols];
           }
-#pragma unroll
-          for (int kk = 0; kk < 8; kk++)
-            if (src[kk]) v[kk] = src[kk][off[kk]];
-#pragma unroll
-          for (int kk = 0; kk < 8; kk++) At[(kh * 16 + kb + kk) * GM_LDA + r] = v[kk];
         }
+#pragma unroll
+        for (int i = 0; i < 16; i++) As[(rbase + i) * GM_LDAR + lane] = v[i];
         for (int e = tid; e < GM_KC * GM_TN; e += GM_THREADS) {
-          const int kc = e >> 6, n = e & 63;
-          double v = 0.0;
-          if (k0 + kc < nDense && n < vc) v = V[(size_t)dd[k0 + kc].vrow * vCols + j0 + n];
-          Bs[kc * GM_LDB + n] = v;
+          const int kk = e >> 6, n = e & 63;
+          double x = 0.0;
+          if (k0 + kk < nDense && n < vc) x = V[(size_t)dd[k0 + kk].vrow * vCols + j0 + n];
+          Bs[kk * GM_LDB + n] = x;
         }
       }
       __syncthreads();
@@ -311,7 +314,7 @@ k_rmm_dmma2(const DevGroup* __restrict__ groups, const DenseDesc* __restrict__ d
       for (int ks = 0; ks < GM_KC; ks += 4) {
         double a[2];
 #pragma unroll
-        for (int mt = 0; mt < 2; mt++) a[mt] = At[(ks + ak) * GM_LDA + warp * 16 + mt * 8 + am];
+        for (int mt = 0; mt < 2; mt++) a[mt] = As[(warp * 16 + mt * 8 + am) * GM_LDAR + ks + ak];
 #pragma unroll
         for (int nt = 0; nt < 8; nt++) {
           const double b = Bs[(ks + ak) * GM_LDB + nt * 8 + am];
