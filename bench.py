@@ -329,6 +329,10 @@ def bench_extras(L, dev, sptr, peak):
     from systemds_b200.native import check
     P = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
     out = {}
+    dm, df = C.c_double(0), C.c_double(0)
+    check(L.cla_measure_fp64_peaks(dev.index, C.byref(dm), C.byref(df)))
+    out["fp64_peaks_measured"] = {"dmma_m8n8k4_TFLOPs": dm.value, "dfma_TFLOPs": df.value,
+                                  "how": "back-to-back independent instructions, 4 CTAs of 256 threads per SM, CUDA events"}
     # configs[0] with ten times the rows: the steady state of the X %*% v kernel (configs[0] itself is 17 us of HBM time)
     n = 10_000_000
     cmb, v = datagen.config1(nRows=n)
@@ -373,8 +377,8 @@ def bench_extras(L, dev, sptr, peak):
     flops = 2.0 * n * 100 * 101 / 2
     out["tsmm_config3"] = {"workload": f"configs[3] at {n} rows: 100 DDC columns, 1000 values, MapToChar, Zipf(1.1)",
                            "ms": ms, "rows_per_s": n / (ms * 1e-3), "algorithmic_TFLOPs": flops / (ms * 1e-3) / 1e12,
-                           "dmma_peak_TFLOPs": 148 * 64 * 2 * 1.965e9 / 1e12,
-                           "note": "peak = 148 SMs x one m8n8k4 DMMA per 4 clocks (ncu: tensor pipe 100 % = that rate) x 1965 MHz"}
+                           "dmma_peak_TFLOPs": dm.value, "dmma_frac": flops / (ms * 1e-3) / 1e12 / dm.value,
+                           "note": "peak = measured back-to-back DMMA rate (fp64_peaks_measured)"}
     cmb.free()
     # configs[4]: lmCG step w = t(X) (X v) + 1e-3 v on one shard
     n = 2_000_000

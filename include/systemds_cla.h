@@ -88,6 +88,9 @@ int64_t cla_stats_get(cla_handle h, cla_stats* out);
  * product call brackets its dominant kernel with CUDA events on the launching stream; cla_stats_get
  * synchronises those events and adds them to main_kernel_ms / main_kernel_count. */
 int64_t cla_set_profile(cla_handle h, int32_t on);
+/* Diagnostics: sustained TFLOP/s of back-to-back FP64 tensor-core instructions (DMMA m8n8k4) and of FP64 FMA on
+ * `device`, the denominators of the tensor-pipe and FMA fractions reported for the kernels. About 0.1 s. */
+int64_t cla_measure_fp64_peaks(int32_t device, double* dmmaTflops, double* dfmaTflops);
 
 /* ---- group registration (host arrays are copied) -------------------------------------------
  * Each returns the index of the new group (>= 0) or a CLA_ERR_* code.

@@ -5,6 +5,7 @@
 #include <vector>
 
 namespace cla {
+int64_t measure_fp64_peaks(int device, double* dmmaTflops, double* dfmaTflops);
 std::shared_ptr<Matrix> lookup(cla_handle h);
 cla_handle table_insert(std::shared_ptr<Matrix> m);
 bool table_erase(cla_handle h, std::shared_ptr<Matrix>* out);
@@ -134,6 +135,11 @@ int64_t cla_stats_get(cla_handle h, cla_stats* out) {
   out->n_cols = m->nCols;
   out->n_groups = (int64_t)m->hg.size();
   return CLA_OK;
+}
+
+int64_t cla_measure_fp64_peaks(int32_t device, double* dmmaTflops, double* dfmaTflops) {
+  if (!dmmaTflops || !dfmaTflops) return fail(CLA_ERR_BAD_ARG, "null output");
+  return measure_fp64_peaks(device, dmmaTflops, dfmaTflops);
 }
 
 int64_t cla_set_profile(cla_handle h, int32_t on) {

@@ -279,6 +279,72 @@ __global__ void k_mirror(double* __restrict__ C, int n) {
   }
 }
 
+// --------------------------------------------------------------------------------------------------
+// FP64 peak probes: the denominators for the tensor-pipe and FMA-pipe fractions quoted for the kernels above.
+// --------------------------------------------------------------------------------------------------
+__global__ void k_peak_dmma(int iters, double* sink) {
+  double c[8][2];
+#pragma unroll
+  for (int i = 0; i < 8; i++) c[i][0] = c[i][1] = 0.0;
+  const double a = 1.0 + threadIdx.x * 1e-9, b = 1.0 - threadIdx.x * 1e-9;
+  for (int it = 0; it < iters; it++) {
+#pragma unroll
+    for (int i = 0; i < 8; i++) dmma884(c[i][0], c[i][1], a, b);
+  }
+  double s = 0;
+#pragma unroll
+  for (int i = 0; i < 8; i++) s += c[i][0] + c[i][1];
+  if (s == 12345.678) sink[0] = s;  // keeps the loop alive
+}
+__global__ void k_peak_dfma(int iters, double* sink) {
+  double c[16];
+#pragma unroll
+  for (int i = 0; i < 16; i++) c[i] = threadIdx.x * 1e-3 + i;
+  const double a = 1.0000001, b = 1e-9;
+  for (int it = 0; it < iters; it++) {
+#pragma unroll
+    for (int i = 0; i < 16; i++) c[i] = fma(c[i], a, b);
+  }
+  double s = 0;
+#pragma unroll
+  for (int i = 0; i < 16; i++) s += c[i];
+  if (s == 12345.678) sink[0] = s;
+}
+
+// TFLOP/s of back-to-back DMMA m8n8k4 (512 flop per warp instruction) and of FP64 FMA, on `device`.
+int64_t measure_fp64_peaks(int device, double* dmmaTflops, double* dfmaTflops) {
+  CLA_CUDA(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  CLA_CUDA(cudaGetDeviceProperties(&prop, device));
+  double* sink = nullptr;
+  CLA_CUDA(cudaMalloc(&sink, 8));
+  cudaEvent_t e0, e1;
+  CLA_CUDA(cudaEventCreate(&e0));
+  CLA_CUDA(cudaEventCreate(&e1));
+  const int blocks = prop.multiProcessorCount * 4, threads = 256, iters = 20000;
+  float ms = 0;
+  for (int pass = 0; pass < 2; pass++) {  // first pass warms up
+    CLA_CUDA(cudaEventRecord(e0));
+    k_peak_dmma<<<blocks, threads>>>(iters, sink);
+    CLA_CUDA(cudaEventRecord(e1));
+    CLA_CUDA(cudaEventSynchronize(e1));
+    CLA_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+  }
+  *dmmaTflops = (double)blocks * (threads / 32) * iters * 8.0 * 512.0 / (ms * 1e-3) / 1e12;
+  for (int pass = 0; pass < 2; pass++) {
+    CLA_CUDA(cudaEventRecord(e0));
+    k_peak_dfma<<<blocks, threads>>>(iters, sink);
+    CLA_CUDA(cudaEventRecord(e1));
+    CLA_CUDA(cudaEventSynchronize(e1));
+    CLA_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+  }
+  *dfmaTflops = (double)blocks * threads * iters * 16.0 * 2.0 / (ms * 1e-3) / 1e12;
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  cudaFree(sink);
+  return CLA_OK;
+}
+
 int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s) {
   const int n = m->nCols;
   if (n == 0) return CLA_OK;

@@ -39,6 +39,7 @@ SIGNATURES = {
     "cla_last_error": [C.c_char_p, _I64],
     "cla_stats_get": [_I64, C.POINTER(cla_stats)],
     "cla_set_profile": [_I64, _I32],
+    "cla_measure_fp64_peaks": [_I32, _P, _P],
     "cla_add_group_ddc": [_I64, _P, _I32, _P, _I32, _I32, _P, _P, _I64],
     "cla_add_group_sdc": [_I64, _P, _I32, _P, _I32, _P, _I32, _I32, _I32, _P, _I64, _I64, _I32, _P, _P],
     "cla_add_group_rle": [_I64, _P, _I32, _P, _I32, _P, _P, _I64],

@@ -15,7 +15,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def header_functions():
     txt = open(os.path.join(ROOT, "include", "systemds_cla.h")).read()
     txt = re.sub(r"/\*.*?\*/", "", txt, flags=re.S)
-    return sorted(set(re.findall(r"\b(cla_[a-z_]+)\s*\(", txt)))
+    return sorted(set(re.findall(r"\b(cla_[a-z0-9_]+)\s*\(", txt)))
 
 
 def test_exports_every_declared_symbol():
