@@ -144,9 +144,17 @@ class OracleMatrix:
         self.k = int(threads) if threads else int(L.ocl_max_threads())
         self.h = L.ocl_create(cmb.rlen, cmb.clen)
         self.nvals = []
+        self.reg_index = []
+        n_native = 0
         for g in cmb.getColGroups():
             cols, gc = _p(g._colIndexes), g.getNumCols()
             self.nvals.append(g.getNumValues())
+            self.reg_index.append(n_native)
+            n_native += 1
+            if hasattr(g, "_reference"):  # frame-of-reference group: extractCommon -> plain group + constant tuple
+                L.ocl_add_const(self.h, cols, gc, _p(g._reference))
+                n_native += 1
+                self.reg_index[-1] = n_native - 1
             if isinstance(g, cg.ColGroupDDC):
                 m = g._data
                 L.ocl_add_ddc(self.h, cols, gc, _p(g._dict), g.getNumValues(), m.type, _p(m.data), _p(m.data2), m.size)
@@ -178,12 +186,12 @@ class OracleMatrix:
 
     def group_row_ids(self, g):
         ids = np.zeros(self.nRows, np.int32)
-        lib().ocl_group_row_ids(self.h, g, _p(ids))
+        lib().ocl_group_row_ids(self.h, self.reg_index[g], _p(ids))
         return ids
 
     def group_counts(self, g):
         c = np.zeros(max(self.nvals[g], 1), np.int64)
-        lib().ocl_group_counts(self.h, g, _p(c))
+        lib().ocl_group_counts(self.h, self.reg_index[g], _p(c))
         return c[: self.nvals[g]]
 
     def decompress(self):

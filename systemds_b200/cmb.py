@@ -19,8 +19,8 @@ import ctypes as C
 import numpy as np
 
 from . import native
-from .colgroup import (AColGroup, ASDC, AColGroupOffset, ColGroupConst, ColGroupDDC, ColGroupEmpty, ColGroupOLE,
-                       ColGroupRLE, ColGroupUncompressed)
+from .colgroup import (AColGroup, ASDC, AColGroupOffset, ColGroupConst, ColGroupDDC, ColGroupDDCFOR, ColGroupEmpty,
+                       ColGroupOLE, ColGroupRLE, ColGroupSDCFOR, ColGroupUncompressed)
 from .native import check, ptr
 
 CHAIN_XtXv, CHAIN_XtwXv = 0, 1
@@ -72,8 +72,16 @@ class CompressedMatrixBlock:
         L = native.lib()
         h = check(L.cla_create(self.rlen, self.clen, int(self.overlappingColGroups)))
         try:
+            self._reg_index = []  # native group index of every column group (FOR groups register a second, constant one)
+            n_native = 0
             for g in self._colGroups:
+                self._reg_index.append(n_native)
                 self._add(L, h, g)
+                n_native += 1
+                if isinstance(g, (ColGroupDDCFOR, ColGroupSDCFOR)):
+                    # IFrameOfReferenceGroup.extractCommon (CLALibUtils.java:196-197): the reference becomes constV
+                    check(L.cla_add_group_const(h, ptr(g._colIndexes), g.getNumCols(), ptr(g._reference)))
+                    n_native += 1
             check(L.cla_finalize(h, int(device)))
         except Exception:
             L.cla_destroy(h)
@@ -158,12 +166,12 @@ class CompressedMatrixBlock:
     # --- decoded index structures --------------------------------------------------------------
     def group_row_ids(self, g: int) -> np.ndarray:
         ids = np.empty(self.rlen, np.int32)
-        check(native.lib().cla_group_decode(self.handle(), g, ptr(ids)))
+        check(native.lib().cla_group_decode(self.handle(), self._reg_index[g], ptr(ids)))
         return ids
 
     def group_counts(self, g: int) -> np.ndarray:
         counts = np.zeros(max(self._colGroups[g].getNumValues(), 1), np.int64)
-        check(native.lib().cla_group_counts(self.handle(), g, ptr(counts)))
+        check(native.lib().cla_group_counts(self.handle(), self._reg_index[g], ptr(counts)))
         return counts[: self._colGroups[g].getNumValues()]
 
 

@@ -79,6 +79,17 @@ class ColGroupDDC(ADictBasedColGroup):
         return self._data.nbytes() + self._dict.nbytes
 
 
+class ColGroupDDCFOR(ColGroupDDC):
+    """Frame-of-reference DDC: value = dict[id] + reference (ColGroupDDCFOR.java:62-75). For the products it is
+    ``ColGroupDDC(dict) + 1 * reference^T``: ``extractCommon`` (:385-389) moves the reference into constV."""
+
+    def __init__(self, colIndexes, dict_, reference, data: AMapToData):
+        super().__init__(colIndexes, dict_, data)
+        self._reference = np.ascontiguousarray(np.asarray(reference, dtype=np.float64).reshape(-1))
+        if self._reference.shape[0] != self.getNumCols():
+            raise ValueError("reference tuple must have one value per column")
+
+
 class ASDC(ADictBasedColGroup):
     """Common state of the four SDC variants (ASDC.java:42-52, ASDCZero.java)."""
 
@@ -115,6 +126,15 @@ class ColGroupSDC(ASDC):
         if not np.any(dt != 0):
             return ColGroupSDCZeros(colIndexes, numRows, dict_, indexes, data)
         return ColGroupSDC(colIndexes, numRows, dict_, dt, indexes, data)
+
+
+class ColGroupSDCFOR(ASDC):
+    """Frame-of-reference SDC: listed rows hold dict[id] + reference, all other rows the reference
+    (ColGroupSDCFOR.java:80-87,162-163); = ``ColGroupSDCZeros(dict) + 1 * reference^T`` for the products."""
+
+    def __init__(self, colIndexes, numRows, dict_, indexes, data, reference):
+        super().__init__(colIndexes, numRows, dict_, indexes, data, None)
+        self._reference = np.ascontiguousarray(np.asarray(reference, dtype=np.float64).reshape(-1))
 
 
 class ColGroupSDCZeros(ASDC):

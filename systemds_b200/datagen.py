@@ -10,8 +10,8 @@ from __future__ import annotations
 
 import numpy as np
 
-from .colgroup import (ColGroupConst, ColGroupDDC, ColGroupEmpty, ColGroupOLE, ColGroupRLE, ColGroupSDC,
-                       ColGroupUncompressed, sdc_from_row_ids)
+from .colgroup import (ColGroupConst, ColGroupDDC, ColGroupDDCFOR, ColGroupEmpty, ColGroupOLE, ColGroupRLE, ColGroupSDC,
+                       ColGroupSDCFOR, ColGroupUncompressed, sdc_from_row_ids)
 from .cmb import CompressedMatrixBlock
 from .mapping import MapToFactory
 
@@ -175,6 +175,15 @@ def random_group(kind, cols, nRows, rng, integer=False):
     if kind in ("ddc", "ddc2"):
         card = int(rng.integers(3, 60))
         return ColGroupDDC(cols, dict_(card), MapToFactory.create_from(rng.integers(0, card, nRows), card))
+    if kind == "ddcfor":
+        card = int(rng.integers(3, 40))
+        return ColGroupDDCFOR(cols, dict_(card), rng.standard_normal(gc), MapToFactory.create_from(rng.integers(0, card, nRows), card))
+    if kind == "sdcfor":
+        base = random_group("sdcz", cols, nRows, rng, integer)
+        if base._data is None:  # one tuple only: give it a map so the FOR class (which always has one) applies
+            base = random_group("ddcfor", cols, nRows, rng, integer)
+            return base
+        return ColGroupSDCFOR(cols, nRows, base._dict, base._indexes, base._data, rng.standard_normal(gc))
     if kind == "ddc_bit":
         return ColGroupDDC(cols, dict_(2), MapToFactory.create_from(rng.integers(0, 2, nRows), 2))
     if kind == "ddc_char":

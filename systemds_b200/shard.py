@@ -32,11 +32,17 @@ def slice_group(g, rl: int, ru: int, nRows: int):
     cols = g.getColIndices()
     if isinstance(g, cg.ColGroupDDC):
         ids = g._data.decode()[rl:ru]
-        return cg.ColGroupDDC(cols, g._dict, MapToFactory.create_from(ids, g._data.unique, force_type=g._data.type))
+        m = MapToFactory.create_from(ids, g._data.unique, force_type=g._data.type)
+        if isinstance(g, cg.ColGroupDDCFOR):
+            return cg.ColGroupDDCFOR(cols, g._dict, g._reference, m)
+        return cg.ColGroupDDC(cols, g._dict, m)
     if isinstance(g, cg.ASDC):
         rows = g._indexes.decode()
         sel = (rows >= rl) & (rows < ru)
         off = OffsetFactory.createOffset(rows[sel] - rl)
+        if isinstance(g, cg.ColGroupSDCFOR):
+            m = MapToFactory.create_from(g._data.decode()[sel], g._data.unique, force_type=g._data.type)
+            return cg.ColGroupSDCFOR(cols, n, g._dict, off, m, g._reference)
         if g._data is None:
             if g._defaultTuple is None:
                 return cg.ColGroupSDCSingleZeros(cols, n, g._dict, off)

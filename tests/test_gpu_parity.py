@@ -13,6 +13,7 @@ pytestmark = pytest.mark.gpu
 
 CASES = [
     ("all", datagen.KINDS, False),
+    ("for", ("ddcfor", "sdcfor", "ddc", "sdcfor", "rle", "ddcfor"), False),
     ("ddc_only", ("ddc", "ddc", "ddc2", "ddc_bit", "ddc_char"), False),
     ("ddc_u8", ("ddc", "ddc", "ddc2", "ddc_bit", "const"), False),
     ("sparse", ("sdc", "sdcz", "sdcs", "sdcsz", "const", "empty"), False),

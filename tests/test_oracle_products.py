@@ -11,6 +11,7 @@ from tests.util import TOL, dense_of, rel_err
 
 CASES = [
     ("all", datagen.KINDS, False),
+    ("for", ("ddcfor", "sdcfor", "ddc", "sdcfor", "rle", "ddcfor"), False),
     ("ddc_only", ("ddc", "ddc", "ddc2", "ddc_bit", "ddc_char"), False),
     ("sparse", ("sdc", "sdcz", "sdcs", "sdcsz", "const", "empty"), False),
     ("runs", ("rle", "rle", "ole", "ddc"), False),

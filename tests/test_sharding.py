@@ -19,7 +19,7 @@ def test_shard_bounds():
 
 @pytest.mark.parametrize("nShards", [2, 3])
 def test_slices_decompress_to_the_right_rows(oracle, nShards):
-    cmb = datagen.random_cmb(21, 70001, datagen.KINDS)
+    cmb = datagen.random_cmb(21, 70001, datagen.KINDS + ("ddcfor", "sdcfor"))
     X = dense_of(cmb)
     for (a, b), s in zip(shard.shard_bounds(cmb.rlen, nShards), shard.shard(cmb, nShards)):
         assert s.rlen == b - a

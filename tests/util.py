@@ -23,6 +23,8 @@ def dense_of(cmb) -> np.ndarray:
                 default = np.zeros(len(cols))
             vals = np.where((ids >= 0)[:, None], d[np.maximum(ids, 0)], default[None, :])
             X[:, cols] += vals
+            if hasattr(g, "_reference"):
+                X[:, cols] += g._reference
     return X
 
 
