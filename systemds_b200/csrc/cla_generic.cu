@@ -15,6 +15,7 @@
 //        4. k_lmm_const    : out += rowSums(Yt) (x) constV  (lib/CLALibLeftMultBy.java:530-629)
 #include "cla_common.cuh"
 #include <algorithm>
+#include <climits>
 
 namespace cla {
 
@@ -173,6 +174,150 @@ k_rmm_tile(const DevGroup* __restrict__ groups, int nGroups, int nRows, const do
   }
 }
 
+// --------------------------------------------------------------------------------------------------
+// X %*% v (one column) for every group type. A CTA owns one 1024-row block (the granularity of the skip
+// indexes) and keeps its 1024 partial sums in shared memory.
+//  * dense-map groups: a thread per row adds P_g[id];
+//  * uncompressed groups: a warp per row, lanes along the dense row, shuffle reduction;
+//  * SDC groups: one lane per group walks that group's delta stream through the block (32 groups per warp in
+//    parallel instead of one after the other) and adds P_g[id] to the listed rows;
+//  * RLE groups: one lane per group; a run [a, b) with value k is recorded as +P[k] at a and -P[k] at b in a
+//    difference array, and one prefix sum over the block's rows turns all runs into per-row sums.
+// --------------------------------------------------------------------------------------------------
+constexpr int RV_THREADS = 256;
+__global__ void __launch_bounds__(RV_THREADS)
+k_rmm_vec_general(const DevGroup* __restrict__ groups, int nGroups, int nRows, const double* __restrict__ P,
+                  const double* __restrict__ v, const double* __restrict__ constRow, double* __restrict__ out,
+                  int afterFast) {
+  __shared__ double acc[SKIP_ROWS];
+  __shared__ double dif[SKIP_ROWS + 1];
+  __shared__ double wsum[RV_THREADS / 32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int r0 = blockIdx.x * SKIP_ROWS, r1 = min(nRows, r0 + SKIP_ROWS);
+  for (int i = tid; i < SKIP_ROWS; i += RV_THREADS) {
+    acc[i] = 0.0;
+    dif[i] = 0.0;
+  }
+  __syncthreads();
+  bool anyRle = false, anyUnc = false;
+  // dense-map groups: a thread owns rows tid, tid + 256, ... of the block
+  for (int gi = 0; gi < nGroups; gi++) {
+    const DevGroup& g = groups[gi];
+    if (afterFast && g.inFast) continue;
+    if (g.type == GT_DDC) {
+      const double* Pg = P + g.valOff;
+      for (int r = r0 + tid; r < r1; r += RV_THREADS) acc[r - r0] += Pg[map_get(g.mapType, g.map, g.mapHi, r)];
+    } else if (g.type == GT_UNC)
+      anyUnc = true;
+    else if (g.type == GT_RLE)
+      anyRle = true;
+  }
+  __syncthreads();
+  // uncompressed groups: a warp owns rows warp, warp + 8, ...
+  if (anyUnc) {
+    for (int gi = 0; gi < nGroups; gi++) {
+      const DevGroup& g = groups[gi];
+      if (g.type != GT_UNC) continue;
+      for (int r = r0 + warp; r < r1; r += RV_THREADS / 32) {
+        double s = 0;
+        for (int c = lane; c < g.gCols; c += 32) s += g.dense[(size_t)r * g.gCols + c] * v[g.cols[c]];
+        for (int d = 16; d; d >>= 1) s += __shfl_down_sync(0xffffffffu, s, d);
+        if (lane == 0) acc[r - r0] += s;
+      }
+    }
+    __syncthreads();
+  }
+  // sparse groups: thread t takes groups t, t + 256, ...
+  for (int gi = tid; gi < nGroups; gi += RV_THREADS) {
+    const DevGroup& g = groups[gi];
+    if (g.type == GT_SDC && g.nOff > 0) {
+      const double* Pg = P + g.valOff;
+      int row, elem;
+      int64_t pos;
+      if (g.offType == CLA_OFF_BYTE || g.offType == CLA_OFF_CHAR) {
+        const SdcSkip sk = g.skip[blockIdx.x];
+        row = sk.row;
+        elem = sk.elem;
+        pos = sk.pos;
+        if (elem >= g.nOff) row = INT_MAX;
+      } else {
+        row = g.first >= r0 ? g.first : ((g.offType == CLA_OFF_TWO && g.last >= r0) ? g.last : INT_MAX);
+        elem = (row == g.first) ? 0 : 1;
+        pos = 0;
+      }
+      const int maxV = g.offType == CLA_OFF_BYTE ? 255 : 65535;
+      while (row < r1) {
+        const int id = g.single ? 0 : map_get(g.mapType, g.map, g.mapHi, elem);
+        atomicAdd(&acc[row - r0], Pg[id]);
+        if (elem + 1 >= g.nOff) break;
+        if (g.offType == CLA_OFF_BYTE) {
+          const uint8_t* dp = (const uint8_t*)g.offData;
+          int d = dp[pos++];
+          while (d == 0) {
+            row += maxV;
+            d = dp[pos++];
+          }
+          row += d;
+        } else if (g.offType == CLA_OFF_CHAR) {
+          const uint16_t* dp = (const uint16_t*)g.offData;
+          int d = dp[pos++];
+          while (d == 0) {
+            row += maxV;
+            d = dp[pos++];
+          }
+          row += d;
+        } else
+          row = g.last;
+        elem++;
+      }
+    } else if (g.type == GT_RLE) {
+      const double* Pg = P + g.valOff;
+      for (int64_t ri = g.runSkip[blockIdx.x]; ri < g.nRuns; ri++) {
+        const RleRun run = g.runs[ri];
+        if (run.start >= r1) break;
+        const int a = max(run.start, r0), b = min(run.start + (int)run.len, r1);
+        if (a < b) {
+          const double p = Pg[run.k];
+          atomicAdd(&dif[a - r0], p);
+          atomicAdd(&dif[b - r0], -p);  // b - r0 may be 1024: the extra slot
+        }
+      }
+    }
+  }
+  __syncthreads();
+  // prefix sum of the difference array (4 consecutive rows per thread, then the warps' totals)
+  double run4[4] = {0, 0, 0, 0};
+  if (anyRle) {
+    double t = 0;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      t += dif[tid * 4 + i];
+      run4[i] = t;
+    }
+    double incl = t;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const double o = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += o;
+    }
+    if (lane == 31) wsum[warp] = incl;
+    __syncthreads();
+    double base = incl - t;
+    for (int w = 0; w < warp; w++) base += wsum[w];
+#pragma unroll
+    for (int i = 0; i < 4; i++) run4[i] += base;
+  }
+  const double c0 = (constRow != nullptr && !afterFast) ? constRow[0] : 0.0;
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int r = r0 + tid * 4 + i;
+    if (r < r1) {
+      const double val = acc[tid * 4 + i] + run4[i] + c0;
+      out[r] = afterFast ? out[r] + val : val;
+    }
+  }
+}
+
 int64_t launch_rmm(Matrix* m, const double* dV, int vCols, double* dOut, cudaStream_t s, bool afterFast) {
   if (m->nRows == 0 || vCols == 0) return CLA_OK;
   int64_t rc;
@@ -192,6 +337,20 @@ int64_t launch_rmm(Matrix* m, const double* dV, int vCols, double* dOut, cudaStr
     constRow = (double*)((char*)m->scratch + cOff);
     k_const_times_v<<<(vCols + 127) / 128, 128, 0, s>>>(m->dConstV, m->nCols, dV, vCols, constRow);
     m->stats.kernel_launches++;
+  }
+  if (vCols == 1) {  // one column: the block kernel with lane-per-group sparse decode
+    if (afterFast) {
+      bool rest = false;
+      for (auto& g : m->groups) rest |= !g.inFast;
+      if (!rest) return CLA_OK;
+    }
+    prof_begin(m, s);
+    k_rmm_vec_general<<<(m->nRows + SKIP_ROWS - 1) / SKIP_ROWS, RV_THREADS, 0, s>>>(m->dGroups, m->nDev, m->nRows, P, dV,
+                                                                                 constRow, dOut, afterFast ? 1 : 0);
+    prof_end(m, s);
+    m->stats.kernel_launches++;
+    CLA_CUDA(cudaGetLastError());
+    return CLA_OK;
   }
   const int vcTile = std::min(vCols, 64);
   int TR = std::min(MAX_TR, std::max(32, TILE_ELEMS / vcTile));
