@@ -191,11 +191,17 @@ struct DenseDesc {
 
 constexpr int Q_CAP = 448;            // items per warp queue
 constexpr int QB_CAP = 512;           // base queue
+constexpr int QD_CAP = 32;            // per-warp queue of run boundaries
 constexpr int GM_SUB = SKIP_ROWS / GM_TR;  // tiles per block
 
 struct WorkItem {
   uint16_t ra, rb;   // rows [ra, rb) of the tile
   uint32_t prow;     // row of the table arena P
+};
+struct DeltaItem {   // "from tile row `row` on, the table row changes by +/- P[prow]" (RLE run boundaries)
+  int16_t row;
+  int16_t sign;
+  uint32_t prow;
 };
 
 __device__ __forceinline__ void push_item(WorkItem* q, int* qn, int w, int ra, int rb, uint32_t prow, double* Cs,
@@ -225,7 +231,10 @@ k_rmm_dmma2(const DevGroup* __restrict__ groups, const DenseDesc* __restrict__ d
   double* Cs = sm;                      // [GM_TR][GM_LDC] (aliases the stage)
   WorkItem* q = (WorkItem*)(sm + GM_TR * GM_LDC);      // [8][Q_CAP]
   uint32_t* qb = (uint32_t*)(q + 8 * Q_CAP);           // [QB_CAP] table rows of tile-covering runs
-  int* qn = (int*)(qb + QB_CAP);                       // [8] queue lengths, [8] = base queue length
+  DeltaItem* qd = (DeltaItem*)(qb + QB_CAP);           // [8][QD_CAP] run boundaries per warp
+  int* qn = (int*)(qd + 8 * QD_CAP);                   // [8] queue lengths, [8] base queue, [9..16] boundary queues
+  double* basep = (double*)(qn + 32);                  // [4][GM_TN] partial base vectors
+  double* basev = basep + 4 * GM_TN;                   // [GM_TN] base vector of the tile
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int blk0 = blockIdx.x * SKIP_ROWS;
   const int j0 = blockIdx.y * GM_TN, vc = min(GM_TN, vCols - j0);
@@ -347,7 +356,7 @@ k_rmm_dmma2(const DevGroup* __restrict__ groups, const DenseDesc* __restrict__ d
 #pragma unroll
         for (int u = 0; u < 2; u++)
           Cs[(warp * 16 + mt * 8 + (lane >> 2)) * GM_LDC + nt * 8 + (lane & 3) * 2 + u] = c[mt][nt][u];
-    if (tid < 9) qn[tid] = 0;
+    if (tid < 17) qn[tid] = 0;
     __syncthreads();
 
     // ---- decode: every lane advances its groups through [r0, r1) and queues the work ----
@@ -398,8 +407,20 @@ k_rmm_dmma2(const DevGroup* __restrict__ groups, const DenseDesc* __restrict__ d
             else
               for (int w = 0; w < 8; w++) push_item(q, qn, w, w * 16, w * 16 + 16, prow, Cs, P, vCols, j0, vc);
           } else {
-            for (int w = (a - r0) >> 4; w <= (b - 1 - r0) >> 4; w++)
-              push_item(q, qn, w, max(a - r0, w * 16), min(b - r0, w * 16 + 16), prow, Cs, P, vCols, j0, vc);
+            // a run that starts or ends inside the tile: every warp whose 16 rows it touches gets "+P from
+            // its first row there on" and, if it ends inside that warp's rows, "-P from the end on"
+            for (int w = (a - r0) >> 4; w <= (b - 1 - r0) >> 4; w++) {
+              const int aw = max(a - r0, w * 16), bw = min(b - r0, w * 16 + 16);
+              const int need = bw < w * 16 + 16 ? 2 : 1;
+              const int slot = atomicAdd(&qn[9 + w], need);
+              if (slot + need <= QD_CAP) {
+                qd[w * QD_CAP + slot] = DeltaItem{(int16_t)aw, 1, prow};
+                if (need == 2) qd[w * QD_CAP + slot + 1] = DeltaItem{(int16_t)bw, -1, prow};
+              } else {
+                atomicAdd(&qn[9 + w], -need);
+                push_item(q, qn, w, aw, bw, prow, Cs, P, vCols, j0, vc);
+              }
+            }
           }
         }
         if (end <= r1) rRun++;
@@ -408,51 +429,88 @@ k_rmm_dmma2(const DevGroup* __restrict__ groups, const DenseDesc* __restrict__ d
     }
     __syncthreads();
 
-    // ---- apply: warp w owns rows [16 w, 16 w + 16); lane owns columns lane and lane + 32 ----
+    // ---- base vector: constV * V plus the table rows of all runs that cover the whole tile. Thread = (one of four
+    //      item slices, column): every thread's loads are independent, so the whole sum costs one or two latencies ----
     {
-      const bool c0ok = lane < vc, c1ok = lane + 32 < vc;
-      double b0 = (constRow && c0ok) ? constRow[j0 + lane] : 0.0, b1 = (constRow && c1ok) ? constRow[j0 + lane + 32] : 0.0;
-      const int nb = min(qn[8], QB_CAP);
-      for (int i0 = 0; i0 < nb; i0 += 8) {
-        double t0[8], t1[8];
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-          const double* p = P + (size_t)qb[min(i0 + i, nb - 1)] * vCols + j0;
-          t0[i] = (i0 + i < nb && c0ok) ? p[lane] : 0.0;
-          t1[i] = (i0 + i < nb && c1ok) ? p[lane + 32] : 0.0;
-        }
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-          b0 += t0[i];
-          b1 += t1[i];
-        }
-      }
+      const int n = tid & 63, sl = tid >> 6;
+      const int nbq = min(qn[8], QB_CAP);
+      double sacc = 0.0;
+      if (n < vc)
+        for (int i = sl; i < nbq; i += 4) sacc += P[(size_t)qb[i] * vCols + j0 + n];
+      basep[sl * GM_TN + n] = sacc;
+      __syncthreads();
+      if (tid < GM_TN)
+        basev[tid] = basep[tid] + basep[GM_TN + tid] + basep[2 * GM_TN + tid] + basep[3 * GM_TN + tid] +
+                     ((constRow && tid < vc) ? constRow[j0 + tid] : 0.0);
+      __syncthreads();
+    }
+    // ---- apply: warp w owns rows [16 w, 16 w + 16); lane owns the adjacent columns 2 lane and 2 lane + 1 ----
+    {
+      const int n0 = 2 * lane;
+      const bool c0ok = n0 < vc, c1ok = n0 + 1 < vc;
+      const bool vec2 = ((vCols | j0) & 1) == 0 && c1ok;  // table rows start 16-byte aligned and both columns exist
+      auto ldp = [&](uint32_t prow) -> double2 {              // two adjacent values of a table row
+        const double* p = P + (size_t)prow * vCols + j0 + n0;
+        if (vec2) return *(const double2*)p;
+        return make_double2(c0ok ? p[0] : 0.0, c1ok ? p[1] : 0.0);
+      };
+      const double2 bsum = make_double2(c0ok ? basev[n0] : 0.0, c1ok ? basev[n0 + 1] : 0.0);
       const int nq = min(qn[warp], Q_CAP);
       const WorkItem* myq = q + warp * Q_CAP;
       for (int i0 = 0; i0 < nq; i0 += 8) {
-        double t0[8], t1[8];
+        double2 t[8];
         WorkItem it[8];
 #pragma unroll
         for (int i = 0; i < 8; i++) {
           it[i] = myq[min(i0 + i, nq - 1)];
-          const double* p = P + (size_t)it[i].prow * vCols + j0;
-          t0[i] = (i0 + i < nq && c0ok) ? p[lane] : 0.0;
-          t1[i] = (i0 + i < nq && c1ok) ? p[lane + 32] : 0.0;
+          t[i] = i0 + i < nq ? ldp(it[i].prow) : make_double2(0.0, 0.0);
         }
 #pragma unroll
         for (int i = 0; i < 8; i++) {
           if (i0 + i < nq)
             for (int r = it[i].ra; r < it[i].rb; r++) {
-              Cs[r * GM_LDC + lane] += t0[i];
-              Cs[r * GM_LDC + lane + 32] += t1[i];
+              double2* cp = (double2*)&Cs[r * GM_LDC + n0];
+              double2 cv = *cp;
+              cv.x += t[i].x;
+              cv.y += t[i].y;
+              *cp = cv;
             }
         }
       }
-      __syncwarp();
+      // run boundaries: eight at a time, their table rows are fetched first; then one walk down the 16 rows carries
+      // the sum of the runs open at the current row (boundaries of later batches add their own walk: it is linear)
+      const int nd = min(qn[9 + warp], QD_CAP);
+      const DeltaItem* myd = qd + warp * QD_CAP;
+      for (int i0 = 0; i0 < nd; i0 += 8) {
+        double2 t[8];
+        int drow[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          const DeltaItem d = myd[min(i0 + i, nd - 1)];
+          drow[i] = i0 + i < nd ? d.row : -1;
+          const double2 pv = i0 + i < nd ? ldp(d.prow) : make_double2(0.0, 0.0);
+          t[i] = make_double2(d.sign * pv.x, d.sign * pv.y);
+        }
+        double2 cur = make_double2(0.0, 0.0);
+        for (int r = warp * 16; r < warp * 16 + 16; r++) {
+#pragma unroll
+          for (int i = 0; i < 8; i++)
+            if (drow[i] == r) {
+              cur.x += t[i].x;
+              cur.y += t[i].y;
+            }
+          double2* cp = (double2*)&Cs[r * GM_LDC + n0];
+          double2 cv = *cp;
+          cv.x += cur.x;
+          cv.y += cur.y;
+          *cp = cv;
+        }
+      }
       for (int r = warp * 16; r < warp * 16 + 16; r++) {
         if (r0 + r >= r1) break;
-        if (c0ok) out[(size_t)(r0 + r) * vCols + j0 + lane] = Cs[r * GM_LDC + lane] + b0;
-        if (c1ok) out[(size_t)(r0 + r) * vCols + j0 + lane + 32] = Cs[r * GM_LDC + lane + 32] + b1;
+        const double2 cv = *(const double2*)&Cs[r * GM_LDC + n0];
+        if (c0ok) out[(size_t)(r0 + r) * vCols + j0 + n0] = cv.x + bsum.x;
+        if (c1ok) out[(size_t)(r0 + r) * vCols + j0 + n0 + 1] = cv.y + bsum.y;
       }
     }
     __syncthreads();  // the stage of the next tile overwrites Cs
@@ -555,7 +613,8 @@ int64_t launch_rmm_dmma(Matrix* m, const double* dV, int vCols, double* dOut, cu
     m->stats.kernel_launches++;
   }
   const size_t smem = std::max((size_t)(GM_KC * GM_LDA + GM_KC * GM_LDB), (size_t)(GM_TR * GM_LDC + GM_TN)) * sizeof(double);
-  const size_t smem2 = (size_t)GM_TR * GM_LDC * sizeof(double) + 8 * Q_CAP * sizeof(WorkItem) + QB_CAP * 4 + 16 * 4;
+  const size_t smem2 = (size_t)GM_TR * GM_LDC * sizeof(double) + 8 * Q_CAP * sizeof(WorkItem) + QB_CAP * 4 +
+                       8 * QD_CAP * sizeof(DeltaItem) + 32 * 4 + 5 * GM_TN * sizeof(double);
   static bool attrSet[64] = {};  // per device: function attributes belong to the device's context
   bool& attr = attrSet[m->device & 63];
   if (!attr) {
