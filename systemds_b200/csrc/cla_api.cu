@@ -329,6 +329,48 @@ static int64_t check_errword(Matrix* m) {
   return CLA_OK;
 }
 
+// Few right-hand columns (or few left-hand rows) are served by the one-vector kernels, once per vector: each
+// pass re-reads the maps, which is cheaper than the general tile kernels up to the limits below.
+static int loop_limit(const char* env, int dflt) {
+  const char* e = getenv(env);
+  return e ? atoi(e) : dflt;
+}
+
+__global__ void k_small_transpose(const double* __restrict__ in, int rows, int cols, double* __restrict__ out) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < rows * cols) out[(size_t)(i % cols) * rows + i / cols] = in[i];
+}
+
+// U holds vCols result vectors of nRows each; out is row-major nRows x vCols.
+__global__ void k_vectors_to_rows(const double* __restrict__ U, int64_t nRows, int64_t stride, int vCols,
+                                  double* __restrict__ out) {
+  for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < nRows; r += (int64_t)gridDim.x * blockDim.x)
+    for (int j = 0; j < vCols; j++) out[r * vCols + j] = U[(int64_t)j * stride + r];
+}
+
+static int64_t rmm_by_vectors(Matrix* m, const double* dV, int32_t vCols, double* dOut, cudaStream_t s) {
+  const size_t vtBytes = (((size_t)vCols * m->nCols * sizeof(double)) + 255) & ~(size_t)255;
+  const size_t rowsPad = ((size_t)m->nRows + 31) & ~(size_t)31;
+  int64_t rc = ensure_scratch2(m, vtBytes + rowsPad * vCols * sizeof(double));
+  if (rc < 0) return rc;
+  double* Vt = (double*)m->scratch2;
+  double* U = (double*)((char*)m->scratch2 + vtBytes);
+  const int cells = m->nCols * vCols;
+  k_small_transpose<<<(cells + 255) / 256, 256, 0, s>>>(dV, m->nCols, vCols, Vt);
+  for (int j = 0; j < vCols; j++) {
+    double* uj = U + rowsPad * j;
+    rc = fast_rmm_vec(m, Vt + (size_t)j * m->nCols, uj, s);
+    if (rc < 0) return rc;
+    if (rc == 2) rc = launch_rmm(m, Vt + (size_t)j * m->nCols, 1, uj, s, true);
+    else if (rc == 0) rc = launch_rmm(m, Vt + (size_t)j * m->nCols, 1, uj, s);
+    if (rc < 0) return rc;
+  }
+  k_vectors_to_rows<<<m->smCount * 8, 256, 0, s>>>(U, m->nRows, (int64_t)rowsPad, vCols, dOut);
+  m->stats.kernel_launches += 2;
+  CLA_CUDA(cudaGetLastError());
+  return CLA_OK;
+}
+
 static int64_t rmm_dev(Matrix* m, const double* dV, int32_t vRows, int32_t vCols, double* dOut, cudaStream_t s) {
   if (vRows != m->nCols) return fail(CLA_ERR_SHAPE, "rmm: V must have nCols rows");
   if (vCols < 0) return fail(CLA_ERR_SHAPE, "rmm: negative column count");
@@ -337,10 +379,16 @@ static int64_t rmm_dev(Matrix* m, const double* dV, int32_t vRows, int32_t vCols
     int64_t rc = fast_rmm_vec(m, dV, dOut, s);
     if (rc < 0) return rc;
     if (rc == 1) return CLA_OK;
-    if (rc == 2) return launch_rmm(m, dV, vCols, dOut, s, true);
+    return launch_rmm(m, dV, 1, dOut, s, rc == 2);
   }
-  if (vCols >= 8) return launch_rmm_dmma(m, dV, vCols, dOut, s);  // wide V: FP64 tensor cores
-  return launch_rmm(m, dV, vCols, dOut, s);
+  // A pass of the one-column kernels per column beats the tensor-core kernel (whose time hardly depends on
+  // the width up to 64 columns) for a few columns; measured crossover: about 16 columns when every group is
+  // a byte-map DDC group (2M x 200: 0.26 ms per column against 4.3 ms), about 5 when SDC / RLE groups take
+  // the general pass as well (1M x 500, 451 groups: 0.64 ms per column against 3.25 ms).
+  static const int loopEnv = loop_limit("CLA_RMM_LOOP_MAX", -1);  // tuning aid
+  const int loopMax = loopEnv >= 0 ? loopEnv : (fast_plan_partial(m) ? 4 : 12);
+  if (vCols >= 2 && vCols <= loopMax && fast_plan_ok(m) && m->nRows > 0) return rmm_by_vectors(m, dV, vCols, dOut, s);
+  return launch_rmm_dmma(m, dV, vCols, dOut, s);  // FP64 tensor cores
 }
 
 static int64_t lmm_dev(Matrix* m, const double* dYt, int32_t yRows, double* dOut, cudaStream_t s) {
@@ -348,6 +396,30 @@ static int64_t lmm_dev(Matrix* m, const double* dYt, int32_t yRows, double* dOut
   m->stats.calls_lmm++;
   if (yRows == 1) {
     int64_t rc = fast_lmm_vec(m, dYt, dOut, s);
+    if (rc < 0) return rc;
+    if (rc == 1) return CLA_OK;
+    if (rc == 2) return launch_lmm(m, dYt, yRows, dOut, s, true);
+  }
+  // Several left rows: one pass of the one-vector kernel per row for the groups it covers (measured 0.17 ms per
+  // row on 2M x 200 against 1.5 ms per row in the general pre-aggregation kernel), the general kernels for the
+  // rest. Rows of an odd-length Yt are not 16-byte aligned, so they are copied to a padded pitch first.
+  static const int lmmLoopMax = loop_limit("CLA_LMM_LOOP_MAX", 1 << 30);  // tuning aid
+  if (yRows >= 2 && yRows <= lmmLoopMax && fast_plan_ok(m) && m->nRows > 0) {
+    const double* rows = dYt;
+    size_t pitch = (size_t)m->nRows;
+    if (m->nRows & 1) {
+      pitch = (size_t)m->nRows + 1;
+      int64_t rc = ensure_scratch2(m, pitch * yRows * sizeof(double));
+      if (rc < 0) return rc;
+      CLA_CUDA(cudaMemcpy2DAsync(m->scratch2, pitch * sizeof(double), dYt, (size_t)m->nRows * sizeof(double),
+                                 (size_t)m->nRows * sizeof(double), yRows, cudaMemcpyDeviceToDevice, s));
+      rows = (const double*)m->scratch2;
+    }
+    int64_t rc = 0;
+    for (int i = 0; i < yRows; i++) {
+      rc = fast_lmm_vec(m, rows + pitch * i, dOut + (size_t)i * m->nCols, s);
+      if (rc <= 0) break;
+    }
     if (rc < 0) return rc;
     if (rc == 1) return CLA_OK;
     if (rc == 2) return launch_lmm(m, dYt, yRows, dOut, s, true);

@@ -220,6 +220,8 @@ int64_t finalize_device(Matrix* m);
 // (the caller then runs the general launcher with afterFast = true), 0 if not applicable, <0 on error
 int64_t fast_plan_build(Matrix* m);
 void fast_plan_free(Matrix* m);
+bool fast_plan_ok(const Matrix* m);       // some or all groups are covered by the specialised kernels
+bool fast_plan_partial(const Matrix* m);  // ... some but not all
 int64_t fast_rmm_vec(Matrix* m, const double* dV, double* dOut, cudaStream_t s);
 int64_t fast_lmm_vec(Matrix* m, const double* dY, double* dOut, cudaStream_t s);
 int64_t fast_lmm_vec_host(Matrix* m, const double* hostY, double* dY, double* dOut, cudaStream_t s);

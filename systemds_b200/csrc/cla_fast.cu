@@ -1091,6 +1091,9 @@ static int64_t fast_rmm_vec_f(Matrix* m, FastPlan* fp, const double* dV, double*
   return 1;
 }
 
+bool fast_plan_ok(const Matrix* m) { return m->fast && m->fast->ok; }
+bool fast_plan_partial(const Matrix* m) { return m->fast && m->fast->ok && m->fast->partial; }
+
 int64_t fast_rmm_vec(Matrix* m, const double* dV, double* dOut, cudaStream_t s) {
   FastPlan* fp = m->fast;
   if (!fp || !fp->ok || ((uintptr_t)dOut & 15)) return 0;  // 128-bit stores need an aligned output

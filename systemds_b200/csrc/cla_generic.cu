@@ -5,8 +5,10 @@
 //   RMM  (CLALibRightMultBy.RMM, lib/CLALibRightMultBy.java:208-258)
 //        1. k_dict_times_v : P_g = D_g * V[cols_g, :] for every dictionary group
 //                            (ADictBasedColGroup.rightMultByMatrix, colgroup/ADictBasedColGroup.java:246-275)
-//        2. k_rmm_tile     : a CTA owns a tile of output rows and sums P_g[id_g(r), :] over all groups,
-//                            then adds constV * V (the decompress-and-sum of lib/CLALibDecompress.java:310-357)
+//        2. k_rmm_vec_general : one right-hand column; a CTA owns a block of output rows and sums
+//                            P_g[id_g(r)] over all groups, then adds constV * v (the decompress-and-sum of
+//                            lib/CLALibDecompress.java:310-357). Wider right-hand sides run on the FP64
+//                            tensor cores (cla_rmm_dmma.cu) or, for a few columns, once per column.
 //   LMM  (CLALibLeftMultBy.LMM, lib/CLALibLeftMultBy.java:286-346)
 //        1. k_lmm_preagg   : A_g[i, k] = sum of Yt[i, r] over rows r holding tuple k
 //                            (APreAgg.preAggregateDense, colgroup/APreAgg.java:137)
@@ -48,130 +50,6 @@ __global__ void k_const_times_v(const double* __restrict__ constV, int nCols, co
   double s = 0;
   for (int c = 0; c < nCols; c++) s += constV[c] * V[(size_t)c * vCols + j];
   constRow[j] = s;
-}
-
-// --------------------------------------------------------------------------------------------------
-// RMM tile kernel. Tile = TR rows x vc columns, TR * vc <= TILE_ELEMS, 256 threads; each thread owns
-// fixed elements of the tile, so dense-map and uncompressed groups accumulate in registers without
-// synchronisation. Sparse groups (SDC) scatter into the shared tile with shared-memory atomics, one
-// group per warp. RLE groups are staged eight at a time as per-row ids in shared memory.
-// --------------------------------------------------------------------------------------------------
-constexpr int RMM_THREADS = 256;
-constexpr int RMM_E = 16;
-constexpr int TILE_ELEMS = RMM_THREADS * RMM_E;  // 4096 doubles = 32 KB
-constexpr int RLE_BATCH = 8;
-constexpr int MAX_TR = 1024;
-
-__global__ void __launch_bounds__(RMM_THREADS)
-k_rmm_tile(const DevGroup* __restrict__ groups, int nGroups, int nRows, const double* __restrict__ P,
-           const double* __restrict__ V, int vCols, const double* __restrict__ constRow, double* __restrict__ out,
-           int TR, int vcTile, int hasSparse, int afterFast) {
-  extern __shared__ double smem[];
-  double* acc = smem;                                         // [TR * vc]
-  uint16_t* ids = (uint16_t*)(smem + TILE_ELEMS);             // [RLE_BATCH][MAX_TR]
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int r0 = blockIdx.x * TR, r1 = min(nRows, r0 + TR);
-  const int j0 = blockIdx.y * vcTile, vc = min(vcTile, vCols - j0);
-  const int nElem = (r1 - r0) * vc;
-
-  double racc[RMM_E];
-  int er[RMM_E], ej[RMM_E];
-#pragma unroll
-  for (int i = 0; i < RMM_E; i++) {
-    const int e = tid + i * RMM_THREADS;
-    er[i] = e / vc;
-    ej[i] = e - er[i] * vc;
-    // after the specialised kernels ran, `out` already holds their groups' sums and the constant part
-    if (afterFast) racc[i] = e < nElem ? out[(size_t)(r0 + er[i]) * vCols + j0 + ej[i]] : 0.0;
-    else racc[i] = (constRow != nullptr && e < nElem) ? constRow[j0 + ej[i]] : 0.0;
-  }
-  // phase A: dense-map and uncompressed groups, registers
-  for (int gi = 0; gi < nGroups; gi++) {
-    const DevGroup& g = groups[gi];
-    if (afterFast && g.inFast) continue;
-    if (g.type == GT_DDC) {
-      const double* Pg = P + g.valOff * vCols + j0;
-#pragma unroll
-      for (int i = 0; i < RMM_E; i++) {
-        if (tid + i * RMM_THREADS < nElem) {
-          const int id = map_get(g.mapType, g.map, g.mapHi, r0 + er[i]);
-          racc[i] += Pg[(size_t)id * vCols + ej[i]];
-        }
-      }
-    } else if (g.type == GT_UNC) {
-#pragma unroll
-      for (int i = 0; i < RMM_E; i++) {
-        if (tid + i * RMM_THREADS < nElem) {
-          const double* x = g.dense + (size_t)(r0 + er[i]) * g.gCols;
-          double s = 0;
-          for (int c = 0; c < g.gCols; c++) s += x[c] * V[(size_t)g.cols[c] * vCols + j0 + ej[i]];
-          racc[i] += s;
-        }
-      }
-    }
-  }
-  if (!hasSparse) {
-#pragma unroll
-    for (int i = 0; i < RMM_E; i++)
-      if (tid + i * RMM_THREADS < nElem) out[(size_t)(r0 + er[i]) * vCols + j0 + ej[i]] = racc[i];
-    return;
-  }
-#pragma unroll
-  for (int i = 0; i < RMM_E; i++)
-    if (tid + i * RMM_THREADS < nElem) acc[tid + i * RMM_THREADS] = racc[i];
-  __syncthreads();
-  // phase B: SDC groups, one per warp at a time, shared atomics (listed rows are sparse)
-  for (int gi = warp; gi < nGroups; gi += RMM_THREADS / 32) {
-    const DevGroup& g = groups[gi];
-    if (g.type != GT_SDC) continue;
-    const double* Pg = P + g.valOff * vCols + j0;
-    sdc_walk_block(g, r0, r1, [&](int row, int e) {
-      const int id = g.single ? 0 : map_get(g.mapType, g.map, g.mapHi, e);
-      double* a = acc + (row - r0) * vc;
-      const double* p = Pg + (size_t)id * vCols;
-      for (int j = 0; j < vc; j++) atomicAdd(&a[j], p[j]);
-    });
-  }
-  __syncthreads();
-  // phase C: RLE groups in batches: stage per-row ids, then every thread adds to its own elements
-  int batch[RLE_BATCH];
-  int nb = 0;
-  for (int gi = 0; gi <= nGroups; gi++) {
-    if (gi < nGroups && groups[gi].type == GT_RLE) batch[nb++] = gi;
-    if (nb == RLE_BATCH || (gi == nGroups && nb > 0)) {
-      for (int e = tid; e < nb * MAX_TR; e += RMM_THREADS) ids[e] = 0xFFFF;
-      __syncthreads();
-      if (warp < nb) {
-        const DevGroup& g = groups[batch[warp]];
-        for (int64_t ri = g.runSkip[r0 / SKIP_ROWS]; ri < g.nRuns; ri++) {
-          const RleRun run = g.runs[ri];
-          if (run.start >= r1) break;
-          const int a = max(run.start, r0), b = min(run.start + (int)run.len, r1);
-          for (int r = a + lane; r < b; r += 32) ids[warp * MAX_TR + (r - r0)] = run.k;
-        }
-      }
-      __syncthreads();
-      for (int bi = 0; bi < nb; bi++) {
-        const DevGroup& g = groups[batch[bi]];
-        const double* Pg = P + g.valOff * vCols + j0;
-#pragma unroll
-        for (int i = 0; i < RMM_E; i++) {
-          const int e = tid + i * RMM_THREADS;
-          if (e < nElem) {
-            const int id = ids[bi * MAX_TR + er[i]];
-            if (id != 0xFFFF) acc[e] += Pg[(size_t)id * vCols + ej[i]];
-          }
-        }
-      }
-      __syncthreads();
-      nb = 0;
-    }
-  }
-#pragma unroll
-  for (int i = 0; i < RMM_E; i++) {
-    const int e = tid + i * RMM_THREADS;
-    if (e < nElem) out[(size_t)(r0 + er[i]) * vCols + j0 + ej[i]] = acc[e];
-  }
 }
 
 // --------------------------------------------------------------------------------------------------
@@ -320,58 +198,33 @@ k_rmm_vec_general(const DevGroup* __restrict__ groups, int nGroups, int nRows, c
 
 int64_t launch_rmm(Matrix* m, const double* dV, int vCols, double* dOut, cudaStream_t s, bool afterFast) {
   if (m->nRows == 0 || vCols == 0) return CLA_OK;
-  int64_t rc;
-  const size_t pBytes = (size_t)std::max<int64_t>(m->totalVals, 1) * vCols * sizeof(double);
-  const size_t cOff = (pBytes + 255) & ~(size_t)255;
-  if ((rc = ensure_scratch(m, cOff + (size_t)vCols * sizeof(double))) < 0) return rc;
-  double* P = (double*)m->scratch;
-  double* constRow = nullptr;
-  if (m->nDev > 0) {
-    int maxE = 1;
-    for (auto& g : m->groups) maxE = std::max<int64_t>(maxE, (int64_t)g.nVals * vCols);
-    dim3 grid(m->nDev, std::max(1, std::min(64, (maxE + 255) / 256)));
-    k_dict_times_v<<<grid, 256, 0, s>>>(m->dGroups, dV, vCols, P, afterFast ? 1 : 0);
-    m->stats.kernel_launches++;
-  }
-  if (m->hasConst && !afterFast) {
-    constRow = (double*)((char*)m->scratch + cOff);
-    k_const_times_v<<<(vCols + 127) / 128, 128, 0, s>>>(m->dConstV, m->nCols, dV, vCols, constRow);
-    m->stats.kernel_launches++;
-  }
-  if (vCols == 1) {  // one column: the block kernel with lane-per-group sparse decode
-    if (afterFast) {
-      bool rest = false;
-      for (auto& g : m->groups) rest |= !g.inFast;
-      if (!rest) return CLA_OK;
-    }
-    prof_begin(m, s);
-    k_rmm_vec_general<<<(m->nRows + SKIP_ROWS - 1) / SKIP_ROWS, RV_THREADS, 0, s>>>(m->dGroups, m->nDev, m->nRows, P, dV,
-                                                                                 constRow, dOut, afterFast ? 1 : 0);
-    prof_end(m, s);
-    m->stats.kernel_launches++;
-    CLA_CUDA(cudaGetLastError());
-    return CLA_OK;
-  }
-  const int vcTile = std::min(vCols, 64);
-  int TR = std::min(MAX_TR, std::max(32, TILE_ELEMS / vcTile));
-  int hasSparse = 0;
-  for (auto& g : m->groups) hasSparse |= (g.type == GT_SDC || g.type == GT_RLE);
-  if (afterFast) {  // nothing left for this pass if the remaining groups are all covered
+  if (vCols != 1) return fail(CLA_ERR_UNSUPPORTED, "rmm: the general kernel takes one right-hand column");
+  if (afterFast) {  // nothing left for this pass if the specialised kernels covered every group
     bool rest = false;
     for (auto& g : m->groups) rest |= !g.inFast;
     if (!rest) return CLA_OK;
   }
-  const size_t smem = TILE_ELEMS * sizeof(double) + (size_t)RLE_BATCH * MAX_TR * sizeof(uint16_t);
-  static bool attrSet[64] = {};  // per device: function attributes belong to the device's context
-  bool& attr = attrSet[m->device & 63];
-  if (!attr) {
-    CLA_CUDA(cudaFuncSetAttribute(k_rmm_tile, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr = true;
+  int64_t rc;
+  const size_t pBytes = (size_t)std::max<int64_t>(m->totalVals, 1) * sizeof(double);
+  const size_t cOff = (pBytes + 255) & ~(size_t)255;
+  if ((rc = ensure_scratch(m, cOff + sizeof(double))) < 0) return rc;
+  double* P = (double*)m->scratch;
+  double* constRow = nullptr;
+  if (m->nDev > 0) {
+    int maxE = 1;
+    for (auto& g : m->groups) maxE = std::max<int64_t>(maxE, (int64_t)g.nVals);
+    dim3 grid(m->nDev, std::max(1, std::min(64, (maxE + 255) / 256)));
+    k_dict_times_v<<<grid, 256, 0, s>>>(m->dGroups, dV, 1, P, afterFast ? 1 : 0);
+    m->stats.kernel_launches++;
   }
-  dim3 grid((m->nRows + TR - 1) / TR, (vCols + vcTile - 1) / vcTile);
+  if (m->hasConst && !afterFast) {
+    constRow = (double*)((char*)m->scratch + cOff);
+    k_const_times_v<<<1, 128, 0, s>>>(m->dConstV, m->nCols, dV, 1, constRow);
+    m->stats.kernel_launches++;
+  }
   prof_begin(m, s);
-  k_rmm_tile<<<grid, RMM_THREADS, smem, s>>>(m->dGroups, m->nDev, m->nRows, P, dV, vCols, constRow, dOut, TR, vcTile,
-                                             hasSparse, afterFast ? 1 : 0);
+  k_rmm_vec_general<<<(m->nRows + SKIP_ROWS - 1) / SKIP_ROWS, RV_THREADS, 0, s>>>(m->dGroups, m->nDev, m->nRows, P, dV,
+                                                                               constRow, dOut, afterFast ? 1 : 0);
   prof_end(m, s);
   m->stats.kernel_launches++;
   CLA_CUDA(cudaGetLastError());

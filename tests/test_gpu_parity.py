@@ -116,8 +116,29 @@ def test_fast_vector_paths(oracle, nRows, shape):
     assert rel_err(CLALibLeftMultBy.leftMultByMatrix(cmb, y), om.lmm(y), np.abs(y) @ aX + 1e-300) < TOL
     s = aX.T @ (aX @ np.abs(v)) + 1e-300
     assert rel_err(CLALibMMChain.mmChain(cmb, v).ravel(), om.mmchain(v).ravel(), s) < 10 * TOL
+    # a few vectors at once: served by the same kernels, one pass per vector
+    V = rng.standard_normal((cmb.clen, 4))
+    Y = rng.standard_normal((3, nRows))
+    assert rel_err(CLALibRightMultBy.rightMultByMatrix(cmb, V), om.rmm(V), aX @ np.abs(V) + 1e-300) < TOL
+    assert rel_err(CLALibLeftMultBy.leftMultByMatrix(cmb, Y), om.lmm(Y), np.abs(Y) @ aX + 1e-300) < TOL
     st = cmb.stats()
     assert st["kernel_launches"] > 0 and st["calls_rmm"] >= 2 and st["calls_lmm"] >= 2
+    cmb.free()
+
+
+def test_products_repeat_bit_identical():
+    """The specialised vector kernels and the tensor-core RMM sum in a fixed order: a second call returns the same
+    bits. (TSMM, the general kernels and the constant-column row sum combine partial sums with atomics, as the
+    reference's parallel paths do with tasks, and are checked to tolerance only.)"""
+    cmb = _ddc_matrix(300001, [16] * 40 + [200] * 30, 9).to_device()
+    rng = np.random.default_rng(3)
+    v = rng.standard_normal(cmb.clen)
+    V = rng.standard_normal((cmb.clen, 64))
+    y = rng.standard_normal((1, 300001))
+    for f in (lambda: CLALibRightMultBy.rightMultByMatrix(cmb, v), lambda: CLALibRightMultBy.rightMultByMatrix(cmb, V),
+              lambda: CLALibLeftMultBy.leftMultByMatrix(cmb, y), lambda: CLALibMMChain.mmChain(cmb, v)):
+        a = np.array(f())
+        assert np.array_equal(a, np.array(f()))
     cmb.free()
 
 
