@@ -135,6 +135,12 @@ int64_t cla_tsmm(cla_handle h, double* out);
 int64_t cla_mmchain(cla_handle h, const double* v, const double* w, int32_t ctype, double* out);
 int64_t cla_decompress(cla_handle h, double* out);
 
+/* t(left) %*% right on two compressed blocks with the same number of rows, finalized on the same device:
+ * replaces lib/CLALibLeftMultBy.java:100  leftMultByMatrixTransposed(right, left, ret, k) with a compressed
+ * left operand (the compressed x compressed case of lib/CLALibMatrixMult.java:96-124).
+ * out [left.nCols x right.nCols], dense row-major. left == right is allowed (same result as cla_tsmm). */
+int64_t cla_tmm(cla_handle left, cla_handle right, double* out);
+
 /* Sum aggregates on the compressed block, the uak+ / uark+ / uack+ cases of lib/CLALibCompAgg.java
  * (colgroup/AColGroupCompressed.java:140-205 computeSum / computeRowSums / computeColSums):
  * CLA_AGG_COL_SUMS -> out[nCols], CLA_AGG_ROW_SUMS -> out[nRows], CLA_AGG_SUM -> out[1]. Host buffer. */
@@ -151,12 +157,13 @@ int64_t cla_unary_agg(cla_handle h, int32_t op, double* out);
 int64_t cla_rmm_dev(cla_handle h, const double* dV, int32_t vRows, int32_t vCols, double* dOut, void* stream);
 int64_t cla_lmm_dev(cla_handle h, const double* dYt, int32_t yRows, double* dOut, void* stream);
 int64_t cla_tsmm_dev(cla_handle h, double* dOut, void* stream);
+int64_t cla_tmm_dev(cla_handle left, cla_handle right, double* dOut, void* stream);
 /* dU: caller-provided scratch of nRows doubles for u = X v (may be NULL: the handle then keeps its own) */
 int64_t cla_mmchain_dev(cla_handle h, const double* dV, const double* dW, int32_t ctype, double* dOut, double* dU,
                         void* stream);
 /* Row sharding needs no special entry point: a handle that holds rows [a, b) of a taller matrix
  * yields the exact product of those rows (constant columns included), so the partial results of
- * cla_lmm_dev / cla_tsmm_dev / cla_mmchain_dev over all shards simply add up. */
+ * cla_lmm_dev / cla_tsmm_dev / cla_tmm_dev / cla_mmchain_dev over all shards simply add up. */
 
 /* t(y) %*% X (one left row) that performs no device allocation. It has no counterpart in the reference.
  * For hosts that must not allocate when they call in -- a runtime whose own pool owns all device memory, or a loop

@@ -325,6 +325,19 @@ struct CLALibLeftMultBy {  // lib/CLALibLeftMultBy.java:126; left is [q x nRows]
     return ret;
   }
 };
+struct CLALibLeftMultByCompressed {  // lib/CLALibLeftMultBy.java:100: t(left) %*% right, both compressed
+  static MatrixBlock leftMultByMatrixTransposed(CompressedMatrixBlock& right, CompressedMatrixBlock& left) {
+    if (left.getNumRows() != right.getNumRows())
+      throw DMLCompressionException(CLA_ERR_SHAPE, "Failed CLA Compressed Transposed LMM: row counts differ");
+    MatrixBlock ret(left.getNumColumns(), right.getNumColumns());
+    try {
+      ret.nonZeros = check(cla_tmm(left.nativeHandle(), right.nativeHandle(), ret.values.data()), "cla_tmm");
+    } catch (const DMLCompressionException& e) {
+      throw DMLCompressionException(e.code, std::string("Failed CLA Compressed Transposed LMM: ") + e.what());  // :109-111
+    }
+    return ret;
+  }
+};
 struct CLALibTSMM {  // lib/CLALibTSMM.java:59
   static MatrixBlock leftMultByTransposeSelf(CompressedMatrixBlock& cmb) {
     MatrixBlock ret(cmb.getNumColumns(), cmb.getNumColumns());

@@ -629,6 +629,141 @@ void mmchain(const ocl_matrix* m, const double* v, const double* w, int ctype, d
   lmm(m, u.data(), 1, out, k);
 }
 
+/* t(left) %*% right on two compressed blocks -- C/lib/CLALibLeftMultBy.java:100-112,170-284
+ * (leftMultByCompressedTransposedMatrix): both sides are filtered to zero-default groups + constV; every pair
+ * (left group lg, right group rg) adds t(lg) rg through rg.leftMultByAColGroup(lg) (CG/APreAgg.java:57-68,
+ * 211-232): the side with the cheaper dictionary is pre-aggregated by the other side's index structure
+ * (shouldPreAggregateLeft :302-310), then one small dictionary product; uncompressed groups on either side
+ * (CG/APreAgg.java:234-248, CG/ColGroupUncompressed.java:732-827) go through their dense rows. Then the rank-1
+ * corrections cL (x) colSums(right'), colSums(left') (x) cR and nRows * cL (x) cR (:206-214). */
+struct RowSrc {  // a filtered group seen as "row r holds tuple id(r) of table T" (id -1: zero row)
+  const double* T;
+  int gc;
+  std::vector<int32_t> id;
+};
+void row_src(const View& v, int n, RowSrc& rs) {
+  const Group& g = *v.g;
+  rs.gc = g.gCols();
+  rs.id.assign(n, -1);
+  if (g.type == G_UNC) {
+    rs.T = g.dense.data();
+    for (int r = 0; r < n; r++) rs.id[r] = r;
+  } else {
+    rs.T = v.dict.data();
+    walk_rows(g, 0, n, [&](int r, int k) { rs.id[r] = k; });
+  }
+}
+
+void tmm_pair(int n, const View& lg, const View& rg, double* res, int nColsOut) {
+  const Group &L = *lg.g, &R = *rg.g;
+  const int lc = L.gCols(), rc = R.gCols();
+  if (L.type == G_UNC || R.type == G_UNC) {  // dense rows on one side: pre-aggregate them by the other side's ids
+    RowSrc a, b;
+    row_src(lg, n, a);
+    row_src(rg, n, b);
+    if (L.type == G_UNC && R.type != G_UNC) {  // APreAgg.leftMultByUncompressedColGroup: preAgg[lc x nVals_r] . D_r
+      std::vector<double> pa((size_t)lc * R.nVals, 0.0);
+      for (int r = 0; r < n; r++)
+        if (b.id[r] >= 0)
+          for (int i = 0; i < lc; i++) pa[(size_t)i * R.nVals + b.id[r]] += a.T[(size_t)r * lc + i];
+      for (int i = 0; i < lc; i++)
+        for (int k = 0; k < R.nVals; k++) {
+          const double x = pa[(size_t)i * R.nVals + k];
+          if (x != 0)
+            for (int j = 0; j < rc; j++) res[(size_t)L.cols[i] * nColsOut + R.cols[j]] += x * rg.dict[(size_t)k * rc + j];
+        }
+    } else {  // right side dense: out[lcols, rcols] += sum_r tuple_l(r)^T row_r(r), row by row
+      for (int r = 0; r < n; r++)
+        if (a.id[r] >= 0 && b.id[r] >= 0)
+          for (int i = 0; i < lc; i++) {
+            const double x = a.T[(size_t)a.id[r] * lc + i];
+            if (x != 0)
+              for (int j = 0; j < rc; j++) res[(size_t)L.cols[i] * nColsOut + R.cols[j]] += x * b.T[(size_t)b.id[r] * rc + j];
+          }
+    }
+    return;
+  }
+  ocl_matrix shape;  // preagg_that only reads the row count
+  shape.nRows = n;
+  shape.nCols = 0;
+  std::vector<double> B;
+  const double costR = (double)R.nVals * rc, costL = (double)L.nVals * lc;
+  if (costR < costL) {  // left pre-aggregation: B[k_l, rcols] = sum of right tuples over rows with left id k_l
+    preagg_that(&shape, lg, rg, B);
+    for (int k = 0; k < L.nVals; k++)
+      for (int i = 0; i < lc; i++) {
+        const double x = lg.dict[(size_t)k * lc + i];
+        if (x != 0)
+          for (int j = 0; j < rc; j++) res[(size_t)L.cols[i] * nColsOut + R.cols[j]] += x * B[(size_t)k * rc + j];
+      }
+  } else {  // right pre-aggregation: B[k_r, lcols]
+    preagg_that(&shape, rg, lg, B);
+    for (int k = 0; k < R.nVals; k++)
+      for (int i = 0; i < lc; i++) {
+        const double x = B[(size_t)k * lc + i];
+        if (x != 0)
+          for (int j = 0; j < rc; j++) res[(size_t)L.cols[i] * nColsOut + R.cols[j]] += x * rg.dict[(size_t)k * rc + j];
+      }
+  }
+}
+
+// CLALibUtils.getColSum (C/lib/CLALibUtils.java:267-269) of filtered groups
+void col_sums_filtered(const ocl_matrix* m, const std::vector<View>& views, std::vector<double>& cs) {
+  cs.assign(m->nCols, 0.0);
+  for (auto& v : views) {
+    const Group& g = *v.g;
+    const int gc = g.gCols();
+    if (g.type == G_UNC) {
+      for (int r = 0; r < m->nRows; r++)
+        for (int j = 0; j < gc; j++) cs[g.cols[j]] += g.dense[(size_t)r * gc + j];
+      continue;
+    }
+    std::vector<int64_t> counts;
+    group_counts(m, g, counts);
+    for (int k = 0; k < g.nVals; k++)
+      for (int j = 0; j < gc; j++) cs[g.cols[j]] += v.dict[(size_t)k * gc + j] * (double)counts[k];
+  }
+}
+
+void tmm(const ocl_matrix* left, const ocl_matrix* right, double* out, int k) {
+  const int rl = left->nCols, cr = right->nCols, sd = right->nRows;
+  std::memset(out, 0, sizeof(double) * (size_t)rl * cr);
+  std::vector<View> fL, fR;
+  std::vector<double> cL, cR;
+  filter_groups(left, fL, cL);
+  filter_groups(right, fR, cR);
+  const bool containsLeft = should_prefilter(left), containsRight = should_prefilter(right);
+  const int nt = std::max(k, 1);
+  // one task per left group with a private result, summed afterwards (:186-200, :216-230)
+  std::vector<std::vector<double>> priv(nt, std::vector<double>((size_t)rl * cr, 0.0));
+#pragma omp parallel for schedule(dynamic, 1) num_threads(nt)
+  for (size_t j = 0; j < fL.size(); j++) {
+#ifdef _OPENMP
+    double* res = priv[omp_get_thread_num()].data();
+#else
+    double* res = priv[0].data();
+#endif
+    for (size_t i = 0; i < fR.size(); i++) tmm_pair(sd, fL[j], fR[i], res, cr);
+  }
+  if (containsLeft && containsRight)  // outerProductWithScaling
+    for (int i = 0; i < rl; i++)
+      for (int j = 0; j < cr; j++) out[(size_t)i * cr + j] += cL[i] * cR[j] * sd;
+  if (containsLeft) {
+    std::vector<double> cs;
+    col_sums_filtered(right, fR, cs);
+    for (int i = 0; i < rl; i++)
+      for (int j = 0; j < cr; j++) out[(size_t)i * cr + j] += cL[i] * cs[j];
+  }
+  if (containsRight) {
+    std::vector<double> cs;
+    col_sums_filtered(left, fL, cs);
+    for (int i = 0; i < rl; i++)
+      for (int j = 0; j < cr; j++) out[(size_t)i * cr + j] += cs[i] * cR[j];
+  }
+  for (int t = 0; t < nt; t++)
+    for (size_t i = 0; i < (size_t)rl * cr; i++) out[i] += priv[t][i];
+}
+
 template <class T>
 std::vector<T> vec(const T* p, size_t n) {
   return p ? std::vector<T>(p, p + n) : std::vector<T>();
@@ -937,6 +1072,7 @@ void ocl_decompress(const ocl_matrix* m, double* out, int k) { decompress(m, out
 void ocl_rmm(const ocl_matrix* m, const double* V, int32_t vCols, double* out, int k) { rmm(m, V, vCols, out, k); }
 void ocl_lmm(const ocl_matrix* m, const double* Yt, int32_t yRows, double* out, int k) { lmm(m, Yt, yRows, out, k); }
 void ocl_tsmm(const ocl_matrix* m, double* out, int k, int allowFallback) { tsmm(m, out, k, allowFallback); }
+void ocl_tmm(const ocl_matrix* left, const ocl_matrix* right, double* out, int k) { tmm(left, right, out, k); }
 void ocl_mmchain(const ocl_matrix* m, const double* v, const double* w, int ctype, double* out, int k) {
   mmchain(m, v, w, ctype, out, k);
 }

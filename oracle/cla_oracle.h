@@ -74,6 +74,8 @@ void ocl_rmm(const ocl_matrix*, const double* V, int32_t vCols, double* out, int
 void ocl_lmm(const ocl_matrix*, const double* Yt, int32_t yRows, double* out, int k);
 void ocl_tsmm(const ocl_matrix*, double* out, int k, int allowFallback);
 void ocl_mmchain(const ocl_matrix*, const double* v, const double* w, int ctype, double* out, int k);
+/* t(left) %*% right on two compressed blocks with the same number of rows; out [left.nCols x right.nCols] */
+void ocl_tmm(const ocl_matrix* left, const ocl_matrix* right, double* out, int k);
 
 /* dense long-double evaluation of the same products from the decompressed matrix */
 void ocl_dense_rmm_ld(const double* X, int64_t n, int32_t m, const double* V, int32_t vCols, double* out);

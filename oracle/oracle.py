@@ -59,6 +59,7 @@ def lib() -> C.CDLL:
             "ocl_lmm": ([_P, _P, _I32, _P, C.c_int], None),
             "ocl_tsmm": ([_P, _P, C.c_int, C.c_int], None),
             "ocl_mmchain": ([_P, _P, _P, C.c_int, _P, C.c_int], None),
+            "ocl_tmm": ([_P, _P, _P, C.c_int], None),
             "ocl_dense_rmm_ld": ([_P, _I64, _I32, _P, _I32, _P], None),
             "ocl_dense_lmm_ld": ([_P, _I64, _I32, _P, _I32, _P], None),
             "ocl_dense_tsmm_ld": ([_P, _I64, _I32, _P], None),
@@ -218,6 +219,12 @@ class OracleMatrix:
     def tsmm(self, allow_fallback=True):
         out = np.zeros((self.nCols, self.nCols))
         lib().ocl_tsmm(self.h, _p(out), self.k, int(allow_fallback))
+        return out
+
+    def tmm(self, right):
+        """t(self) %*% right for another OracleMatrix with the same number of rows."""
+        out = np.zeros((self.nCols, right.nCols))
+        lib().ocl_tmm(self.h, right.h, _p(out), self.k)
         return out
 
     def mmchain(self, v, w=None, ctype=0):

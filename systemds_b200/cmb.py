@@ -196,8 +196,10 @@ class CLALibMatrixMult:
     @staticmethod
     def matrixMultiply(m1, m2, transposeLeft: bool = False, transposeRight: bool = False) -> np.ndarray:
         c1, c2 = isinstance(m1, CompressedMatrixBlock), isinstance(m2, CompressedMatrixBlock)
-        if c1 == c2:
-            raise native.CLAError(-3, "matrixMultiply: exactly one operand must be compressed")
+        if c1 and c2:
+            return CLALibMatrixMult._doubleCompressedMatrixMultiply(m1, m2, transposeLeft, transposeRight)
+        if not c1 and not c2:
+            raise native.CLAError(-3, "matrixMultiply: at least one operand must be compressed")
         if (c1 and transposeLeft) or (c2 and transposeRight):
             # t(X) %*% B = t(t(B) %*% X) and A %*% t(X) = t(X %*% t(A)): swap sides (:50-59), transpose the result
             r = CLALibMatrixMult.matrixMultiply(m2, m1, not transposeRight, not transposeLeft)
@@ -209,6 +211,21 @@ class CLALibMatrixMult:
         A = _f64(m1)
         A = A.reshape(1, -1) if A.ndim == 1 else A
         return CLALibLeftMultBy.leftMultByMatrix(m2, np.ascontiguousarray(A.T) if transposeLeft else A)
+
+
+    @staticmethod
+    def _doubleCompressedMatrixMultiply(m1, m2, transposeLeft: bool, transposeRight: bool) -> np.ndarray:
+        """Both operands compressed (CLALibMatrixMult.java:96-124): ``m1 %*% m2`` decompresses the right side,
+        ``t(m1) %*% m2`` stays compressed on both sides, ``m1 %*% t(m2)`` is not implemented by the reference
+        either, and ``t(m1) %*% t(m2)`` is ``t(m2 %*% m1)``."""
+        if not transposeLeft and not transposeRight:
+            return CLALibRightMultBy.rightMultByMatrix(m1, np.asarray(CLALibDecompress.decompress(m2)))
+        if transposeLeft and not transposeRight:
+            return CLALibLeftMultBy.leftMultByMatrixTransposed(m2, m1)
+        if not transposeLeft and transposeRight:
+            raise native.CLAError(-3, "Not Implemented compressed Matrix Mult to produce larger matrix")
+        r = CLALibMatrixMult.matrixMultiply(m2, m1)
+        return _wrap(np.ascontiguousarray(np.asarray(r).T), r.nnz)
 
 
 class CLALibRightMultBy:
@@ -239,7 +256,14 @@ class CLALibLeftMultBy:
 
     @staticmethod
     def leftMultByMatrixTransposed(right: CompressedMatrixBlock, left) -> np.ndarray:
-        """``t(left) %*% right`` with ``left`` dense ``[nRows x q]`` (CLALibLeftMultBy.java:73-83)."""
+        """``t(left) %*% right`` with ``left`` dense ``[nRows x q]`` (CLALibLeftMultBy.java:73-83) or a second
+        compressed block over the same rows (:100-112)."""
+        if isinstance(left, CompressedMatrixBlock):
+            if left.rlen != right.rlen:
+                raise native.CLAError(-4, "leftMultByMatrixTransposed: inner dimensions do not match")
+            out = np.empty((left.clen, right.clen), np.float64)
+            nnz = check(native.lib().cla_tmm(left.handle(), right.handle(), ptr(out)))
+            return _wrap(out, nnz)
         L = _f64(left)
         if L.ndim == 1:
             L = L.reshape(-1, 1)

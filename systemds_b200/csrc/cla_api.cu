@@ -515,7 +515,54 @@ static int64_t host_call(Matrix* m, const double* in1, size_t n1, const double* 
   return (int64_t)nnz;
 }
 
+// Two handles for one product: both are looked up, locked in address order (so two concurrent calls with the
+// operands swapped cannot deadlock) and checked to be finalized on the same device over the same rows.
+struct PairLock {
+  std::shared_ptr<Matrix> l, r;
+  std::unique_lock<std::mutex> k1, k2;
+};
+static int64_t lock_pair(cla_handle hl, cla_handle hr, PairLock& p) {
+  p.l = lookup(hl);
+  p.r = lookup(hr);
+  if (!p.l || !p.r) return fail(CLA_ERR_BAD_HANDLE, "unknown or destroyed handle");
+  Matrix *a = p.l.get(), *b = p.r.get();
+  if (a == b)
+    p.k1 = std::unique_lock<std::mutex>(a->mu);
+  else {
+    Matrix *first = a < b ? a : b, *second = a < b ? b : a;
+    p.k1 = std::unique_lock<std::mutex>(first->mu);
+    p.k2 = std::unique_lock<std::mutex>(second->mu);
+  }
+  if (!a->finalized || !b->finalized) return fail(CLA_ERR_STATE, "cla_finalize has not been called on both handles");
+  if (a->device != b->device) return fail(CLA_ERR_BAD_ARG, "tmm: both blocks must be on the same device");
+  if (a->nRows != b->nRows) return fail(CLA_ERR_SHAPE, "tmm: the blocks must have the same number of rows");
+  return CLA_OK;
+}
+static int64_t tmm_dev(Matrix* l, Matrix* r, double* dOut, cudaStream_t s) {
+  l->stats.calls_tsmm++;
+  if (l == r) return launch_tsmm(l, dOut, s);  // one block on both sides: the symmetric kernel
+  return launch_tmm(l, r, dOut, s);
+}
+
 extern "C" {
+
+int64_t cla_tmm(cla_handle left, cla_handle right, double* out) {
+  PairLock p;
+  int64_t rc = lock_pair(left, right, p);
+  if (rc < 0) return rc;
+  Matrix *l = p.l.get(), *r = p.r.get();
+  if (!out && (size_t)l->nCols * r->nCols) return fail(CLA_ERR_BAD_ARG, "tmm: null buffer");
+  return host_call(l, nullptr, 0, nullptr, 0, out, (size_t)l->nCols * r->nCols,
+                   [&](double*, double*, double* dOut, cudaStream_t s) { return tmm_dev(l, r, dOut, s); });
+}
+
+int64_t cla_tmm_dev(cla_handle left, cla_handle right, double* dOut, void* stream) {
+  PairLock p;
+  int64_t rc = lock_pair(left, right, p);
+  if (rc < 0) return rc;
+  CLA_CUDA(cudaSetDevice(p.l->device));
+  return tmm_dev(p.l.get(), p.r.get(), dOut, (cudaStream_t)stream);
+}
 
 int64_t cla_rmm(cla_handle h, const double* V, int32_t vRows, int32_t vCols, double* out) {
   GET_MATRIX(h);

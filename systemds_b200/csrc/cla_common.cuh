@@ -207,6 +207,7 @@ int64_t launch_rmm(Matrix* m, const double* dV, int vCols, double* dOut, cudaStr
 int64_t launch_rmm_dmma(Matrix* m, const double* dV, int vCols, double* dOut, cudaStream_t s);
 int64_t launch_lmm(Matrix* m, const double* dYt, int q, double* dOut, cudaStream_t s, bool afterFast = false);
 int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s);
+int64_t launch_tmm(Matrix* left, Matrix* right, double* dOut, cudaStream_t s);  // t(left) %*% right, both compressed
 int64_t launch_decompress(Matrix* m, double* dOut, cudaStream_t s);
 int64_t launch_decompress_range(Matrix* m, int r0, int r1, double* dOut, cudaStream_t s);
 int64_t launch_group_decode(Matrix* m, int devGroup, int32_t* dIds, cudaStream_t s);

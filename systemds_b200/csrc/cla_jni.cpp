@@ -91,6 +91,10 @@ JFN(jlong, tsmm)(JNIEnv* env, jclass, jlong h, jdoubleArray out) {
   Out o(env, out);
   return cla_tsmm(h, (double*)o.p);
 }
+JFN(jlong, tmm)(JNIEnv* env, jclass, jlong left, jlong right, jdoubleArray out) {
+  Out o(env, out);
+  return cla_tmm(left, right, (double*)o.p);
+}
 JFN(jlong, mmchain)(JNIEnv* env, jclass, jlong h, jdoubleArray v, jdoubleArray w, jint ctype, jdoubleArray out) {
   In vv(env, v), ww(env, w);
   Out o(env, out);

@@ -73,6 +73,51 @@ k_syrk_dmma(const double* __restrict__ X, int rows, int nCols, int nBlk, double*
   }
 }
 
+// grid: (blocks of A columns x blocks of B columns, k splits). A: [rows x aCols], B: [rows x bCols], both row-major
+// chunks of the same rows. C [aCols x bCols] += A^T B. Same staging and fragment layout as k_syrk_dmma.
+__global__ void __launch_bounds__(TS_THREADS)
+k_gemm_tn_dmma(const double* __restrict__ A, int aCols, const double* __restrict__ B, int bCols, int rows, int nBlkB,
+               double* __restrict__ C, int rowsPerSplit) {
+  __shared__ double sI[TS_KT * TS_LD];
+  __shared__ double sJ[TS_KT * TS_LD];
+  const int bi = blockIdx.x / nBlkB, bj = blockIdx.x - bi * nBlkB;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int rBeg = blockIdx.y * rowsPerSplit, rEnd = min(rows, rBeg + rowsPerSplit);
+  double c[8][2];
+#pragma unroll
+  for (int t = 0; t < 8; t++) c[t][0] = c[t][1] = 0.0;
+  const int am = lane >> 2, ak = lane & 3;
+  for (int r = rBeg; r < rEnd; r += TS_KT) {
+    for (int e = tid; e < TS_KT * TS_BLK; e += TS_THREADS) {
+      const int kk = e / TS_BLK, cc = e - kk * TS_BLK;
+      const int row = r + kk;
+      const int ci = bi * TS_BLK + cc, cj = bj * TS_BLK + cc;
+      sI[kk * TS_LD + cc] = (row < rEnd && ci < aCols) ? A[(size_t)row * aCols + ci] : 0.0;
+      sJ[kk * TS_LD + cc] = (row < rEnd && cj < bCols) ? B[(size_t)row * bCols + cj] : 0.0;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k0 = 0; k0 < TS_KT; k0 += 4) {
+      const double a = sI[(k0 + ak) * TS_LD + warp * 8 + am];
+#pragma unroll
+      for (int t = 0; t < 8; t++) {
+        const double b = sJ[(k0 + ak) * TS_LD + t * 8 + am];
+        dmma884(c[t][0], c[t][1], a, b);
+      }
+    }
+    __syncthreads();
+  }
+  const int gi = bi * TS_BLK + warp * 8 + (lane >> 2);
+#pragma unroll
+  for (int t = 0; t < 8; t++) {
+#pragma unroll
+    for (int u = 0; u < 2; u++) {
+      const int gj = bj * TS_BLK + t * 8 + (lane & 3) * 2 + u;
+      if (gi < aCols && gj < bCols && c[t][u] != 0.0) atomicAdd(&C[(size_t)gi * bCols + gj], c[t][u]);
+    }
+  }
+}
+
 // --------------------------------------------------------------------------------------------------
 // Up to 128 columns: one CTA holds the whole upper triangle of the result (8x8 DMMA tiles, split over the 8
 // warps in row-major order so a warp's tiles share their A fragment), so nothing of the product is computed
@@ -411,6 +456,43 @@ int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s) {
   }
   k_mirror<<<std::max(1, std::min(1024, (int)(((int64_t)n * n + 255) / 256))), 256, 0, s>>>(dOut, n);
   m->stats.kernel_launches++;
+  CLA_CUDA(cudaGetLastError());
+  return CLA_OK;
+}
+
+// t(L) %*% R for two compressed matrices over the same rows (CLALibLeftMultBy.leftMultByMatrixTransposed on two
+// compressed blocks, lib/CLALibLeftMultBy.java:100-112,170-284). Both sides are decompressed one L2-sized row
+// chunk at a time (constants included, so no rank-1 corrections are needed) and the chunks are multiplied on
+// the FP64 tensor cores; the dense forms never reach HBM-sized buffers.
+int64_t launch_tmm(Matrix* L, Matrix* R, double* dOut, cudaStream_t s) {
+  const int a = L->nCols, b = R->nCols;
+  if ((int64_t)a * b == 0) return CLA_OK;
+  CLA_CUDA(cudaMemsetAsync(dOut, 0, sizeof(double) * (size_t)a * b, s));
+  if (L->nRows == 0) return CLA_OK;
+  int64_t rc;
+  int64_t chunk = (48ll << 20) / ((int64_t)(a + b) * 8);
+  chunk = std::max<int64_t>(SKIP_ROWS, (chunk / SKIP_ROWS) * SKIP_ROWS);
+  chunk = std::min<int64_t>(chunk, ((int64_t)L->nRows + SKIP_ROWS - 1) / SKIP_ROWS * SKIP_ROWS);
+  if ((rc = ensure_scratch2(L, (size_t)chunk * a * sizeof(double))) < 0) return rc;
+  if ((rc = ensure_scratch2(R, (size_t)chunk * b * sizeof(double))) < 0) return rc;
+  double* XL = (double*)L->scratch2;
+  double* XR = (double*)R->scratch2;
+  const int nBlkA = (a + TS_BLK - 1) / TS_BLK, nBlkB = (b + TS_BLK - 1) / TS_BLK;
+  const int nBlocks = nBlkA * nBlkB;
+  for (int64_t r0 = 0; r0 < L->nRows; r0 += chunk) {
+    const int r1 = (int)std::min<int64_t>(L->nRows, r0 + chunk);
+    if ((rc = launch_decompress_range(L, (int)r0, r1, XL, s)) < 0) return rc;
+    if ((rc = launch_decompress_range(R, (int)r0, r1, XR, s)) < 0) return rc;
+    const int rows = r1 - (int)r0;
+    int splits = std::max(1, std::min((rows + TS_KT * 8 - 1) / (TS_KT * 8), (4 * L->smCount + nBlocks - 1) / nBlocks));
+    int rowsPerSplit = ((rows + splits - 1) / splits + TS_KT - 1) / TS_KT * TS_KT;
+    splits = (rows + rowsPerSplit - 1) / rowsPerSplit;
+    dim3 grid(nBlocks, splits);
+    if (r0 == 0) prof_begin(L, s);
+    k_gemm_tn_dmma<<<grid, TS_THREADS, 0, s>>>(XL, a, XR, b, rows, nBlkB, dOut, rowsPerSplit);
+    if (r0 == 0) prof_end(L, s);
+    L->stats.kernel_launches++;
+  }
   CLA_CUDA(cudaGetLastError());
   return CLA_OK;
 }

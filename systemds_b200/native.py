@@ -50,6 +50,7 @@ SIGNATURES = {
     "cla_rmm": [_I64, _P, _I32, _I32, _P],
     "cla_lmm": [_I64, _P, _I32, _P],
     "cla_tsmm": [_I64, _P],
+    "cla_tmm": [_I64, _I64, _P],
     "cla_mmchain": [_I64, _P, _P, _I32, _P],
     "cla_decompress": [_I64, _P],
     "cla_unary_agg": [_I64, _I32, _P],
@@ -57,6 +58,7 @@ SIGNATURES = {
     "cla_lmm_dev": [_I64, _P, _I32, _P, _P],
     "cla_lmm_vec_noalloc_dev": [_I64, _P, _P, _P],
     "cla_tsmm_dev": [_I64, _P, _P],
+    "cla_tmm_dev": [_I64, _I64, _P, _P],
     "cla_mmchain_dev": [_I64, _P, _P, _I32, _P, _P, _P],
     "cla_group_decode": [_I64, _I32, _P],
     "cla_group_counts": [_I64, _I32, _P],

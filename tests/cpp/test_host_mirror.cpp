@@ -127,6 +127,21 @@ int main() {
         }
       report("mmchain", relErr(W.values, refw, scw), 1e-11);
     }
+    {  // t(B) %*% X with B a second compressed block over the same rows (two dense columns)
+      std::vector<double> Bv((size_t)n * 2);
+      for (auto& x : Bv) x = N(rng);
+      CompressedMatrixBlock B(n, 2);
+      B.allocateColGroup(std::make_shared<ColGroupUncompressed>(std::vector<int32_t>{0, 1}, Bv));
+      MatrixBlock T = CLALibLeftMultByCompressed::leftMultByMatrixTransposed(cmb, B);
+      std::vector<double> ref(2 * m, 0.0), sc(2 * m, 0.0);
+      for (int r = 0; r < n; r++)
+        for (int a = 0; a < 2; a++)
+          for (int b = 0; b < m; b++) {
+            ref[a * m + b] += Bv[(size_t)r * 2 + a] * X[(size_t)r * m + b];
+            sc[a * m + b] += std::fabs(Bv[(size_t)r * 2 + a] * X[(size_t)r * m + b]);
+          }
+      report("tmm", relErr(T.values, ref, sc), 1e-12);
+    }
     {  // error behaviour: shape mismatch surfaces as the reference's exception with its message prefix
       bool thrown = false;
       try {

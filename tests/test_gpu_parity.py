@@ -4,7 +4,7 @@ import pytest
 
 from systemds_b200 import CLAError, CompressedMatrixBlock, datagen
 from systemds_b200 import colgroup as cg
-from systemds_b200.cmb import (CHAIN_XtwXv, CLALibDecompress, CLALibLeftMultBy, CLALibMMChain, CLALibRightMultBy,
+from systemds_b200.cmb import (CHAIN_XtwXv, CLALibDecompress, CLALibLeftMultBy, CLALibMatrixMult, CLALibMMChain, CLALibRightMultBy,
                                CLALibTSMM)
 from systemds_b200.mapping import MapToFactory
 from tests.util import TOL, dense_of, rel_err
@@ -335,6 +335,58 @@ def test_offset_and_run_edge_cases(oracle):
     assert rel_err(CLALibTSMM.leftMultByTransposeSelf(cmb), oracle.dense_tsmm_ld(X), np.abs(X).T @ np.abs(X) + 1e-300) < TOL
     assert rel_err(CLALibDecompress.decompress(cmb), X) < 1e-14
     cmb.free()
+
+
+TMM_CASES = [
+    (("ddc", "sdc", "rle", "const"), ("ddc2", "sdcz", "ole", "unc")),
+    (("unc", "ddc", "sdcs"), ("unc", "rle", "ddc_char", "sdc", "empty")),
+    (("ddc",) * 70, ("ddc",) * 3),
+    (("ddcfor", "sdcfor", "ddc_bit"), ("sdcsz", "ddc", "ddc")),
+]
+
+
+@pytest.mark.parametrize("case", range(len(TMM_CASES)))
+@pytest.mark.parametrize("nRows", [1, 1000, 70001])
+def test_compressed_times_compressed(oracle, case, nRows):
+    """t(A) %*% B with both sides compressed (leftMultByMatrixTransposed on two blocks, and the transpose
+    cases of CLALibMatrixMult.matrixMultiply for two compressed operands)."""
+    ka, kb = TMM_CASES[case]
+    A = datagen.random_cmb(500 + case, nRows, ka).to_device()
+    B = datagen.random_cmb(600 + case, nRows, kb).to_device()
+    XA, XB = dense_of(A), dense_of(B)
+    scale = np.abs(XA).T @ np.abs(XB) + 1e-300
+    want = oracle.OracleMatrix(A).tmm(oracle.OracleMatrix(B))
+    got = CLALibLeftMultBy.leftMultByMatrixTransposed(B, A)
+    assert got.shape == (A.clen, B.clen)
+    assert rel_err(got, want, scale) < TOL
+    assert rel_err(got, XA.T @ XB, scale) < TOL
+    assert got.nnz == int(np.count_nonzero(got))
+    assert rel_err(CLALibMatrixMult.matrixMultiply(A, B, True, False), want, scale) < TOL
+    # same block on both sides equals TSMM
+    if not any(k == "unc" for k in ka):
+        both = CLALibLeftMultBy.leftMultByMatrixTransposed(A, A)
+        assert rel_err(both, XA.T @ XA, np.abs(XA).T @ np.abs(XA) + 1e-300) < TOL
+    with pytest.raises(CLAError):
+        CLALibMatrixMult.matrixMultiply(A, B, False, True)
+    A.free()
+    B.free()
+
+
+def test_double_compressed_transpose_rules():
+    """The remaining flag combinations for two compressed operands (CLALibMatrixMult.java:96-124)."""
+    m1 = datagen.random_cmb(801, 40, ("ddc", "sdc", "rle", "const")).to_device()       # [40 x c1]
+    m2 = datagen.random_cmb(802, 6, ("ddc",) * 37 + ("sdcz", "unc")).to_device()       # [6 x 40]
+    X1, X2 = dense_of(m1), dense_of(m2)
+    if X2.shape[1] == 40:
+        r = CLALibMatrixMult.matrixMultiply(m2, m1)                                    # plain: right side decompressed
+        assert rel_err(r, X2 @ X1, np.abs(X2) @ np.abs(X1) + 1e-300) < TOL
+        r = CLALibMatrixMult.matrixMultiply(m1, m2, True, True)                        # t(m1) t(m2) = t(m2 m1)
+        assert r.shape == (X1.shape[1], 6)
+        assert rel_err(r, X1.T @ X2.T, np.abs(X1).T @ np.abs(X2).T + 1e-300) < TOL
+    else:
+        pytest.fail("generator produced %d columns" % X2.shape[1])
+    m1.free()
+    m2.free()
 
 
 def test_sum_aggregates():

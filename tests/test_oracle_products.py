@@ -47,6 +47,23 @@ def test_oracle_vs_dense(oracle, name, kinds, overlap, nRows):
     assert rel_err(om.mmchain(v, w, 1).ravel(), X.T @ (w * ref_u), np.abs(X).T @ (np.abs(w) * (np.abs(X) @ np.abs(v))) + 1e-300) < 1e-11
 
 
+@pytest.mark.parametrize("nRows", [1, 37, 5000])
+def test_oracle_compressed_times_compressed(oracle, nRows):
+    """t(A) %*% B on two compressed blocks against the dense product (and against itself with one thread)."""
+    pairs = [(("ddc", "sdc", "rle", "const"), ("ddc2", "sdcz", "ole", "unc")),
+             (("unc", "ddc", "sdcs", "sdcfor"), ("unc", "rle", "ddc_char", "sdc", "empty")),
+             (datagen.KINDS, datagen.KINDS)]
+    for i, (ka, kb) in enumerate(pairs):
+        A = datagen.random_cmb(31 + i + nRows, nRows, ka)
+        B = datagen.random_cmb(41 + i + nRows, nRows, kb)
+        XA, XB = dense_of(A), dense_of(B)
+        sc = np.abs(XA).T @ np.abs(XB) + 1e-300
+        got = oracle.OracleMatrix(A, threads=3).tmm(oracle.OracleMatrix(B, threads=3))
+        assert got.shape == (A.clen, B.clen)
+        assert rel_err(got, XA.T @ XB, sc) < TOL
+        assert rel_err(got, oracle.OracleMatrix(A, threads=1).tmm(oracle.OracleMatrix(B, threads=1)), sc) < TOL
+
+
 def test_tsmm_integer_exact(oracle):
     """CLALibMMChainTest.java:159-171: integer-valued dictionaries give a 0-ULP self product."""
     cmb = datagen.random_cmb(11, 3000, ("ddc", "ddc2", "sdcz", "rle", "ddc_bit"), integer=True)
