@@ -92,6 +92,15 @@ int64_t cla_set_profile(cla_handle h, int32_t on);
  * `device`, the denominators of the tensor-pipe and FMA fractions reported for the kernels. About 0.1 s. */
 int64_t cla_measure_fp64_peaks(int32_t device, double* dmmaTflops, double* dfmaTflops);
 
+/* Builds a handle from the serialized form of a block: replaces CompressedMatrixBlock.read(DataInput)
+ * (runtime/compress/CompressedMatrixBlock.java:486-496) and ColGroupIO.readGroups (colgroup/ColGroupIO.java:48-63).
+ * `bytes` is the big-endian stream CompressedMatrixBlock.write(DataOutput) produced (what a Spark broadcast, an
+ * evicted buffer-pool entry or a binary file holds). Returns the new, not yet finalized handle (> 0) or a CLA_ERR_*
+ * code: CLA_ERR_BAD_ARG for a truncated stream, CLA_ERR_UNSUPPORTED for classes outside this library (LZW / delta /
+ * linear-functional groups, quantised / delta / placeholder / identity-slice dictionaries, de-duplicated dense
+ * blocks). *nonZeros receives the header's count, *consumed the bytes read; both may be NULL. */
+cla_handle cla_read_block(const uint8_t* bytes, int64_t len, int64_t* nonZeros, int64_t* consumed);
+
 /* ---- group registration (host arrays are copied) -------------------------------------------
  * Each returns the index of the new group (>= 0) or a CLA_ERR_* code.
  * colIdx: the group's IColIndex flattened to int32 (colgroup/indexes/ColIndexFactory.java:38-118).

@@ -64,6 +64,37 @@ class CompressedMatrixBlock:
     def index_bytes(self) -> int:
         return sum(g.index_bytes() for g in self._colGroups)
 
+    # --- serialized form (CompressedMatrixBlock.java:470-519) -----------------------------------
+    def write(self, nonZeros: int = -1) -> bytes:
+        """The byte stream of ``write(DataOutput)``."""
+        from . import wire
+        return wire.write_compressed_matrix_block(self, nonZeros)
+
+    @staticmethod
+    def read(buf) -> "CompressedMatrixBlock":
+        """``CompressedMatrixBlock.read(DataInput)``: host-side groups, not yet on the device."""
+        from . import wire
+        return wire.read_compressed_matrix_block(buf)[0]
+
+    @staticmethod
+    def read_to_device(buf, device: int = 0) -> "CompressedMatrixBlock":
+        """Hands the byte stream to the native library's own reader (``cla_read_block``) and uploads: no host-side
+        group objects are built, ``getColGroups()`` stays empty."""
+        L = native.lib()
+        raw = np.frombuffer(bytes(buf), dtype=np.uint8)
+        used = C.c_int64(0)
+        h = check(L.cla_read_block(ptr(raw), raw.shape[0], None, C.byref(used)))
+        st = native.cla_stats()
+        try:
+            check(L.cla_stats_get(h, C.byref(st)))
+            check(L.cla_finalize(h, int(device)))
+        except Exception:
+            L.cla_destroy(h)
+            raise
+        cmb = CompressedMatrixBlock(st.n_rows, st.n_cols)
+        cmb._handle, cmb.device, cmb._reg_index = h, int(device), list(range(st.n_groups))
+        return cmb
+
     # --- device residency ----------------------------------------------------------------------
     def to_device(self, device: int = 0) -> "CompressedMatrixBlock":
         """Register every group with the native library and upload (cla_create .. cla_finalize)."""

@@ -30,6 +30,12 @@ struct Out {  // pinned output array, contents copied back
 JFN(jlong, create)(JNIEnv*, jclass, jint nRows, jint nCols, jboolean overlapping) {
   return cla_create(nRows, nCols, overlapping ? 1 : 0);
 }
+// the serialized block (CompressedMatrixBlock.write into a byte[]) in one call instead of one call per group
+JFN(jlong, readBlock)(JNIEnv* env, jclass, jbyteArray bytes) {
+  const jint len = bytes ? env->GetArrayLength(bytes) : 0;  // before pinning: no JNI calls inside a critical region
+  In b(env, bytes);
+  return cla_read_block((const uint8_t*)b.p, len, nullptr, nullptr);
+}
 JFN(jlong, destroy)(JNIEnv*, jclass, jlong h) { return cla_destroy(h); }
 JFN(jlong, finalizeUpload)(JNIEnv*, jclass, jlong h, jint device) { return cla_finalize(h, device); }
 JFN(jstring, lastError)(JNIEnv* env, jclass) {

@@ -49,6 +49,7 @@ SIGNATURES = {
     "cla_add_group_empty": [_I64, _P, _I32],
     "cla_rmm": [_I64, _P, _I32, _I32, _P],
     "cla_lmm": [_I64, _P, _I32, _P],
+    "cla_read_block": [_P, _I64, _P, _P],
     "cla_tsmm": [_I64, _P],
     "cla_tmm": [_I64, _I64, _P],
     "cla_mmchain": [_I64, _P, _P, _I32, _P],
