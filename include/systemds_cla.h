@@ -152,10 +152,20 @@ int64_t cla_tmm(cla_handle left, cla_handle right, double* out);
 
 /* Sum aggregates on the compressed block, the uak+ / uark+ / uack+ cases of lib/CLALibCompAgg.java
  * (colgroup/AColGroupCompressed.java:140-205 computeSum / computeRowSums / computeColSums):
- * CLA_AGG_COL_SUMS -> out[nCols], CLA_AGG_ROW_SUMS -> out[nRows], CLA_AGG_SUM -> out[1]. Host buffer. */
+ * CLA_AGG_COL_* -> out[nCols], CLA_AGG_ROW_* -> out[nRows], CLA_AGG_SUM / MIN / MAX -> out[1]. Host buffer. */
 #define CLA_AGG_COL_SUMS 0
 #define CLA_AGG_ROW_SUMS 1
 #define CLA_AGG_SUM 2
+/* min / max (uacmin, uacmax, uarmin, uarmax, uamin, uamax). Column-wise and full extrema of a block whose groups
+ * do not overlap follow the reference's dictionary-based definition (AColGroupCompressed.computeMxx /
+ * computeColMxx: every dictionary entry counts, plus the default tuple or 0 where rows fall outside the
+ * index structure); row-wise extrema and overlapping blocks go through decompressed row chunks. */
+#define CLA_AGG_COL_MINS 3
+#define CLA_AGG_COL_MAXS 4
+#define CLA_AGG_ROW_MINS 5
+#define CLA_AGG_ROW_MAXS 6
+#define CLA_AGG_MIN 7
+#define CLA_AGG_MAX 8
 int64_t cla_unary_agg(cla_handle h, int32_t op, double* out);
 
 /* ---- products, device buffers --------------------------------------------------------------

@@ -258,3 +258,43 @@ def dense_tsmm_ld(X):
     out = np.zeros((X.shape[1], X.shape[1]))
     lib().ocl_dense_tsmm_ld(_p(X), X.shape[0], X.shape[1], _p(out))
     return out
+
+
+def col_minmax(cmb):
+    """Column minima and maxima of a non-overlapping block as the reference computes them: per group from the
+    dictionary, every entry counting whether used or not (AColGroupCompressed.computeColMxx): DDC / Const
+    ``_dict.aggregateCols`` (ColGroupDDC.java:831-833, ColGroupConst.java:370-372); SDC / SDCSingle dictionary and
+    default tuple (ColGroupSDC.java:182-186); SDCZeros / SDCSingleZeros dictionary and 0 (ColGroupSDCZeros.java:
+    807-812); RLE / OLE dictionary and 0 when ``_zeros`` (ColGroupRLE.java:730-735); FOR groups dictionary +
+    reference (and the reference itself for SDCFOR's unlisted rows); Empty 0; Uncompressed from its data."""
+    from systemds_b200 import colgroup as cg
+    lo = np.full(cmb.getNumColumns(), np.inf)
+    hi = np.full(cmb.getNumColumns(), -np.inf)
+
+    def add(cols, vals):
+        vals = np.atleast_2d(np.asarray(vals, dtype=np.float64))
+        lo[cols] = np.minimum(lo[cols], vals.min(axis=0))
+        hi[cols] = np.maximum(hi[cols], vals.max(axis=0))
+
+    n = cmb.getNumRows()
+    for g in cmb.getColGroups():
+        cols = g.getColIndices()
+        if isinstance(g, cg.ColGroupEmpty):
+            add(cols, np.zeros(len(cols)))
+        elif isinstance(g, cg.ColGroupUncompressed):
+            add(cols, g._data)
+        elif isinstance(g, cg.ColGroupDDCFOR):
+            add(cols, g._dict + g._reference)
+        elif isinstance(g, cg.ColGroupSDCFOR):
+            add(cols, g._dict + g._reference)
+            add(cols, g._reference)
+        elif isinstance(g, (cg.ColGroupDDC, cg.ColGroupConst)):
+            add(cols, g._dict)
+        elif isinstance(g, cg.ASDC):
+            add(cols, g._dict)
+            add(cols, np.zeros(len(cols)) if g._defaultTuple is None else g._defaultTuple)
+        elif isinstance(g, cg.AColGroupOffset):
+            add(cols, g._dict)
+            if int((g.row_ids(n) >= 0).sum()) < n:
+                add(cols, np.zeros(len(cols)))
+    return lo, hi

@@ -328,7 +328,8 @@ class CLALibMMChain:
 
 
 class CLALibCompAgg:
-    """Sum aggregates of ``CLALibCompAgg.aggregateUnary`` (runtime/compress/lib/CLALibCompAgg.java): uack+, uark+, uak+."""
+    """Sum and min / max aggregates of ``CLALibCompAgg.aggregateUnary`` (runtime/compress/lib/CLALibCompAgg.java):
+    uack+, uark+, uak+, uacmin/max, uarmin/max, uamin/max."""
 
     @staticmethod
     def colSums(cmb: CompressedMatrixBlock) -> np.ndarray:
@@ -347,6 +348,37 @@ class CLALibCompAgg:
         out = np.empty(1, np.float64)
         check(native.lib().cla_unary_agg(cmb.handle(), 2, ptr(out)))
         return float(out[0])
+
+
+    @staticmethod
+    def _agg(cmb, op, shape):
+        out = np.empty(shape, np.float64)
+        check(native.lib().cla_unary_agg(cmb.handle(), op, ptr(out)))
+        return out
+
+    @staticmethod
+    def colMins(cmb: CompressedMatrixBlock) -> np.ndarray:
+        return CLALibCompAgg._agg(cmb, 3, (1, cmb.clen))
+
+    @staticmethod
+    def colMaxs(cmb: CompressedMatrixBlock) -> np.ndarray:
+        return CLALibCompAgg._agg(cmb, 4, (1, cmb.clen))
+
+    @staticmethod
+    def rowMins(cmb: CompressedMatrixBlock) -> np.ndarray:
+        return CLALibCompAgg._agg(cmb, 5, (cmb.rlen, 1))
+
+    @staticmethod
+    def rowMaxs(cmb: CompressedMatrixBlock) -> np.ndarray:
+        return CLALibCompAgg._agg(cmb, 6, (cmb.rlen, 1))
+
+    @staticmethod
+    def min(cmb: CompressedMatrixBlock) -> float:
+        return float(CLALibCompAgg._agg(cmb, 7, (1,))[0])
+
+    @staticmethod
+    def max(cmb: CompressedMatrixBlock) -> float:
+        return float(CLALibCompAgg._agg(cmb, 8, (1,))[0])
 
 
 class CLALibDecompress:

@@ -1,5 +1,6 @@
 // extern "C" entry points declared in include/systemds_cla.h.
 #include "cla_common.cuh"
+#include <cmath>
 #include <cstring>
 #include <memory>
 #include <vector>
@@ -619,8 +620,35 @@ int64_t cla_mmchain(cla_handle h, const double* v, const double* w, int32_t ctyp
 int64_t cla_unary_agg(cla_handle h, int32_t op, double* out) {
   GET_MATRIX(h);
   REQUIRE_FINAL();
-  if (op < CLA_AGG_COL_SUMS || op > CLA_AGG_SUM) return fail(CLA_ERR_BAD_ARG, "unary aggregate: unknown operation");
+  if (op < CLA_AGG_COL_SUMS || op > CLA_AGG_MAX) return fail(CLA_ERR_BAD_ARG, "unary aggregate: unknown operation");
   if (!out) return fail(CLA_ERR_BAD_ARG, "unary aggregate: null buffer");
+  if (op == CLA_AGG_ROW_MINS || op == CLA_AGG_ROW_MAXS)
+    return host_call(m, nullptr, 0, nullptr, 0, out, (size_t)m->nRows, [&](double*, double*, double* dOut, cudaStream_t s) {
+      return row_minmax(m, op == CLA_AGG_ROW_MAXS, dOut, s);
+    });
+  if (op >= CLA_AGG_COL_MINS) {
+    CLA_CUDA(cudaSetDevice(m->device));
+    std::vector<double> lo, hi;
+    int64_t rc = col_minmax(m, lo, hi, m->stream);
+    if (rc < 0) return rc;
+    if ((rc = check_errword(m)) < 0) return rc;
+    const bool wantMax = (op == CLA_AGG_COL_MAXS || op == CLA_AGG_MAX);
+    const std::vector<double>& v = wantMax ? hi : lo;
+    int64_t nnz = 0;
+    if (op == CLA_AGG_MIN || op == CLA_AGG_MAX) {
+      // an empty block aggregates to 0 like an empty MatrixBlock (runtime/matrix/data/MatrixBlock.java min / max)
+      double r = (m->nRows == 0 || m->nCols == 0) ? 0.0 : (wantMax ? -INFINITY : INFINITY);
+      if (m->nRows > 0)
+        for (double x : v) r = wantMax ? std::fmax(r, x) : std::fmin(r, x);
+      out[0] = r;
+      return r != 0.0 ? 1 : 0;
+    }
+    for (int c = 0; c < m->nCols; c++) {
+      out[c] = m->nRows == 0 ? 0.0 : v[c];
+      nnz += out[c] != 0.0;
+    }
+    return nnz;
+  }
   if (op == CLA_AGG_ROW_SUMS) {
     std::vector<double> ones((size_t)m->nCols, 1.0);
     return host_call(m, ones.data(), ones.size(), nullptr, 0, out, (size_t)m->nRows,

@@ -147,6 +147,8 @@ struct Matrix {
   int nDev = 0;
   int64_t totalVals = 0;         // sum of nVals over dictionary groups
   std::vector<double> constV;    // host copy
+  std::vector<double> colMin, colMax;  // per-column extrema over the compressed groups, dictionary-based (cla_agg.cu)
+  bool multiCover = false;             // some column is held by more than one registered group (e.g. FOR group + reference)
   double* dConstV = nullptr;     // [nCols]
   void* dDenseCols = nullptr;    // list of dense-operand columns for the tensor-core RMM (built on first use)
   int nDenseCols = 0;
@@ -206,6 +208,9 @@ int64_t ensure_small(Matrix* m, size_t bytes);
 int64_t launch_rmm(Matrix* m, const double* dV, int vCols, double* dOut, cudaStream_t s, bool afterFast = false);
 int64_t launch_rmm_dmma(Matrix* m, const double* dV, int vCols, double* dOut, cudaStream_t s);
 int64_t launch_lmm(Matrix* m, const double* dYt, int q, double* dOut, cudaStream_t s, bool afterFast = false);
+void minmax_of_group(const HostGroup& hg, int nRows, std::vector<double>& colMin, std::vector<double>& colMax);
+int64_t col_minmax(Matrix* m, std::vector<double>& lo, std::vector<double>& hi, cudaStream_t s);
+int64_t row_minmax(Matrix* m, int wantMax, double* dOut, cudaStream_t s);
 int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s);
 int64_t launch_tmm(Matrix* left, Matrix* right, double* dOut, cudaStream_t s);  // t(left) %*% right, both compressed
 int64_t launch_decompress(Matrix* m, double* dOut, cudaStream_t s);

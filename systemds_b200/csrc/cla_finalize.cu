@@ -2,6 +2,7 @@
 // kernels that turn the reference's index structures into row ids (used by the bit-exact checks
 // and, for RLE / OLE, once at upload to build the row-ordered forms the product kernels read).
 #include "cla_common.cuh"
+#include <cmath>
 #include <cub/cub.cuh>
 #include <algorithm>
 #include <cstring>
@@ -400,9 +401,21 @@ int64_t finalize_device(Matrix* m) {
   m->regToDev.assign(m->hg.size(), -1);
   m->groups.clear();
   int64_t valOff = 0;
+  m->colMin.assign(m->nCols, INFINITY);
+  m->colMax.assign(m->nCols, -INFINITY);
+  {
+    std::vector<uint8_t> seen(m->nCols, 0);
+    m->multiCover = false;
+    for (auto& hg : m->hg)
+      for (int c : hg.cols) {
+        m->multiCover |= seen[c] != 0;
+        seen[c] = 1;
+      }
+  }
   for (size_t gi = 0; gi < m->hg.size(); gi++) {
     HostGroup& hg = m->hg[gi];
     const int gc = (int)hg.cols.size();
+    minmax_of_group(hg, m->nRows, m->colMin, m->colMax);
     if (hg.type == GT_EMPTY) continue;
     if (hg.type == GT_CONST) {  // ColGroupConst.addToCommon
       for (int j = 0; j < gc; j++) m->constV[hg.cols[j]] += hg.dict[j];

@@ -372,6 +372,31 @@ def test_compressed_times_compressed(oracle, case, nRows):
     B.free()
 
 
+@pytest.mark.parametrize("name,kinds,overlap", CASES)
+@pytest.mark.parametrize("nRows", [1, 37, 5000, 70001])
+def test_min_max_aggregates(oracle, name, kinds, overlap, nRows):
+    """uacmin / uacmax / uarmin / uarmax / uamin / uamax. Row-wise and overlapping cases are true extrema of the
+    decompressed rows (one rounding for default + (dict - default)); column-wise and full extrema of
+    non-overlapping blocks follow the reference's dictionary-based definition."""
+    from systemds_b200.cmb import CLALibCompAgg
+    cmb = datagen.random_cmb(seed_of(name, nRows) + 5, nRows, kinds, overlap).to_device()
+    X = dense_of(cmb)
+    sc = np.abs(X).max() + 1.0
+    assert np.abs(CLALibCompAgg.rowMins(cmb).ravel() - X.min(axis=1)).max() < 1e-14 * sc
+    assert np.abs(CLALibCompAgg.rowMaxs(cmb).ravel() - X.max(axis=1)).max() < 1e-14 * sc
+    has_for = any(isinstance(g, (cg.ColGroupDDCFOR, cg.ColGroupSDCFOR)) for g in cmb.getColGroups())
+    if overlap or has_for:
+        lo, hi = X.min(axis=0), X.max(axis=0)
+    else:
+        lo, hi = oracle.col_minmax(cmb)
+        assert np.all(lo <= X.min(axis=0) + 1e-14 * sc) and np.all(hi >= X.max(axis=0) - 1e-14 * sc)
+    tol = 1e-14 * sc if (overlap or has_for) else 0.0
+    assert np.abs(CLALibCompAgg.colMins(cmb).ravel() - lo).max() <= tol
+    assert np.abs(CLALibCompAgg.colMaxs(cmb).ravel() - hi).max() <= tol
+    assert abs(CLALibCompAgg.min(cmb) - lo.min()) <= tol and abs(CLALibCompAgg.max(cmb) - hi.max()) <= tol
+    cmb.free()
+
+
 def test_double_compressed_transpose_rules():
     """The remaining flag combinations for two compressed operands (CLALibMatrixMult.java:96-124)."""
     m1 = datagen.random_cmb(801, 40, ("ddc", "sdc", "rle", "const")).to_device()       # [40 x c1]
