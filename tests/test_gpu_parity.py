@@ -397,6 +397,41 @@ def test_min_max_aggregates(oracle, name, kinds, overlap, nRows):
     cmb.free()
 
 
+def test_concurrent_handles_and_shared_handle():
+    """Calls on different handles may run concurrently (one stream per handle); calls on one handle are serialised
+    by its mutex. Both must give the single-threaded bits."""
+    import threading
+    a = _ddc_matrix(200001, [16] * 30 + [250] * 10, 21).to_device()
+    b = datagen.random_cmb(99, 50000, ("ddc", "sdc", "rle", "unc", "const", "ddc_char")).to_device()
+    rng = np.random.default_rng(5)
+    va, vb = rng.standard_normal(a.clen), rng.standard_normal(b.clen)
+    Vb = rng.standard_normal((b.clen, 16))
+    want = [np.array(CLALibRightMultBy.rightMultByMatrix(a, va)), np.array(CLALibMMChain.mmChain(a, va)),
+            np.array(CLALibRightMultBy.rightMultByMatrix(b, vb)), np.array(CLALibRightMultBy.rightMultByMatrix(b, Vb))]
+    bad = []
+
+    def work(which):
+        for _ in range(10):
+            if which == 0:
+                got = [CLALibRightMultBy.rightMultByMatrix(a, va), CLALibMMChain.mmChain(a, va)]
+                ref = want[:2]
+            else:
+                got = [CLALibRightMultBy.rightMultByMatrix(b, vb), CLALibRightMultBy.rightMultByMatrix(b, Vb)]
+                ref = want[2:]
+            for g, w in zip(got, ref):
+                if not np.array_equal(np.array(g), w):
+                    bad.append(which)
+
+    threads = [threading.Thread(target=work, args=(i % 2,)) for i in range(4)]  # two threads per handle
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not bad
+    a.free()
+    b.free()
+
+
 def test_double_compressed_transpose_rules():
     """The remaining flag combinations for two compressed operands (CLALibMatrixMult.java:96-124)."""
     m1 = datagen.random_cmb(801, 40, ("ddc", "sdc", "rle", "const")).to_device()       # [40 x c1]
