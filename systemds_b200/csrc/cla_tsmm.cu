@@ -315,6 +315,211 @@ k_tsmm_tri(const DevGroup* __restrict__ groups, const int32_t* __restrict__ colS
   }
 }
 
+// --------------------------------------------------------------------------------------------------
+// The same product with 16 warps in one CTA per SM. The triangle's tiles are dealt to the warps as contiguous
+// runs of the row-major tile order (at most T16_MAXT tiles each, so a warp's A fragment changes at most twice),
+// which cuts the accumulators from 96 to 18 registers per thread and leaves room for a two-deep register
+// pipeline of the decode: while the DMMAs of stage s run, the dictionary gathers of stage s+1 and the map loads
+// of stage s+2 are in flight, and their results are written to the other shared-memory buffer only after the
+// DMMAs have been issued. The 8-warp kernel above stalls on those gathers (its decode must finish, values in
+// shared memory, before its DMMAs start).
+// --------------------------------------------------------------------------------------------------
+__device__ __forceinline__ double ld_f64_here(const double* p) {
+  double v;
+  asm volatile("ld.global.nc.f64 %0, [%1];" : "=d"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_u8_here(const uint8_t* p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.u8 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_u16_here(const uint16_t* p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+
+constexpr int T16_WARPS = 16;
+constexpr int T16_THREADS = T16_WARPS * 32;
+constexpr int T16_MAXC = 8;   // columns decoded per warp and stage at 128 columns
+
+template <bool FUSED, int MT, int TPW>
+__global__ void __launch_bounds__(T16_THREADS, 1)
+k_tsmm_tri16(const DevGroup* __restrict__ groups, const int32_t* __restrict__ colSrc, const double* __restrict__ constV,
+             const double* __restrict__ X, int rowBegin, int rowEnd, int nCols, double* __restrict__ C) {
+  extern __shared__ __align__(16) double XtAll[];  // two stages of [NT * 8][TT_LD], then the column records
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int NT = (nCols + 7) >> 3;
+  const int nColsPad = NT * 8;
+  const int stageDoubles = nColsPad * TT_LD;
+  TsmmCol* cols = (TsmmCol*)(XtAll + 2 * stageDoubles);
+  if (FUSED) {
+    for (int cc = tid; cc < nColsPad; cc += T16_THREADS) {
+      TsmmCol d;
+      d.map = nullptr;
+      d.mapHi = nullptr;
+      d.src = nullptr;
+      d.cst = (constV && cc < nCols) ? constV[cc] : 0.0;
+      d.mapType = 0;
+      d.gCols = 1;
+      if (cc < nCols && colSrc[2 * cc] >= 0) {
+        const DevGroup& g = groups[colSrc[2 * cc]];
+        const int j = colSrc[2 * cc + 1];
+        d.gCols = g.gCols;
+        if (g.type == GT_UNC) {
+          d.mapType = -1;
+          d.src = g.dense + j;
+          d.map = g.dense;  // non-null marker
+        } else {
+          d.mapType = g.mapType;
+          d.map = g.mapType == CLA_MAP_ZERO ? (const void*)g.dict : g.map;
+          d.mapHi = g.mapHi;
+          d.src = g.dict + j;
+        }
+      }
+      cols[cc] = d;
+    }
+    __syncthreads();
+  }
+  // this warp's tiles: [t0, t1) of the row-major order of the upper triangle
+  const int nTiles = NT * (NT + 1) / 2;
+  const int t0 = nTiles * warp / T16_WARPS, t1 = nTiles * (warp + 1) / T16_WARPS;
+  const int am = lane >> 2, ak = lane & 3;
+  // Fragment offsets of each of the TPW tile slots. A slot the warp does not own points at tile (0, 0) and its
+  // accumulator is never written out: the inner loop then needs no test per slot. aMask bit sl: slot sl starts
+  // a new tile row, i.e. needs a fresh A fragment (bit 0 always).
+  int offA[TPW], offB[TPW];
+  uint32_t aMask = 1;
+  {
+    int I = 0, base = 0;  // base = linear index of tile (I, I)
+    while (I < NT && base + (NT - I) <= t0) {
+      base += NT - I;
+      I++;
+    }
+    int J = I + (t0 - base);
+#pragma unroll
+    for (int sl = 0; sl < TPW; sl++) {
+      if (t0 + sl < t1) {
+        offA[sl] = (I * 8 + am) * TT_LD + ak;
+        offB[sl] = (J * 8 + am) * TT_LD + ak;
+        if (J == I) aMask |= 1u << sl;
+        if (++J == NT) {
+          I++;
+          J = I;
+        }
+      } else {
+        offA[sl] = offB[sl] = am * TT_LD + ak;
+        aMask |= 1u << sl;
+      }
+    }
+  }
+  double c[TPW][2];
+#pragma unroll
+  for (int i = 0; i < TPW; i++) c[i][0] = c[i][1] = 0.0;
+
+  const int64_t nStages = ((int64_t)(rowEnd - rowBegin) + TT_KT - 1) / TT_KT;
+  const int64_t sa = nStages * blockIdx.x / gridDim.x, sb = nStages * (blockIdx.x + 1) / gridDim.x;
+  if (sa >= sb) return;
+
+  // ---- decode pipeline: column warp + 16 * b of the stage, lanes along the 32 rows ----
+  uint32_t ids[T16_MAXC];  // dictionary ids of the stage two ahead
+  double vals[T16_MAXC];   // values of the stage one ahead
+  auto load_ids = [&](int64_t st) {
+    if (!FUSED) return;
+    const int row = rowBegin + (int)st * TT_KT + lane;
+    const bool inRange = row < rowEnd;
+#pragma unroll
+    for (int b = 0; b < T16_MAXC; b++) {
+      const int cc = warp + T16_WARPS * b;
+      ids[b] = 0;
+      if (cc < nColsPad && inRange) {
+        const TsmmCol& d = cols[cc];
+        if (d.map && d.mapType >= 0) {
+          // the raw id only: any arithmetic on it here would wait for the load
+          if (MT == CLA_MAP_BYTE) ids[b] = ld_u8_here((const uint8_t*)d.map + row);
+          else if (MT == CLA_MAP_CHAR) ids[b] = ld_u16_here((const uint16_t*)d.map + row);
+          else ids[b] = (uint32_t)map_get(d.mapType, d.map, d.mapHi, row);
+        }
+      }
+    }
+  };
+  auto gather = [&](int64_t st) {  // issues the loads of a stage's values (uses ids for dense-map columns)
+    const int row = rowBegin + (int)st * TT_KT + lane;
+    const bool inRange = row < rowEnd;
+#pragma unroll
+    for (int b = 0; b < T16_MAXC; b++) {
+      const int cc = warp + T16_WARPS * b;
+      vals[b] = 0.0;
+      if (cc < nColsPad && inRange) {
+        // volatile asm keeps the load where it is written, ahead of the (volatile) DMMAs: left to itself the
+        // compiler sinks it to its use behind them and the pipeline is gone
+        if (FUSED) {
+          const TsmmCol& d = cols[cc];
+          if (d.map) vals[b] = ld_f64_here(d.src + (d.mapType < 0 ? (size_t)row : (size_t)ids[b]) * d.gCols);
+        } else if (cc < nCols)
+          vals[b] = ld_f64_here(X + (size_t)(row - rowBegin) * nCols + cc);
+      }
+    }
+  };
+  auto store = [&](int64_t st, double* Xt) {  // adds the constant part of the column (rows inside the matrix only)
+    const bool inRange = rowBegin + (int)st * TT_KT + lane < rowEnd;
+#pragma unroll
+    for (int b = 0; b < T16_MAXC; b++) {
+      const int cc = warp + T16_WARPS * b;
+      if (cc < nColsPad) Xt[cc * TT_LD + lane] = vals[b] + ((FUSED && inRange) ? cols[cc].cst : 0.0);
+    }
+  };
+  load_ids(sa);
+  gather(sa);
+  if (sa + 1 < sb) load_ids(sa + 1);
+  store(sa, XtAll);
+  __syncthreads();
+  for (int64_t st = sa; st < sb; st++) {
+    const int cur = (int)(st - sa) & 1;
+    if (st + 1 < sb) gather(st + 1);    // addresses from ids (loaded one iteration ago)
+    if (st + 2 < sb) load_ids(st + 2);  // then the registers take the next stage's ids
+    const double* Xt = XtAll + cur * stageDoubles;
+    // k-step outermost, tile slots innermost: consecutive DMMAs go to different accumulators, so none waits for
+    // the one before it; no branch in the loop body (the A reload is a predicated load)
+#pragma unroll
+    for (int ks = 0; ks < TT_KT; ks += 4) {
+      double a = 0.0;
+#pragma unroll
+      for (int sl = 0; sl < TPW; sl++) {
+        if ((aMask >> sl) & 1u) a = Xt[offA[sl] + ks];
+        dmma884(c[sl][0], c[sl][1], a, Xt[offB[sl] + ks]);
+      }
+    }
+    if (st + 1 < sb) store(st + 1, XtAll + (cur ^ 1) * stageDoubles);
+    __syncthreads();
+  }
+  // ---- add the partial tiles ----
+  {
+    int I = 0, base = 0;
+    while (I < NT && base + (NT - I) <= t0) {
+      base += NT - I;
+      I++;
+    }
+    int J = I + (t0 - base);
+#pragma unroll
+    for (int sl = 0; sl < TPW; sl++) {
+      if (t0 + sl < t1) {
+        const int gi = I * 8 + (lane >> 2);
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+          const int gj = J * 8 + (lane & 3) * 2 + u;
+          if (gi < nCols && gj < nCols && gi <= gj && c[sl][u] != 0.0) atomicAdd(&C[(size_t)gi * nCols + gj], c[sl][u]);
+        }
+        if (++J == NT) {
+          I++;
+          J = I;
+        }
+      }
+    }
+  }
+}
+
 // LibMatrixMult.copyUpperToLowerTriangle (runtime/matrix/data/LibMatrixMult.java:4769-4799)
 __global__ void k_mirror(double* __restrict__ C, int n) {
   const int64_t total = (int64_t)n * n;
@@ -390,6 +595,38 @@ int64_t measure_fp64_peaks(int device, double* dmmaTflops, double* dfmaTflops) {
   return CLA_OK;
 }
 
+// The 16-warp kernel is instantiated for 3, 6 and 9 tile slots per warp (up to 48, 104 and 128 columns) and for
+// the map widths the decode specialises on.
+template <int TPW>
+static void tri16_go(bool fused, int mt, int grid, size_t smem, cudaStream_t s, const DevGroup* groups, const int32_t* colSrc,
+                     const double* constV, const double* X, int rows, int n, double* dOut) {
+  if (!fused) k_tsmm_tri16<false, -2, TPW><<<grid, T16_THREADS, smem, s>>>(groups, colSrc, constV, X, 0, rows, n, dOut);
+  else if (mt == CLA_MAP_BYTE)
+    k_tsmm_tri16<true, CLA_MAP_BYTE, TPW><<<grid, T16_THREADS, smem, s>>>(groups, colSrc, constV, X, 0, rows, n, dOut);
+  else if (mt == CLA_MAP_CHAR)
+    k_tsmm_tri16<true, CLA_MAP_CHAR, TPW><<<grid, T16_THREADS, smem, s>>>(groups, colSrc, constV, X, 0, rows, n, dOut);
+  else k_tsmm_tri16<true, -2, TPW><<<grid, T16_THREADS, smem, s>>>(groups, colSrc, constV, X, 0, rows, n, dOut);
+}
+static void launch_tri16(bool fused, int mt, int n, int grid, size_t smem, cudaStream_t s, const DevGroup* groups,
+                         const int32_t* colSrc, const double* constV, const double* X, int rows, double* dOut) {
+  const int NT = (n + 7) / 8, perWarp = (NT * (NT + 1) / 2 + T16_WARPS - 1) / T16_WARPS;
+  if (perWarp <= 3) tri16_go<3>(fused, mt, grid, smem, s, groups, colSrc, constV, X, rows, n, dOut);
+  else if (perWarp <= 6) tri16_go<6>(fused, mt, grid, smem, s, groups, colSrc, constV, X, rows, n, dOut);
+  else tri16_go<9>(fused, mt, grid, smem, s, groups, colSrc, constV, X, rows, n, dOut);
+}
+template <int TPW>
+static void tri16_set_smem_t(int bytes) {
+  cudaFuncSetAttribute(k_tsmm_tri16<true, -2, TPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  cudaFuncSetAttribute(k_tsmm_tri16<true, CLA_MAP_BYTE, TPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  cudaFuncSetAttribute(k_tsmm_tri16<true, CLA_MAP_CHAR, TPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  cudaFuncSetAttribute(k_tsmm_tri16<false, -2, TPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+}
+static void tri16_set_smem(int bytes) {
+  tri16_set_smem_t<3>(bytes);
+  tri16_set_smem_t<6>(bytes);
+  tri16_set_smem_t<9>(bytes);
+}
+
 int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s) {
   const int n = m->nCols;
   if (n == 0) return CLA_OK;
@@ -408,8 +645,10 @@ int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s) {
     CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri<true, CLA_MAP_BYTE>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxSmem));
     CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri<true, CLA_MAP_CHAR>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxSmem));
     CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri<false, -2>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxSmem));
+    tri16_set_smem(maxSmem);
     attr = true;
   }
+  static const bool use16 = !getenv("CLA_TSMM_8WARP");  // tuning aid: the first-generation 8-warp kernel
   if (tri && denseOnly) {  // one launch over all rows, decoding as it goes
     const int64_t nStages = ((int64_t)m->nRows + TT_KT - 1) / TT_KT;
     const int grid = (int)std::min<int64_t>(2 * m->smCount, nStages);
@@ -421,10 +660,15 @@ int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s) {
                     : (g.mapType == CLA_MAP_CHAR ? CLA_MAP_CHAR : -2);
       mt = (mt == -1 || mt == w) ? w : -2;
     }
-    auto kern = mt == CLA_MAP_BYTE ? k_tsmm_tri<true, CLA_MAP_BYTE> : (mt == CLA_MAP_CHAR ? k_tsmm_tri<true, CLA_MAP_CHAR> : k_tsmm_tri<true, -2>);
     prof_begin(m, s);
-    kern<<<grid, TT_THREADS, triSmem, s>>>(m->dGroups, m->dColSrc, m->hasConst ? m->dConstV : nullptr, nullptr, 0, m->nRows, n,
-                                          dOut);
+    if (use16) {
+      launch_tri16(true, mt, n, (int)std::min<int64_t>(m->smCount, nStages), triSmem, s, m->dGroups, m->dColSrc,
+                   m->hasConst ? m->dConstV : nullptr, nullptr, m->nRows, dOut);
+    } else {
+      auto kern = mt == CLA_MAP_BYTE ? k_tsmm_tri<true, CLA_MAP_BYTE> : (mt == CLA_MAP_CHAR ? k_tsmm_tri<true, CLA_MAP_CHAR> : k_tsmm_tri<true, -2>);
+      kern<<<grid, TT_THREADS, triSmem, s>>>(m->dGroups, m->dColSrc, m->hasConst ? m->dConstV : nullptr, nullptr, 0, m->nRows,
+                                            n, dOut);
+    }
     prof_end(m, s);
     m->stats.kernel_launches++;
   } else {
@@ -443,7 +687,11 @@ int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s) {
       if (tri) {
         const int64_t nStages = ((int64_t)rows + TT_KT - 1) / TT_KT;
         const int grid = (int)std::min<int64_t>(2 * m->smCount, nStages);
-        k_tsmm_tri<false, -2><<<grid, TT_THREADS, triSmem, s>>>(nullptr, nullptr, nullptr, X, 0, rows, n, dOut);
+        if (use16)
+          launch_tri16(false, -2, n, (int)std::min<int64_t>(m->smCount, nStages), triSmem, s, nullptr, nullptr, nullptr, X,
+                       rows, dOut);
+        else
+          k_tsmm_tri<false, -2><<<grid, TT_THREADS, triSmem, s>>>(nullptr, nullptr, nullptr, X, 0, rows, n, dOut);
       } else {
         int splits = std::max(1, std::min((rows + TS_KT * 8 - 1) / (TS_KT * 8), (4 * m->smCount + nPairs - 1) / nPairs));
         int rowsPerSplit = ((rows + splits - 1) / splits + TS_KT - 1) / TS_KT * TS_KT;
