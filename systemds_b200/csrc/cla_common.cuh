@@ -157,6 +157,7 @@ struct Matrix {
   void* dRleIdx = nullptr;
   int nSdcGroups = 0, nRleGroups = 0;
   bool denseColsBuilt = false;
+  bool denseQuad = false;        // some stage of the tensor-core RMM takes the quad-column decode
   int32_t* dColSrc = nullptr;    // [nCols][2]: dense-map / uncompressed group holding the column and the position in it (-1: none)
   bool colSrcValid = false;      // false when some column is held by more than one such group (overlapping input)
   bool hasConst = false;

@@ -220,6 +220,7 @@ __device__ __forceinline__ void push_item(WorkItem* q, int* qn, int w, int ra, i
   }
 }
 
+template <bool QUAD>  // QUAD: the quad-column decode is compiled in (it costs registers the other stages then spill)
 __global__ void __launch_bounds__(GM_THREADS, 2)
 k_rmm_dmma2(const DevGroup* __restrict__ groups, const DenseDesc* __restrict__ dd, int nDense,
             const int32_t* __restrict__ sdcIdx, int nSdc, const int32_t* __restrict__ rleIdx, int nRle, int nRows,
@@ -283,11 +284,47 @@ k_rmm_dmma2(const DevGroup* __restrict__ groups, const DenseDesc* __restrict__ d
       for (int nt = 0; nt < 8; nt++) c[mt][nt][0] = c[mt][nt][1] = 0.0;
 
     for (int k0 = 0; k0 < nDense; k0 += GM_KC) {
-      {  // stage: warp = 16 rows of the tile, lane = one of the 32 dense columns. A dense-map column costs its lane
+      const int rbase = warp * 16;
+      if (QUAD && dd[k0].pad && r0 + GM_TR <= nRows) {
+        // stage, all 32 columns single-column byte-map groups: a load instruction covers 8 rows x 4 adjacent
+        // columns (lane = 4 * row + column). The four dictionaries of such a quad lie next to each other in the
+        // packed copy, so a gather touches one or two cache lines where a lane-per-column gather touches 32 (the
+        // L1 tag stage, one line per cycle, was the limit of this loop); the stores hit 16 distinct banks.
+        const int kk = lane & 3, r8 = lane >> 2;
+        const int rowA = r0 + rbase + r8;
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+          const uint8_t* mp[4];
+          const double* sp[4];
+#pragma unroll
+          for (int g4 = 0; g4 < 4; g4++) {
+            const int col = k0 + (half * 4 + g4) * 4 + kk;
+            mp[g4] = nullptr;
+            sp[g4] = nullptr;
+            if (col < nDense) {
+              mp[g4] = (const uint8_t*)dd[col].map;
+              sp[g4] = dd[col].src;
+            }
+          }
+          uint32_t id[4][2];
+#pragma unroll
+          for (int g4 = 0; g4 < 4; g4++)
+#pragma unroll
+            for (int h = 0; h < 2; h++) id[g4][h] = mp[g4] ? (uint32_t)__ldg(mp[g4] + rowA + 8 * h) : 0u;
+          double vv[4][2];
+#pragma unroll
+          for (int g4 = 0; g4 < 4; g4++)
+#pragma unroll
+            for (int h = 0; h < 2; h++) vv[g4][h] = sp[g4] ? sp[g4][id[g4][h]] : 0.0;
+#pragma unroll
+          for (int g4 = 0; g4 < 4; g4++)
+#pragma unroll
+            for (int h = 0; h < 2; h++) As[(rbase + r8 + 8 * h) * GM_LDAR + (half * 4 + g4) * 4 + kk] = vv[g4][h];
+        }
+      } else {  // stage: warp = 16 rows of the tile, lane = one of the 32 dense columns. A dense-map column costs its lane
          // one 128-bit map load (16 ids) and 16 dictionary reads; an uncompressed column is read row by row, the
          // warp covering 32 consecutive values of a dense row. A warp-wide store is one row of the stage.
         const int kc = k0 + lane;
-        const int rbase = warp * 16;
         double v[16];
 #pragma unroll
         for (int i = 0; i < 16; i++) v[i] = 0.0;
@@ -311,6 +348,8 @@ k_rmm_dmma2(const DevGroup* __restrict__ groups, const DenseDesc* __restrict__ d
         }
 #pragma unroll
         for (int i = 0; i < 16; i++) As[(rbase + i) * GM_LDAR + lane] = v[i];
+      }
+      {
         for (int e = tid; e < GM_KC * GM_TN; e += GM_THREADS) {
           const int kk = e >> 6, n = e & 63;
           double x = 0.0;
@@ -546,11 +585,31 @@ static int64_t ensure_dense_cols(Matrix* m) {
   std::vector<DenseCol> dc;
   std::vector<DenseDesc> dd;
   std::vector<int32_t> sdc, rle;
+  // The staging loop reads the dictionaries of 32 different columns with one gather. Registered one by one they
+  // each start a cache line of their own, so such a gather touches 32 lines; a packed copy of all dense-map
+  // dictionaries brings small ones (4 values = 32 bytes) four to a line.
+  size_t packDoubles = 0;
+  for (int gi = 0; gi < m->nDev; gi++)
+    if (m->groups[gi].type == GT_DDC) packDoubles += (size_t)m->groups[gi].nVals * m->groups[gi].gCols;
+  double* packed = nullptr;
+  if (packDoubles) {
+    cudaError_t e = cudaMalloc((void**)&packed, packDoubles * sizeof(double));
+    if (e != cudaSuccess) return fail(CLA_ERR_NOMEM, std::string("cudaMalloc packed dictionaries: ") + cudaGetErrorString(e));
+    m->allocs.push_back(packed);
+  }
+  size_t packAt = 0;
   for (int gi = 0; gi < m->nDev; gi++) {
     const DevGroup& g = m->groups[gi];
     if (g.type == GT_SDC) sdc.push_back(gi);
     if (g.type == GT_RLE) rle.push_back(gi);
     if (g.type != GT_DDC && g.type != GT_UNC) continue;
+    const double* dictAt = g.dict;
+    if (g.type == GT_DDC) {
+      const size_t n = (size_t)g.nVals * g.gCols;
+      CLA_CUDA(cudaMemcpy(packed + packAt, g.dict, n * sizeof(double), cudaMemcpyDeviceToDevice));
+      dictAt = packed + packAt;
+      packAt += n;
+    }
     std::vector<int32_t> cols(g.gCols);
     CLA_CUDA(cudaMemcpy(cols.data(), g.cols, cols.size() * 4, cudaMemcpyDeviceToHost));
     for (int j = 0; j < g.gCols; j++) {
@@ -558,13 +617,28 @@ static int64_t ensure_dense_cols(Matrix* m) {
       DenseDesc d;
       d.map = g.type == GT_UNC ? nullptr : g.map;
       d.mapHi = g.mapHi;
-      d.src = (g.type == GT_UNC ? g.dense : g.dict) + j;
+      d.src = (g.type == GT_UNC ? g.dense : dictAt) + j;
       d.mapType = g.type == GT_UNC ? -1 : g.mapType;
       d.gCols = g.gCols;
       d.vrow = cols[j];
       d.pad = 0;
       dd.push_back(d);
     }
+  }
+  // pad of a stage's first column: 1 if the stage takes the quad-column decode: all its columns single-column
+  // byte-map groups, and deep dictionaries (measured: 256 values 4.3 -> 3.2 ms on 2M x 200 x 16, but with 4 values
+  // the extra byte loads and descriptor reads cost more than the saved cache-line lookups, 1.33 -> 1.59 ms per
+  // 1M x 200 x 64)
+  for (size_t k0 = 0; k0 < dd.size(); k0 += GM_KC) {
+    bool all = true;
+    int64_t vals = 0;
+    const size_t k1 = std::min(dd.size(), k0 + GM_KC);
+    for (size_t k = k0; k < k1; k++) {
+      all &= (dd[k].mapType == CLA_MAP_UBYTE || dd[k].mapType == CLA_MAP_BYTE) && dd[k].gCols == 1;
+      vals += m->groups[dc[k].group].nVals;
+    }
+    dd[k0].pad = (all && vals >= 64 * (int64_t)(k1 - k0)) ? 1 : 0;
+    m->denseQuad |= dd[k0].pad != 0;
   }
   auto up = [&](const void* src, size_t bytes, void** dst) -> int64_t {
     *dst = nullptr;
@@ -619,13 +693,15 @@ int64_t launch_rmm_dmma(Matrix* m, const double* dV, int vCols, double* dOut, cu
   bool& attr = attrSet[m->device & 63];
   if (!attr) {
     CLA_CUDA(cudaFuncSetAttribute(k_rmm_dmma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    CLA_CUDA(cudaFuncSetAttribute(k_rmm_dmma2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2));
+    CLA_CUDA(cudaFuncSetAttribute(k_rmm_dmma2<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2));
+    CLA_CUDA(cudaFuncSetAttribute(k_rmm_dmma2<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2));
     attr = true;
   }
   prof_begin(m, s);
   if (m->nSdcGroups <= 256 && m->nRleGroups <= 256 && m->totalVals < (1ll << 32)) {
     dim3 grid((m->nRows + SKIP_ROWS - 1) / SKIP_ROWS, (vCols + GM_TN - 1) / GM_TN);
-    k_rmm_dmma2<<<grid, GM_THREADS, smem2, s>>>(m->dGroups, (const DenseDesc*)m->dDenseDesc, m->nDenseCols,
+    auto kern = m->denseQuad ? k_rmm_dmma2<true> : k_rmm_dmma2<false>;
+    kern<<<grid, GM_THREADS, smem2, s>>>(m->dGroups, (const DenseDesc*)m->dDenseDesc, m->nDenseCols,
                                                (const int32_t*)m->dSdcIdx, m->nSdcGroups, (const int32_t*)m->dRleIdx,
                                                m->nRleGroups, m->nRows, dV, vCols, P, constRow, dOut);
   } else {
