@@ -199,6 +199,44 @@ def test_full_size_checksum_config2(oracle):
     cmb.free()
 
 
+def test_benchmark_shapes_against_oracle(oracle):
+    """The five benchmark configurations at sizes the oracle finishes in seconds, each through its own operation."""
+    # configs[0] at full size: X %*% v, 1M x 100, 16 values per column
+    cmb, v = datagen.config1()
+    om = oracle.OracleMatrix(cmb.to_device())
+    got, want = CLALibRightMultBy.rightMultByMatrix(cmb, v), om.rmm(v)
+    assert rel_err(got, want, np.abs(want) + np.sqrt(100.0)) < TOL
+    cmb.free()
+    # configs[1] at 300k rows: t(y) %*% X, 256 values per column; variant b holds two-column dictionaries
+    for variant in ("a", "b"):
+        cmb, y = datagen.config2(nRows=300_000, variant=variant)
+        om = oracle.OracleMatrix(cmb.to_device())
+        y = y.reshape(1, -1)
+        got, want = CLALibLeftMultBy.leftMultByMatrix(cmb, y), om.lmm(y)
+        assert rel_err(got, want, np.abs(want) + np.sqrt(cmb.rlen)) < TOL
+        cmb.free()
+    # configs[2] at 60k rows: X %*% V with DDC / SDCZeros / RLE / uncompressed groups, V 500 x 64
+    cmb, V = datagen.config3(nRows=60_000)
+    om = oracle.OracleMatrix(cmb.to_device())
+    got, want = CLALibRightMultBy.rightMultByMatrix(cmb, V), om.rmm(V)
+    assert rel_err(got, want, np.abs(want) + np.sqrt(500.0)) < TOL
+    cmb.free()
+    # configs[3] at 200k rows: t(X) %*% X, 1000 values per column, Zipf ids, MapToChar
+    cmb = datagen.config4(nRows=200_000).to_device()
+    X = dense_of(cmb)
+    got = CLALibTSMM.leftMultByTransposeSelf(cmb)
+    assert rel_err(got, oracle.dense_tsmm_ld(X), np.abs(X).T @ np.abs(X)) < TOL
+    assert np.array_equal(got, got.T)
+    cmb.free()
+    # configs[4] at 30k rows x 1000 columns: one lmCG step t(X)(Xv) with bit / ubyte / byte maps
+    cmb, v = datagen.config5(nRows=30_000)
+    om = oracle.OracleMatrix(cmb.to_device())
+    aX = np.abs(dense_of(cmb))
+    got, want = CLALibMMChain.mmChain(cmb, v).ravel(), om.mmchain(v).ravel()
+    assert rel_err(got, want, aX.T @ (aX @ np.abs(v).ravel())) < 10 * TOL
+    cmb.free()
+
+
 @pytest.mark.parametrize("force", ["CHAR_BYTE", "INT", "BYTE", "CHAR"])
 def test_wide_map_types(oracle, force):
     """MapToCharPByte / MapToInt (and forced wider storage of small ids, MappingTestUtil.getAllHigherVersions)."""
