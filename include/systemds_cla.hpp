@@ -284,6 +284,22 @@ class CompressedMatrixBlock {
     if (handle_) throw DMLCompressionException(CLA_ERR_STATE, "block is already on the device");
     _colGroups.push_back(std::move(g));
   }
+  // CompressedMatrixBlock.read(DataInput) (CompressedMatrixBlock.java:486-496): the serialized form goes to the
+  // library's own reader and straight to the device; no host-side group objects are built.
+  static std::unique_ptr<CompressedMatrixBlock> read(const uint8_t* bytes, int64_t len, int device = 0) {
+    cla_handle h = check(cla_read_block(bytes, len, nullptr, nullptr), "cla_read_block");
+    cla_stats st;
+    try {
+      check(cla_stats_get(h, &st), "cla_stats_get");
+      check(cla_finalize(h, device), "cla_finalize");
+    } catch (...) {
+      cla_destroy(h);
+      throw;
+    }
+    std::unique_ptr<CompressedMatrixBlock> b(new CompressedMatrixBlock((int)st.n_rows, (int)st.n_cols));
+    b->handle_ = h;
+    return b;
+  }
   // uploads the groups on first use (cla_create .. cla_finalize)
   cla_handle nativeHandle(int device = 0) {
     if (!handle_) {
@@ -352,6 +368,24 @@ struct CLALibMMChain {  // lib/CLALibMMChain.java:92; w may be null for XtXv
     ret.nonZeros = check(cla_mmchain(x.nativeHandle(), v.values.data(), w ? w->values.data() : nullptr, ctype, ret.values.data()), "cla_mmchain");
     return ret;
   }
+};
+struct CLALibCompAgg {  // lib/CLALibCompAgg.java: uack+ / uark+ / uak+ and the min / max cases
+  static MatrixBlock aggregate(CompressedMatrixBlock& cmb, int op) {
+    const bool col = op == CLA_AGG_COL_SUMS || op == CLA_AGG_COL_MINS || op == CLA_AGG_COL_MAXS;
+    const bool row = op == CLA_AGG_ROW_SUMS || op == CLA_AGG_ROW_MINS || op == CLA_AGG_ROW_MAXS;
+    MatrixBlock ret(row ? cmb.getNumRows() : 1, col ? cmb.getNumColumns() : 1);
+    ret.nonZeros = check(cla_unary_agg(cmb.nativeHandle(), op, ret.values.data()), "cla_unary_agg");
+    return ret;
+  }
+  static MatrixBlock colSums(CompressedMatrixBlock& c) { return aggregate(c, CLA_AGG_COL_SUMS); }
+  static MatrixBlock rowSums(CompressedMatrixBlock& c) { return aggregate(c, CLA_AGG_ROW_SUMS); }
+  static MatrixBlock colMins(CompressedMatrixBlock& c) { return aggregate(c, CLA_AGG_COL_MINS); }
+  static MatrixBlock colMaxs(CompressedMatrixBlock& c) { return aggregate(c, CLA_AGG_COL_MAXS); }
+  static MatrixBlock rowMins(CompressedMatrixBlock& c) { return aggregate(c, CLA_AGG_ROW_MINS); }
+  static MatrixBlock rowMaxs(CompressedMatrixBlock& c) { return aggregate(c, CLA_AGG_ROW_MAXS); }
+  static double sum(CompressedMatrixBlock& c) { return aggregate(c, CLA_AGG_SUM).values[0]; }
+  static double min(CompressedMatrixBlock& c) { return aggregate(c, CLA_AGG_MIN).values[0]; }
+  static double max(CompressedMatrixBlock& c) { return aggregate(c, CLA_AGG_MAX).values[0]; }
 };
 struct CLALibDecompress {  // lib/CLALibDecompress.java:56
   static MatrixBlock decompress(CompressedMatrixBlock& cmb) {

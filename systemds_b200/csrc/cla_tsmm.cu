@@ -482,13 +482,29 @@ k_tsmm_tri16(const DevGroup* __restrict__ groups, const int32_t* __restrict__ co
     const double* Xt = XtAll + cur * stageDoubles;
     // k-step outermost, tile slots innermost: consecutive DMMAs go to different accumulators, so none waits for
     // the one before it; no branch in the loop body (the A reload is a predicated load)
+    // (the fragments of k-step ks + 4 are loaded into registers before the DMMAs of k-step ks are issued, so the
+    // shared-memory latency is covered by the warp's own DMMAs rather than by the three other warps of its scheduler)
+    double bC[TPW], aC = Xt[offA[0]];
+#pragma unroll
+    for (int sl = 0; sl < TPW; sl++) bC[sl] = Xt[offB[sl]];
 #pragma unroll
     for (int ks = 0; ks < TT_KT; ks += 4) {
-      double a = 0.0;
+      double bN[TPW], aN = 0.0;
+      if (ks + 4 < TT_KT) {
+        aN = Xt[offA[0] + ks + 4];
+#pragma unroll
+        for (int sl = 0; sl < TPW; sl++) bN[sl] = Xt[offB[sl] + ks + 4];
+      }
+      double a = aC;
 #pragma unroll
       for (int sl = 0; sl < TPW; sl++) {
-        if ((aMask >> sl) & 1u) a = Xt[offA[sl] + ks];
-        dmma884(c[sl][0], c[sl][1], a, Xt[offB[sl] + ks]);
+        if (sl > 0 && ((aMask >> sl) & 1u)) a = Xt[offA[sl] + ks];
+        dmma884(c[sl][0], c[sl][1], a, bC[sl]);
+      }
+      if (ks + 4 < TT_KT) {
+        aC = aN;
+#pragma unroll
+        for (int sl = 0; sl < TPW; sl++) bC[sl] = bN[sl];
       }
     }
     if (st + 1 < sb) store(st + 1, XtAll + (cur ^ 1) * stageDoubles);
@@ -615,16 +631,18 @@ static void launch_tri16(bool fused, int mt, int n, int grid, size_t smem, cudaS
   else tri16_go<9>(fused, mt, grid, smem, s, groups, colSrc, constV, X, rows, n, dOut);
 }
 template <int TPW>
-static void tri16_set_smem_t(int bytes) {
-  cudaFuncSetAttribute(k_tsmm_tri16<true, -2, TPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-  cudaFuncSetAttribute(k_tsmm_tri16<true, CLA_MAP_BYTE, TPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-  cudaFuncSetAttribute(k_tsmm_tri16<true, CLA_MAP_CHAR, TPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-  cudaFuncSetAttribute(k_tsmm_tri16<false, -2, TPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+static int64_t tri16_set_smem_t(int bytes) {
+  CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri16<true, -2, TPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri16<true, CLA_MAP_BYTE, TPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri16<true, CLA_MAP_CHAR, TPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri16<false, -2, TPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  return CLA_OK;
 }
-static void tri16_set_smem(int bytes) {
-  tri16_set_smem_t<3>(bytes);
-  tri16_set_smem_t<6>(bytes);
-  tri16_set_smem_t<9>(bytes);
+static int64_t tri16_set_smem(int bytes) {
+  int64_t rc;
+  if ((rc = tri16_set_smem_t<3>(bytes)) < 0) return rc;
+  if ((rc = tri16_set_smem_t<6>(bytes)) < 0) return rc;
+  return tri16_set_smem_t<9>(bytes);
 }
 
 int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s) {
@@ -645,7 +663,7 @@ int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s) {
     CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri<true, CLA_MAP_BYTE>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxSmem));
     CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri<true, CLA_MAP_CHAR>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxSmem));
     CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri<false, -2>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxSmem));
-    tri16_set_smem(maxSmem);
+    if ((rc = tri16_set_smem(maxSmem)) < 0) return rc;
     attr = true;
   }
   static const bool use16 = !getenv("CLA_TSMM_8WARP");  // tuning aid: the first-generation 8-warp kernel

@@ -80,9 +80,10 @@ struct In {
     for (int64_t i = 0; i < k; i++) out[i] = (uint16_t)((q[2 * i] << 8) | q[2 * i + 1]);
   }
   void i32s(std::vector<int32_t>& out, int64_t k) {
-    take(0);
+    const uint8_t* q = take(4 * k);
     out.resize(k);
-    for (int64_t i = 0; i < k; i++) out[i] = i32();
+    for (int64_t i = 0; i < k; i++)
+      out[i] = (int32_t)(((uint32_t)q[4 * i] << 24) | ((uint32_t)q[4 * i + 1] << 16) | ((uint32_t)q[4 * i + 2] << 8) | (uint32_t)q[4 * i + 3]);
   }
   void f64s(std::vector<double>& out, int64_t k) {
     const uint8_t* q = take(8 * k);

@@ -142,6 +142,19 @@ int main() {
           }
       report("tmm", relErr(T.values, ref, sc), 1e-12);
     }
+    {  // aggregates: column sums against the dense matrix, extrema bracket it
+      MatrixBlock cs = CLALibCompAgg::colSums(cmb), lo = CLALibCompAgg::colMins(cmb), hi = CLALibCompAgg::colMaxs(cmb);
+      std::vector<double> ref(m, 0.0), sc(m, 0.0);
+      bool bracket = true;
+      for (int r = 0; r < n; r++)
+        for (int c = 0; c < m; c++) {
+          ref[c] += X[(size_t)r * m + c];
+          sc[c] += std::fabs(X[(size_t)r * m + c]);
+          bracket &= lo.values[c] <= X[(size_t)r * m + c] && X[(size_t)r * m + c] <= hi.values[c];
+        }
+      report("colSums", relErr(cs.values, ref, sc), 1e-12);
+      if (!bracket || !(CLALibCompAgg::min(cmb) <= CLALibCompAgg::max(cmb))) { std::printf("min/max do not bracket the data\n"); bad++; }
+    }
     {  // error behaviour: shape mismatch surfaces as the reference's exception with its message prefix
       bool thrown = false;
       try {
