@@ -365,8 +365,15 @@ def bench_extras(L, dev, sptr, peak):
     algl = cmb.index_bytes() + n * 8
     out["lmm_mixed_config2"] = {"workload": "t(y) %*% X on the same matrix", "ms": ms, "rows_per_s": n / (ms * 1e-3),
                                 "algorithmic_GBps": algl / (ms * 1e-3) / 1e9, "hbm_frac": algl / (ms * 1e-3) / 1e9 / peak}
-    cmb.free()
     del Vd, Od
+    Dd = torch.empty((n, 500), dtype=torch.float64, device=dev)
+    ms = _time_dev(lambda: check(L.cla_decompress_dev(h, P(Dd), sptr)))
+    algd = cmb.index_bytes() + n * 500 * 8
+    out["decompress_mixed_config2"] = {"workload": "decompress of the same matrix into a device buffer (4 GB)", "ms": ms,
+                                       "rows_per_s": n / (ms * 1e-3), "algorithmic_GBps": algd / (ms * 1e-3) / 1e9,
+                                       "hbm_frac": algd / (ms * 1e-3) / 1e9 / peak}
+    cmb.free()
+    del Dd
     # configs[3]: t(X) %*% X, 100 DDC columns with 1000 values (MapToChar), Zipf ids
     n = 2_000_000
     cmb = datagen.config4(nRows=n)

@@ -177,6 +177,8 @@ int64_t cla_rmm_dev(cla_handle h, const double* dV, int32_t vRows, int32_t vCols
 int64_t cla_lmm_dev(cla_handle h, const double* dYt, int32_t yRows, double* dOut, void* stream);
 int64_t cla_tsmm_dev(cla_handle h, double* dOut, void* stream);
 int64_t cla_tmm_dev(cla_handle left, cla_handle right, double* dOut, void* stream);
+/* decompress into a device buffer of nRows x nCols doubles (lib/CLALibDecompress.java:56) */
+int64_t cla_decompress_dev(cla_handle h, double* dOut, void* stream);
 /* dU: caller-provided scratch of nRows doubles for u = X v (may be NULL: the handle then keeps its own) */
 int64_t cla_mmchain_dev(cla_handle h, const double* dV, const double* dW, int32_t ctype, double* dOut, double* dU,
                         void* stream);

@@ -474,6 +474,13 @@ int64_t cla_tsmm_dev(cla_handle h, double* dOut, void* stream) {
   m->stats.calls_tsmm++;
   return launch_tsmm(m, dOut, (cudaStream_t)stream);
 }
+int64_t cla_decompress_dev(cla_handle h, double* dOut, void* stream) {
+  GET_MATRIX(h);
+  REQUIRE_FINAL();
+  CLA_CUDA(cudaSetDevice(m->device));
+  m->stats.calls_decompress++;
+  return launch_decompress(m, dOut, (cudaStream_t)stream);
+}
 int64_t cla_mmchain_dev(cla_handle h, const double* dV, const double* dW, int32_t ctype, double* dOut, double* dU,
                         void* stream) {
   GET_MATRIX(h);

@@ -569,21 +569,18 @@ int64_t finalize_device(Matrix* m) {
   const double* dc = nullptr;
   if ((rc = upload(m, m->constV.data(), m->constV.size(), &dc, false)) < 0) return rc;
   m->dConstV = const_cast<double*>(dc);
-  {  // column -> (dense-map or uncompressed group, position) for the fused decompress kernel
+  {  // column -> (group, position); valid when no column is held by two product groups (decompress, fused TSMM)
     std::vector<int32_t> colSrc((size_t)m->nCols * 2, -1);
     m->colSrcValid = true;
-    int di = 0;
     for (size_t gi = 0; gi < m->hg.size(); gi++) {
       if (m->regToDev[gi] < 0) continue;
       const DevGroup& g = m->groups[m->regToDev[gi]];
-      if (g.type == GT_DDC || g.type == GT_UNC)
-        for (int j = 0; j < g.gCols; j++) {
-          const int c = m->hg[gi].cols[j];
-          if (colSrc[2 * c] >= 0) m->colSrcValid = false;
-          colSrc[2 * c] = m->regToDev[gi];
-          colSrc[2 * c + 1] = j;
-        }
-      di++;
+      for (int j = 0; j < g.gCols; j++) {  // every product group: dense-map, uncompressed, SDC, RLE
+        const int c = m->hg[gi].cols[j];
+        if (colSrc[2 * c] >= 0) m->colSrcValid = false;
+        colSrc[2 * c] = m->regToDev[gi];
+        colSrc[2 * c + 1] = j;
+      }
     }
     const int32_t* dcs = nullptr;
     if ((rc = upload(m, colSrc.data(), colSrc.size(), &dcs, false)) < 0) return rc;

@@ -276,23 +276,93 @@ __global__ void k_decomp_rle(DevGroup g, double* __restrict__ out, int r0, int r
   }
 }
 
-// All dense-map and uncompressed groups in one pass: every output cell is written once, from constV plus the
-// value of the one such group that holds its column (colSrc). Sparse groups are added afterwards.
-__global__ void k_decomp_fused(const DevGroup* __restrict__ groups, const int32_t* __restrict__ colSrc,
-                               const double* __restrict__ constV, double* __restrict__ out, int r0, int r1, int nCols) {
-  const int64_t n = (int64_t)(r1 - r0) * nCols;
-  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < n; e += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = e / nCols;
-    const int c = (int)(e - r * nCols);
-    double v = constV ? constV[c] : 0.0;
-    const int gi = colSrc[2 * c];
-    if (gi >= 0) {
-      const DevGroup& g = groups[gi];
-      const int j = colSrc[2 * c + 1];
-      if (g.type == GT_UNC) v += g.dense[(size_t)(r0 + r) * g.gCols + j];
-      else v += g.dict[(size_t)map_get(g.mapType, g.map, g.mapHi, r0 + r) * g.gCols + j];
+// Decompress of a block whose columns each belong to at most one group, every group type, one pass: a CTA owns a
+// 1024-row block (the granularity of the skip indexes) x 8 columns and builds them in shared memory, one warp per
+// column with lanes along the rows -- a dense-map column reads 32 consecutive ids per load, an SDC column fills its
+// constant and then scatters the listed rows (warp-scan decode from the skip entry), an RLE column fills its runs --
+// and then writes the tile out with lanes along the columns (64-byte segments of 4 output rows per instruction).
+// Uncompressed columns skip the tile: adjacent columns are adjacent in memory, so the write-out loop reads them.
+// Every output cell is written exactly once; nothing is read back.
+constexpr int DB_COLS = 8;
+constexpr int DB_LD = SKIP_ROWS + 2;  // column stride of the tile: 2 w + row spreads a write-out instruction over the banks
+__global__ void __launch_bounds__(256)
+k_decomp_block(const DevGroup* __restrict__ groups, const int32_t* __restrict__ colSrc, const double* __restrict__ constV,
+               double* __restrict__ out, int r0, int r1, int nCols) {
+  extern __shared__ double dtile[];  // [DB_COLS][DB_LD]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int rb = r0 + blockIdx.x * SKIP_ROWS, re = min(r1, rb + SKIP_ROWS), nr = re - rb;
+  const int c0 = blockIdx.y * DB_COLS, nc = min(DB_COLS, nCols - c0);
+  __shared__ const double* uncSrc[DB_COLS];  // uncompressed columns: first value of the column (+ constant below)
+  __shared__ int uncStride[DB_COLS];
+  __shared__ double uncCst[DB_COLS];
+  if (tid < DB_COLS) {
+    uncSrc[tid] = nullptr;
+    if (tid < nc) {
+      const int gi = colSrc[2 * (c0 + tid)];
+      if (gi >= 0 && groups[gi].type == GT_UNC) {
+        uncSrc[tid] = groups[gi].dense + colSrc[2 * (c0 + tid) + 1];
+        uncStride[tid] = groups[gi].gCols;
+        uncCst[tid] = constV ? constV[c0 + tid] : 0.0;
+      }
     }
-    out[e] = v;
+  }
+  if (warp < nc) {
+    const int c = c0 + warp;
+    const int gi = colSrc[2 * c];
+    const double cst = constV ? constV[c] : 0.0;
+    double* col = dtile + warp * DB_LD;
+    if (gi < 0) {
+      for (int rr = lane; rr < nr; rr += 32) col[rr] = cst;
+    } else {
+      const DevGroup& g = groups[gi];
+      const int j = colSrc[2 * c + 1], gc = g.gCols;
+      const double* dict = g.dict + j;
+      if (g.type == GT_DDC) {
+        const int mt = g.mapType;
+        // eight rows per lane in flight: all ids are loaded before the first dictionary read that needs one
+        for (int base = 0; base < nr; base += 256) {
+          int id[8];
+#pragma unroll
+          for (int u = 0; u < 8; u++) {
+            const int rr = base + u * 32 + lane;
+            id[u] = rr < nr ? map_get(mt, g.map, g.mapHi, rb + rr) : 0;
+          }
+          double v[8];
+#pragma unroll
+          for (int u = 0; u < 8; u++) v[u] = dict[(size_t)id[u] * gc];
+#pragma unroll
+          for (int u = 0; u < 8; u++) {
+            const int rr = base + u * 32 + lane;
+            if (rr < nr) col[rr] = cst + v[u];
+          }
+        }
+      } else if (g.type == GT_SDC) {
+        for (int rr = lane; rr < nr; rr += 32) col[rr] = cst;
+        __syncwarp();
+        sdc_walk_block(g, rb, re, [&](int row, int e) {
+          const int id = g.single ? 0 : map_get(g.mapType, g.map, g.mapHi, e);
+          col[row - rb] = cst + dict[(size_t)id * gc];
+        });
+      } else if (g.type == GT_RLE) {
+        for (int rr = lane; rr < nr; rr += 32) col[rr] = cst;
+        __syncwarp();
+        for (int64_t ri = g.runSkip[rb / SKIP_ROWS]; ri < g.nRuns; ri++) {
+          const RleRun run = g.runs[ri];
+          if (run.start >= re) break;
+          const int a = max(run.start, rb), b = min(run.start + (int)run.len, re);
+          const double v = cst + dict[(size_t)run.k * gc];
+          for (int i = a + lane; i < b; i += 32) col[i - rb] = v;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  for (int e = tid; e < nr * DB_COLS; e += 256) {
+    const int rr = e / DB_COLS, cc = e - rr * DB_COLS;
+    if (cc >= nc) continue;
+    const double* us = uncSrc[cc];
+    const double v = us ? uncCst[cc] + us[(size_t)(rb + rr) * uncStride[cc]] : dtile[cc * DB_LD + rr];
+    out[(size_t)(rb - r0 + rr) * nCols + c0 + cc] = v;
   }
 }
 
@@ -300,18 +370,26 @@ __global__ void k_decomp_fused(const DevGroup* __restrict__ groups, const int32_
 int64_t launch_decompress_range(Matrix* m, int r0, int r1, double* dOut, cudaStream_t s) {
   const int64_t n = (int64_t)(r1 - r0) * m->nCols;
   if (n <= 0) return CLA_OK;
-  const bool fused = m->colSrcValid;
-  if (fused) {
-    k_decomp_fused<<<grid_for(n, 256, 148 * 32), 256, 0, s>>>(m->dGroups, m->dColSrc, m->hasConst ? m->dConstV : nullptr,
-                                                             dOut, r0, r1, m->nCols);
-    m->stats.kernel_launches++;
-  } else
-    k_decomp_init<<<grid_for(n, 256), 256, 0, s>>>(dOut, m->hasConst ? m->dConstV : nullptr, r1 - r0, m->nCols);
-  for (auto& g : m->groups) {
-    if (g.type == GT_DDC || g.type == GT_UNC) {
-      if (fused) continue;
-      k_decomp_dense<<<grid_for((int64_t)(r1 - r0) * g.gCols, 256), 256, 0, s>>>(g, dOut, r0, r1, m->nCols);
+  if (m->colSrcValid) {  // no column held by two groups: one pass, every cell written once
+    const size_t smem = (size_t)DB_COLS * DB_LD * sizeof(double);
+    static bool attrSet[64] = {};  // per device: function attributes belong to the device's context
+    bool& attr = attrSet[m->device & 63];
+    if (!attr) {
+      CLA_CUDA(cudaFuncSetAttribute(k_decomp_block, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      attr = true;
     }
+    dim3 grid((r1 - r0 + SKIP_ROWS - 1) / SKIP_ROWS, (m->nCols + DB_COLS - 1) / DB_COLS);
+    k_decomp_block<<<grid, 256, smem, s>>>(m->dGroups, m->dColSrc, m->hasConst ? m->dConstV : nullptr, dOut, r0, r1, m->nCols);
+    m->stats.kernel_launches++;
+    CLA_CUDA(cudaGetLastError());
+    return CLA_OK;
+  }
+  // overlapping groups: constants first, then every group adds its values (the reference's list-order summation)
+  k_decomp_init<<<grid_for(n, 256), 256, 0, s>>>(dOut, m->hasConst ? m->dConstV : nullptr, r1 - r0, m->nCols);
+  m->stats.kernel_launches++;
+  for (auto& g : m->groups) {
+    if (g.type == GT_DDC || g.type == GT_UNC)
+      k_decomp_dense<<<grid_for((int64_t)(r1 - r0) * g.gCols, 256), 256, 0, s>>>(g, dOut, r0, r1, m->nCols);
     else if (g.type == GT_SDC) {
       const int nb = (r1 - r0 + SKIP_ROWS - 1) / SKIP_ROWS;
       k_decomp_sdc<<<(nb * 32 + 255) / 256, 256, 0, s>>>(g, dOut, r0, r1, m->nCols);

@@ -59,6 +59,7 @@ SIGNATURES = {
     "cla_lmm_dev": [_I64, _P, _I32, _P, _P],
     "cla_lmm_vec_noalloc_dev": [_I64, _P, _P, _P],
     "cla_tsmm_dev": [_I64, _P, _P],
+    "cla_decompress_dev": [_I64, _P, _P],
     "cla_tmm_dev": [_I64, _I64, _P, _P],
     "cla_mmchain_dev": [_I64, _P, _P, _I32, _P, _P, _P],
     "cla_group_decode": [_I64, _I32, _P],
