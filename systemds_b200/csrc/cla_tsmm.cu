@@ -22,6 +22,24 @@ __device__ __forceinline__ void dmma884(double& c0, double& c1, double a, double
                : "d"(a), "d"(b));
 }
 
+// Loads pinned where they are written: volatile asm is not moved across the (volatile) DMMAs, so a load issued
+// before a block of DMMAs stays in flight during them instead of being sunk to its first use behind them.
+__device__ __forceinline__ double ld_f64_here(const double* p) {
+  double v;
+  asm volatile("ld.global.nc.f64 %0, [%1];" : "=d"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_u8_here(const uint8_t* p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.u8 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_u16_here(const uint16_t* p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+
 // grid: (upper block pairs, k splits). X: [rows x nCols] row-major chunk. C += X^T X (upper blocks only).
 __global__ void __launch_bounds__(TS_THREADS)
 k_syrk_dmma(const double* __restrict__ X, int rows, int nCols, int nBlk, double* __restrict__ C, int rowsPerSplit) {
@@ -74,38 +92,59 @@ k_syrk_dmma(const double* __restrict__ X, int rows, int nCols, int nBlk, double*
 }
 
 // grid: (blocks of A columns x blocks of B columns, k splits). A: [rows x aCols], B: [rows x bCols], both row-major
-// chunks of the same rows. C [aCols x bCols] += A^T B. Same staging and fragment layout as k_syrk_dmma.
+// chunks of the same rows. C [aCols x bCols] += A^T B. A CTA owns one 64 x 64 block of C; warp w its rows 8 w .. 8 w + 8.
+// 16-row stages, double buffered (static shared memory, 35 KB): the loads of the next stage are issued into registers before the DMMAs of the
+// current one and stored to the other buffer after them, so one barrier per stage and no exposed load latency.
+constexpr int GT_KT = 16;
 __global__ void __launch_bounds__(TS_THREADS)
 k_gemm_tn_dmma(const double* __restrict__ A, int aCols, const double* __restrict__ B, int bCols, int rows, int nBlkB,
                double* __restrict__ C, int rowsPerSplit) {
-  __shared__ double sI[TS_KT * TS_LD];
-  __shared__ double sJ[TS_KT * TS_LD];
+  __shared__ double sI[2][GT_KT * TS_LD];
+  __shared__ double sJ[2][GT_KT * TS_LD];
   const int bi = blockIdx.x / nBlkB, bj = blockIdx.x - bi * nBlkB;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int rBeg = blockIdx.y * rowsPerSplit, rEnd = min(rows, rBeg + rowsPerSplit);
+  if (rBeg >= rEnd) return;
   double c[8][2];
 #pragma unroll
   for (int t = 0; t < 8; t++) c[t][0] = c[t][1] = 0.0;
   const int am = lane >> 2, ak = lane & 3;
-  for (int r = rBeg; r < rEnd; r += TS_KT) {
-    for (int e = tid; e < TS_KT * TS_BLK; e += TS_THREADS) {
-      const int kk = e / TS_BLK, cc = e - kk * TS_BLK;
-      const int row = r + kk;
-      const int ci = bi * TS_BLK + cc, cj = bj * TS_BLK + cc;
-      sI[kk * TS_LD + cc] = (row < rEnd && ci < aCols) ? A[(size_t)row * aCols + ci] : 0.0;
-      sJ[kk * TS_LD + cc] = (row < rEnd && cj < bCols) ? B[(size_t)row * bCols + cj] : 0.0;
-    }
-    __syncthreads();
+  // this thread's cells of a stage: column cc of rows kk0, kk0 + 4, ... (GT_KT * 64 / 256 = 4 cells per operand)
+  const int cc = tid & 63, kk0 = tid >> 6;
+  const int ci = bi * TS_BLK + cc, cj = bj * TS_BLK + cc;
+  constexpr int GT_CELLS = GT_KT * TS_BLK / TS_THREADS;
+  double va[GT_CELLS], vb[GT_CELLS];
+  auto load = [&](int r) {
 #pragma unroll
-    for (int k0 = 0; k0 < TS_KT; k0 += 4) {
-      const double a = sI[(k0 + ak) * TS_LD + warp * 8 + am];
-#pragma unroll
-      for (int t = 0; t < 8; t++) {
-        const double b = sJ[(k0 + ak) * TS_LD + t * 8 + am];
-        dmma884(c[t][0], c[t][1], a, b);
-      }
+    for (int u = 0; u < GT_CELLS; u++) {
+      const int row = r + kk0 + 4 * u;
+      va[u] = (row < rEnd && ci < aCols) ? ld_f64_here(A + (size_t)row * aCols + ci) : 0.0;
+      vb[u] = (row < rEnd && cj < bCols) ? ld_f64_here(B + (size_t)row * bCols + cj) : 0.0;
     }
+  };
+  auto store = [&](int buf) {
+#pragma unroll
+    for (int u = 0; u < GT_CELLS; u++) {
+      sI[buf][(kk0 + 4 * u) * TS_LD + cc] = va[u];
+      sJ[buf][(kk0 + 4 * u) * TS_LD + cc] = vb[u];
+    }
+  };
+  load(rBeg);
+  store(0);
+  __syncthreads();
+  int cur = 0;
+  for (int r = rBeg; r < rEnd; r += GT_KT) {
+    const bool more = r + GT_KT < rEnd;
+    if (more) load(r + GT_KT);
+#pragma unroll
+    for (int k0 = 0; k0 < GT_KT; k0 += 4) {
+      const double a = sI[cur][(k0 + ak) * TS_LD + warp * 8 + am];  // A[m][k] = A[k][bi*64 + warp*8 + m]
+#pragma unroll
+      for (int t = 0; t < 8; t++) dmma884(c[t][0], c[t][1], a, sJ[cur][(k0 + ak) * TS_LD + t * 8 + am]);
+    }
+    if (more) store(cur ^ 1);
     __syncthreads();
+    cur ^= 1;
   }
   const int gi = bi * TS_BLK + warp * 8 + (lane >> 2);
 #pragma unroll
@@ -324,22 +363,6 @@ k_tsmm_tri(const DevGroup* __restrict__ groups, const int32_t* __restrict__ colS
 // DMMAs have been issued. The 8-warp kernel above stalls on those gathers (its decode must finish, values in
 // shared memory, before its DMMAs start).
 // --------------------------------------------------------------------------------------------------
-__device__ __forceinline__ double ld_f64_here(const double* p) {
-  double v;
-  asm volatile("ld.global.nc.f64 %0, [%1];" : "=d"(v) : "l"(p));
-  return v;
-}
-__device__ __forceinline__ uint32_t ld_u8_here(const uint8_t* p) {
-  uint32_t v;
-  asm volatile("ld.global.nc.u8 %0, [%1];" : "=r"(v) : "l"(p));
-  return v;
-}
-__device__ __forceinline__ uint32_t ld_u16_here(const uint16_t* p) {
-  uint32_t v;
-  asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(v) : "l"(p));
-  return v;
-}
-
 constexpr int T16_WARPS = 16;
 constexpr int T16_THREADS = T16_WARPS * 32;
 constexpr int T16_MAXC = 8;   // columns decoded per warp and stage at 128 columns
@@ -751,7 +774,7 @@ int64_t launch_tmm(Matrix* L, Matrix* R, double* dOut, cudaStream_t s) {
     if ((rc = launch_decompress_range(R, (int)r0, r1, XR, s)) < 0) return rc;
     const int rows = r1 - (int)r0;
     int splits = std::max(1, std::min((rows + TS_KT * 8 - 1) / (TS_KT * 8), (4 * L->smCount + nBlocks - 1) / nBlocks));
-    int rowsPerSplit = ((rows + splits - 1) / splits + TS_KT - 1) / TS_KT * TS_KT;
+    int rowsPerSplit = ((rows + splits - 1) / splits + GT_KT - 1) / GT_KT * GT_KT;
     splits = (rows + rowsPerSplit - 1) / rowsPerSplit;
     dim3 grid(nBlocks, splits);
     if (r0 == 0) prof_begin(L, s);
