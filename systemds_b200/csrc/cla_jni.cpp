@@ -106,6 +106,10 @@ JFN(jlong, mmchain)(JNIEnv* env, jclass, jlong h, jdoubleArray v, jdoubleArray w
   Out o(env, out);
   return cla_mmchain(h, (const double*)vv.p, (const double*)ww.p, ctype, (double*)o.p);
 }
+JFN(jlong, unaryAgg)(JNIEnv* env, jclass, jlong h, jint op, jdoubleArray out) {
+  Out o(env, out);
+  return cla_unary_agg(h, op, (double*)o.p);
+}
 JFN(jlong, decompress)(JNIEnv* env, jclass, jlong h, jdoubleArray out) {
   Out o(env, out);
   return cla_decompress(h, (double*)o.p);
