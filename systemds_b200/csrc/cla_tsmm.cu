@@ -40,68 +40,32 @@ __device__ __forceinline__ uint32_t ld_u16_here(const uint16_t* p) {
   return v;
 }
 
-// grid: (upper block pairs, k splits). X: [rows x nCols] row-major chunk. C += X^T X (upper blocks only).
-__global__ void __launch_bounds__(TS_THREADS)
-k_syrk_dmma(const double* __restrict__ X, int rows, int nCols, int nBlk, double* __restrict__ C, int rowsPerSplit) {
-  __shared__ double sI[TS_KT * TS_LD];
-  __shared__ double sJ[TS_KT * TS_LD];
-  // decode the linear pair index into (bi <= bj)
-  int p = blockIdx.x, bi = 0;
-  while (p >= nBlk - bi) {
-    p -= nBlk - bi;
-    bi++;
-  }
-  const int bj = bi + p;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int rBeg = blockIdx.y * rowsPerSplit, rEnd = min(rows, rBeg + rowsPerSplit);
-  double c[8][2];
-#pragma unroll
-  for (int t = 0; t < 8; t++) c[t][0] = c[t][1] = 0.0;
-  const int am = lane >> 2, ak = lane & 3;
-  for (int r = rBeg; r < rEnd; r += TS_KT) {
-    // stage KT rows of column blocks bi and bj (zero padded)
-    for (int e = tid; e < TS_KT * TS_BLK; e += TS_THREADS) {
-      const int kk = e / TS_BLK, cc = e - kk * TS_BLK;
-      const int row = r + kk;
-      const int ci = bi * TS_BLK + cc, cj = bj * TS_BLK + cc;
-      sI[kk * TS_LD + cc] = (row < rEnd && ci < nCols) ? X[(size_t)row * nCols + ci] : 0.0;
-      sJ[kk * TS_LD + cc] = (row < rEnd && cj < nCols) ? X[(size_t)row * nCols + cj] : 0.0;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int k0 = 0; k0 < TS_KT; k0 += 4) {
-      const double a = sI[(k0 + ak) * TS_LD + warp * 8 + am];  // A[m][k] = X[k][bi*64 + warp*8 + m]
-#pragma unroll
-      for (int t = 0; t < 8; t++) {
-        const double b = sJ[(k0 + ak) * TS_LD + t * 8 + am];   // B[k][n] = X[k][bj*64 + t*8 + n]
-        dmma884(c[t][0], c[t][1], a, b);
-      }
-    }
-    __syncthreads();
-  }
-  // C fragment: row = lane >> 2, cols = (lane & 3) * 2 + {0, 1}
-  const int gi = bi * TS_BLK + warp * 8 + (lane >> 2);
-#pragma unroll
-  for (int t = 0; t < 8; t++) {
-#pragma unroll
-    for (int u = 0; u < 2; u++) {
-      const int gj = bj * TS_BLK + t * 8 + (lane & 3) * 2 + u;
-      if (gi < nCols && gj < nCols && gi <= gj && c[t][u] != 0.0) atomicAdd(&C[(size_t)gi * nCols + gj], c[t][u]);
-    }
-  }
-}
-
 // grid: (blocks of A columns x blocks of B columns, k splits). A: [rows x aCols], B: [rows x bCols], both row-major
 // chunks of the same rows. C [aCols x bCols] += A^T B. A CTA owns one 64 x 64 block of C; warp w its rows 8 w .. 8 w + 8.
 // 16-row stages, double buffered (static shared memory, 35 KB): the loads of the next stage are issued into registers before the DMMAs of the
 // current one and stored to the other buffer after them, so one barrier per stage and no exposed load latency.
+// SYRK: B is A, blockIdx.x enumerates the block pairs bi <= bj of the upper triangle, only cells on or above the
+// diagonal are added (t(X) %*% X with more than 128 columns).
 constexpr int GT_KT = 16;
+template <bool SYRK>
 __global__ void __launch_bounds__(TS_THREADS)
 k_gemm_tn_dmma(const double* __restrict__ A, int aCols, const double* __restrict__ B, int bCols, int rows, int nBlkB,
                double* __restrict__ C, int rowsPerSplit) {
   __shared__ double sI[2][GT_KT * TS_LD];
   __shared__ double sJ[2][GT_KT * TS_LD];
-  const int bi = blockIdx.x / nBlkB, bj = blockIdx.x - bi * nBlkB;
+  int bi, bj;
+  if (SYRK) {  // decode the linear pair index into (bi <= bj)
+    int p = blockIdx.x;
+    bi = 0;
+    while (p >= nBlkB - bi) {
+      p -= nBlkB - bi;
+      bi++;
+    }
+    bj = bi + p;
+  } else {
+    bi = blockIdx.x / nBlkB;
+    bj = blockIdx.x - bi * nBlkB;
+  }
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int rBeg = blockIdx.y * rowsPerSplit, rEnd = min(rows, rBeg + rowsPerSplit);
   if (rBeg >= rEnd) return;
@@ -152,7 +116,7 @@ k_gemm_tn_dmma(const double* __restrict__ A, int aCols, const double* __restrict
 #pragma unroll
     for (int u = 0; u < 2; u++) {
       const int gj = bj * TS_BLK + t * 8 + (lane & 3) * 2 + u;
-      if (gi < aCols && gj < bCols && c[t][u] != 0.0) atomicAdd(&C[(size_t)gi * bCols + gj], c[t][u]);
+      if (gi < aCols && gj < bCols && (!SYRK || gi <= gj) && c[t][u] != 0.0) atomicAdd(&C[(size_t)gi * bCols + gj], c[t][u]);
     }
   }
 }
@@ -735,10 +699,10 @@ int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s) {
           k_tsmm_tri<false, -2><<<grid, TT_THREADS, triSmem, s>>>(nullptr, nullptr, nullptr, X, 0, rows, n, dOut);
       } else {
         int splits = std::max(1, std::min((rows + TS_KT * 8 - 1) / (TS_KT * 8), (4 * m->smCount + nPairs - 1) / nPairs));
-        int rowsPerSplit = ((rows + splits - 1) / splits + TS_KT - 1) / TS_KT * TS_KT;
+        int rowsPerSplit = ((rows + splits - 1) / splits + GT_KT - 1) / GT_KT * GT_KT;
         splits = (rows + rowsPerSplit - 1) / rowsPerSplit;
         dim3 grid(nPairs, splits);
-        k_syrk_dmma<<<grid, TS_THREADS, 0, s>>>(X, rows, n, nBlk, dOut, rowsPerSplit);
+        k_gemm_tn_dmma<true><<<grid, TS_THREADS, 0, s>>>(X, n, X, n, rows, nBlk, dOut, rowsPerSplit);
       }
       m->stats.kernel_launches++;
     }
@@ -778,7 +742,7 @@ int64_t launch_tmm(Matrix* L, Matrix* R, double* dOut, cudaStream_t s) {
     splits = (rows + rowsPerSplit - 1) / rowsPerSplit;
     dim3 grid(nBlocks, splits);
     if (r0 == 0) prof_begin(L, s);
-    k_gemm_tn_dmma<<<grid, TS_THREADS, 0, s>>>(XL, a, XR, b, rows, nBlkB, dOut, rowsPerSplit);
+    k_gemm_tn_dmma<false><<<grid, TS_THREADS, 0, s>>>(XL, a, XR, b, rows, nBlkB, dOut, rowsPerSplit);
     if (r0 == 0) prof_end(L, s);
     L->stats.kernel_launches++;
   }
