@@ -99,7 +99,9 @@ def cpu_reference_rate(rows: int, steps: int, warmup: int):
     from systemds_b200 import datagen
     o.build()
     cmb, y = datagen.config2(nRows=rows, nCols=N_COLS)
-    om = o.OracleMatrix(cmb)
+    # every host thread this process may run on, named explicitly: torchrun exports OMP_NUM_THREADS=1 to its
+    # ranks, which would otherwise shrink the OpenMP default and with it the baseline
+    om = o.OracleMatrix(cmb, threads=len(os.sched_getaffinity(0)))
     for _ in range(warmup):
         om.lmm(y)
     ts = []
