@@ -322,11 +322,13 @@ k_tsmm_tri(const DevGroup* __restrict__ groups, const int32_t* __restrict__ colS
 // The same product with 16 warps in one CTA per SM. The triangle's tiles are dealt to the warps as contiguous
 // runs of the row-major tile order (at most T16_MAXT tiles each, so a warp's A fragment changes at most twice),
 // which cuts the accumulators from 96 to 18 registers per thread and leaves room for a two-deep register
-// pipeline of the decode: while the DMMAs of stage s run, the dictionary gathers of stage s+1 and the map loads
-// of stage s+2 are in flight, and their results are written to the other shared-memory buffer only after the
-// DMMAs have been issued. The 8-warp kernel above stalls on those gathers (its decode must finish, values in
-// shared memory, before its DMMAs start).
+// pipeline of the decode: while the DMMAs of stage s run, the dictionary gathers of stage s+2 and the map loads
+// of stage s+3 are in flight; their values go to one of four shared-memory stage buffers an iteration later.
+// The 8-warp kernel above stalls on those gathers (its decode must finish, values in shared memory, before its
+// DMMAs start).
 // --------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
 constexpr int T16_WARPS = 16;
 constexpr int T16_THREADS = T16_WARPS * 32;
 constexpr int T16_MAXC = 8;   // columns decoded per warp and stage at 128 columns
@@ -334,13 +336,19 @@ constexpr int T16_MAXC = 8;   // columns decoded per warp and stage at 128 colum
 template <bool FUSED, int MT, int TPW>
 __global__ void __launch_bounds__(T16_THREADS, 1)
 k_tsmm_tri16(const DevGroup* __restrict__ groups, const int32_t* __restrict__ colSrc, const double* __restrict__ constV,
-             const double* __restrict__ X, int rowBegin, int rowEnd, int nCols, double* __restrict__ C) {
-  extern __shared__ __align__(16) double XtAll[];  // two stages of [NT * 8][TT_LD], then the column records
+             const double* __restrict__ X, int rowBegin, int rowEnd, int nCols, double* __restrict__ C, int32_t* err) {
+  extern __shared__ __align__(16) double XtAll[];  // four stages of [NT * 8][TT_LD], the column records, four mbarriers
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int NT = (nCols + 7) >> 3;
   const int nColsPad = NT * 8;
   const int stageDoubles = nColsPad * TT_LD;
-  TsmmCol* cols = (TsmmCol*)(XtAll + 2 * stageDoubles);
+  TsmmCol* cols = (TsmmCol*)(XtAll + 4 * stageDoubles);
+  uint64_t* bars = (uint64_t*)(cols + nColsPad);
+  if (tid == 0) {
+    for (int b = 0; b < 4; b++) asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&bars[b])), "r"(T16_THREADS));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
   if (FUSED) {
     for (int cc = tid; cc < nColsPad; cc += T16_THREADS) {
       TsmmCol d;
@@ -457,16 +465,46 @@ k_tsmm_tri16(const DevGroup* __restrict__ groups, const int32_t* __restrict__ co
       if (cc < nColsPad) Xt[cc * TT_LD + lane] = vals[b] + ((FUSED && inRange) ? cols[cc].cst : 0.0);
     }
   };
+  // Four stage buffers, each with an mbarrier that counts the 512 threads' "my part of this stage is stored". A warp
+  // stores its part of stage s + 1 and signals, issues the loads of the stages behind it, and only then waits for
+  // stage s -- which every warp finished storing a whole iteration earlier -- so the warps drift up to a stage apart
+  // and their DMMA phases no longer coincide (with one __syncthreads per stage they did: the tensor pipe was 47 %
+  // busy yet throttling). Buffer (s + 1) % 4 was last read by the DMMAs of stage s - 3; a warp that is about to
+  // store stage s + 1 has seen stage s - 1 complete, i.e. every warp had stored it, which each did after its
+  // DMMAs of stage s - 3: no barrier is needed before the store.
+  auto bar_addr = [&](int b) { return smem_addr(&bars[b]); };
+  auto signal = [&](int b) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_addr(b)) : "memory"); };
+  auto wait_for = [&](int b, uint32_t parity) -> bool {  // bounded: gives up after 2^20 polls and reports it
+    uint32_t done = 0;
+    for (int it = 0; it < (1 << 20) && !done; it++)
+      asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                   : "=r"(done)
+                   : "r"(bar_addr(b)), "r"(parity)
+                   : "memory");
+    return done != 0;
+  };
   load_ids(sa);
   gather(sa);
-  if (sa + 1 < sb) load_ids(sa + 1);
   store(sa, XtAll);
-  __syncthreads();
+  signal(0);
+  if (sa + 1 < sb) {
+    load_ids(sa + 1);
+    gather(sa + 1);
+  }
+  if (sa + 2 < sb) load_ids(sa + 2);
   for (int64_t st = sa; st < sb; st++) {
-    const int cur = (int)(st - sa) & 1;
-    if (st + 1 < sb) gather(st + 1);    // addresses from ids (loaded one iteration ago)
-    if (st + 2 < sb) load_ids(st + 2);  // then the registers take the next stage's ids
-    const double* Xt = XtAll + cur * stageDoubles;
+    const int it = (int)(st - sa);
+    if (st + 1 < sb) {  // vals holds stage st + 1 (gathered one iteration ago)
+      store(st + 1, XtAll + ((it + 1) & 3) * stageDoubles);
+      signal((it + 1) & 3);
+    }
+    if (st + 2 < sb) gather(st + 2);    // addresses from ids (loaded one iteration ago)
+    if (st + 3 < sb) load_ids(st + 3);  // then the registers take the ids of the stage after that
+    if (!wait_for(it & 3, (uint32_t)(it >> 2) & 1u)) {
+      if (lane == 0) atomicExch(err, 7);  // stage never completed: give up, the host reports the self-check
+      return;
+    }
+    const double* Xt = XtAll + (it & 3) * stageDoubles;
     // k-step outermost, tile slots innermost: consecutive DMMAs go to different accumulators, so none waits for
     // the one before it; no branch in the loop body (the A reload is a predicated load)
     // (the fragments of k-step ks + 4 are loaded into registers before the DMMAs of k-step ks are issued, so the
@@ -494,8 +532,6 @@ k_tsmm_tri16(const DevGroup* __restrict__ groups, const int32_t* __restrict__ co
         for (int sl = 0; sl < TPW; sl++) bC[sl] = bN[sl];
       }
     }
-    if (st + 1 < sb) store(st + 1, XtAll + (cur ^ 1) * stageDoubles);
-    __syncthreads();
   }
   // ---- add the partial tiles ----
   {
@@ -602,20 +638,20 @@ int64_t measure_fp64_peaks(int device, double* dmmaTflops, double* dfmaTflops) {
 // the map widths the decode specialises on.
 template <int TPW>
 static void tri16_go(bool fused, int mt, int grid, size_t smem, cudaStream_t s, const DevGroup* groups, const int32_t* colSrc,
-                     const double* constV, const double* X, int rows, int n, double* dOut) {
-  if (!fused) k_tsmm_tri16<false, -2, TPW><<<grid, T16_THREADS, smem, s>>>(groups, colSrc, constV, X, 0, rows, n, dOut);
+                     const double* constV, const double* X, int rows, int n, double* dOut, int32_t* err) {
+  if (!fused) k_tsmm_tri16<false, -2, TPW><<<grid, T16_THREADS, smem, s>>>(groups, colSrc, constV, X, 0, rows, n, dOut, err);
   else if (mt == CLA_MAP_BYTE)
-    k_tsmm_tri16<true, CLA_MAP_BYTE, TPW><<<grid, T16_THREADS, smem, s>>>(groups, colSrc, constV, X, 0, rows, n, dOut);
+    k_tsmm_tri16<true, CLA_MAP_BYTE, TPW><<<grid, T16_THREADS, smem, s>>>(groups, colSrc, constV, X, 0, rows, n, dOut, err);
   else if (mt == CLA_MAP_CHAR)
-    k_tsmm_tri16<true, CLA_MAP_CHAR, TPW><<<grid, T16_THREADS, smem, s>>>(groups, colSrc, constV, X, 0, rows, n, dOut);
-  else k_tsmm_tri16<true, -2, TPW><<<grid, T16_THREADS, smem, s>>>(groups, colSrc, constV, X, 0, rows, n, dOut);
+    k_tsmm_tri16<true, CLA_MAP_CHAR, TPW><<<grid, T16_THREADS, smem, s>>>(groups, colSrc, constV, X, 0, rows, n, dOut, err);
+  else k_tsmm_tri16<true, -2, TPW><<<grid, T16_THREADS, smem, s>>>(groups, colSrc, constV, X, 0, rows, n, dOut, err);
 }
 static void launch_tri16(bool fused, int mt, int n, int grid, size_t smem, cudaStream_t s, const DevGroup* groups,
-                         const int32_t* colSrc, const double* constV, const double* X, int rows, double* dOut) {
+                         const int32_t* colSrc, const double* constV, const double* X, int rows, double* dOut, int32_t* err) {
   const int NT = (n + 7) / 8, perWarp = (NT * (NT + 1) / 2 + T16_WARPS - 1) / T16_WARPS;
-  if (perWarp <= 3) tri16_go<3>(fused, mt, grid, smem, s, groups, colSrc, constV, X, rows, n, dOut);
-  else if (perWarp <= 6) tri16_go<6>(fused, mt, grid, smem, s, groups, colSrc, constV, X, rows, n, dOut);
-  else tri16_go<9>(fused, mt, grid, smem, s, groups, colSrc, constV, X, rows, n, dOut);
+  if (perWarp <= 3) tri16_go<3>(fused, mt, grid, smem, s, groups, colSrc, constV, X, rows, n, dOut, err);
+  else if (perWarp <= 6) tri16_go<6>(fused, mt, grid, smem, s, groups, colSrc, constV, X, rows, n, dOut, err);
+  else tri16_go<9>(fused, mt, grid, smem, s, groups, colSrc, constV, X, rows, n, dOut, err);
 }
 template <int TPW>
 static int64_t tri16_set_smem_t(int bytes) {
@@ -642,6 +678,7 @@ int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s) {
   bool denseOnly = m->colSrcValid;
   for (auto& g : m->groups) denseOnly &= (g.type == GT_DDC || g.type == GT_UNC);
   const size_t triSmem = (size_t)((n + 7) / 8 * 8) * (2 * TT_LD * sizeof(double) + sizeof(TsmmCol));
+  const size_t tri16Smem = (size_t)((n + 7) / 8 * 8) * (4 * TT_LD * sizeof(double) + sizeof(TsmmCol)) + 4 * sizeof(uint64_t);
   static bool attrSet[64] = {};  // per device: function attributes belong to the device's context
   bool& attr = attrSet[m->device & 63];
   if (!attr) {
@@ -650,7 +687,7 @@ int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s) {
     CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri<true, CLA_MAP_BYTE>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxSmem));
     CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri<true, CLA_MAP_CHAR>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxSmem));
     CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri<false, -2>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxSmem));
-    if ((rc = tri16_set_smem(maxSmem)) < 0) return rc;
+    if ((rc = tri16_set_smem(128 * (4 * TT_LD * 8 + (int)sizeof(TsmmCol)) + 32)) < 0) return rc;
     attr = true;
   }
   static const bool use16 = !getenv("CLA_TSMM_8WARP");  // tuning aid: the first-generation 8-warp kernel
@@ -667,8 +704,8 @@ int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s) {
     }
     prof_begin(m, s);
     if (use16) {
-      launch_tri16(true, mt, n, (int)std::min<int64_t>(m->smCount, nStages), triSmem, s, m->dGroups, m->dColSrc,
-                   m->hasConst ? m->dConstV : nullptr, nullptr, m->nRows, dOut);
+      launch_tri16(true, mt, n, (int)std::min<int64_t>(m->smCount, nStages), tri16Smem, s, m->dGroups, m->dColSrc,
+                   m->hasConst ? m->dConstV : nullptr, nullptr, m->nRows, dOut, m->dErr);
     } else {
       auto kern = mt == CLA_MAP_BYTE ? k_tsmm_tri<true, CLA_MAP_BYTE> : (mt == CLA_MAP_CHAR ? k_tsmm_tri<true, CLA_MAP_CHAR> : k_tsmm_tri<true, -2>);
       kern<<<grid, TT_THREADS, triSmem, s>>>(m->dGroups, m->dColSrc, m->hasConst ? m->dConstV : nullptr, nullptr, 0, m->nRows,
@@ -693,8 +730,8 @@ int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s) {
         const int64_t nStages = ((int64_t)rows + TT_KT - 1) / TT_KT;
         const int grid = (int)std::min<int64_t>(2 * m->smCount, nStages);
         if (use16)
-          launch_tri16(false, -2, n, (int)std::min<int64_t>(m->smCount, nStages), triSmem, s, nullptr, nullptr, nullptr, X,
-                       rows, dOut);
+          launch_tri16(false, -2, n, (int)std::min<int64_t>(m->smCount, nStages), tri16Smem, s, nullptr, nullptr, nullptr, X,
+                       rows, dOut, m->dErr);
         else
           k_tsmm_tri<false, -2><<<grid, TT_THREADS, triSmem, s>>>(nullptr, nullptr, nullptr, X, 0, rows, n, dOut);
       } else {
