@@ -122,19 +122,14 @@ k_gemm_tn_dmma(const double* __restrict__ A, int aCols, const double* __restrict
 }
 
 // --------------------------------------------------------------------------------------------------
-// Up to 128 columns: one CTA holds the whole upper triangle of the result (8x8 DMMA tiles, split over the 8
-// warps in row-major order so a warp's tiles share their A fragment), so nothing of the product is computed
-// twice and only the triangle's tiles are computed at all. Rows are split across CTAs; each adds its partial
-// triangle to the result with atomics at the end.
+// Up to 128 columns: one CTA holds the whole upper triangle of the result as 8x8 DMMA tiles, so nothing of the
+// product is computed twice and only the triangle's tiles are computed at all. Rows are split across CTAs; each
+// adds its partial triangle to the result with atomics at the end.
 // FUSED: the 32-row stage is decoded straight from the maps and dictionaries (dense-map and uncompressed groups
 // only), so the dense form of X never exists, not even in L2. Otherwise the stage is read from a decompressed chunk.
 // --------------------------------------------------------------------------------------------------
 constexpr int TT_KT = 32;             // rows per stage
 constexpr int TT_LD = TT_KT + 4;      // stride of the transposed stage Xt[col][row]: = 4 mod 16
-constexpr int TT_MAXJ = 16;           // tile columns at 128 matrix columns
-constexpr int TT_CONS = 8;            // warps issuing DMMA
-constexpr int TT_PROD = 0;            // extra warps that only decode (0: every warp decodes, then multiplies)
-constexpr int TT_THREADS = (TT_CONS + TT_PROD) * 32;
 
 // What the staging loop needs to know about one matrix column, kept in shared memory.
 struct TsmmCol {
@@ -146,186 +141,13 @@ struct TsmmCol {
   int32_t gCols;
 };
 
-// Warp w owns tile rows I1 = w and I2 = NT-1-w of the upper triangle (NT+1 tiles together, for every w), so the
-// B fragment of tile column J serves both rows and every fragment address is the warp's base plus a constant.
-// MT: map type shared by every column (CLA_MAP_BYTE for 1-byte, CLA_MAP_CHAR for 2-byte cells), or -2 = mixed.
-template <bool FUSED, int MT>
-__global__ void __launch_bounds__(TT_THREADS, 2)
-k_tsmm_tri(const DevGroup* __restrict__ groups, const int32_t* __restrict__ colSrc, const double* __restrict__ constV,
-           const double* __restrict__ X, int rowBegin, int rowEnd, int nCols, double* __restrict__ C) {
-  extern __shared__ __align__(16) double XtAll[];  // two stages of [NT * 8][TT_LD], then the column records
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int NT = (nCols + 7) >> 3;
-  const int nColsPad = NT * 8;
-  const int stageDoubles = nColsPad * TT_LD;
-  TsmmCol* cols = (TsmmCol*)(XtAll + 2 * stageDoubles);
-  if (FUSED) {
-    for (int cc = tid; cc < nColsPad; cc += TT_THREADS) {
-      TsmmCol d;
-      d.map = nullptr;
-      d.mapHi = nullptr;
-      d.src = nullptr;
-      d.cst = (constV && cc < nCols) ? constV[cc] : 0.0;
-      d.mapType = 0;
-      d.gCols = 1;
-      if (cc < nCols && colSrc[2 * cc] >= 0) {
-        const DevGroup& g = groups[colSrc[2 * cc]];
-        const int j = colSrc[2 * cc + 1];
-        d.gCols = g.gCols;
-        if (g.type == GT_UNC) {
-          d.mapType = -1;
-          d.src = g.dense + j;
-          d.map = g.dense;  // non-null marker
-        } else {
-          d.mapType = g.mapType;
-          d.map = g.mapType == CLA_MAP_ZERO ? (const void*)g.dict : g.map;
-          d.mapHi = g.mapHi;
-          d.src = g.dict + j;
-        }
-      }
-      cols[cc] = d;
-    }
-    __syncthreads();
-  }
-  // this warp's two tile rows; len = number of tiles of each (counted from the last tile column backwards)
-  const int half = NT >> 1;
-  const int I1 = warp, I2 = NT - 1 - warp;
-  int len1 = 0, len2 = 0;
-  if (warp < half) {
-    len1 = NT - I1;
-    len2 = NT - I2;  // = I1 + 1
-  } else if ((NT & 1) && warp == half)
-    len1 = NT - I1;
-  double c1[TT_MAXJ][2], c2[TT_MAXJ / 2][2];  // the second row of a pair has at most NT / 2 tiles
-#pragma unroll
-  for (int i = 0; i < TT_MAXJ; i++) c1[i][0] = c1[i][1] = 0.0;
-#pragma unroll
-  for (int i = 0; i < TT_MAXJ / 2; i++) c2[i][0] = c2[i][1] = 0.0;
-  const int am = lane >> 2, ak = lane & 3;
-  const int a1o = (min(I1, NT - 1) * 8 + am) * TT_LD + ak;
-  const int a2o = (min(max(I2, 0), NT - 1) * 8 + am) * TT_LD + ak;
-  const int bo = ((NT - 1) * 8 + am) * TT_LD + ak;  // tile column NT-1; column NT-1-jr is 8*TT_LD*jr below
-
-  const int64_t nStages = ((int64_t)(rowEnd - rowBegin) + TT_KT - 1) / TT_KT;
-  const int64_t sa = nStages * blockIdx.x / gridDim.x, sb = nStages * (blockIdx.x + 1) / gridDim.x;
-  // Decode one 32-row stage; a warp takes every nw-th column, four at a time so that the map loads of a batch
-  // are all in flight before the first dictionary load that depends on one of them.
-  constexpr int NB = 4;
-  auto stage = [&](int64_t st, double* Xt, int w, int nw) {
-    const int row = rowBegin + (int)st * TT_KT + lane;  // lanes run along rows
-    const bool inRange = row < rowEnd;
-    for (int c0 = w; c0 < nColsPad; c0 += nw * NB) {
-      double v[NB];
-      if (FUSED) {
-        const double* src[NB];
-        size_t off[NB];
-#pragma unroll
-        for (int b = 0; b < NB; b++) {
-          const int cc = c0 + b * nw;
-          v[b] = 0.0;
-          src[b] = nullptr;
-          off[b] = 0;
-          if (cc < nColsPad && inRange) {
-            if (MT == CLA_MAP_BYTE || MT == CLA_MAP_CHAR) {  // every column is a dense-map column of this width
-              const TsmmCol& d = cols[cc];
-              v[b] = d.cst;
-              src[b] = d.src;
-              if (src[b])
-                off[b] = (size_t)(MT == CLA_MAP_BYTE ? (int)((const uint8_t*)d.map)[row] : (int)((const uint16_t*)d.map)[row]) *
-                         d.gCols;
-            } else {
-              const TsmmCol d = cols[cc];
-              v[b] = d.cst;
-              if (d.map) {
-                src[b] = d.src;
-                off[b] = (d.mapType < 0 ? (size_t)row : (size_t)map_get(d.mapType, d.map, d.mapHi, row)) * d.gCols;
-              }
-            }
-          }
-        }
-#pragma unroll
-        for (int b = 0; b < NB; b++)
-          if (src[b]) v[b] += src[b][off[b]];
-      } else {
-#pragma unroll
-        for (int b = 0; b < NB; b++) {
-          const int cc = c0 + b * nw;
-          v[b] = (inRange && cc < nCols) ? X[(size_t)(row - rowBegin) * nCols + cc] : 0.0;
-        }
-      }
-#pragma unroll
-      for (int b = 0; b < NB; b++) {
-        const int cc = c0 + b * nw;
-        if (cc < nColsPad) Xt[cc * TT_LD + lane] = v[b];
-      }
-    }
-  };
-  if (sa < sb) stage(sa, XtAll, warp, TT_CONS);
-  __syncthreads();
-  for (int64_t st = sa; st < sb; st++) {
-    const int cur = (int)(st - sa) & 1;
-    // issue the next stage's decode first: its loads overlap the DMMAs below (other buffer, no hazard)
-    if (st + 1 < sb) stage(st + 1, XtAll + (cur ^ 1) * stageDoubles, warp, TT_CONS);
-    {
-      const double* Xt = XtAll + cur * stageDoubles;
-      // four k-steps at a time: the A fragments of both tile rows stay in registers while the warp walks its tile
-      // columns, so the "does this warp own tile column jr" tests run once per four DMMAs instead of once per DMMA
-#pragma unroll
-      for (int kh = 0; kh < TT_KT; kh += 16) {
-        double a1[4], a2[4];
-#pragma unroll
-        for (int q = 0; q < 4; q++) {
-          a1[q] = Xt[a1o + kh + 4 * q];
-          a2[q] = Xt[a2o + kh + 4 * q];
-        }
-#pragma unroll
-        for (int jr = 0; jr < TT_MAXJ; jr++) {
-          if (jr < TT_MAXJ / 2 && jr < len2) {
-#pragma unroll
-            for (int q = 0; q < 4; q++) {
-              const double b = Xt[bo + kh + 4 * q - jr * 8 * TT_LD];
-              dmma884(c1[jr][0], c1[jr][1], a1[q], b);
-              dmma884(c2[jr < TT_MAXJ / 2 ? jr : 0][0], c2[jr < TT_MAXJ / 2 ? jr : 0][1], a2[q], b);
-            }
-          } else if (jr < len1) {
-#pragma unroll
-            for (int q = 0; q < 4; q++) {
-              const double b = Xt[bo + kh + 4 * q - jr * 8 * TT_LD];
-              dmma884(c1[jr][0], c1[jr][1], a1[q], b);
-            }
-          }
-        }
-      }
-    }
-    __syncthreads();
-  }
-#pragma unroll
-  for (int jr = 0; jr < TT_MAXJ; jr++) {
-    const int J = NT - 1 - jr;
-#pragma unroll
-    for (int u = 0; u < 2; u++) {
-      const int gj = J * 8 + (lane & 3) * 2 + u;
-      if (jr < len1) {
-        const int gi = I1 * 8 + (lane >> 2);
-        if (gi < nCols && gj < nCols && gi <= gj && c1[jr][u] != 0.0) atomicAdd(&C[(size_t)gi * nCols + gj], c1[jr][u]);
-      }
-      if (jr < TT_MAXJ / 2 && jr < len2) {
-        const int gi = I2 * 8 + (lane >> 2);
-        if (gi < nCols && gj < nCols && gi <= gj && c2[jr < TT_MAXJ / 2 ? jr : 0][u] != 0.0)
-          atomicAdd(&C[(size_t)gi * nCols + gj], c2[jr < TT_MAXJ / 2 ? jr : 0][u]);
-      }
-    }
-  }
-}
-
 // --------------------------------------------------------------------------------------------------
-// The same product with 16 warps in one CTA per SM. The triangle's tiles are dealt to the warps as contiguous
-// runs of the row-major tile order (at most T16_MAXT tiles each, so a warp's A fragment changes at most twice),
-// which cuts the accumulators from 96 to 18 registers per thread and leaves room for a two-deep register
-// pipeline of the decode: while the DMMAs of stage s run, the dictionary gathers of stage s+2 and the map loads
+// 16 warps in one CTA per SM. The triangle's tiles are dealt to the warps as contiguous runs of the row-major tile
+// order (TPW tiles each, so a warp's A fragment changes at most a few times), which keeps the accumulators at
+// 2 * TPW registers per thread and leaves room for a two-deep register pipeline of the decode: while the DMMAs of stage s run, the dictionary gathers of stage s+2 and the map loads
 // of stage s+3 are in flight; their values go to one of four shared-memory stage buffers an iteration later.
-// The 8-warp kernel above stalls on those gathers (its decode must finish, values in shared memory, before its
-// DMMAs start).
+// (An earlier 8-warp version, whose decode had to finish, values in shared memory, before its DMMAs started,
+// stalled 7.6 cycles per issue on those gathers; this one 0.5.)
 // --------------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -677,23 +499,15 @@ int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s) {
   const bool tri = n <= 128;
   bool denseOnly = m->colSrcValid;
   for (auto& g : m->groups) denseOnly &= (g.type == GT_DDC || g.type == GT_UNC);
-  const size_t triSmem = (size_t)((n + 7) / 8 * 8) * (2 * TT_LD * sizeof(double) + sizeof(TsmmCol));
   const size_t tri16Smem = (size_t)((n + 7) / 8 * 8) * (4 * TT_LD * sizeof(double) + sizeof(TsmmCol)) + 4 * sizeof(uint64_t);
   static bool attrSet[64] = {};  // per device: function attributes belong to the device's context
   bool& attr = attrSet[m->device & 63];
   if (!attr) {
-    const int maxSmem = 128 * (2 * TT_LD * 8 + (int)sizeof(TsmmCol));
-    CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri<true, -2>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxSmem));
-    CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri<true, CLA_MAP_BYTE>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxSmem));
-    CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri<true, CLA_MAP_CHAR>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxSmem));
-    CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri<false, -2>, cudaFuncAttributeMaxDynamicSharedMemorySize, maxSmem));
     if ((rc = tri16_set_smem(128 * (4 * TT_LD * 8 + (int)sizeof(TsmmCol)) + 32)) < 0) return rc;
     attr = true;
   }
-  static const bool use16 = !getenv("CLA_TSMM_8WARP");  // tuning aid: the first-generation 8-warp kernel
   if (tri && denseOnly) {  // one launch over all rows, decoding as it goes
     const int64_t nStages = ((int64_t)m->nRows + TT_KT - 1) / TT_KT;
-    const int grid = (int)std::min<int64_t>(2 * m->smCount, nStages);
     // one map width for every column (and every column held by a dense-map group): the specialised decode
     int mt = -1;
     for (auto& g : m->groups) {
@@ -703,14 +517,8 @@ int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s) {
       mt = (mt == -1 || mt == w) ? w : -2;
     }
     prof_begin(m, s);
-    if (use16) {
-      launch_tri16(true, mt, n, (int)std::min<int64_t>(m->smCount, nStages), tri16Smem, s, m->dGroups, m->dColSrc,
-                   m->hasConst ? m->dConstV : nullptr, nullptr, m->nRows, dOut, m->dErr);
-    } else {
-      auto kern = mt == CLA_MAP_BYTE ? k_tsmm_tri<true, CLA_MAP_BYTE> : (mt == CLA_MAP_CHAR ? k_tsmm_tri<true, CLA_MAP_CHAR> : k_tsmm_tri<true, -2>);
-      kern<<<grid, TT_THREADS, triSmem, s>>>(m->dGroups, m->dColSrc, m->hasConst ? m->dConstV : nullptr, nullptr, 0, m->nRows,
-                                            n, dOut);
-    }
+    launch_tri16(true, mt, n, (int)std::min<int64_t>(m->smCount, nStages), tri16Smem, s, m->dGroups, m->dColSrc,
+                 m->hasConst ? m->dConstV : nullptr, nullptr, m->nRows, dOut, m->dErr);
     prof_end(m, s);
     m->stats.kernel_launches++;
   } else {
@@ -728,12 +536,8 @@ int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s) {
       const int rows = r1 - (int)r0;
       if (tri) {
         const int64_t nStages = ((int64_t)rows + TT_KT - 1) / TT_KT;
-        const int grid = (int)std::min<int64_t>(2 * m->smCount, nStages);
-        if (use16)
-          launch_tri16(false, -2, n, (int)std::min<int64_t>(m->smCount, nStages), tri16Smem, s, nullptr, nullptr, nullptr, X,
-                       rows, dOut, m->dErr);
-        else
-          k_tsmm_tri<false, -2><<<grid, TT_THREADS, triSmem, s>>>(nullptr, nullptr, nullptr, X, 0, rows, n, dOut);
+        launch_tri16(false, -2, n, (int)std::min<int64_t>(m->smCount, nStages), tri16Smem, s, nullptr, nullptr, nullptr, X, rows,
+                     dOut, m->dErr);
       } else {
         int splits = std::max(1, std::min((rows + TS_KT * 8 - 1) / (TS_KT * 8), (4 * m->smCount + nPairs - 1) / nPairs));
         int rowsPerSplit = ((rows + splits - 1) / splits + GT_KT - 1) / GT_KT * GT_KT;
