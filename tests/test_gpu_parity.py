@@ -470,6 +470,23 @@ def test_concurrent_handles_and_shared_handle():
     b.free()
 
 
+def test_many_sparse_groups_wide_rhs(oracle):
+    """More than 256 SDC / RLE groups: the tensor-core RMM falls back to its first-generation kernel (one lane per
+    group covers 256 of each)."""
+    kinds = ("sdcz",) * 150 + ("sdc",) * 120 + ("rle",) * 270 + ("ddc",) * 5
+    cmb = datagen.random_cmb(4242, 3001, kinds).to_device()
+    om = oracle.OracleMatrix(cmb)
+    aX = np.abs(dense_of(cmb))
+    rng = np.random.default_rng(8)
+    V = rng.standard_normal((cmb.clen, 17))
+    assert rel_err(CLALibRightMultBy.rightMultByMatrix(cmb, V), om.rmm(V), aX @ np.abs(V) + 1e-300) < TOL
+    v = rng.standard_normal(cmb.clen)
+    assert rel_err(CLALibRightMultBy.rightMultByMatrix(cmb, v), om.rmm(v), aX @ np.abs(v).reshape(-1, 1) + 1e-300) < TOL
+    y = rng.standard_normal((1, cmb.rlen))
+    assert rel_err(CLALibLeftMultBy.leftMultByMatrix(cmb, y), om.lmm(y), np.abs(y) @ aX + 1e-300) < TOL
+    cmb.free()
+
+
 def test_double_compressed_transpose_rules():
     """The remaining flag combinations for two compressed operands (CLALibMatrixMult.java:96-124)."""
     m1 = datagen.random_cmb(801, 40, ("ddc", "sdc", "rle", "const")).to_device()       # [40 x c1]
