@@ -155,7 +155,10 @@ constexpr int T16_WARPS = 16;
 constexpr int T16_THREADS = T16_WARPS * 32;
 constexpr int T16_MAXC = 8;   // columns decoded per warp and stage at 128 columns
 
-template <bool FUSED, int MT, int TPW>
+// SIMPLE (with MT = byte or char): every column is held by a single-column dense-map group of that width and
+// there is no constant part, so a column needs two pointers (map, dictionary) instead of the full record: the
+// record reads were 40 % of the kernel's shared-memory load instructions.
+template <bool FUSED, int MT, int TPW, bool SIMPLE>
 __global__ void __launch_bounds__(T16_THREADS, 1)
 k_tsmm_tri16(const DevGroup* __restrict__ groups, const int32_t* __restrict__ colSrc, const double* __restrict__ constV,
              const double* __restrict__ X, int rowBegin, int rowEnd, int nCols, double* __restrict__ C, int32_t* err) {
@@ -196,6 +199,16 @@ k_tsmm_tri16(const DevGroup* __restrict__ groups, const int32_t* __restrict__ co
         }
       }
       cols[cc] = d;
+    }
+    __syncthreads();
+  }
+  // SIMPLE: the two pointers per column, packed behind the mbarriers
+  const void** mapArr = (const void**)(bars + 4);
+  const double** srcArr = (const double**)(mapArr + nColsPad);
+  if (SIMPLE) {
+    for (int cc = tid; cc < nColsPad; cc += T16_THREADS) {
+      mapArr[cc] = cols[cc].map;
+      srcArr[cc] = cols[cc].src;
     }
     __syncthreads();
   }
@@ -250,7 +263,10 @@ k_tsmm_tri16(const DevGroup* __restrict__ groups, const int32_t* __restrict__ co
     for (int b = 0; b < T16_MAXC; b++) {
       const int cc = warp + T16_WARPS * b;
       ids[b] = 0;
-      if (cc < nColsPad && inRange) {
+      if (SIMPLE) {
+        if (cc < nCols && inRange)
+          ids[b] = MT == CLA_MAP_BYTE ? ld_u8_here((const uint8_t*)mapArr[cc] + row) : ld_u16_here((const uint16_t*)mapArr[cc] + row);
+      } else if (cc < nColsPad && inRange) {
         const TsmmCol& d = cols[cc];
         if (d.map && d.mapType >= 0) {
           // the raw id only: any arithmetic on it here would wait for the load
@@ -268,7 +284,9 @@ k_tsmm_tri16(const DevGroup* __restrict__ groups, const int32_t* __restrict__ co
     for (int b = 0; b < T16_MAXC; b++) {
       const int cc = warp + T16_WARPS * b;
       vals[b] = 0.0;
-      if (cc < nColsPad && inRange) {
+      if (SIMPLE) {
+        if (cc < nCols && inRange) vals[b] = ld_f64_here(srcArr[cc] + ids[b]);
+      } else if (cc < nColsPad && inRange) {
         // volatile asm keeps the load where it is written, ahead of the (volatile) DMMAs: left to itself the
         // compiler sinks it to its use behind them and the pipeline is gone
         if (FUSED) {
@@ -284,7 +302,7 @@ k_tsmm_tri16(const DevGroup* __restrict__ groups, const int32_t* __restrict__ co
 #pragma unroll
     for (int b = 0; b < T16_MAXC; b++) {
       const int cc = warp + T16_WARPS * b;
-      if (cc < nColsPad) Xt[cc * TT_LD + lane] = vals[b] + ((FUSED && inRange) ? cols[cc].cst : 0.0);
+      if (cc < nColsPad) Xt[cc * TT_LD + lane] = vals[b] + ((FUSED && !SIMPLE && inRange) ? cols[cc].cst : 0.0);
     }
   };
   // Four stage buffers, each with an mbarrier that counts the 512 threads' "my part of this stage is stored". A warp
@@ -459,28 +477,34 @@ int64_t measure_fp64_peaks(int device, double* dmmaTflops, double* dfmaTflops) {
 // The 16-warp kernel is instantiated for 3, 6 and 9 tile slots per warp (up to 48, 104 and 128 columns) and for
 // the map widths the decode specialises on.
 template <int TPW>
-static void tri16_go(bool fused, int mt, int grid, size_t smem, cudaStream_t s, const DevGroup* groups, const int32_t* colSrc,
-                     const double* constV, const double* X, int rows, int n, double* dOut, int32_t* err) {
-  if (!fused) k_tsmm_tri16<false, -2, TPW><<<grid, T16_THREADS, smem, s>>>(groups, colSrc, constV, X, 0, rows, n, dOut, err);
+static void tri16_go(bool fused, int mt, bool simple, int grid, size_t smem, cudaStream_t s, const DevGroup* groups,
+                     const int32_t* colSrc, const double* constV, const double* X, int rows, int n, double* dOut, int32_t* err) {
+  if (!fused) k_tsmm_tri16<false, -2, TPW, false><<<grid, T16_THREADS, smem, s>>>(groups, colSrc, constV, X, 0, rows, n, dOut, err);
+  else if (mt == CLA_MAP_BYTE && simple)
+    k_tsmm_tri16<true, CLA_MAP_BYTE, TPW, true><<<grid, T16_THREADS, smem, s>>>(groups, colSrc, constV, X, 0, rows, n, dOut, err);
+  else if (mt == CLA_MAP_CHAR && simple)
+    k_tsmm_tri16<true, CLA_MAP_CHAR, TPW, true><<<grid, T16_THREADS, smem, s>>>(groups, colSrc, constV, X, 0, rows, n, dOut, err);
   else if (mt == CLA_MAP_BYTE)
-    k_tsmm_tri16<true, CLA_MAP_BYTE, TPW><<<grid, T16_THREADS, smem, s>>>(groups, colSrc, constV, X, 0, rows, n, dOut, err);
+    k_tsmm_tri16<true, CLA_MAP_BYTE, TPW, false><<<grid, T16_THREADS, smem, s>>>(groups, colSrc, constV, X, 0, rows, n, dOut, err);
   else if (mt == CLA_MAP_CHAR)
-    k_tsmm_tri16<true, CLA_MAP_CHAR, TPW><<<grid, T16_THREADS, smem, s>>>(groups, colSrc, constV, X, 0, rows, n, dOut, err);
-  else k_tsmm_tri16<true, -2, TPW><<<grid, T16_THREADS, smem, s>>>(groups, colSrc, constV, X, 0, rows, n, dOut, err);
+    k_tsmm_tri16<true, CLA_MAP_CHAR, TPW, false><<<grid, T16_THREADS, smem, s>>>(groups, colSrc, constV, X, 0, rows, n, dOut, err);
+  else k_tsmm_tri16<true, -2, TPW, false><<<grid, T16_THREADS, smem, s>>>(groups, colSrc, constV, X, 0, rows, n, dOut, err);
 }
-static void launch_tri16(bool fused, int mt, int n, int grid, size_t smem, cudaStream_t s, const DevGroup* groups,
+static void launch_tri16(bool fused, int mt, bool simple, int n, int grid, size_t smem, cudaStream_t s, const DevGroup* groups,
                          const int32_t* colSrc, const double* constV, const double* X, int rows, double* dOut, int32_t* err) {
   const int NT = (n + 7) / 8, perWarp = (NT * (NT + 1) / 2 + T16_WARPS - 1) / T16_WARPS;
-  if (perWarp <= 3) tri16_go<3>(fused, mt, grid, smem, s, groups, colSrc, constV, X, rows, n, dOut, err);
-  else if (perWarp <= 6) tri16_go<6>(fused, mt, grid, smem, s, groups, colSrc, constV, X, rows, n, dOut, err);
-  else tri16_go<9>(fused, mt, grid, smem, s, groups, colSrc, constV, X, rows, n, dOut, err);
+  if (perWarp <= 3) tri16_go<3>(fused, mt, simple, grid, smem, s, groups, colSrc, constV, X, rows, n, dOut, err);
+  else if (perWarp <= 6) tri16_go<6>(fused, mt, simple, grid, smem, s, groups, colSrc, constV, X, rows, n, dOut, err);
+  else tri16_go<9>(fused, mt, simple, grid, smem, s, groups, colSrc, constV, X, rows, n, dOut, err);
 }
 template <int TPW>
 static int64_t tri16_set_smem_t(int bytes) {
-  CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri16<true, -2, TPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-  CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri16<true, CLA_MAP_BYTE, TPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-  CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri16<true, CLA_MAP_CHAR, TPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-  CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri16<false, -2, TPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri16<true, -2, TPW, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri16<true, CLA_MAP_BYTE, TPW, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri16<true, CLA_MAP_CHAR, TPW, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri16<true, CLA_MAP_BYTE, TPW, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri16<true, CLA_MAP_CHAR, TPW, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri16<false, -2, TPW, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
   return CLA_OK;
 }
 static int64_t tri16_set_smem(int bytes) {
@@ -499,11 +523,11 @@ int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s) {
   const bool tri = n <= 128;
   bool denseOnly = m->colSrcValid;
   for (auto& g : m->groups) denseOnly &= (g.type == GT_DDC || g.type == GT_UNC);
-  const size_t tri16Smem = (size_t)((n + 7) / 8 * 8) * (4 * TT_LD * sizeof(double) + sizeof(TsmmCol)) + 4 * sizeof(uint64_t);
+  const size_t tri16Smem = (size_t)((n + 7) / 8 * 8) * (4 * TT_LD * sizeof(double) + sizeof(TsmmCol) + 16) + 4 * sizeof(uint64_t);
   static bool attrSet[64] = {};  // per device: function attributes belong to the device's context
   bool& attr = attrSet[m->device & 63];
   if (!attr) {
-    if ((rc = tri16_set_smem(128 * (4 * TT_LD * 8 + (int)sizeof(TsmmCol)) + 32)) < 0) return rc;
+    if ((rc = tri16_set_smem(128 * (4 * TT_LD * 8 + (int)sizeof(TsmmCol) + 16) + 32)) < 0) return rc;
     attr = true;
   }
   if (tri && denseOnly) {  // one launch over all rows, decoding as it goes
@@ -516,8 +540,11 @@ int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s) {
                     : (g.mapType == CLA_MAP_CHAR ? CLA_MAP_CHAR : -2);
       mt = (mt == -1 || mt == w) ? w : -2;
     }
+    // the two-pointer records: every column in exactly one single-column group of that width, no constant part
+    bool simple = (mt == CLA_MAP_BYTE || mt == CLA_MAP_CHAR) && !m->hasConst && (int)m->groups.size() == n;
+    for (auto& g : m->groups) simple &= g.gCols == 1;
     prof_begin(m, s);
-    launch_tri16(true, mt, n, (int)std::min<int64_t>(m->smCount, nStages), tri16Smem, s, m->dGroups, m->dColSrc,
+    launch_tri16(true, mt, simple, n, (int)std::min<int64_t>(m->smCount, nStages), tri16Smem, s, m->dGroups, m->dColSrc,
                  m->hasConst ? m->dConstV : nullptr, nullptr, m->nRows, dOut, m->dErr);
     prof_end(m, s);
     m->stats.kernel_launches++;
@@ -536,8 +563,8 @@ int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s) {
       const int rows = r1 - (int)r0;
       if (tri) {
         const int64_t nStages = ((int64_t)rows + TT_KT - 1) / TT_KT;
-        launch_tri16(false, -2, n, (int)std::min<int64_t>(m->smCount, nStages), tri16Smem, s, nullptr, nullptr, nullptr, X, rows,
-                     dOut, m->dErr);
+        launch_tri16(false, -2, false, n, (int)std::min<int64_t>(m->smCount, nStages), tri16Smem, s, nullptr, nullptr, nullptr,
+                     X, rows, dOut, m->dErr);
       } else {
         int splits = std::max(1, std::min((rows + TS_KT * 8 - 1) / (TS_KT * 8), (4 * m->smCount + nPairs - 1) / nPairs));
         int rowsPerSplit = ((rows + splits - 1) / splits + GT_KT - 1) / GT_KT * GT_KT;
