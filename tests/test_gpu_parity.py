@@ -470,6 +470,41 @@ def test_concurrent_handles_and_shared_handle():
     b.free()
 
 
+@pytest.mark.parametrize("seed", range(24))
+def test_random_blocks_every_product(oracle, seed):
+    """Randomly drawn blocks (group kinds, row counts around the 256 / 1024 / 65535 boundaries of the index
+    structures, operand widths) through every product, against the oracle."""
+    rng = np.random.default_rng(9000 + seed)
+    nRows = int(rng.choice([1, 2, 31, 32, 33, 255, 256, 257, 1023, 1024, 1025, 2049, 4097, 65535, 65536, 65537, 70001,
+                            131073]))
+    pool = datagen.KINDS + ("ddcfor", "sdcfor", "ddc", "ddc", "ddc")
+    kinds = tuple(rng.choice(pool, size=int(rng.integers(1, 14))))
+    overlap = bool(rng.integers(0, 4) == 0)
+    cmb = datagen.random_cmb(9100 + seed, nRows, kinds, overlap).to_device()
+    om = oracle.OracleMatrix(cmb)
+    X = dense_of(cmb)
+    aX = np.abs(X)
+    vc = int(rng.choice([1, 2, 3, 7, 8, 13, 64, 65]))
+    V = rng.standard_normal((cmb.clen, vc))
+    got = CLALibRightMultBy.rightMultByMatrix(cmb, V)
+    assert rel_err(got, om.rmm(V), aX @ np.abs(V) + 1e-300) < TOL, (kinds, nRows, vc)
+    q = int(rng.choice([1, 2, 5]))
+    Yt = rng.standard_normal((q, nRows))
+    assert rel_err(CLALibLeftMultBy.leftMultByMatrix(cmb, Yt), om.lmm(Yt), np.abs(Yt) @ aX + 1e-300) < TOL, (kinds, nRows, q)
+    # a cell of a plain block is one dictionary value (rounded once where a default tuple is folded in); cells of
+    # overlapping or frame-of-reference blocks are sums whose terms may cancel
+    summed = overlap or any(k in ("ddcfor", "sdcfor") for k in kinds)
+    assert rel_err(CLALibDecompress.decompress(cmb), X) < (TOL if summed else 1e-14), (kinds, nRows)
+    if not overlap:
+        got = CLALibTSMM.leftMultByTransposeSelf(cmb)
+        assert rel_err(got, oracle.dense_tsmm_ld(X), aX.T @ aX + 1e-300) < TOL, (kinds, nRows)
+    v = rng.standard_normal(cmb.clen)
+    w = rng.standard_normal(nRows)
+    sw = aX.T @ (np.abs(w) * (aX @ np.abs(v))) + 1e-300
+    assert rel_err(CLALibMMChain.mmChain(cmb, v, w, CHAIN_XtwXv).ravel(), om.mmchain(v, w, 1).ravel(), sw) < 10 * TOL
+    cmb.free()
+
+
 def test_many_sparse_groups_wide_rhs(oracle):
     """More than 256 SDC / RLE groups: the tensor-core RMM falls back to its first-generation kernel (one lane per
     group covers 256 of each)."""
