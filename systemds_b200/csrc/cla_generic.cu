@@ -59,8 +59,7 @@ __global__ void k_const_times_v(const double* __restrict__ constV, int nCols, co
 //  * uncompressed groups: a warp per row, lanes along the dense row, shuffle reduction;
 //  * SDC groups: one lane per group walks that group's delta stream through the block (32 groups per warp in
 //    parallel instead of one after the other) and adds P_g[id] to the listed rows;
-//  * RLE groups: one lane per group; a run [a, b) with value k is recorded as +P[k] at a and -P[k] at b in a
-//    difference array, and one prefix sum over the block's rows turns all runs into per-row sums.
+//  * RLE groups: a warp per group; a run adds P[k] to each of its rows.
 // --------------------------------------------------------------------------------------------------
 constexpr int RV_THREADS = 256;
 __global__ void __launch_bounds__(RV_THREADS)
@@ -68,14 +67,9 @@ k_rmm_vec_general(const DevGroup* __restrict__ groups, int nGroups, int nRows, c
                   const double* __restrict__ v, const double* __restrict__ constRow, double* __restrict__ out,
                   int afterFast) {
   __shared__ double acc[SKIP_ROWS];
-  __shared__ double dif[SKIP_ROWS + 1];
-  __shared__ double wsum[RV_THREADS / 32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int r0 = blockIdx.x * SKIP_ROWS, r1 = min(nRows, r0 + SKIP_ROWS);
-  for (int i = tid; i < SKIP_ROWS; i += RV_THREADS) {
-    acc[i] = 0.0;
-    dif[i] = 0.0;
-  }
+  for (int i = tid; i < SKIP_ROWS; i += RV_THREADS) acc[i] = 0.0;
   __syncthreads();
   bool anyRle = false, anyUnc = false;
   // dense-map groups: a thread owns rows tid, tid + 256, ... of the block
@@ -148,49 +142,32 @@ k_rmm_vec_general(const DevGroup* __restrict__ groups, int nGroups, int nRows, c
           row = g.last;
         elem++;
       }
-    } else if (g.type == GT_RLE) {
+    }
+  }
+  // RLE groups: a warp per group; a run adds its value to each of its rows (the reference's own way,
+  // colgroup/ColGroupRLE.java:104-141). Turning the runs into +P / -P boundaries and a prefix sum is cheaper but
+  // leaves rounding residue of earlier, possibly much larger, values in later rows.
+  if (anyRle) {
+    for (int gi = warp; gi < nGroups; gi += RV_THREADS / 32) {
+      const DevGroup& g = groups[gi];
+      if (g.type != GT_RLE || (afterFast && g.inFast)) continue;
       const double* Pg = P + g.valOff;
       for (int64_t ri = g.runSkip[blockIdx.x]; ri < g.nRuns; ri++) {
         const RleRun run = g.runs[ri];
         if (run.start >= r1) break;
         const int a = max(run.start, r0), b = min(run.start + (int)run.len, r1);
-        if (a < b) {
-          const double p = Pg[run.k];
-          atomicAdd(&dif[a - r0], p);
-          atomicAdd(&dif[b - r0], -p);  // b - r0 may be 1024: the extra slot
-        }
+        const double p = Pg[run.k];
+        for (int i = a + lane; i < b; i += 32) atomicAdd(&acc[i - r0], p);
       }
     }
   }
   __syncthreads();
-  // prefix sum of the difference array (4 consecutive rows per thread, then the warps' totals)
-  double run4[4] = {0, 0, 0, 0};
-  if (anyRle) {
-    double t = 0;
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-      t += dif[tid * 4 + i];
-      run4[i] = t;
-    }
-    double incl = t;
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-      const double o = __shfl_up_sync(0xffffffffu, incl, d);
-      if (lane >= d) incl += o;
-    }
-    if (lane == 31) wsum[warp] = incl;
-    __syncthreads();
-    double base = incl - t;
-    for (int w = 0; w < warp; w++) base += wsum[w];
-#pragma unroll
-    for (int i = 0; i < 4; i++) run4[i] += base;
-  }
   const double c0 = (constRow != nullptr && !afterFast) ? constRow[0] : 0.0;
 #pragma unroll
   for (int i = 0; i < 4; i++) {
     const int r = r0 + tid * 4 + i;
     if (r < r1) {
-      const double val = acc[tid * 4 + i] + run4[i] + c0;
+      const double val = acc[tid * 4 + i] + c0;
       out[r] = afterFast ? out[r] + val : val;
     }
   }

@@ -198,9 +198,9 @@ struct WorkItem {
   uint16_t ra, rb;   // rows [ra, rb) of the tile
   uint32_t prow;     // row of the table arena P
 };
-struct DeltaItem {   // "from tile row `row` on, the table row changes by +/- P[prow]" (RLE run boundaries)
+struct DeltaItem {   // rows [row, end) of the tile (inside one warp's 16-row slice) hold table row P[prow] of an RLE group
   int16_t row;
-  int16_t sign;
+  int16_t end;
   uint32_t prow;
 };
 
@@ -446,17 +446,14 @@ k_rmm_dmma2(const DevGroup* __restrict__ groups, const DenseDesc* __restrict__ d
             else
               for (int w = 0; w < 8; w++) push_item(q, qn, w, w * 16, w * 16 + 16, prow, Cs, P, vCols, j0, vc);
           } else {
-            // a run that starts or ends inside the tile: every warp whose 16 rows it touches gets "+P from
-            // its first row there on" and, if it ends inside that warp's rows, "-P from the end on"
+            // a run that starts or ends inside the tile: every warp whose 16 rows it touches gets the piece of
+            // the run that lies in its slice
             for (int w = (a - r0) >> 4; w <= (b - 1 - r0) >> 4; w++) {
               const int aw = max(a - r0, w * 16), bw = min(b - r0, w * 16 + 16);
-              const int need = bw < w * 16 + 16 ? 2 : 1;
-              const int slot = atomicAdd(&qn[9 + w], need);
-              if (slot + need <= QD_CAP) {
-                qd[w * QD_CAP + slot] = DeltaItem{(int16_t)aw, 1, prow};
-                if (need == 2) qd[w * QD_CAP + slot + 1] = DeltaItem{(int16_t)bw, -1, prow};
-              } else {
-                atomicAdd(&qn[9 + w], -need);
+              const int slot = atomicAdd(&qn[9 + w], 1);
+              if (slot < QD_CAP) qd[w * QD_CAP + slot] = DeltaItem{(int16_t)aw, (int16_t)bw, prow};
+              else {
+                atomicAdd(&qn[9 + w], -1);
                 push_item(q, qn, w, aw, bw, prow, Cs, P, vCols, j0, vc);
               }
             }
@@ -516,33 +513,39 @@ k_rmm_dmma2(const DevGroup* __restrict__ groups, const DenseDesc* __restrict__ d
             }
         }
       }
-      // run boundaries: eight at a time, their table rows are fetched first; then one walk down the 16 rows carries
-      // the sum of the runs open at the current row (boundaries of later batches add their own walk: it is linear)
+      // run pieces: eight at a time, their table rows are fetched first; then every row of the slice adds the
+      // table rows of the pieces that cover it. (Walking the slice with a running sum, +P at a start and -P at an
+      // end, is cheaper but leaves rounding residue of earlier, possibly much larger, values in later rows; the
+      // reference adds a row's own values and nothing else.)
       const int nd = min(qn[9 + warp], QD_CAP);
       const DeltaItem* myd = qd + warp * QD_CAP;
       for (int i0 = 0; i0 < nd; i0 += 8) {
         double2 t[8];
-        int drow[8];
+        int da[8], db[8];
 #pragma unroll
         for (int i = 0; i < 8; i++) {
           const DeltaItem d = myd[min(i0 + i, nd - 1)];
-          drow[i] = i0 + i < nd ? d.row : -1;
-          const double2 pv = i0 + i < nd ? ldp(d.prow) : make_double2(0.0, 0.0);
-          t[i] = make_double2(d.sign * pv.x, d.sign * pv.y);
+          da[i] = i0 + i < nd ? d.row : 0;
+          db[i] = i0 + i < nd ? d.end : 0;
+          t[i] = i0 + i < nd ? ldp(d.prow) : make_double2(0.0, 0.0);
         }
-        double2 cur = make_double2(0.0, 0.0);
         for (int r = warp * 16; r < warp * 16 + 16; r++) {
+          double2 add = make_double2(0.0, 0.0);
+          bool any = false;
 #pragma unroll
           for (int i = 0; i < 8; i++)
-            if (drow[i] == r) {
-              cur.x += t[i].x;
-              cur.y += t[i].y;
+            if (da[i] <= r && r < db[i]) {
+              add.x += t[i].x;
+              add.y += t[i].y;
+              any = true;
             }
-          double2* cp = (double2*)&Cs[r * GM_LDC + n0];
-          double2 cv = *cp;
-          cv.x += cur.x;
-          cv.y += cur.y;
-          *cp = cv;
+          if (any) {
+            double2* cp = (double2*)&Cs[r * GM_LDC + n0];
+            double2 cv = *cp;
+            cv.x += add.x;
+            cv.y += add.y;
+            *cp = cv;
+          }
         }
       }
       for (int r = warp * 16; r < warp * 16 + 16; r++) {

@@ -505,6 +505,31 @@ def test_random_blocks_every_product(oracle, seed):
     cmb.free()
 
 
+def test_rows_without_open_runs_are_exact_zeros(oracle):
+    """X v on RLE groups whose runs leave rows uncovered: those rows are exactly zero (the kernel turns runs into
+    +P / -P boundaries and prefix sums, whose rounding residue must not leak into rows where no run is open),
+    and the returned non-zero count matches."""
+    rng = np.random.default_rng(12)
+    groups = []
+    for c in range(7):
+        ids = np.full(3 * 1024 + 1, -1)
+        pos = int(rng.integers(0, 40))
+        while pos < ids.shape[0]:
+            ln = int(rng.integers(1, 300))
+            ids[pos:pos + ln] = int(rng.integers(0, 5))
+            pos += ln + int(rng.integers(1, 200))
+        groups.append(cg.ColGroupRLE.from_row_ids([c], rng.standard_normal((5, 1)) * 10.0 ** rng.integers(-3, 4), ids))
+    cmb = CompressedMatrixBlock(3 * 1024 + 1, 7, groups).to_device()
+    X = dense_of(cmb)
+    v = rng.standard_normal(7)
+    got = CLALibRightMultBy.rightMultByMatrix(cmb, v)
+    zero_rows = np.flatnonzero(np.abs(X).sum(axis=1) == 0)
+    assert zero_rows.size > 0 and np.all(np.asarray(got)[zero_rows] == 0.0)
+    assert rel_err(got, oracle.OracleMatrix(cmb).rmm(v), np.abs(X) @ np.abs(v).reshape(-1, 1) + 1e-300) < TOL
+    assert got.nnz == int(np.count_nonzero(X @ v))
+    cmb.free()
+
+
 def test_many_sparse_groups_wide_rhs(oracle):
     """More than 256 SDC / RLE groups: the tensor-core RMM falls back to its first-generation kernel (one lane per
     group covers 256 of each)."""
