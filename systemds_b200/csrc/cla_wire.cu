@@ -134,7 +134,9 @@ void read_matrix_block(In& s, std::vector<double>& out, int32_t& rlen, int32_t& 
   }
   if (fmt == 4) throw Unsupported("de-duplicated dense blocks are not supported");
   if (fmt > 4) throw Unsupported("unknown block format " + std::to_string(fmt));
-  if (cells > (int64_t)s.n * 64) throw Truncated("block dimensions exceed what the stream can hold");
+  // a corrupted length must not allocate without bound: an empty block may be large (it needs no bytes), the
+  // sparse formats must be accounted for by what is left of the stream
+  if (cells > (fmt == 0 ? (int64_t)1 << 28 : (int64_t)s.n * 64)) throw Truncated("block dimensions exceed what the stream can hold");
   out.assign((size_t)cells, 0.0);
   if (fmt == 0) return;  // EMPTY_BLOCK
   if (fmt == 2) {        // SPARSE_BLOCK

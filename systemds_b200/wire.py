@@ -123,6 +123,11 @@ def read_matrix_block(s: _In) -> np.ndarray:
     """A ``MatrixBlock`` as a dense ``[rlen x clen]`` array (MatrixBlock.java:2111-2165)."""
     rlen, clen = s.int(), s.int()
     fmt = _ordinal(s.byte(), 5, "block format")
+    # an empty block needs no bytes at all, every other format at least an eighth of a byte per cell would be odd:
+    # refuse dimensions the rest of the stream cannot account for (a corrupted length must not allocate without bound)
+    limit = (1 << 28) if fmt == BT_EMPTY else 64 * (len(s.b) - s.p) + 1024
+    if rlen < 0 or clen < 0 or rlen * clen > limit:
+        raise WireFormatError("block of %d x %d cells cannot come from the %d bytes left" % (rlen, clen, len(s.b) - s.p))
     out = np.zeros((rlen, clen), np.float64)
     if fmt == BT_EMPTY:
         return out
