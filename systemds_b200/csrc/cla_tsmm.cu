@@ -155,10 +155,11 @@ constexpr int T16_WARPS = 16;
 constexpr int T16_THREADS = T16_WARPS * 32;
 constexpr int T16_MAXC = 8;   // columns decoded per warp and stage at 128 columns
 
-// SIMPLE (with MT = byte or char): every column is held by a single-column dense-map group of that width and
-// there is no constant part, so a column needs two pointers (map, dictionary) instead of the full record: the
-// record reads were 40 % of the kernel's shared-memory load instructions.
-template <bool FUSED, int MT, int TPW, bool SIMPLE>
+// SIMPLE (with MT = byte or char): every column is held by a dense-map group of that width, so a column needs two
+// pointers (map, dictionary) instead of the full record, whose reads were 40 % of the kernel's shared-memory load
+// instructions. SIMPLE = 1: single-column groups and no constant part; SIMPLE = 2: also the group width (co-coded
+// columns) and the constant part of the column.
+template <bool FUSED, int MT, int TPW, int SIMPLE>
 __global__ void __launch_bounds__(T16_THREADS, 1)
 k_tsmm_tri16(const DevGroup* __restrict__ groups, const int32_t* __restrict__ colSrc, const double* __restrict__ constV,
              const double* __restrict__ X, int rowBegin, int rowEnd, int nCols, double* __restrict__ C, int32_t* err) {
@@ -205,10 +206,14 @@ k_tsmm_tri16(const DevGroup* __restrict__ groups, const int32_t* __restrict__ co
   // SIMPLE: the two pointers per column, packed behind the mbarriers
   const void** mapArr = (const void**)(bars + 4);
   const double** srcArr = (const double**)(mapArr + nColsPad);
+  double* cstArr = (double*)(srcArr + nColsPad);
+  int* gcArr = (int*)(cstArr + nColsPad);
   if (SIMPLE) {
     for (int cc = tid; cc < nColsPad; cc += T16_THREADS) {
       mapArr[cc] = cols[cc].map;
       srcArr[cc] = cols[cc].src;
+      cstArr[cc] = cols[cc].cst;
+      gcArr[cc] = cols[cc].gCols;
     }
     __syncthreads();
   }
@@ -285,7 +290,7 @@ k_tsmm_tri16(const DevGroup* __restrict__ groups, const int32_t* __restrict__ co
       const int cc = warp + T16_WARPS * b;
       vals[b] = 0.0;
       if (SIMPLE) {
-        if (cc < nCols && inRange) vals[b] = ld_f64_here(srcArr[cc] + ids[b]);
+        if (cc < nCols && inRange) vals[b] = ld_f64_here(srcArr[cc] + (SIMPLE == 2 ? (size_t)ids[b] * gcArr[cc] : (size_t)ids[b]));
       } else if (cc < nColsPad && inRange) {
         // volatile asm keeps the load where it is written, ahead of the (volatile) DMMAs: left to itself the
         // compiler sinks it to its use behind them and the pipeline is gone
@@ -302,7 +307,8 @@ k_tsmm_tri16(const DevGroup* __restrict__ groups, const int32_t* __restrict__ co
 #pragma unroll
     for (int b = 0; b < T16_MAXC; b++) {
       const int cc = warp + T16_WARPS * b;
-      if (cc < nColsPad) Xt[cc * TT_LD + lane] = vals[b] + ((FUSED && !SIMPLE && inRange) ? cols[cc].cst : 0.0);
+      if (cc < nColsPad)
+        Xt[cc * TT_LD + lane] = vals[b] + ((FUSED && inRange && SIMPLE != 1) ? (SIMPLE == 2 ? cstArr[cc] : cols[cc].cst) : 0.0);
     }
   };
   // Four stage buffers, each with an mbarrier that counts the 512 threads' "my part of this stage is stored". A warp
@@ -477,20 +483,20 @@ int64_t measure_fp64_peaks(int device, double* dmmaTflops, double* dfmaTflops) {
 // The 16-warp kernel is instantiated for 3, 6 and 9 tile slots per warp (up to 48, 104 and 128 columns) and for
 // the map widths the decode specialises on.
 template <int TPW>
-static void tri16_go(bool fused, int mt, bool simple, int grid, size_t smem, cudaStream_t s, const DevGroup* groups,
+static void tri16_go(bool fused, int mt, int simple, int grid, size_t smem, cudaStream_t s, const DevGroup* groups,
                      const int32_t* colSrc, const double* constV, const double* X, int rows, int n, double* dOut, int32_t* err) {
-  if (!fused) k_tsmm_tri16<false, -2, TPW, false><<<grid, T16_THREADS, smem, s>>>(groups, colSrc, constV, X, 0, rows, n, dOut, err);
-  else if (mt == CLA_MAP_BYTE && simple)
-    k_tsmm_tri16<true, CLA_MAP_BYTE, TPW, true><<<grid, T16_THREADS, smem, s>>>(groups, colSrc, constV, X, 0, rows, n, dOut, err);
-  else if (mt == CLA_MAP_CHAR && simple)
-    k_tsmm_tri16<true, CLA_MAP_CHAR, TPW, true><<<grid, T16_THREADS, smem, s>>>(groups, colSrc, constV, X, 0, rows, n, dOut, err);
-  else if (mt == CLA_MAP_BYTE)
-    k_tsmm_tri16<true, CLA_MAP_BYTE, TPW, false><<<grid, T16_THREADS, smem, s>>>(groups, colSrc, constV, X, 0, rows, n, dOut, err);
-  else if (mt == CLA_MAP_CHAR)
-    k_tsmm_tri16<true, CLA_MAP_CHAR, TPW, false><<<grid, T16_THREADS, smem, s>>>(groups, colSrc, constV, X, 0, rows, n, dOut, err);
-  else k_tsmm_tri16<true, -2, TPW, false><<<grid, T16_THREADS, smem, s>>>(groups, colSrc, constV, X, 0, rows, n, dOut, err);
+#define TRI16(F, M, S) k_tsmm_tri16<F, M, TPW, S><<<grid, T16_THREADS, smem, s>>>(groups, colSrc, constV, X, 0, rows, n, dOut, err)
+  if (!fused) TRI16(false, -2, 0);
+  else if (mt == CLA_MAP_BYTE && simple == 1) TRI16(true, CLA_MAP_BYTE, 1);
+  else if (mt == CLA_MAP_BYTE && simple == 2) TRI16(true, CLA_MAP_BYTE, 2);
+  else if (mt == CLA_MAP_CHAR && simple == 1) TRI16(true, CLA_MAP_CHAR, 1);
+  else if (mt == CLA_MAP_CHAR && simple == 2) TRI16(true, CLA_MAP_CHAR, 2);
+  else if (mt == CLA_MAP_BYTE) TRI16(true, CLA_MAP_BYTE, 0);
+  else if (mt == CLA_MAP_CHAR) TRI16(true, CLA_MAP_CHAR, 0);
+  else TRI16(true, -2, 0);
+#undef TRI16
 }
-static void launch_tri16(bool fused, int mt, bool simple, int n, int grid, size_t smem, cudaStream_t s, const DevGroup* groups,
+static void launch_tri16(bool fused, int mt, int simple, int n, int grid, size_t smem, cudaStream_t s, const DevGroup* groups,
                          const int32_t* colSrc, const double* constV, const double* X, int rows, double* dOut, int32_t* err) {
   const int NT = (n + 7) / 8, perWarp = (NT * (NT + 1) / 2 + T16_WARPS - 1) / T16_WARPS;
   if (perWarp <= 3) tri16_go<3>(fused, mt, simple, grid, smem, s, groups, colSrc, constV, X, rows, n, dOut, err);
@@ -499,12 +505,17 @@ static void launch_tri16(bool fused, int mt, bool simple, int n, int grid, size_
 }
 template <int TPW>
 static int64_t tri16_set_smem_t(int bytes) {
-  CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri16<true, -2, TPW, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-  CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri16<true, CLA_MAP_BYTE, TPW, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-  CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri16<true, CLA_MAP_CHAR, TPW, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-  CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri16<true, CLA_MAP_BYTE, TPW, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-  CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri16<true, CLA_MAP_CHAR, TPW, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-  CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri16<false, -2, TPW, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+#define TRI16_ATTR(F, M, S) \
+  CLA_CUDA(cudaFuncSetAttribute(k_tsmm_tri16<F, M, TPW, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes))
+  TRI16_ATTR(true, -2, 0);
+  TRI16_ATTR(true, CLA_MAP_BYTE, 0);
+  TRI16_ATTR(true, CLA_MAP_CHAR, 0);
+  TRI16_ATTR(true, CLA_MAP_BYTE, 1);
+  TRI16_ATTR(true, CLA_MAP_CHAR, 1);
+  TRI16_ATTR(true, CLA_MAP_BYTE, 2);
+  TRI16_ATTR(true, CLA_MAP_CHAR, 2);
+  TRI16_ATTR(false, -2, 0);
+#undef TRI16_ATTR
   return CLA_OK;
 }
 static int64_t tri16_set_smem(int bytes) {
@@ -523,11 +534,11 @@ int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s) {
   const bool tri = n <= 128;
   bool denseOnly = m->colSrcValid;
   for (auto& g : m->groups) denseOnly &= (g.type == GT_DDC || g.type == GT_UNC);
-  const size_t tri16Smem = (size_t)((n + 7) / 8 * 8) * (4 * TT_LD * sizeof(double) + sizeof(TsmmCol) + 16) + 4 * sizeof(uint64_t);
+  const size_t tri16Smem = (size_t)((n + 7) / 8 * 8) * (4 * TT_LD * sizeof(double) + sizeof(TsmmCol) + 28) + 4 * sizeof(uint64_t);
   static bool attrSet[64] = {};  // per device: function attributes belong to the device's context
   bool& attr = attrSet[m->device & 63];
   if (!attr) {
-    if ((rc = tri16_set_smem(128 * (4 * TT_LD * 8 + (int)sizeof(TsmmCol) + 16) + 32)) < 0) return rc;
+    if ((rc = tri16_set_smem(128 * (4 * TT_LD * 8 + (int)sizeof(TsmmCol) + 28) + 32)) < 0) return rc;
     attr = true;
   }
   if (tri && denseOnly) {  // one launch over all rows, decoding as it goes
@@ -540,9 +551,18 @@ int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s) {
                     : (g.mapType == CLA_MAP_CHAR ? CLA_MAP_CHAR : -2);
       mt = (mt == -1 || mt == w) ? w : -2;
     }
-    // the two-pointer records: every column in exactly one single-column group of that width, no constant part
-    bool simple = (mt == CLA_MAP_BYTE || mt == CLA_MAP_CHAR) && !m->hasConst && (int)m->groups.size() == n;
-    for (auto& g : m->groups) simple &= g.gCols == 1;
+    // the compact records: every column in exactly one dense-map group of that width (1: single-column groups
+    // and no constant part; 2: any group width, constants allowed)
+    int simple = 0;
+    if (mt == CLA_MAP_BYTE || mt == CLA_MAP_CHAR) {
+      int covered = 0;
+      bool single = true;
+      for (auto& g : m->groups) {
+        covered += g.gCols;
+        single &= g.gCols == 1;
+      }
+      if (covered == n) simple = (single && !m->hasConst) ? 1 : 2;  // colSrcValid: no column is counted twice
+    }
     prof_begin(m, s);
     launch_tri16(true, mt, simple, n, (int)std::min<int64_t>(m->smCount, nStages), tri16Smem, s, m->dGroups, m->dColSrc,
                  m->hasConst ? m->dConstV : nullptr, nullptr, m->nRows, dOut, m->dErr);
@@ -563,7 +583,7 @@ int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s) {
       const int rows = r1 - (int)r0;
       if (tri) {
         const int64_t nStages = ((int64_t)rows + TT_KT - 1) / TT_KT;
-        launch_tri16(false, -2, false, n, (int)std::min<int64_t>(m->smCount, nStages), tri16Smem, s, nullptr, nullptr, nullptr,
+        launch_tri16(false, -2, 0, n, (int)std::min<int64_t>(m->smCount, nStages), tri16Smem, s, nullptr, nullptr, nullptr,
                      X, rows, dOut, m->dErr);
       } else {
         int splits = std::max(1, std::min((rows + TS_KT * 8 - 1) / (TS_KT * 8), (4 * m->smCount + nPairs - 1) / nPairs));

@@ -150,6 +150,19 @@ def test_tsmm_integer_exact(oracle):
     cmb.free()
 
 
+@pytest.mark.parametrize("kinds", [("ddc",) * 9, ("ddc", "ddc2", "ddcfor", "ddc2", "ddc"), ("ddc_char", "ddc_char", "ddc_char")])
+def test_tsmm_compact_records(oracle, kinds):
+    """t(X) X on blocks of dense-map groups of one map width: the kernel's compact column records (single-column
+    groups; co-coded groups and constant parts; 16-bit maps)."""
+    for nRows in (33, 70001):
+        cmb = datagen.random_cmb(321 + nRows, nRows, kinds).to_device()
+        X = dense_of(cmb)
+        got = CLALibTSMM.leftMultByTransposeSelf(cmb)
+        assert rel_err(got, oracle.dense_tsmm_ld(X), np.abs(X).T @ np.abs(X) + 1e-300) < TOL
+        assert np.array_equal(got, got.T)
+        cmb.free()
+
+
 def test_tsmm_wide(oracle):
     """More than one 64-column block, ragged edge."""
     cmb = _ddc_matrix(9000, [7] * 150, 5).to_device()
