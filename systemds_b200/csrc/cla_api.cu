@@ -445,48 +445,64 @@ static int64_t mmchain_dev(Matrix* m, const double* dV, const double* dW, int32_
   return lmm_dev(m, dU, 1, dOut, s);
 }
 
+// Device-buffer calls return once their work is enqueued. All calls on a handle share its scratch buffers, so
+// a call on another stream than the handle's previous call is made to wait for that call on the device.
+template <class F>
+static int64_t ordered(Matrix* m, cudaStream_t s, F&& run) {
+  int64_t rc = order_begin(m, s);
+  if (rc < 0) return rc;
+  rc = run();
+  const int64_t rc2 = order_end(m, s);  // also after a failed launch sequence: part of it may be enqueued
+  return rc < 0 ? rc : (rc2 < 0 ? rc2 : rc);
+}
+
 extern "C" {
 
 int64_t cla_rmm_dev(cla_handle h, const double* dV, int32_t vRows, int32_t vCols, double* dOut, void* stream) {
   GET_MATRIX(h);
   REQUIRE_FINAL();
   CLA_CUDA(cudaSetDevice(m->device));
-  return rmm_dev(m, dV, vRows, vCols, dOut, (cudaStream_t)stream);
+  cudaStream_t s = (cudaStream_t)stream;
+  return ordered(m, s, [&] { return rmm_dev(m, dV, vRows, vCols, dOut, s); });
 }
 int64_t cla_lmm_dev(cla_handle h, const double* dYt, int32_t yRows, double* dOut, void* stream) {
   GET_MATRIX(h);
   REQUIRE_FINAL();
   CLA_CUDA(cudaSetDevice(m->device));
-  return lmm_dev(m, dYt, yRows, dOut, (cudaStream_t)stream);
+  cudaStream_t s = (cudaStream_t)stream;
+  return ordered(m, s, [&] { return lmm_dev(m, dYt, yRows, dOut, s); });
 }
 int64_t cla_lmm_vec_noalloc_dev(cla_handle h, const double* dY, double* dOut, void* stream) {
   GET_MATRIX(h);
   REQUIRE_FINAL();
   CLA_CUDA(cudaSetDevice(m->device));
   if (!dY || !dOut) return fail(CLA_ERR_BAD_ARG, "no-allocation product: null buffer");
-  m->stats.calls_lmm++;
-  return fast_lmm_vec_noalloc(m, dY, dOut, (cudaStream_t)stream);
+  cudaStream_t s = (cudaStream_t)stream;
+  return ordered(m, s, [&] { return fast_lmm_vec_noalloc(m, dY, dOut, s); });
 }
 int64_t cla_tsmm_dev(cla_handle h, double* dOut, void* stream) {
   GET_MATRIX(h);
   REQUIRE_FINAL();
   CLA_CUDA(cudaSetDevice(m->device));
   m->stats.calls_tsmm++;
-  return launch_tsmm(m, dOut, (cudaStream_t)stream);
+  cudaStream_t s = (cudaStream_t)stream;
+  return ordered(m, s, [&] { return launch_tsmm(m, dOut, s); });
 }
 int64_t cla_decompress_dev(cla_handle h, double* dOut, void* stream) {
   GET_MATRIX(h);
   REQUIRE_FINAL();
   CLA_CUDA(cudaSetDevice(m->device));
   m->stats.calls_decompress++;
-  return launch_decompress(m, dOut, (cudaStream_t)stream);
+  cudaStream_t s = (cudaStream_t)stream;
+  return ordered(m, s, [&] { return launch_decompress(m, dOut, s); });
 }
 int64_t cla_mmchain_dev(cla_handle h, const double* dV, const double* dW, int32_t ctype, double* dOut, double* dU,
                         void* stream) {
   GET_MATRIX(h);
   REQUIRE_FINAL();
   CLA_CUDA(cudaSetDevice(m->device));
-  return mmchain_dev(m, dV, dW, ctype, dOut, dU, (cudaStream_t)stream);
+  cudaStream_t s = (cudaStream_t)stream;
+  return ordered(m, s, [&] { return mmchain_dev(m, dV, dW, ctype, dOut, dU, s); });
 }
 
 }  // extern "C"
@@ -507,6 +523,7 @@ static int64_t host_call(Matrix* m, const double* in1, size_t n1, const double* 
   double* dOut = (double*)(base + oOut);
   unsigned long long* dCnt = (unsigned long long*)(base + oCnt);
   cudaStream_t s = m->stream;
+  if ((rc = order_begin(m, s)) < 0) return rc;
   if (n1 && !deferIn1) CLA_CUDA(cudaMemcpyAsync(d1, in1, n1 * 8, cudaMemcpyHostToDevice, s));  // deferred: run() uploads it
   if (n2) CLA_CUDA(cudaMemcpyAsync(d2, in2, n2 * 8, cudaMemcpyHostToDevice, s));
   CLA_CUDA(cudaEventRecord(m->ev0, s));
@@ -517,6 +534,7 @@ static int64_t host_call(Matrix* m, const double* in1, size_t n1, const double* 
   unsigned long long nnz = 0;
   CLA_CUDA(cudaMemcpyAsync(&nnz, dCnt, sizeof(nnz), cudaMemcpyDeviceToHost, s));
   CLA_CUDA(cudaStreamSynchronize(s));
+  m->lastValid = false;  // nothing of this handle is in flight any more
   float ms = 0;
   if (cudaEventElapsedTime(&ms, m->ev0, m->ev1) == cudaSuccess) m->stats.last_kernel_ms = ms;
   if ((rc = check_errword(m)) < 0) return rc;
@@ -560,8 +578,14 @@ int64_t cla_tmm(cla_handle left, cla_handle right, double* out) {
   if (rc < 0) return rc;
   Matrix *l = p.l.get(), *r = p.r.get();
   if (!out && (size_t)l->nCols * r->nCols) return fail(CLA_ERR_BAD_ARG, "tmm: null buffer");
-  return host_call(l, nullptr, 0, nullptr, 0, out, (size_t)l->nCols * r->nCols,
-                   [&](double*, double*, double* dOut, cudaStream_t s) { return tmm_dev(l, r, dOut, s); });
+  if (r != l && l->stream) {
+    CLA_CUDA(cudaSetDevice(l->device));
+    if ((rc = order_begin(r, l->stream)) < 0) return rc;
+  }
+  rc = host_call(l, nullptr, 0, nullptr, 0, out, (size_t)l->nCols * r->nCols,
+                 [&](double*, double*, double* dOut, cudaStream_t s) { return tmm_dev(l, r, dOut, s); });
+  if (r != l && rc >= 0) r->lastValid = false;  // host_call synchronised the stream both blocks' kernels ran on
+  return rc;
 }
 
 int64_t cla_tmm_dev(cla_handle left, cla_handle right, double* dOut, void* stream) {
@@ -569,7 +593,13 @@ int64_t cla_tmm_dev(cla_handle left, cla_handle right, double* dOut, void* strea
   int64_t rc = lock_pair(left, right, p);
   if (rc < 0) return rc;
   CLA_CUDA(cudaSetDevice(p.l->device));
-  return tmm_dev(p.l.get(), p.r.get(), dOut, (cudaStream_t)stream);
+  cudaStream_t s = (cudaStream_t)stream;
+  Matrix *l = p.l.get(), *r = p.r.get();
+  if ((rc = order_begin(l, s)) < 0) return rc;
+  if (r != l && (rc = order_begin(r, s)) < 0) return rc;
+  rc = tmm_dev(l, r, dOut, s);
+  const int64_t e1 = order_end(l, s), e2 = r != l ? order_end(r, s) : CLA_OK;
+  return rc < 0 ? rc : (e1 < 0 ? e1 : (e2 < 0 ? e2 : rc));
 }
 
 int64_t cla_rmm(cla_handle h, const double* V, int32_t vRows, int32_t vCols, double* out) {

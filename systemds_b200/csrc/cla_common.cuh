@@ -44,6 +44,7 @@ struct DevGroup {
   int64_t valOff;  // first row of this group's table in the per-call value arenas (sum of nVals before it)
   const int32_t* cols;
   const double* dict;  // effective dictionary (default tuple subtracted), [nVals x gCols]
+  const double* dictRaw;  // the dictionary as registered (== dict unless a default tuple was folded into constV)
   const void* map;
   const void* mapHi;
   const void* offData;
@@ -157,6 +158,9 @@ struct Matrix {
   void* dRleIdx = nullptr;
   int nSdcGroups = 0, nRleGroups = 0;
   bool denseColsBuilt = false;
+  int32_t* dSparseIdx = nullptr;  // device group indices of the SDC groups with listed rows and RLE groups with runs, list order
+  int nSparse = 0;
+  bool sparseListBuilt = false;
   bool denseQuad = false;        // some stage of the tensor-core RMM takes the quad-column decode
   int32_t* dColSrc = nullptr;    // [nCols][2]: dense-map / uncompressed group holding the column and the position in it (-1: none)
   bool colSrcValid = false;      // false when some column is held by more than one such group (overlapping input)
@@ -177,6 +181,12 @@ struct Matrix {
   cudaStream_t copyStream = nullptr;  // uploads overlapped with kernels in the host-buffer left product
   cudaEvent_t copyDone[4] = {nullptr, nullptr, nullptr, nullptr};
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  // Every product call uses the handle's one set of scratch buffers. A call that arrives on another stream than
+  // the previous one first waits for `lastDone` (recorded when the previous call had enqueued its work), so two
+  // calls on one handle never overlap on the GPU even when their streams would allow it.
+  cudaEvent_t lastDone = nullptr;
+  cudaStream_t lastStream = nullptr;
+  bool lastValid = false;
   FastPlan* fast = nullptr;
   bool profile = false;
   std::vector<std::pair<cudaEvent_t, cudaEvent_t>> profEvents;  // ring of event pairs
@@ -200,6 +210,8 @@ void prof_begin(Matrix* m, cudaStream_t s);
 void prof_end(Matrix* m, cudaStream_t s);
 void prof_collect(Matrix* m);
 
+int64_t order_begin(Matrix* m, cudaStream_t s);  // see Matrix::lastDone
+int64_t order_end(Matrix* m, cudaStream_t s);
 int64_t ensure_scratch(Matrix* m, size_t bytes);
 int64_t ensure_scratch2(Matrix* m, size_t bytes);
 int64_t ensure_io(Matrix* m, size_t bytes);

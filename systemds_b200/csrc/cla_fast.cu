@@ -296,7 +296,10 @@ __device__ __forceinline__ void lmm_vec_body(const LmmChunk& ch, const uint8_t* 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int slot = lane & 15, half = lane >> 4;
   if (!tma_load_to_smem(smraw, tablesImg + ch.tblOff, (uint32_t)ch.tblDoubles * 8u, mbar)) {
+    // the tables never arrived: flag it, and make the failure visible in the result as well (the final kernel sums
+    // this row whatever happens, and a device-buffer caller only sees the error word at its next cla_stats_get)
     if (tid == 0) atomicExch(err, 101);
+    for (int u = tid; u < NP * 32; u += LMM_T) partial[(size_t)blockIdx.x * (LMM_MAX_PAIRS * 32) + u] = __longlong_as_double(0x7ff8000000000000ll);
     return;
   }
   // table base of each slab for this lane (slot offset folded in), and this lane's map pointers
@@ -1250,6 +1253,7 @@ int64_t fast_lmm_vec_noalloc(Matrix* m, const double* dY, double* dOut, cudaStre
   double* scratch = nullptr;
   int64_t rc = noalloc_address(m->device, &scratch);
   if (rc < 0) return rc;
+  m->stats.calls_lmm++;
   double* partial = scratch;                           // fully rewritten by every launch
   double* rowSum = scratch + NOALLOC_PARTIAL_DOUBLES;  // accumulated with atomics: cleared below before use
   CLA_CUDA(cudaMemsetAsync(dOut, 0, sizeof(double) * (size_t)m->nCols, s));

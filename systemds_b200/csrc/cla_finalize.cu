@@ -40,6 +40,16 @@ static int64_t grow(void** p, size_t* cur, size_t bytes) {
   *cur = want;
   return CLA_OK;
 }
+int64_t order_begin(Matrix* m, cudaStream_t s) {
+  if (m->lastValid && m->lastStream != s) CLA_CUDA(cudaStreamWaitEvent(s, m->lastDone, 0));
+  return CLA_OK;
+}
+int64_t order_end(Matrix* m, cudaStream_t s) {
+  CLA_CUDA(cudaEventRecord(m->lastDone, s));
+  m->lastStream = s;
+  m->lastValid = true;
+  return CLA_OK;
+}
 int64_t ensure_scratch(Matrix* m, size_t bytes) { return grow(&m->scratch, &m->scratchBytes, bytes); }
 int64_t ensure_scratch2(Matrix* m, size_t bytes) { return grow(&m->scratch2, &m->scratch2Bytes, bytes); }
 int64_t ensure_io(Matrix* m, size_t bytes) { return grow(&m->io, &m->ioBytes, bytes); }
@@ -392,6 +402,7 @@ int64_t finalize_device(Matrix* m) {
   CLA_CUDA(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
   CLA_CUDA(cudaEventCreate(&m->ev0));
   CLA_CUDA(cudaEventCreate(&m->ev1));
+  CLA_CUDA(cudaEventCreateWithFlags(&m->lastDone, cudaEventDisableTiming));
   void* errp = nullptr;
   CLA_CUDA(cudaMalloc(&errp, 64));
   CLA_CUDA(cudaMemset(errp, 0, 64));
@@ -441,8 +452,13 @@ int64_t finalize_device(Matrix* m) {
       dict.resize((size_t)(hg.nVals + 1) * gc, 0.0);
       g.nVals = hg.nVals + 1;
     }
-    if (hg.type != GT_UNC)
+    if (hg.type != GT_UNC) {
       if ((rc = upload(m, dict.data(), dict.size(), &g.dict, true)) < 0) return rc;
+      g.dictRaw = g.dict;
+      // decompress of a non-overlapping block writes the registered values themselves, not (d - default) + default
+      if (hg.type == GT_SDC && !hg.def.empty())
+        if ((rc = upload(m, hg.dict.data(), hg.dict.size(), &g.dictRaw, true)) < 0) return rc;
+    }
 
     if (hg.type == GT_DDC || hg.type == GT_SDC) {
       size_t hiB;
@@ -622,6 +638,9 @@ void release(Matrix* m) {
   m->profEvents.clear();
   if (m->ev0) cudaEventDestroy(m->ev0);
   if (m->ev1) cudaEventDestroy(m->ev1);
+  if (m->lastDone) cudaEventDestroy(m->lastDone);
+  m->lastDone = nullptr;
+  m->lastValid = false;
   for (auto& e : m->copyDone)
     if (e) {
       cudaEventDestroy(e);

@@ -54,24 +54,33 @@ __global__ void k_const_times_v(const double* __restrict__ constV, int nCols, co
 
 // --------------------------------------------------------------------------------------------------
 // X %*% v (one column) for every group type. A CTA owns one 1024-row block (the granularity of the skip
-// indexes) and keeps its 1024 partial sums in shared memory.
-//  * dense-map groups: a thread per row adds P_g[id];
-//  * uncompressed groups: a warp per row, lanes along the dense row, shuffle reduction;
-//  * SDC groups: one lane per group walks that group's delta stream through the block (32 groups per warp in
-//    parallel instead of one after the other) and adds P_g[id] to the listed rows;
-//  * RLE groups: a warp per group; a run adds P[k] to each of its rows.
+// indexes) and keeps its 1024 partial sums in shared memory. Every row's sum is formed in a fixed order, so a
+// repeated call returns the same bits whatever else runs on the GPU:
+//  1. dense-map groups in list order: a thread per row adds P_g[id];
+//  2. uncompressed groups in list order: a warp per row, lanes along the dense row, shuffle reduction;
+//  3. SDC and RLE groups in list order, eight at a time: warp w writes the values group 8 i + w contributes to the
+//     block's rows into its own row of a staging tile (SDC: warp-scan decode of the delta stream from the block's
+//     skip entry; RLE: the runs that reach into the block), then the thread that owns a row adds the eight staged
+//     values in group order. No atomics: each staging row has one writer, each sum one owner.
+//  4. the constant part.
+// (The reference sums a row's groups in list order and the constants last, lib/CLALibDecompress.java:427-434;
+// here the order is by kind, then list order.)
 // --------------------------------------------------------------------------------------------------
 constexpr int RV_THREADS = 256;
+constexpr int RV_WARPS = RV_THREADS / 32;
+constexpr size_t RV_SMEM = (size_t)(RV_WARPS + 1) * SKIP_ROWS * sizeof(double);
 __global__ void __launch_bounds__(RV_THREADS)
-k_rmm_vec_general(const DevGroup* __restrict__ groups, int nGroups, int nRows, const double* __restrict__ P,
-                  const double* __restrict__ v, const double* __restrict__ constRow, double* __restrict__ out,
-                  int afterFast) {
-  __shared__ double acc[SKIP_ROWS];
+k_rmm_vec_general(const DevGroup* __restrict__ groups, int nGroups, const int32_t* __restrict__ sparseIdx, int nSparse,
+                  int nRows, const double* __restrict__ P, const double* __restrict__ v,
+                  const double* __restrict__ constRow, double* __restrict__ out, int afterFast) {
+  extern __shared__ __align__(16) double rvsm[];
+  double* acc = rvsm;                  // [SKIP_ROWS]
+  double* stage = rvsm + SKIP_ROWS;    // [RV_WARPS][SKIP_ROWS]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int r0 = blockIdx.x * SKIP_ROWS, r1 = min(nRows, r0 + SKIP_ROWS);
   for (int i = tid; i < SKIP_ROWS; i += RV_THREADS) acc[i] = 0.0;
   __syncthreads();
-  bool anyRle = false, anyUnc = false;
+  bool anyUnc = false;
   // dense-map groups: a thread owns rows tid, tid + 256, ... of the block
   for (int gi = 0; gi < nGroups; gi++) {
     const DevGroup& g = groups[gi];
@@ -81,8 +90,6 @@ k_rmm_vec_general(const DevGroup* __restrict__ groups, int nGroups, int nRows, c
       for (int r = r0 + tid; r < r1; r += RV_THREADS) acc[r - r0] += Pg[map_get(g.mapType, g.map, g.mapHi, r)];
     } else if (g.type == GT_UNC)
       anyUnc = true;
-    else if (g.type == GT_RLE)
-      anyRle = true;
   }
   __syncthreads();
   // uncompressed groups: a warp owns rows warp, warp + 8, ...
@@ -90,7 +97,7 @@ k_rmm_vec_general(const DevGroup* __restrict__ groups, int nGroups, int nRows, c
     for (int gi = 0; gi < nGroups; gi++) {
       const DevGroup& g = groups[gi];
       if (g.type != GT_UNC) continue;
-      for (int r = r0 + warp; r < r1; r += RV_THREADS / 32) {
+      for (int r = r0 + warp; r < r1; r += RV_WARPS) {
         double s = 0;
         for (int c = lane; c < g.gCols; c += 32) s += g.dense[(size_t)r * g.gCols + c] * v[g.cols[c]];
         for (int d = 16; d; d >>= 1) s += __shfl_down_sync(0xffffffffu, s, d);
@@ -99,78 +106,75 @@ k_rmm_vec_general(const DevGroup* __restrict__ groups, int nGroups, int nRows, c
     }
     __syncthreads();
   }
-  // sparse groups: thread t takes groups t, t + 256, ...
-  for (int gi = tid; gi < nGroups; gi += RV_THREADS) {
-    const DevGroup& g = groups[gi];
-    if (g.type == GT_SDC && g.nOff > 0) {
+  // SDC / RLE groups, eight per round. From here on thread t owns rows 4 t .. 4 t + 3.
+  double a4[4];
+  {
+    const double2 lo = *(const double2*)&acc[tid * 4], hi = *(const double2*)&acc[tid * 4 + 2];
+    a4[0] = lo.x, a4[1] = lo.y, a4[2] = hi.x, a4[3] = hi.y;
+  }
+  double* mine = stage + warp * SKIP_ROWS;
+  for (int s0 = 0; s0 < nSparse; s0 += RV_WARPS) {
+    const int si = s0 + warp;
+    if (si < nSparse) {
+      double2* m2 = (double2*)mine;
+      for (int i = lane; i < SKIP_ROWS / 2; i += 32) m2[i] = make_double2(0.0, 0.0);
+      __syncwarp();
+      const DevGroup& g = groups[sparseIdx[si]];
       const double* Pg = P + g.valOff;
-      int row, elem;
-      int64_t pos;
-      if (g.offType == CLA_OFF_BYTE || g.offType == CLA_OFF_CHAR) {
-        const SdcSkip sk = g.skip[blockIdx.x];
-        row = sk.row;
-        elem = sk.elem;
-        pos = sk.pos;
-        if (elem >= g.nOff) row = INT_MAX;
-      } else {
-        row = g.first >= r0 ? g.first : ((g.offType == CLA_OFF_TWO && g.last >= r0) ? g.last : INT_MAX);
-        elem = (row == g.first) ? 0 : 1;
-        pos = 0;
-      }
-      const int maxV = g.offType == CLA_OFF_BYTE ? 255 : 65535;
-      while (row < r1) {
-        const int id = g.single ? 0 : map_get(g.mapType, g.map, g.mapHi, elem);
-        atomicAdd(&acc[row - r0], Pg[id]);
-        if (elem + 1 >= g.nOff) break;
-        if (g.offType == CLA_OFF_BYTE) {
-          const uint8_t* dp = (const uint8_t*)g.offData;
-          int d = dp[pos++];
-          while (d == 0) {
-            row += maxV;
-            d = dp[pos++];
-          }
-          row += d;
-        } else if (g.offType == CLA_OFF_CHAR) {
-          const uint16_t* dp = (const uint16_t*)g.offData;
-          int d = dp[pos++];
-          while (d == 0) {
-            row += maxV;
-            d = dp[pos++];
-          }
-          row += d;
-        } else
-          row = g.last;
-        elem++;
+      if (g.type == GT_SDC) {
+        sdc_walk_block(g, r0, r1, [&](int row, int e) {
+          mine[row - r0] = Pg[g.single ? 0 : map_get(g.mapType, g.map, g.mapHi, e)];
+        });
+      } else {  // RLE: a run writes its value to each of its rows (colgroup/ColGroupRLE.java:104-141)
+        for (int64_t ri = g.runSkip[blockIdx.x]; ri < g.nRuns; ri++) {
+          const RleRun run = g.runs[ri];
+          if (run.start >= r1) break;
+          const int a = max(run.start, r0), b = min(run.start + (int)run.len, r1);
+          const double p = Pg[run.k];
+          for (int i = a + lane; i < b; i += 32) mine[i - r0] = p;
+        }
       }
     }
-  }
-  // RLE groups: a warp per group; a run adds its value to each of its rows (the reference's own way,
-  // colgroup/ColGroupRLE.java:104-141). Turning the runs into +P / -P boundaries and a prefix sum is cheaper but
-  // leaves rounding residue of earlier, possibly much larger, values in later rows.
-  if (anyRle) {
-    for (int gi = warp; gi < nGroups; gi += RV_THREADS / 32) {
-      const DevGroup& g = groups[gi];
-      if (g.type != GT_RLE || (afterFast && g.inFast)) continue;
-      const double* Pg = P + g.valOff;
-      for (int64_t ri = g.runSkip[blockIdx.x]; ri < g.nRuns; ri++) {
-        const RleRun run = g.runs[ri];
-        if (run.start >= r1) break;
-        const int a = max(run.start, r0), b = min(run.start + (int)run.len, r1);
-        const double p = Pg[run.k];
-        for (int i = a + lane; i < b; i += 32) atomicAdd(&acc[i - r0], p);
-      }
+    __syncthreads();
+    const int nw = min(RV_WARPS, nSparse - s0);
+    for (int w = 0; w < nw; w++) {
+      const double2 lo = *(const double2*)&stage[w * SKIP_ROWS + tid * 4];
+      const double2 hi = *(const double2*)&stage[w * SKIP_ROWS + tid * 4 + 2];
+      // rows a group does not list hold 0.0 here; adding it changes nothing
+      a4[0] += lo.x, a4[1] += lo.y, a4[2] += hi.x, a4[3] += hi.y;
     }
+    __syncthreads();
   }
-  __syncthreads();
   const double c0 = (constRow != nullptr && !afterFast) ? constRow[0] : 0.0;
 #pragma unroll
   for (int i = 0; i < 4; i++) {
     const int r = r0 + tid * 4 + i;
     if (r < r1) {
-      const double val = acc[tid * 4 + i] + c0;
+      const double val = a4[i] + c0;
       out[r] = afterFast ? out[r] + val : val;
     }
   }
+}
+
+// SDC groups with listed rows and RLE groups with runs, in list order (built once per handle)
+static int64_t ensure_sparse_list(Matrix* m) {
+  if (m->sparseListBuilt) return CLA_OK;
+  std::vector<int32_t> idx;
+  for (int gi = 0; gi < m->nDev; gi++) {
+    const DevGroup& g = m->groups[gi];
+    if ((g.type == GT_SDC && g.nOff > 0) || (g.type == GT_RLE && g.nRuns > 0)) idx.push_back(gi);
+  }
+  if (!idx.empty()) {
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, idx.size() * sizeof(int32_t));
+    if (e != cudaSuccess) return fail(CLA_ERR_NOMEM, std::string("cudaMalloc sparse group list: ") + cudaGetErrorString(e));
+    m->allocs.push_back(p);
+    CLA_CUDA(cudaMemcpy(p, idx.data(), idx.size() * sizeof(int32_t), cudaMemcpyHostToDevice));
+    m->dSparseIdx = (int32_t*)p;
+  }
+  m->nSparse = (int)idx.size();
+  m->sparseListBuilt = true;
+  return CLA_OK;
 }
 
 int64_t launch_rmm(Matrix* m, const double* dV, int vCols, double* dOut, cudaStream_t s, bool afterFast) {
@@ -182,6 +186,7 @@ int64_t launch_rmm(Matrix* m, const double* dV, int vCols, double* dOut, cudaStr
     if (!rest) return CLA_OK;
   }
   int64_t rc;
+  if ((rc = ensure_sparse_list(m)) < 0) return rc;
   const size_t pBytes = (size_t)std::max<int64_t>(m->totalVals, 1) * sizeof(double);
   const size_t cOff = (pBytes + 255) & ~(size_t)255;
   if ((rc = ensure_scratch(m, cOff + sizeof(double))) < 0) return rc;
@@ -199,9 +204,15 @@ int64_t launch_rmm(Matrix* m, const double* dV, int vCols, double* dOut, cudaStr
     k_const_times_v<<<1, 128, 0, s>>>(m->dConstV, m->nCols, dV, 1, constRow);
     m->stats.kernel_launches++;
   }
+  static bool attrSet[64] = {};  // per device: function attributes belong to the device's context
+  bool& attr = attrSet[m->device & 63];
+  if (!attr) {
+    CLA_CUDA(cudaFuncSetAttribute(k_rmm_vec_general, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RV_SMEM));
+    attr = true;
+  }
   prof_begin(m, s);
-  k_rmm_vec_general<<<(m->nRows + SKIP_ROWS - 1) / SKIP_ROWS, RV_THREADS, 0, s>>>(m->dGroups, m->nDev, m->nRows, P, dV,
-                                                                               constRow, dOut, afterFast ? 1 : 0);
+  k_rmm_vec_general<<<(m->nRows + SKIP_ROWS - 1) / SKIP_ROWS, RV_THREADS, RV_SMEM, s>>>(
+      m->dGroups, m->nDev, m->dSparseIdx, m->nSparse, m->nRows, P, dV, constRow, dOut, afterFast ? 1 : 0);
   prof_end(m, s);
   m->stats.kernel_launches++;
   CLA_CUDA(cudaGetLastError());
@@ -267,7 +278,7 @@ constexpr int DB_ROWS = 256;         // a quarter of a skip-index block: 16 KB o
 constexpr int DB_LD = DB_ROWS + 2;   // column stride of the tile: 2 w + row spreads a write-out instruction over the banks
 __global__ void __launch_bounds__(256)
 k_decomp_block(const DevGroup* __restrict__ groups, const int32_t* __restrict__ colSrc, const double* __restrict__ constV,
-               double* __restrict__ out, int r0, int r1, int nCols) {
+               double* __restrict__ out, int r0, int r1, int nCols, int exactSdc) {
   extern __shared__ double dtile[];  // [DB_COLS][DB_LD]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int rb = r0 + blockIdx.x * DB_ROWS, re = min(r1, rb + DB_ROWS), nr = re - rb;
@@ -319,9 +330,12 @@ k_decomp_block(const DevGroup* __restrict__ groups, const int32_t* __restrict__ 
       } else if (g.type == GT_SDC) {
         for (int rr = lane; rr < nr; rr += 32) col[rr] = cst;
         __syncwarp();
+        // exactSdc: the column belongs to this group alone, so its constant is exactly the group's default tuple and
+        // a listed row holds the registered value itself (the reference writes d, lib/CLALibDecompress.java:310-357)
+        const double* raw = g.dictRaw + j;
         sdc_walk_block(g, rb, re, [&](int row, int e) {
           const int id = g.single ? 0 : map_get(g.mapType, g.map, g.mapHi, e);
-          col[row - rb] = cst + dict[(size_t)id * gc];
+          col[row - rb] = exactSdc ? raw[(size_t)id * gc] : cst + dict[(size_t)id * gc];
         });
       } else if (g.type == GT_RLE) {
         for (int rr = lane; rr < nr; rr += 32) col[rr] = cst;
@@ -359,7 +373,8 @@ int64_t launch_decompress_range(Matrix* m, int r0, int r1, double* dOut, cudaStr
       attr = true;
     }
     dim3 grid((r1 - r0 + DB_ROWS - 1) / DB_ROWS, (m->nCols + DB_COLS - 1) / DB_COLS);
-    k_decomp_block<<<grid, 256, smem, s>>>(m->dGroups, m->dColSrc, m->hasConst ? m->dConstV : nullptr, dOut, r0, r1, m->nCols);
+    k_decomp_block<<<grid, 256, smem, s>>>(m->dGroups, m->dColSrc, m->hasConst ? m->dConstV : nullptr, dOut, r0, r1, m->nCols,
+                                           m->multiCover ? 0 : 1);
     m->stats.kernel_launches++;
     CLA_CUDA(cudaGetLastError());
     return CLA_OK;

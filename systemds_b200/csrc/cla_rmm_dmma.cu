@@ -39,6 +39,48 @@ struct DenseCol {
   int32_t pad;
 };
 
+// Adds the SDC and RLE groups to a 128-row tile of partial results in shared memory, in list order and without
+// atomics: warp w owns rows [16 w, 16 w + 16) of the tile and walks the groups one after the other (`list` = their
+// device group indices, or null: every group of `groups`). An SDC group is decoded from the skip entry of its
+// 1024-row block (32 deltas per step, warp scan); the lane that finds a listed row adds that row's table row. An
+// RLE group's runs are clipped to the warp's rows; lane n adds columns n and n + 32. This is the slow, always
+// available form: the second-generation kernel uses it when one of its work queues overflows.
+__device__ __forceinline__ void sparse_rows_in_order(const DevGroup* __restrict__ groups, int n,
+                                                     const int32_t* __restrict__ list, const double* __restrict__ P,
+                                                     int vCols, int j0, int vc, double* Cs, int r0, int r1, int skipBlock) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int ra = r0 + warp * 16, rb = min(r1, ra + 16);
+  if (ra >= rb) return;
+  for (int i = 0; i < n; i++) {
+    const DevGroup& g = groups[list ? list[i] : i];
+    if (g.type == GT_SDC) {
+      const double* Pg = P + g.valOff * vCols + j0;
+      sdc_walk_block(g, ra, rb, [&](int row, int e) {
+        const int id = g.single ? 0 : map_get(g.mapType, g.map, g.mapHi, e);
+        double* cr = Cs + (row - r0) * GM_LDC;
+        const double* p = Pg + (size_t)id * vCols;
+        for (int c = 0; c < vc; c++) cr[c] += p[c];
+      });
+      __syncwarp();
+    } else if (g.type == GT_RLE) {
+      const double* Pg = P + g.valOff * vCols + j0;
+      for (int64_t ri = g.runSkip[skipBlock]; ri < g.nRuns; ri++) {
+        const RleRun run = g.runs[ri];
+        if (run.start >= rb) break;
+        const int a = max(run.start, ra), b = min(run.start + (int)run.len, rb);
+        if (a >= b) continue;
+        const double* p = Pg + (size_t)run.k * vCols;
+        const double p0 = lane < vc ? p[lane] : 0.0, p1 = lane + 32 < vc ? p[lane + 32] : 0.0;
+        for (int r = a; r < b; r++) {
+          if (lane < vc) Cs[(r - r0) * GM_LDC + lane] += p0;
+          if (lane + 32 < vc) Cs[(r - r0) * GM_LDC + lane + 32] += p1;
+        }
+      }
+      __syncwarp();
+    }
+  }
+}
+
 __global__ void __launch_bounds__(GM_THREADS, 2)
 k_rmm_dmma(const DevGroup* __restrict__ groups, int nGroups, const DenseCol* __restrict__ dcols, int nDense, int nRows,
            const double* __restrict__ V, int vCols, const double* __restrict__ P, const double* __restrict__ constRow,
@@ -124,42 +166,8 @@ k_rmm_dmma(const DevGroup* __restrict__ groups, int nGroups, const DenseCol* __r
         Cs[(warp * 16 + mt * 8 + (lane >> 2)) * GM_LDC + nt * 8 + (lane & 3) * 2 + u] = c[mt][nt][u];
   if (tid < GM_TN) base[tid] = constRow && tid < vc ? constRow[j0 + tid] : 0.0;
   __syncthreads();
-  // ---- sparse groups, one per warp at a time ----
-  double b0 = 0.0, b1 = 0.0;  // this warp's share of the base vector: columns lane and lane + 32
-  for (int gi = warp; gi < nGroups; gi += GM_THREADS / 32) {
-    const DevGroup& g = groups[gi];
-    if (g.type == GT_SDC) {
-      const double* Pg = P + g.valOff * vCols + j0;
-      // listed rows of the tile: decode 32 at a time, then the whole warp adds one table row per listed row
-      sdc_walk_block(g, r0, r1, [&](int row, int e) {
-        const int id = g.single ? 0 : map_get(g.mapType, g.map, g.mapHi, e);
-        double* cr = Cs + (row - r0) * GM_LDC;
-        const double* p = Pg + (size_t)id * vCols;
-        for (int n = 0; n < vc; n++) atomicAdd(&cr[n], p[n]);
-      });
-    } else if (g.type == GT_RLE) {
-      const double* Pg = P + g.valOff * vCols + j0;
-      for (int64_t ri = g.runSkip[r0 / SKIP_ROWS]; ri < g.nRuns; ri++) {
-        const RleRun run = g.runs[ri];
-        if (run.start >= r1) break;
-        const int a = max(run.start, r0), b = min(run.start + (int)run.len, r1);
-        if (a >= b) continue;
-        const double* p = Pg + (size_t)run.k * vCols;
-        const double p0 = lane < vc ? p[lane] : 0.0, p1 = lane + 32 < vc ? p[lane + 32] : 0.0;
-        if (a == r0 && b == r1) {  // the run covers the tile: one add to the base vector
-          b0 += p0;
-          b1 += p1;
-        } else {
-          for (int r = a; r < b; r++) {
-            if (lane < vc) atomicAdd(&Cs[(r - r0) * GM_LDC + lane], p0);
-            if (lane + 32 < vc) atomicAdd(&Cs[(r - r0) * GM_LDC + lane + 32], p1);
-          }
-        }
-      }
-    }
-  }
-  if (b0 != 0.0) atomicAdd(&base[lane], b0);
-  if (b1 != 0.0) atomicAdd(&base[lane + 32], b1);
+  // ---- sparse groups: warp w owns rows [16 w, 16 w + 16) of the tile and adds every group in list order ----
+  sparse_rows_in_order(groups, nGroups, nullptr, P, vCols, j0, vc, Cs, r0, r1, blockIdx.x * GM_TR / SKIP_ROWS);
   __syncthreads();
   for (int e = tid; e < GM_TR * GM_TN; e += GM_THREADS) {
     const int r = e >> 6, n = e & 63;
@@ -189,12 +197,12 @@ struct DenseDesc {
   int32_t pad;
 };
 
-constexpr int Q_CAP = 448;            // items per warp queue
+constexpr int Q_CAP = 512;            // items per warp queue (a power of two: sorted in place)
 constexpr int QB_CAP = 512;           // base queue
 constexpr int QD_CAP = 32;            // per-warp queue of run boundaries
 constexpr int GM_SUB = SKIP_ROWS / GM_TR;  // tiles per block
 
-struct WorkItem {
+struct WorkItem {    // read as one little-endian 64-bit key, the table row is the most significant part
   uint16_t ra, rb;   // rows [ra, rb) of the tile
   uint32_t prow;     // row of the table arena P
 };
@@ -203,9 +211,13 @@ struct DeltaItem {   // rows [row, end) of the tile (inside one warp's 16-row sl
   int16_t end;
   uint32_t prow;
 };
+static_assert(sizeof(WorkItem) == 8 && sizeof(DeltaItem) == 8, "queue items are sorted as 64-bit keys");
 
-__device__ __forceinline__ void push_item(WorkItem* q, int* qn, int w, int ra, int rb, uint32_t prow, double* Cs,
-                                          const double* __restrict__ P, int vCols, int j0, int vc) {
+// Queue slots are handed out in arrival order, which depends on warp timing; the queues are sorted by table row
+// before they are applied (a group's table rows lie behind those of every earlier group, and one group never has
+// two items on the same output row), so every output row receives its groups' terms in list order.
+// A full queue drops the item: the count keeps growing and the tile then takes sparse_rows_in_order instead.
+__device__ __forceinline__ void push_item(WorkItem* q, int* qn, int w, int ra, int rb, uint32_t prow) {
   const int slot = atomicAdd(&qn[w], 1);
   if (slot < Q_CAP) {
     WorkItem it;
@@ -213,11 +225,51 @@ __device__ __forceinline__ void push_item(WorkItem* q, int* qn, int w, int ra, i
     it.rb = (uint16_t)rb;
     it.prow = prow;
     q[w * Q_CAP + slot] = it;
-  } else {  // queue full: add directly (atomics, since the owning warp may be working on the same rows)
-    const double* p = P + (size_t)prow * vCols + j0;
-    for (int r = ra; r < rb; r++)
-      for (int n = 0; n < vc; n++) atomicAdd(&Cs[r * GM_LDC + n], p[n]);
   }
+}
+
+// Bitonic sort of n 64-bit keys in shared memory by one warp; the array must have room for the next power of two.
+__device__ __forceinline__ void warp_sort_u64(unsigned long long* a, int n) {
+  const int lane = threadIdx.x & 31;
+  int np = 1;
+  while (np < n) np <<= 1;
+  for (int i = n + lane; i < np; i += 32) a[i] = ~0ull;
+  __syncwarp();
+  for (int k = 2; k <= np; k <<= 1)
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      for (int t = lane; t < (np >> 1); t += 32) {
+        const int i = ((t & ~(j - 1)) << 1) | (t & (j - 1));  // lower index of the t-th pair at distance j
+        const int l = i | j;
+        const unsigned long long x = a[i], y = a[l];
+        const bool up = (i & k) == 0;
+        if ((x > y) == up) {
+          a[i] = y;
+          a[l] = x;
+        }
+      }
+      __syncwarp();
+    }
+}
+__device__ __forceinline__ void warp_sort_u32(uint32_t* a, int n) {
+  const int lane = threadIdx.x & 31;
+  int np = 1;
+  while (np < n) np <<= 1;
+  for (int i = n + lane; i < np; i += 32) a[i] = ~0u;
+  __syncwarp();
+  for (int k = 2; k <= np; k <<= 1)
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      for (int t = lane; t < (np >> 1); t += 32) {
+        const int i = ((t & ~(j - 1)) << 1) | (t & (j - 1));
+        const int l = i | j;
+        const uint32_t x = a[i], y = a[l];
+        const bool up = (i & k) == 0;
+        if ((x > y) == up) {
+          a[i] = y;
+          a[l] = x;
+        }
+      }
+      __syncwarp();
+    }
 }
 
 template <bool QUAD>  // QUAD: the quad-column decode is compiled in (it costs registers the other stages then spill)
@@ -405,7 +457,7 @@ k_rmm_dmma2(const DevGroup* __restrict__ groups, const DenseDesc* __restrict__ d
         if (sRow >= r0) {
           const int id = gs.single ? 0 : map_get(gs.mapType, gs.map, gs.mapHi, sElem);
           const int rl = sRow - r0;
-          push_item(q, qn, rl >> 4, rl, rl + 1, (uint32_t)(gs.valOff + id), Cs, P, vCols, j0, vc);
+          push_item(q, qn, rl >> 4, rl, rl + 1, (uint32_t)(gs.valOff + id));
         }
         if (sElem + 1 >= gs.nOff) {
           sRow = INT_MAX;
@@ -444,7 +496,7 @@ k_rmm_dmma2(const DevGroup* __restrict__ groups, const DenseDesc* __restrict__ d
             const int slot = atomicAdd(&qn[8], 1);
             if (slot < QB_CAP) qb[slot] = prow;
             else
-              for (int w = 0; w < 8; w++) push_item(q, qn, w, w * 16, w * 16 + 16, prow, Cs, P, vCols, j0, vc);
+              for (int w = 0; w < 8; w++) push_item(q, qn, w, w * 16, w * 16 + 16, prow);
           } else {
             // a run that starts or ends inside the tile: every warp whose 16 rows it touches gets the piece of
             // the run that lies in its slice
@@ -452,10 +504,8 @@ k_rmm_dmma2(const DevGroup* __restrict__ groups, const DenseDesc* __restrict__ d
               const int aw = max(a - r0, w * 16), bw = min(b - r0, w * 16 + 16);
               const int slot = atomicAdd(&qn[9 + w], 1);
               if (slot < QD_CAP) qd[w * QD_CAP + slot] = DeltaItem{(int16_t)aw, (int16_t)bw, prow};
-              else {
-                atomicAdd(&qn[9 + w], -1);
-                push_item(q, qn, w, aw, bw, prow, Cs, P, vCols, j0, vc);
-              }
+              else
+                push_item(q, qn, w, aw, bw, prow);
             }
           }
         }
@@ -465,11 +515,23 @@ k_rmm_dmma2(const DevGroup* __restrict__ groups, const DenseDesc* __restrict__ d
     }
     __syncthreads();
 
+    // ---- fix the summation order: sort every queue by table row. A tile with an overflowed work queue drops its
+    //      queues and takes the slow in-order walk below instead ----
+    bool ovf = false;
+#pragma unroll
+    for (int w = 0; w < 8; w++) ovf |= qn[w] > Q_CAP;
+    if (!ovf) {
+      warp_sort_u64((unsigned long long*)(q + warp * Q_CAP), qn[warp]);
+      warp_sort_u64((unsigned long long*)(qd + warp * QD_CAP), min(qn[9 + warp], QD_CAP));
+      if (warp == 0) warp_sort_u32(qb, min(qn[8], QB_CAP));
+    }
+    __syncthreads();
+
     // ---- base vector: constV * V plus the table rows of all runs that cover the whole tile. Thread = (one of four
     //      item slices, column): every thread's loads are independent, so the whole sum costs one or two latencies ----
     {
       const int n = tid & 63, sl = tid >> 6;
-      const int nbq = min(qn[8], QB_CAP);
+      const int nbq = ovf ? 0 : min(qn[8], QB_CAP);
       double sacc = 0.0;
       if (n < vc)
         for (int i = sl; i < nbq; i += 4) sacc += P[(size_t)qb[i] * vCols + j0 + n];
@@ -491,7 +553,11 @@ k_rmm_dmma2(const DevGroup* __restrict__ groups, const DenseDesc* __restrict__ d
         return make_double2(c0ok ? p[0] : 0.0, c1ok ? p[1] : 0.0);
       };
       const double2 bsum = make_double2(c0ok ? basev[n0] : 0.0, c1ok ? basev[n0 + 1] : 0.0);
-      const int nq = min(qn[warp], Q_CAP);
+      if (ovf) {
+        sparse_rows_in_order(groups, nSdc, sdcIdx, P, vCols, j0, vc, Cs, r0, r1, blockIdx.x);
+        sparse_rows_in_order(groups, nRle, rleIdx, P, vCols, j0, vc, Cs, r0, r1, blockIdx.x);
+      }
+      const int nq = ovf ? 0 : qn[warp];
       const WorkItem* myq = q + warp * Q_CAP;
       for (int i0 = 0; i0 < nq; i0 += 8) {
         double2 t[8];
@@ -517,7 +583,7 @@ k_rmm_dmma2(const DevGroup* __restrict__ groups, const DenseDesc* __restrict__ d
       // table rows of the pieces that cover it. (Walking the slice with a running sum, +P at a start and -P at an
       // end, is cheaper but leaves rounding residue of earlier, possibly much larger, values in later rows; the
       // reference adds a row's own values and nothing else.)
-      const int nd = min(qn[9 + warp], QD_CAP);
+      const int nd = ovf ? 0 : min(qn[9 + warp], QD_CAP);
       const DeltaItem* myd = qd + warp * QD_CAP;
       for (int i0 = 0; i0 < nd; i0 += 8) {
         double2 t[8];

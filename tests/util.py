@@ -28,6 +28,24 @@ def dense_of(cmb) -> np.ndarray:
     return X
 
 
+def abs_dense_of(cmb) -> np.ndarray:
+    """Sum over the groups of the absolute values each contributes to a cell: the magnitude of the terms behind a
+    cell of an overlapping or frame-of-reference block (equals |X| for a plain block)."""
+    A = np.zeros((cmb.rlen, cmb.clen))
+    for g in cmb.getColGroups():
+        one = type(cmb)(cmb.rlen, cmb.clen, [g], False)
+        ref = getattr(g, "_reference", None)
+        if ref is not None:  # a frame-of-reference cell is dictionary value + reference: two terms
+            cols = g.getColIndices()
+            X = dense_of(one)
+            X[:, cols] -= ref
+            A += np.abs(X)
+            A[:, cols] += np.abs(ref)
+        else:
+            A += np.abs(dense_of(one))
+    return A
+
+
 def rel_err(got, ref, scale=None) -> float:
     """max |got - ref| relative to the magnitude of the terms that were summed (norm-wise relative error)."""
     got, ref = np.asarray(got, float), np.asarray(ref, float)
