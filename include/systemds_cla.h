@@ -14,6 +14,16 @@
  *
  * Threading: calls on one handle are serialised by an internal mutex; different handles may be
  * used concurrently. The thread budget "k" of the reference's calls has no meaning here.
+ * Device-buffer calls (cla_*_dev) return once their work is enqueued on the caller's stream; all
+ * calls on a handle share that handle's scratch buffers, so the library orders them on the device
+ * as well: a call that arrives on another stream than the handle's previous call waits (event
+ * wait on the device, not on the host) until that call's kernels have finished. A kernel's
+ * self-check that trips in a device-buffer call is reported by the next cla_stats_get or
+ * host-buffer call on the handle (CLA_ERR_DEVICE_CHECK); callers that never make one should poll
+ * cla_stats_get. The right products (X %*% v, X %*% V), the specialised left vector product and
+ * the chain built from them form every output cell's sum in a fixed order and are reproducible
+ * bit for bit; the general left product, the self-product and the constant-column terms combine
+ * partial sums with floating-point atomics and are reproducible to rounding only.
  */
 #ifndef SYSTEMDS_CLA_H
 #define SYSTEMDS_CLA_H
@@ -126,6 +136,14 @@ int64_t cla_add_group_ole(cla_handle h, const int32_t* colIdx, int32_t gCols, co
                           const int32_t* ptr, const uint16_t* data, int64_t dataLen);
 /* ColGroupUncompressed {_data} dense [nRows x gCols] (colgroup/ColGroupUncompressed.java:84) */
 int64_t cla_add_group_uncompressed(cla_handle h, const int32_t* colIdx, int32_t gCols, const double* values);
+/* The same two groups when the index map / dense block already lives in device memory (same layouts; colIdx and
+ * dict stay host arrays). The device buffer is read by cla_finalize (device-to-device copy, ids checked by a
+ * kernel: an id at or above nVals makes cla_finalize fail with CLA_ERR_BAD_ARG) and must stay valid and unchanged
+ * until cla_finalize has returned. Maps: MapToBit, MapToUByte, MapToByte, MapToChar or MapToInt. These have no
+ * counterpart in the reference, whose column groups always live on the JVM heap (colgroup/ColGroupDDC.java:79-89). */
+int64_t cla_add_group_ddc_dev(cla_handle h, const int32_t* colIdx, int32_t gCols, const double* dict, int32_t nVals,
+                              int32_t mapType, const void* dMap, int64_t mapSize);
+int64_t cla_add_group_uncompressed_dev(cla_handle h, const int32_t* colIdx, int32_t gCols, const double* dValues);
 /* ColGroupConst (one tuple) and ColGroupEmpty; both fold into the constant row vector that
  * lib/CLALibUtils.java:188-206 (filterGroups) builds. */
 int64_t cla_add_group_const(cla_handle h, const int32_t* colIdx, int32_t gCols, const double* tuple);
@@ -189,11 +207,11 @@ int64_t cla_mmchain_dev(cla_handle h, const double* dV, const double* dW, int32_
 /* t(y) %*% X (one left row) that performs no device allocation. It has no counterpart in the reference.
  * For hosts that must not allocate when they call in -- a runtime whose own pool owns all device memory, or a loop
  * that cannot afford the device-wide synchronisation inside cudaMalloc -- the kernel's scratch (per-CTA partial
- * sums, the row sum of dY) is a fixed array inside the library, about 385 KB, held by every GPU that loads the
+ * sums, the row sum of dY) is a fixed array inside the library, about 450 KB, held by every GPU that loads the
  * library until the process exits. Inputs and output are still the caller's: dY [nRows] and dOut [nCols] are
  * device addresses, dY 16-byte aligned. Same result as cla_lmm_dev with yRows = 1.
  * Limits: the matrix must consist of dense-map (DDC) groups with at most 256 tuples and 1-byte (or 1-bit) maps,
- * and need at most 512 partial-sum rows (one per launched CTA: the SM count, or the number of 96-column chunks if
+ * and need at most 512 partial-sum rows (one per launched CTA: the SM count, or the number of 112-column chunks if
  * that is larger); otherwise CLA_ERR_UNSUPPORTED is returned and nothing runs.
  * The first call on a device looks up the array's device address; make that call outside any stream capture.
  * All calls share the array and it keeps the previous call's contents (what must start at zero is cleared on the

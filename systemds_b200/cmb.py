@@ -20,7 +20,8 @@ import numpy as np
 
 from . import native
 from .colgroup import (AColGroup, ASDC, AColGroupOffset, ColGroupConst, ColGroupDDC, ColGroupDDCFOR, ColGroupEmpty,
-                       ColGroupOLE, ColGroupRLE, ColGroupSDCFOR, ColGroupUncompressed)
+                       ColGroupOLE, ColGroupRLE, ColGroupSDCFOR, ColGroupUncompressed, ColGroupUncompressedDev)
+from .mapping import DeviceMap
 from .native import check, ptr
 
 CHAIN_XtXv, CHAIN_XtwXv = 0, 1
@@ -123,7 +124,14 @@ class CompressedMatrixBlock:
 
     def _add(self, L, h, g: AColGroup):
         cols, gc = ptr(g._colIndexes), g.getNumCols()
-        if isinstance(g, ColGroupDDC):
+        if isinstance(g, ColGroupDDC) and isinstance(g._data, DeviceMap):
+            m = g._data
+            check(L.cla_add_group_ddc_dev(h, cols, gc, ptr(g._dict), g.getNumValues(), m.type, C.c_void_p(m.dptr), m.size))
+        elif isinstance(g, ColGroupUncompressedDev):
+            if g._numRows != self.rlen:
+                raise ValueError("uncompressed group must have one row per matrix row")
+            check(L.cla_add_group_uncompressed_dev(h, cols, gc, C.c_void_p(g.dptr)))
+        elif isinstance(g, ColGroupDDC):
             m = g._data
             check(L.cla_add_group_ddc(h, cols, gc, ptr(g._dict), g.getNumValues(), m.type, ptr(m.data), ptr(m.data2),
                                       m.size))

@@ -199,6 +199,47 @@ class ColGroupRLE(AColGroupOffset):
         return out.reshape(-1)
 
     @staticmethod
+    def from_runs(colIndexes, dict_, starts, lens, vals, numRows) -> "ColGroupRLE":
+        """Encode runs given as (first row, length, tuple id), sorted by first row and not overlapping, without
+        materialising one id per row: per value, ``(gap, len)`` pairs under the encoder's rules
+        (ColGroupRLE.java:1073-1157: gaps above 65535 become ``(65535, 0)`` fillers, runs are cut at 65535 rows)."""
+        starts = np.asarray(starts, dtype=np.int64)
+        lens = np.asarray(lens, dtype=np.int64)
+        vals = np.asarray(vals, dtype=np.int64)
+        nVals = _dict(dict_, len(_cols(colIndexes))).shape[0]
+        chunks, ptr = [], [0]
+        covered = int(lens.sum())
+        for k in range(nVals):
+            sel = np.flatnonzero((vals == k) & (lens > 0))
+            st, ln = starts[sel], lens[sel]
+            if st.size:
+                # merge runs of this value that touch (the per-row encoder would see them as one run)
+                touch = np.concatenate([[False], st[1:] == (st + ln)[:-1]])
+                first = np.flatnonzero(~touch)
+                ends = np.concatenate([(st + ln)[first[1:] - 1], [(st + ln)[-1]]])
+                st, ln = st[first], ends - st[first]
+                pieces = (ln + CM - 1) // CM
+                rep = np.repeat(np.arange(st.size), pieces)
+                within = np.arange(rep.size) - np.repeat(np.cumsum(pieces) - pieces, pieces)
+                s2 = st[rep] + within * CM
+                l2 = np.minimum(ln[rep] - within * CM, CM)
+                prev_end = np.concatenate([[0], (s2 + l2)[:-1]])
+                gaps = s2 - prev_end
+                fill = np.maximum(gaps - 1, 0) // CM
+                enc = np.zeros((int(np.sum(fill) + s2.size), 2), np.uint16)
+                enc[:, 0] = CM
+                pos = np.cumsum(fill + 1) - 1
+                enc[pos, 0] = (gaps - fill * CM).astype(np.uint16)
+                enc[pos, 1] = l2.astype(np.uint16)
+                enc = enc.reshape(-1)
+            else:
+                enc = np.zeros(0, np.uint16)
+            chunks.append(enc)
+            ptr.append(ptr[-1] + enc.shape[0])
+        data = np.concatenate(chunks) if chunks else np.zeros(0, np.uint16)
+        return ColGroupRLE(colIndexes, int(numRows), covered < int(numRows), dict_, data, ptr)
+
+    @staticmethod
     def from_row_ids(colIndexes, dict_, ids, numRows=None) -> "ColGroupRLE":
         """Encode per-row ids (-1 = no tuple, i.e. zero row) into the RLE group."""
         ids = np.asarray(ids)
@@ -279,6 +320,20 @@ class ColGroupUncompressed(AColGroup):
 
     def index_bytes(self) -> int:
         return self._data.nbytes
+
+
+class ColGroupUncompressedDev(AColGroup):
+    """An uncompressed group whose dense ``[nRows x gCols]`` block already lives in device memory (``dptr``; ``owner``
+    keeps it alive). Registered with ``cla_add_group_uncompressed_dev``."""
+
+    def __init__(self, colIndexes, numRows: int, dptr: int, owner=None):
+        super().__init__(colIndexes)
+        self._numRows = int(numRows)
+        self.dptr = int(dptr)
+        self.owner = owner
+
+    def index_bytes(self) -> int:
+        return self._numRows * self.getNumCols() * 8
 
 
 class ColGroupConst(ADictBasedColGroup):

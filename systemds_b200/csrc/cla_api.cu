@@ -277,6 +277,55 @@ int64_t cla_add_group_uncompressed(cla_handle h, const int32_t* colIdx, int32_t 
   return (int64_t)m->hg.size() - 1;
 }
 
+// Registration from device memory: the index map / dense block already lives on the GPU (a block that was compressed,
+// sliced or generated there). The buffer is read at cla_finalize, which copies it device to device and checks the
+// ids with a reduction kernel; it must stay valid and unchanged until cla_finalize has returned.
+int64_t cla_add_group_ddc_dev(cla_handle h, const int32_t* colIdx, int32_t gCols, const double* dict, int32_t nVals,
+                              int32_t mapType, const void* dMap, int64_t mapSize) {
+  GET_MATRIX(h);
+  REQUIRE_OPEN();
+  HostGroup g;
+  int64_t rc = add_dict_group(m, g, GT_DDC, colIdx, gCols, dict, nVals);
+  if (rc < 0) return rc;
+  if (mapSize != m->nRows) return fail(CLA_ERR_SHAPE, "DDC map must have one cell per row");
+  if (m->nRows > 0 && nVals == 0) return fail(CLA_ERR_BAD_ARG, "DDC group without dictionary tuples");
+  if (mapType != CLA_MAP_BIT && mapType != CLA_MAP_UBYTE && mapType != CLA_MAP_BYTE && mapType != CLA_MAP_CHAR &&
+      mapType != CLA_MAP_INT)
+    return fail(CLA_ERR_UNSUPPORTED, "device-resident maps: MapToBit, MapToUByte, MapToByte, MapToChar or MapToInt");
+  if (mapSize > 0 && !dMap) return fail(CLA_ERR_BAD_ARG, "map array missing");
+  cudaPointerAttributes at{};
+  if (mapSize > 0 && (cudaPointerGetAttributes(&at, dMap) != cudaSuccess || at.type != cudaMemoryTypeDevice)) {
+    cudaGetLastError();
+    return fail(CLA_ERR_BAD_ARG, "device-resident map: not a device pointer");
+  }
+  g.mapType = mapType;
+  g.mapSize = mapSize;
+  g.devMap = dMap;
+  g.devSrcDevice = mapSize > 0 ? at.device : -1;
+  m->hg.push_back(std::move(g));
+  return (int64_t)m->hg.size() - 1;
+}
+
+int64_t cla_add_group_uncompressed_dev(cla_handle h, const int32_t* colIdx, int32_t gCols, const double* dValues) {
+  GET_MATRIX(h);
+  REQUIRE_OPEN();
+  int64_t rc = check_cols(m, colIdx, gCols);
+  if (rc < 0) return rc;
+  if (m->nRows > 0 && !dValues) return fail(CLA_ERR_BAD_ARG, "dense block missing");
+  cudaPointerAttributes at{};
+  if (m->nRows > 0 && (cudaPointerGetAttributes(&at, dValues) != cudaSuccess || at.type != cudaMemoryTypeDevice)) {
+    cudaGetLastError();
+    return fail(CLA_ERR_BAD_ARG, "device-resident dense block: not a device pointer");
+  }
+  HostGroup g;
+  g.type = GT_UNC;
+  g.cols.assign(colIdx, colIdx + gCols);
+  g.devDense = dValues;
+  g.devSrcDevice = m->nRows > 0 ? at.device : -1;
+  m->hg.push_back(std::move(g));
+  return (int64_t)m->hg.size() - 1;
+}
+
 int64_t cla_add_group_const(cla_handle h, const int32_t* colIdx, int32_t gCols, const double* tuple) {
   GET_MATRIX(h);
   REQUIRE_OPEN();

@@ -131,6 +131,11 @@ struct HostGroup {
   std::vector<int32_t> ptr;
   std::vector<uint16_t> data;
   std::vector<double> dense;
+  // Groups registered from device memory (cla_add_group_ddc_dev / cla_add_group_uncompressed_dev): the caller's
+  // buffer, read once at cla_finalize and copied device to device.
+  const void* devMap = nullptr;
+  const double* devDense = nullptr;
+  int devSrcDevice = -1;
 };
 
 struct FastPlan;  // plans of the specialised DDC kernels (cla_fast.cu)

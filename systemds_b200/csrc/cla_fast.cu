@@ -10,11 +10,12 @@
 //    sit in shared memory back to back. A table of <= 16 entries spans each 8-byte bank once, so random
 //    ids never conflict; larger tables conflict in proportion to their size.
 //
-//  * k_lmm_vec_u8: a lane owns *columns*, not rows. Tables are interleaved 32 columns wide
-//    (entry k of slot s at byte k*256 + s*8), so lane s only ever touches bank pair s mod 16 whatever the
-//    ids are: conflict free for any cardinality, without replicating tables. The two half-warps of a warp
-//    work on different rows of the same 2 x 16 column slots. The left vector is read with warp-uniform
-//    128-bit loads and kept in registers for all columns of the CTA.
+//  * k_lmm_vec_u8: a lane owns *columns*, not rows. Tables are interleaved 16 columns wide, one such
+//    "unit" after the other (entry k of slot s of a unit at byte k*128 + s*8), so lane s only ever touches
+//    bank pair s whatever the ids are: conflict free for any cardinality, without replicating tables. The
+//    two half-warps of a warp work on different rows of the same 16 column slots per unit; a CTA holds up
+//    to seven units (7 x 32 KB at 256 tuples). The left vector is read with warp-uniform 128-bit loads and
+//    kept in registers for all columns of the CTA.
 //
 // Tables are staged into shared memory with TMA bulk copies (cp.async.bulk + mbarrier, no multicast).
 #include "cla_common.cuh"
@@ -38,7 +39,8 @@ constexpr int RMM_TILE = RMM_T * RMM_ROWS_PT;
 // ---- LMM plan ----
 constexpr int LMM_W = 12;             // warps per CTA
 constexpr int LMM_T = LMM_W * 32;
-constexpr int LMM_MAX_PAIRS = 3;      // 32-column table slabs per CTA (3 x 64 KB at 256 tuples)
+constexpr int LMM_MAX_UNITS = 7;      // 16-column table units per CTA (7 x 32 KB at 256 tuples)
+constexpr int LMM_PART = LMM_MAX_UNITS * 16;  // partial sums a CTA writes
 constexpr int LMM_STEP = 64;          // rows per warp step (32 per half-warp)
 
 struct RmmChunk {
@@ -47,12 +49,11 @@ struct RmmChunk {
   int64_t tblOff;      // offset of the chunk's tables in the P image (doubles, even)
 };
 struct LmmChunk {
-  int pair0, nPairs;     // slabs of 32 column slots
-  int nk[LMM_MAX_PAIRS]; // table depth (max tuples) of each slab
+  int unit0, nUnits;     // units of 16 column slots
+  int nk[LMM_MAX_UNITS]; // table depth (max tuples) of each unit
   int64_t tblOff;        // offset in the table image (doubles)
   int tblDoubles;
   int cta0, nCta;        // CTA range of the launch that works on this chunk
-  int halfLast;          // the chunk's last slab only uses its first 16 column slots
 };
 
 struct FastPlan {
@@ -261,33 +262,28 @@ k_rmm_vec_u8(const uint8_t* const* __restrict__ maps, const int* __restrict__ tb
 // --------------------------------------------------------------------------------------------------
 // LMM: column-per-lane kernel
 // --------------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t byte_x256(uint32_t w, int i) {  // (byte i of w) << 8, one PRMT
-  // selector nibbles (low to high): result byte0 = 0 (take byte 4 of {w, 0} pair = zero operand), byte1 = byte i
-  return __byte_perm(w, 0u, 0x4404u | ((uint32_t)i << 4));
+__device__ __forceinline__ uint32_t byte_x128(uint32_t w, int i) {  // (byte i of w) << 7
+  return i == 0 ? (w << 7) & 0x7F80u : (i == 3 ? (w >> 17) & 0x7F80u : (w >> (8 * i - 7)) & 0x7F80u);
 }
 
-template <int NP, bool HALF>
-__device__ __forceinline__ void lmm_cells(const uint4 (&m)[NP][2][2], int sub, const double (&yv)[16],
-                                          const unsigned char* const (&tbase)[NP], double (&acc)[NP][2]) {
+template <int NU>
+__device__ __forceinline__ void lmm_cells(const uint4 (&m)[NU][2], int sub, const double (&yv)[16],
+                                          const unsigned char* const (&tbase)[NU], double (&acc)[NU]) {
 #pragma unroll
-  for (int p = 0; p < NP; p++) {
+  for (int u = 0; u < NU; u++) {
+    const uint4 w = m[u][sub];
+    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+    const unsigned char* T = tbase[u];
 #pragma unroll
-    for (int ab = 0; ab < 2; ab++) {
-      if (HALF && p == NP - 1 && ab == 1) continue;
-      const uint4 w = m[p][ab][sub];
-      const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-      const unsigned char* T = tbase[p] + ab * 128;
-#pragma unroll
-      for (int i = 0; i < 16; i++) {
-        const double t = *(const double*)(T + byte_x256(ww[i >> 2], i & 3));
-        acc[p][ab] = fma(yv[i], t, acc[p][ab]);
-      }
+    for (int i = 0; i < 16; i++) {
+      const double t = *(const double*)(T + byte_x128(ww[i >> 2], i & 3));
+      acc[u] = fma(yv[i], t, acc[u]);
     }
   }
 }
 
-// partial: [gridDim.x][LMM_MAX_PAIRS * 32]
-template <int NP, bool HALF>
+// partial: [gridDim.x][LMM_PART]
+template <int NU>
 __device__ __forceinline__ void lmm_vec_body(const LmmChunk& ch, const uint8_t* __restrict__ imaps, int64_t nRB,
                                              const double* __restrict__ tablesImg, const double* __restrict__ y,
                                              int nRows, int64_t stepBegin, int64_t stepEnd,
@@ -299,25 +295,24 @@ __device__ __forceinline__ void lmm_vec_body(const LmmChunk& ch, const uint8_t* 
     // the tables never arrived: flag it, and make the failure visible in the result as well (the final kernel sums
     // this row whatever happens, and a device-buffer caller only sees the error word at its next cla_stats_get)
     if (tid == 0) atomicExch(err, 101);
-    for (int u = tid; u < NP * 32; u += LMM_T) partial[(size_t)blockIdx.x * (LMM_MAX_PAIRS * 32) + u] = __longlong_as_double(0x7ff8000000000000ll);
+    for (int u = tid; u < NU * 16; u += LMM_T) partial[(size_t)blockIdx.x * LMM_PART + u] = __longlong_as_double(0x7ff8000000000000ll);
     return;
   }
-  // table base of each slab for this lane (slot offset folded in), and this lane's map pointers
-  const unsigned char* tbase[NP];
-  const uint8_t* mp[NP][2];
+  // table base of each unit for this lane (slot offset folded in), and this lane's map pointers
+  const unsigned char* tbase[NU];
+  const uint8_t* mp[NU];
   {
     size_t off = 0;
 #pragma unroll
-    for (int p = 0; p < NP; p++) {
-      tbase[p] = smraw + off + slot * 8;
-      off += (size_t)ch.nk[p] * 256;
-      mp[p][0] = imaps + (size_t)((ch.pair0 + p) * 2 + 0) * nRB * 256 + slot * 16;
-      mp[p][1] = imaps + (size_t)((ch.pair0 + p) * 2 + 1) * nRB * 256 + slot * 16;
+    for (int u = 0; u < NU; u++) {
+      tbase[u] = smraw + off + slot * 8;
+      off += (size_t)ch.nk[u] * 128;
+      mp[u] = imaps + (size_t)(ch.unit0 + u) * nRB * 256 + slot * 16;
     }
   }
-  double acc[NP][2];
+  double acc[NU];
 #pragma unroll
-  for (int p = 0; p < NP; p++) acc[p][0] = acc[p][1] = 0.0;
+  for (int u = 0; u < NU; u++) acc[u] = 0.0;
 
   // rows of this CTA: contiguous range of 64-row steps
   const int ctaInChunk = blockIdx.x - ch.cta0;
@@ -326,16 +321,13 @@ __device__ __forceinline__ void lmm_vec_body(const LmmChunk& ch, const uint8_t* 
   for (int64_t st = s0 + warp; st < s1; st += LMM_W) {
     const int64_t r0 = st * LMM_STEP + half * 32;
     if (st * LMM_STEP + LMM_STEP <= nRows) {
-      uint4 m[NP][2][2];
+      uint4 m[NU][2];
 #pragma unroll
-      for (int p = 0; p < NP; p++)
-#pragma unroll
-        for (int ab = 0; ab < 2; ab++) {
-          if (HALF && p == NP - 1 && ab == 1) continue;
-          const uint8_t* src = mp[p][ab] + (r0 >> 4) * 256;
-          m[p][ab][0] = __ldg((const uint4*)src);
-          m[p][ab][1] = __ldg((const uint4*)(src + 256));
-        }
+      for (int u = 0; u < NU; u++) {
+        const uint8_t* src = mp[u] + (r0 >> 4) * 256;
+        m[u][0] = __ldg((const uint4*)src);
+        m[u][1] = __ldg((const uint4*)(src + 256));
+      }
 #pragma unroll
       for (int sub = 0; sub < 2; sub++) {
         double yv[16];
@@ -346,38 +338,31 @@ __device__ __forceinline__ void lmm_vec_body(const LmmChunk& ch, const uint8_t* 
           yv[2 * i] = t.x;
           yv[2 * i + 1] = t.y;
         }
-        lmm_cells<NP, HALF>(m, sub, yv, tbase, acc);
+        lmm_cells<NU>(m, sub, yv, tbase, acc);
       }
     } else {  // ragged last step
       for (int64_t r = r0; r < min((int64_t)nRows, r0 + 32); r++) {
         const double yy = y[r];
 #pragma unroll
-        for (int p = 0; p < NP; p++)
-#pragma unroll
-          for (int ab = 0; ab < 2; ab++) {
-            if (HALF && p == NP - 1 && ab == 1) continue;
-            acc[p][ab] = fma(yy, *(const double*)(tbase[p] + ab * 128 + 256 * (int)mp[p][ab][(r >> 4) * 256 + (r & 15)]),
-                             acc[p][ab]);
-          }
+        for (int u = 0; u < NU; u++)
+          acc[u] = fma(yy, *(const double*)(tbase[u] + 128 * (int)mp[u][(r >> 4) * 256 + (r & 15)]), acc[u]);
       }
     }
   }
   // combine the two half-warps (same column slots, different rows), then the warps through shared memory
   __syncthreads();  // tables no longer needed
-  double* red = (double*)smraw;  // [LMM_W][NP*32]
+  double* red = (double*)smraw;  // [LMM_W][NU*16]
 #pragma unroll
-  for (int p = 0; p < NP; p++)
-#pragma unroll
-    for (int ab = 0; ab < 2; ab++) {
-      double a = acc[p][ab];
-      a += __shfl_xor_sync(0xffffffffu, a, 16);
-      if (half == 0) red[warp * (NP * 32) + p * 32 + ab * 16 + slot] = a;
-    }
+  for (int u = 0; u < NU; u++) {
+    double a = acc[u];
+    a += __shfl_xor_sync(0xffffffffu, a, 16);
+    if (half == 0) red[warp * (NU * 16) + u * 16 + slot] = a;
+  }
   __syncthreads();
-  for (int u = tid; u < NP * 32; u += LMM_T) {
+  for (int u = tid; u < NU * 16; u += LMM_T) {
     double s = 0;
-    for (int w = 0; w < LMM_W; w++) s += red[w * (NP * 32) + u];
-    partial[(size_t)blockIdx.x * (LMM_MAX_PAIRS * 32) + u] = s;
+    for (int w = 0; w < LMM_W; w++) s += red[w * (NU * 16) + u];
+    partial[(size_t)blockIdx.x * LMM_PART + u] = s;
   }
 }
 
@@ -394,14 +379,12 @@ k_lmm_vec_u8(const LmmChunk* __restrict__ chunks, int nChunks, const uint8_t* __
     ch = chunks[c];
   }
   __syncthreads();
-  switch (ch.nPairs * 2 + (ch.halfLast ? 1 : 0)) {
-    case 2: lmm_vec_body<1, false>(ch, imaps, nRB, tablesImg, y, nRows, stepBegin, stepEnd, partial, smraw, &mbar, err); break;
-    case 3: lmm_vec_body<1, true>(ch, imaps, nRB, tablesImg, y, nRows, stepBegin, stepEnd, partial, smraw, &mbar, err); break;
-    case 4: lmm_vec_body<2, false>(ch, imaps, nRB, tablesImg, y, nRows, stepBegin, stepEnd, partial, smraw, &mbar, err); break;
-    case 5: lmm_vec_body<2, true>(ch, imaps, nRB, tablesImg, y, nRows, stepBegin, stepEnd, partial, smraw, &mbar, err); break;
-    case 6: lmm_vec_body<3, false>(ch, imaps, nRB, tablesImg, y, nRows, stepBegin, stepEnd, partial, smraw, &mbar, err); break;
-    default: lmm_vec_body<3, true>(ch, imaps, nRB, tablesImg, y, nRows, stepBegin, stepEnd, partial, smraw, &mbar, err); break;
+#define LMM_CASE(N) case N: lmm_vec_body<N>(ch, imaps, nRB, tablesImg, y, nRows, stepBegin, stepEnd, partial, smraw, &mbar, err); break;
+  switch (ch.nUnits) {
+    LMM_CASE(1) LMM_CASE(2) LMM_CASE(3) LMM_CASE(4) LMM_CASE(5) LMM_CASE(6)
+    default: lmm_vec_body<7>(ch, imaps, nRB, tablesImg, y, nRows, stepBegin, stepEnd, partial, smraw, &mbar, err); break;
   }
+#undef LMM_CASE
 }
 
 // out[col] += sum over the chunk's CTAs of partial[cta][slot], in CTA order (deterministic per column)
@@ -410,13 +393,13 @@ __global__ void k_lmm_vec_final(const LmmChunk* __restrict__ chunks, int nChunks
   const int c = blockIdx.x;
   if (c >= nChunks) return;
   const LmmChunk ch = chunks[c];
-  for (int u = threadIdx.x; u < ch.nPairs * 32; u += blockDim.x) {
-    const int col = slotCol[ch.pair0 * 32 + u];
+  for (int u = threadIdx.x; u < ch.nUnits * 16; u += blockDim.x) {
+    const int col = slotCol[ch.unit0 * 16 + u];
     if (col < 0) continue;
     double s = 0;
     for (int part = 0; part < nParts; part++)  // row ranges that were launched separately, in row order
       for (int b = 0; b < ch.nCta; b++)
-        s += partial[((size_t)part * gridPerPart + ch.cta0 + b) * (LMM_MAX_PAIRS * 32) + u];
+        s += partial[((size_t)part * gridPerPart + ch.cta0 + b) * LMM_PART + u];
     atomicAdd(&out[col], s);
   }
 }
@@ -434,60 +417,55 @@ __global__ void k_rmm_b_tables(const LmmChunk* __restrict__ chunks, const int* _
                                const double* __restrict__ T, const double* __restrict__ v, double* __restrict__ P) {
   const LmmChunk ch = chunks[blockIdx.x];
   int base = 0;
-  for (int p = 0; p < ch.nPairs; p++) {
-    const int n = ch.nk[p] * 32;
+  for (int u = 0; u < ch.nUnits; u++) {
+    const int n = ch.nk[u] * 16;
     for (int e = threadIdx.x; e < n; e += blockDim.x) {
-      const int col = slotCol[(ch.pair0 + p) * 32 + (e & 31)];
+      const int col = slotCol[(ch.unit0 + u) * 16 + (e & 15)];
       P[ch.tblOff + base + e] = col >= 0 ? T[ch.tblOff + base + e] * v[col] : 0.0;
     }
     base += n;
   }
 }
 
-template <int NP>
+template <int NU>
 __device__ __forceinline__ void rmm_b_chunk(const LmmChunk& ch, const uint8_t* __restrict__ imaps, int64_t nRB,
                                             int64_t s0, int64_t s1, int nRows, double init, bool first,
                                             double* __restrict__ out, const unsigned char* smraw) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int slot = lane & 15, half = lane >> 4;
-  const unsigned char* tbase[NP];
-  const uint8_t* mp[NP][2];
+  const unsigned char* tbase[NU];
+  const uint8_t* mp[NU];
   {
     size_t off = 0;
 #pragma unroll
-    for (int p = 0; p < NP; p++) {
-      tbase[p] = smraw + off + slot * 8;
-      off += (size_t)ch.nk[p] * 256;
-      mp[p][0] = imaps + (size_t)((ch.pair0 + p) * 2 + 0) * nRB * 256 + slot * 16;
-      mp[p][1] = imaps + (size_t)((ch.pair0 + p) * 2 + 1) * nRB * 256 + slot * 16;
+    for (int u = 0; u < NU; u++) {
+      tbase[u] = smraw + off + slot * 8;
+      off += (size_t)ch.nk[u] * 128;
+      mp[u] = imaps + (size_t)(ch.unit0 + u) * nRB * 256 + slot * 16;
     }
   }
   for (int64_t st = s0 + warp; st < s1; st += LMM_W) {
     const int64_t r0 = st * LMM_STEP + half * 32;
-    uint4 m[NP][2][2];
+    uint4 m[NU][2];
 #pragma unroll
-    for (int p = 0; p < NP; p++)
-#pragma unroll
-      for (int ab = 0; ab < 2; ab++) {
-        const uint8_t* src = mp[p][ab] + (r0 >> 4) * 256;
-        m[p][ab][0] = __ldg((const uint4*)src);
-        m[p][ab][1] = __ldg((const uint4*)(src + 256));
-      }
+    for (int u = 0; u < NU; u++) {
+      const uint8_t* src = mp[u] + (r0 >> 4) * 256;
+      m[u][0] = __ldg((const uint4*)src);
+      m[u][1] = __ldg((const uint4*)(src + 256));
+    }
 #pragma unroll
     for (int sub = 0; sub < 2; sub++) {
       double acc[16];
 #pragma unroll
       for (int i = 0; i < 16; i++) acc[i] = 0.0;
 #pragma unroll
-      for (int p = 0; p < NP; p++)
+      for (int u = 0; u < NU; u++) {
+        const uint4 w = m[u][sub];
+        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+        const unsigned char* T = tbase[u];
 #pragma unroll
-        for (int ab = 0; ab < 2; ab++) {
-          const uint4 w = m[p][ab][sub];
-          const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-          const unsigned char* T = tbase[p] + ab * 128;
-#pragma unroll
-          for (int i = 0; i < 16; i++) acc[i] += *(const double*)(T + byte_x256(ww[i >> 2], i & 3));
-        }
+        for (int i = 0; i < 16; i++) acc[i] += *(const double*)(T + byte_x128(ww[i >> 2], i & 3));
+      }
       // reduce-scatter over the half-warp: after the stage with distance d, a lane keeps the rows whose bit d
       // equals its own slot bit
 #pragma unroll
@@ -525,11 +503,12 @@ k_rmm_vec_b(const LmmChunk* __restrict__ chunks, int nChunks, const uint8_t* __r
       if (threadIdx.x == 0) atomicExch(err, 102);
       return;
     }
-    switch (ch.nPairs) {
-      case 1: rmm_b_chunk<1>(ch, imaps, nRB, s0, s1, nRows, init, c == 0, out, smraw); break;
-      case 2: rmm_b_chunk<2>(ch, imaps, nRB, s0, s1, nRows, init, c == 0, out, smraw); break;
-      default: rmm_b_chunk<3>(ch, imaps, nRB, s0, s1, nRows, init, c == 0, out, smraw); break;
+#define RB_CASE(N) case N: rmm_b_chunk<N>(ch, imaps, nRB, s0, s1, nRows, init, c == 0, out, smraw); break;
+    switch (ch.nUnits) {
+      RB_CASE(1) RB_CASE(2) RB_CASE(3) RB_CASE(4) RB_CASE(5) RB_CASE(6)
+      default: rmm_b_chunk<7>(ch, imaps, nRB, s0, s1, nRows, init, c == 0, out, smraw); break;
     }
+#undef RB_CASE
   }
 }
 
@@ -545,11 +524,11 @@ __global__ void k_rmm_f_tables(const DevGroup* __restrict__ groups, const LmmChu
                                double* __restrict__ P) {
   const LmmChunk ch = chunks[blockIdx.x];
   int base = 0;
-  for (int p = 0; p < ch.nPairs; p++) {
-    const int n = ch.nk[p] * 32;
+  for (int q = 0; q < ch.nUnits; q++) {
+    const int n = ch.nk[q] * 16;
     for (int e = threadIdx.x; e < n; e += blockDim.x) {
-      const FusedUnit u = units[(ch.pair0 + p) * 32 + (e & 31)];
-      const int k = e >> 5;
+      const FusedUnit u = units[(ch.unit0 + q) * 16 + (e & 15)];
+      const int k = e >> 4;
       double val = 0.0;
       if (u.ga >= 0) {
         const int a = k >> u.sh, b = k & ((1 << u.sh) - 1);
@@ -570,56 +549,49 @@ __global__ void k_rmm_f_tables(const DevGroup* __restrict__ groups, const LmmChu
   }
 }
 
-template <int NP>
+template <int NU>
 __device__ __forceinline__ void rmm_f_chunk(const LmmChunk& ch, const FusedUnit* __restrict__ units,
                                             const uint8_t* __restrict__ fmaps, int64_t nRB, int64_t s0, int64_t s1,
                                             int nRows, double init, bool first, double* __restrict__ out,
                                             const unsigned char* smraw) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int slot = lane & 15, half = lane >> 4;
-  const unsigned char* tbase[NP];
-  const uint8_t* mp[NP][2];
-  uint32_t mul[NP][2];  // 1 << sh of this lane's slot
+  const unsigned char* tbase[NU];
+  const uint8_t* mp[NU];
+  uint32_t mul[NU];  // 1 << sh of this lane's slot
   {
     size_t off = 0;
 #pragma unroll
-    for (int p = 0; p < NP; p++) {
-      tbase[p] = smraw + off + slot * 8;
-      off += (size_t)ch.nk[p] * 256;
-#pragma unroll
-      for (int ab = 0; ab < 2; ab++) {
-        mp[p][ab] = fmaps + (size_t)((ch.pair0 + p) * 2 + ab) * nRB * 512 + slot * 32;
-        mul[p][ab] = 1u << units[(ch.pair0 + p) * 32 + ab * 16 + slot].sh;
-      }
+    for (int u = 0; u < NU; u++) {
+      tbase[u] = smraw + off + slot * 8;
+      off += (size_t)ch.nk[u] * 128;
+      mp[u] = fmaps + (size_t)(ch.unit0 + u) * nRB * 512 + slot * 32;
+      mul[u] = 1u << units[(ch.unit0 + u) * 16 + slot].sh;
     }
   }
   for (int64_t st = s0 + warp; st < s1; st += LMM_W) {
     const int64_t r0 = st * LMM_STEP + half * 32;
 #pragma unroll
     for (int sub = 0; sub < 2; sub++) {
-      uint4 ma[NP][2], mb[NP][2];
+      uint4 ma[NU], mb[NU];
 #pragma unroll
-      for (int p = 0; p < NP; p++)
-#pragma unroll
-        for (int ab = 0; ab < 2; ab++) {
-          const uint8_t* src = mp[p][ab] + ((r0 >> 4) + sub) * 512;
-          ma[p][ab] = __ldg((const uint4*)src);
-          mb[p][ab] = __ldg((const uint4*)(src + 16));
-        }
+      for (int u = 0; u < NU; u++) {
+        const uint8_t* src = mp[u] + ((r0 >> 4) + sub) * 512;
+        ma[u] = __ldg((const uint4*)src);
+        mb[u] = __ldg((const uint4*)(src + 16));
+      }
       double acc[16];
 #pragma unroll
       for (int i = 0; i < 16; i++) acc[i] = 0.0;
 #pragma unroll
-      for (int p = 0; p < NP; p++)
+      for (int u = 0; u < NU; u++) {
+        // ids stay below 256 after the shift, so the four bytes of a word never carry into each other
+        const uint32_t ww[4] = {ma[u].x * mul[u] + mb[u].x, ma[u].y * mul[u] + mb[u].y, ma[u].z * mul[u] + mb[u].z,
+                                ma[u].w * mul[u] + mb[u].w};
+        const unsigned char* T = tbase[u];
 #pragma unroll
-        for (int ab = 0; ab < 2; ab++) {
-          // ids stay below 256 after the shift, so the four bytes of a word never carry into each other
-          const uint32_t ww[4] = {ma[p][ab].x * mul[p][ab] + mb[p][ab].x, ma[p][ab].y * mul[p][ab] + mb[p][ab].y,
-                                  ma[p][ab].z * mul[p][ab] + mb[p][ab].z, ma[p][ab].w * mul[p][ab] + mb[p][ab].w};
-          const unsigned char* T = tbase[p] + ab * 128;
-#pragma unroll
-          for (int i = 0; i < 16; i++) acc[i] += *(const double*)(T + byte_x256(ww[i >> 2], i & 3));
-        }
+        for (int i = 0; i < 16; i++) acc[i] += *(const double*)(T + byte_x128(ww[i >> 2], i & 3));
+      }
 #pragma unroll
       for (int d = 8; d >= 1; d >>= 1) {
         const bool up = (slot & d) != 0;
@@ -655,8 +627,12 @@ k_rmm_vec_f(const LmmChunk* __restrict__ chunks, int nChunks, const FusedUnit* _
       if (threadIdx.x == 0) atomicExch(err, 103);
       return;
     }
-    if (ch.nPairs == 1) rmm_f_chunk<1>(ch, units, fmaps, nRB, s0, s1, nRows, init, c == 0, out, smraw);
-    else rmm_f_chunk<2>(ch, units, fmaps, nRB, s0, s1, nRows, init, c == 0, out, smraw);
+    switch (ch.nUnits) {
+      case 1: rmm_f_chunk<1>(ch, units, fmaps, nRB, s0, s1, nRows, init, c == 0, out, smraw); break;
+      case 2: rmm_f_chunk<2>(ch, units, fmaps, nRB, s0, s1, nRows, init, c == 0, out, smraw); break;
+      case 3: rmm_f_chunk<3>(ch, units, fmaps, nRB, s0, s1, nRows, init, c == 0, out, smraw); break;
+      default: rmm_f_chunk<4>(ch, units, fmaps, nRB, s0, s1, nRows, init, c == 0, out, smraw); break;
+    }
   }
 }
 
@@ -814,63 +790,62 @@ int64_t fast_plan_build(Matrix* m) {
   if ((rc = plan_upload(fp, groupOf, &fp->dGroupOf)) < 0) return rc;
   if ((rc = plan_upload(fp, imgOff, &fp->dImgOff)) < 0) return rc;
 
-  // ---- LMM: one unit per (group, column); units ordered by table depth; 32 per slab ----
+  // ---- LMM: one column slot per (group, column), ordered by table depth; 16 slots per unit ----
   struct Unit { int g, j, nv; };
   std::vector<Unit> units;
   for (int gi = 0; gi < nG; gi++)
     for (int j = 0; j < G[gi].gCols; j++) units.push_back({gi, j, G[gi].nVals});
   std::stable_sort(units.begin(), units.end(), [](const Unit& a, const Unit& b) { return a.nv > b.nv; });
   fp->nUnits = (int)units.size();
-  const int nPairs = (fp->nUnits + 31) / 32;
-  fp->nSlots = nPairs * 32;
-  // unused slots of the last slab read the map of the last unit (its ids stay inside the slab's table depth)
+  const int nU16 = (fp->nUnits + 15) / 16;
+  fp->nSlots = nU16 * 16;
+  // unused slots of the last unit read the map of the last column (its ids stay inside the unit's table depth)
   std::vector<const uint8_t*> slotMap(fp->nSlots, gmap[units.back().g]);
   std::vector<int> slotCol(fp->nSlots, -1);
-  std::vector<int> pairNk(nPairs, 1);
+  std::vector<int> unitNk(nU16, 1);
   // host copies of the dictionaries
   std::vector<std::vector<double>> dicts(nG);
   for (int gi = 0; gi < nG; gi++) {
     dicts[gi].resize((size_t)G[gi].nVals * G[gi].gCols);
     CLA_CUDA(cudaMemcpy(dicts[gi].data(), G[gi].dict, dicts[gi].size() * 8, cudaMemcpyDeviceToHost));
   }
-  for (int u = 0; u < fp->nUnits; u++) pairNk[u / 32] = std::max(pairNk[u / 32], units[u].nv);
-  // chunks: greedily pack slabs up to the shared-memory budget and LMM_MAX_PAIRS
-  const size_t redBytes = (size_t)LMM_W * LMM_MAX_PAIRS * 32 * 8;
+  for (int u = 0; u < fp->nUnits; u++) unitNk[u / 16] = std::max(unitNk[u / 16], units[u].nv);
+  // chunks: greedily pack units up to the shared-memory budget and LMM_MAX_UNITS
+  const size_t redBytes = (size_t)LMM_W * LMM_PART * 8;
   const size_t lmmBudget = SMEM_MAX - 2048;
   std::vector<double> image;
   LmmChunk lc{};
-  lc.pair0 = 0;
+  lc.unit0 = 0;
   auto flush = [&]() {
     lc.tblDoubles = 0;
-    for (int p = 0; p < lc.nPairs; p++) lc.tblDoubles += lc.nk[p] * 32;
+    for (int q = 0; q < lc.nUnits; q++) lc.tblDoubles += lc.nk[q] * 16;
     lc.tblOff = (int64_t)image.size();
     image.resize(image.size() + lc.tblDoubles, 0.0);
     size_t off = lc.tblOff;
-    for (int p = 0; p < lc.nPairs; p++) {
-      for (int s = 0; s < 32; s++) {
-        const int u = (lc.pair0 + p) * 32 + s;
+    for (int q = 0; q < lc.nUnits; q++) {
+      for (int s = 0; s < 16; s++) {
+        const int u = (lc.unit0 + q) * 16 + s;
         if (u >= fp->nUnits) continue;
         const Unit& un = units[u];
         const int gc = G[un.g].gCols;
-        for (int k = 0; k < un.nv; k++) image[off + (size_t)k * 32 + s] = dicts[un.g][(size_t)k * gc + un.j];
+        for (int k = 0; k < un.nv; k++) image[off + (size_t)k * 16 + s] = dicts[un.g][(size_t)k * gc + un.j];
       }
-      off += (size_t)lc.nk[p] * 32;
+      off += (size_t)lc.nk[q] * 16;
     }
-    lc.halfLast = ((lc.pair0 + lc.nPairs) * 32 - fp->nUnits >= 16) ? 1 : 0;  // only the very last slab can be half empty
     fp->lchunks.push_back(lc);
   };
   size_t curBytes = 0;
-  lc.nPairs = 0;
-  for (int p = 0; p < nPairs; p++) {
-    const size_t b = (size_t)pairNk[p] * 256;
-    if (lc.nPairs == LMM_MAX_PAIRS || (lc.nPairs > 0 && std::max(curBytes + b, redBytes) > lmmBudget)) {
+  lc.nUnits = 0;
+  for (int q = 0; q < nU16; q++) {
+    const size_t b = (size_t)unitNk[q] * 128;
+    if (lc.nUnits == LMM_MAX_UNITS || (lc.nUnits > 0 && std::max(curBytes + b, redBytes) > lmmBudget)) {
       flush();
       lc = LmmChunk{};
-      lc.pair0 = p;
-      lc.nPairs = 0;
+      lc.unit0 = q;
+      lc.nUnits = 0;
       curBytes = 0;
     }
-    lc.nk[lc.nPairs++] = pairNk[p];
+    lc.nk[lc.nUnits++] = unitNk[q];
     curBytes += b;
   }
   flush();
@@ -878,7 +853,7 @@ int64_t fast_plan_build(Matrix* m) {
     slotMap[u] = gmap[units[u].g];
     slotCol[u] = 0;  // filled below from the device column lists
   }
-  {  // output column of every unit
+  {  // output column of every slot
     for (int gi = 0; gi < nG; gi++) {
       std::vector<int32_t> cols(G[gi].gCols);
       CLA_CUDA(cudaMemcpy(cols.data(), G[gi].cols, cols.size() * 4, cudaMemcpyDeviceToHost));
@@ -887,11 +862,11 @@ int64_t fast_plan_build(Matrix* m) {
     }
   }
   // CTAs per chunk in proportion to its cost, one CTA per SM in total. Cost per 64-row warp step in
-  // L1 data-pipe wavefronts: 128 per slab for the dictionary reads, 16 per slab for the map loads and
-  // 64 for the left vector (which does not depend on the number of slabs).
+  // L1 data-pipe wavefronts: 64 per unit for the dictionary reads, 8 per unit for the map loads and
+  // 64 for the left vector (which does not depend on the number of units).
   const int totalCta = std::max(m->smCount, (int)fp->lchunks.size());
   double totalCost = 0;
-  auto chunkCost = [](const LmmChunk& c) { return 144.0 * (c.nPairs - 0.5 * c.halfLast) + 64.0; };
+  auto chunkCost = [](const LmmChunk& c) { return 72.0 * c.nUnits + 64.0; };
   for (auto& c : fp->lchunks) totalCost += chunkCost(c);
   int cta = 0;
   const int64_t nSteps = ((int64_t)m->nRows + LMM_STEP - 1) / LMM_STEP;
@@ -962,39 +937,39 @@ int64_t fast_plan_build(Matrix* m) {
     if (paired * 2 >= nG && !fp->partial) {
       std::stable_sort(fu.begin(), fu.end(), [](const FusedUnit& x, const FusedUnit& y) { return (x.nva << x.sh) > (y.nva << y.sh); });
       fp->nFused = (int)fu.size();
-      const int nPairsF = (fp->nFused + 31) / 32;
-      const int nSlotsF = nPairsF * 32;
+      const int nU16F = (fp->nFused + 15) / 16;
+      const int nSlotsF = nU16F * 16;
       std::vector<const uint8_t*> mapA(nSlotsF, nullptr), mapB(nSlotsF, nullptr);
       std::vector<FusedUnit> units(nSlotsF, FusedUnit{-1, -1, 0, 1, 1});
-      std::vector<int> nk(nPairsF, 1);
+      std::vector<int> nk(nU16F, 1);
       for (int u = 0; u < fp->nFused; u++) {
         mapA[u] = gmap[fu[u].ga];
         mapB[u] = fu[u].gb >= 0 ? gmap[fu[u].gb] : nullptr;
         units[u] = FusedUnit{selIdx[fu[u].ga], fu[u].gb >= 0 ? selIdx[fu[u].gb] : -1, fu[u].sh, fu[u].nva, fu[u].nvb};
-        nk[u / 32] = std::max(nk[u / 32], fu[u].nva << fu[u].sh);
+        nk[u / 16] = std::max(nk[u / 16], fu[u].nva << fu[u].sh);
       }
       LmmChunk fc{};
       int64_t img = 0;
       size_t cur = 0;
       auto flushF = [&]() {
         fc.tblDoubles = 0;
-        for (int p = 0; p < fc.nPairs; p++) fc.tblDoubles += fc.nk[p] * 32;
+        for (int q = 0; q < fc.nUnits; q++) fc.tblDoubles += fc.nk[q] * 16;
         fc.tblOff = img;
         img += fc.tblDoubles;
         fp->fchunks.push_back(fc);
       };
-      fc.pair0 = 0;
-      fc.nPairs = 0;
-      for (int p = 0; p < nPairsF; p++) {
-        const size_t b = (size_t)nk[p] * 256;
-        if (fc.nPairs == 2 || (fc.nPairs > 0 && cur + b > (size_t)SMEM_MAX - 2048)) {
+      fc.unit0 = 0;
+      fc.nUnits = 0;
+      for (int q = 0; q < nU16F; q++) {
+        const size_t b = (size_t)nk[q] * 128;
+        if (fc.nUnits == 4 || (fc.nUnits > 0 && cur + b > (size_t)SMEM_MAX - 2048)) {
           flushF();
           fc = LmmChunk{};
-          fc.pair0 = p;
-          fc.nPairs = 0;
+          fc.unit0 = q;
+          fc.nUnits = 0;
           cur = 0;
         }
-        fc.nk[fc.nPairs++] = nk[p];
+        fc.nk[fc.nUnits++] = nk[q];
         cur += b;
       }
       flushF();
@@ -1145,11 +1120,11 @@ int64_t fast_lmm_vec(Matrix* m, const double* dY, double* dOut, cudaStream_t s) 
   FastPlan* fp = m->fast;
   if (!fp || !fp->ok || ((uintptr_t)dY & 15)) return 0;  // 128-bit loads of the left vector need alignment
   int64_t rc;
-  const size_t partBytes = (size_t)fp->lmmGrid * LMM_MAX_PAIRS * 32 * 8;
+  const size_t partBytes = (size_t)fp->lmmGrid * LMM_PART * 8;
   if ((rc = ensure_scratch(m, partBytes + 256)) < 0) return rc;
   double* partial = (double*)m->scratch;
   CLA_CUDA(cudaMemsetAsync(dOut, 0, sizeof(double) * (size_t)m->nCols, s));
-  size_t smem = (size_t)LMM_W * LMM_MAX_PAIRS * 32 * 8;
+  size_t smem = (size_t)LMM_W * LMM_PART * 8;
   for (auto& c : fp->lchunks) smem = std::max(smem, (size_t)c.tblDoubles * 8);
   prof_begin(m, s);
   const int64_t nSteps = ((int64_t)m->nRows + LMM_STEP - 1) / LMM_STEP;
@@ -1174,7 +1149,7 @@ int64_t fast_lmm_vec_host(Matrix* m, const double* hostY, double* dY, double* dO
   FastPlan* fp = m->fast;
   if (!fp || !fp->ok || fp->partial || ((uintptr_t)dY & 15) || m->nRows < (1 << 20)) return 0;
   int64_t rc;
-  const size_t partBytes = (size_t)LMM_PIPE * fp->lmmGrid * LMM_MAX_PAIRS * 32 * 8;
+  const size_t partBytes = (size_t)LMM_PIPE * fp->lmmGrid * LMM_PART * 8;
   if ((rc = ensure_scratch(m, partBytes + 256)) < 0) return rc;
   if (!m->copyStream) {
     CLA_CUDA(cudaStreamCreateWithFlags(&m->copyStream, cudaStreamNonBlocking));
@@ -1182,7 +1157,7 @@ int64_t fast_lmm_vec_host(Matrix* m, const double* hostY, double* dY, double* dO
   }
   double* partial = (double*)m->scratch;
   CLA_CUDA(cudaMemsetAsync(dOut, 0, sizeof(double) * (size_t)m->nCols, s));
-  size_t smem = (size_t)LMM_W * LMM_MAX_PAIRS * 32 * 8;
+  size_t smem = (size_t)LMM_W * LMM_PART * 8;
   for (auto& c : fp->lchunks) smem = std::max(smem, (size_t)c.tblDoubles * 8);
   const int64_t nSteps = ((int64_t)m->nRows + LMM_STEP - 1) / LMM_STEP;
   // the copy stream must not run ahead of work already queued on s that still reads dY
@@ -1196,7 +1171,7 @@ int64_t fast_lmm_vec_host(Matrix* m, const double* hostY, double* dY, double* dO
     CLA_CUDA(cudaStreamWaitEvent(s, m->copyDone[i], 0));
     if (i == 0) prof_begin(m, s);
     k_lmm_vec_u8<<<fp->lmmGrid, LMM_T, smem, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dLmmMaps, fp->nRB, fp->dLmmTables,
-                                                 dY, m->nRows, sb, se, partial + (size_t)i * fp->lmmGrid * LMM_MAX_PAIRS * 32,
+                                                 dY, m->nRows, sb, se, partial + (size_t)i * fp->lmmGrid * LMM_PART,
                                                  m->dErr);
     if (i == LMM_PIPE - 1) prof_end(m, s);
     m->stats.kernel_launches++;
@@ -1217,10 +1192,10 @@ int64_t fast_lmm_vec_host(Matrix* m, const double* hostY, double* dY, double* dO
 // its own memory pool (SystemDS's GPU memory manager works that way), or a service loop that must not hit
 // cudaMalloc because the driver synchronises the device inside it. For them the per-CTA partial sums and the
 // row sum of the left vector live in this fixed array instead of the handle's growable scratch. Every GPU
-// whose context loads the library holds the array (about 385 KB) until the process exits.
+// whose context loads the library holds the array (about 450 KB) until the process exits.
 // --------------------------------------------------------------------------------------------------
 constexpr int NOALLOC_MAX_CTAS = 512;  // partial-sum rows available; one CTA per SM is launched, more only with > 148 column chunks
-constexpr size_t NOALLOC_PARTIAL_DOUBLES = (size_t)NOALLOC_MAX_CTAS * LMM_MAX_PAIRS * 32;
+constexpr size_t NOALLOC_PARTIAL_DOUBLES = (size_t)NOALLOC_MAX_CTAS * LMM_PART;
 static __device__ __align__(256) double g_noalloc_scratch[NOALLOC_PARTIAL_DOUBLES + 32];
 
 static std::mutex g_noallocMu;
@@ -1257,7 +1232,7 @@ int64_t fast_lmm_vec_noalloc(Matrix* m, const double* dY, double* dOut, cudaStre
   double* partial = scratch;                           // fully rewritten by every launch
   double* rowSum = scratch + NOALLOC_PARTIAL_DOUBLES;  // accumulated with atomics: cleared below before use
   CLA_CUDA(cudaMemsetAsync(dOut, 0, sizeof(double) * (size_t)m->nCols, s));
-  size_t smem = (size_t)LMM_W * LMM_MAX_PAIRS * 32 * 8;
+  size_t smem = (size_t)LMM_W * LMM_PART * 8;
   for (auto& c : fp->lchunks) smem = std::max(smem, (size_t)c.tblDoubles * 8);
   const int64_t nSteps = ((int64_t)m->nRows + LMM_STEP - 1) / LMM_STEP;
   k_lmm_vec_u8<<<fp->lmmGrid, LMM_T, smem, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dLmmMaps, fp->nRB, fp->dLmmTables,

@@ -317,6 +317,14 @@ int64_t launch_group_counts(Matrix* m, int gi, unsigned long long* dCounts, cuda
   return CLA_OK;
 }
 
+// ids of a map registered from device memory must stay below nVals (host-registered maps are checked on the host)
+__global__ void k_check_ids(int mapType, const void* __restrict__ map, int64_t n, int nVals, int32_t* err) {
+  bool bad = false;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    bad |= map_get(mapType, map, nullptr, i) >= nVals;
+  if (bad) atomicExch(err, 3);
+}
+
 // ------------------------------------------------------------------------------------------------
 // upload
 // ------------------------------------------------------------------------------------------------
@@ -460,7 +468,19 @@ int64_t finalize_device(Matrix* m) {
         if ((rc = upload(m, hg.dict.data(), hg.dict.size(), &g.dictRaw, true)) < 0) return rc;
     }
 
-    if (hg.type == GT_DDC || hg.type == GT_SDC) {
+    if (hg.type == GT_DDC && hg.devMap) {  // registered from device memory: copy, then check the ids on the device
+      size_t hiB;
+      const size_t mb = map_bytes(hg.mapType, hg.mapSize, &hiB);
+      uint8_t* dm = nullptr;
+      if ((rc = dev_alloc(m, mb, &dm)) < 0) return rc;
+      m->indexBytes += mb;
+      if (hg.devSrcDevice == m->device || hg.devSrcDevice < 0)
+        CLA_CUDA(cudaMemcpyAsync(dm, hg.devMap, mb, cudaMemcpyDeviceToDevice, m->stream));
+      else
+        CLA_CUDA(cudaMemcpyPeerAsync(dm, m->device, hg.devMap, hg.devSrcDevice, mb, m->stream));
+      k_check_ids<<<grid_for(hg.mapSize, 256), 256, 0, m->stream>>>(hg.mapType, dm, hg.mapSize, hg.nVals, m->dErr);
+      g.map = dm;
+    } else if (hg.type == GT_DDC || hg.type == GT_SDC) {
       size_t hiB;
       const size_t mb = map_bytes(hg.mapType, hg.mapSize, &hiB);
       const uint8_t *dm = nullptr, *dh = nullptr;
@@ -561,7 +581,17 @@ int64_t finalize_device(Matrix* m) {
       g.mapSize = n;
       g.type = GT_DDC;
     }
-    if (hg.type == GT_UNC) {
+    if (hg.type == GT_UNC && hg.devDense) {
+      double* dd = nullptr;
+      const size_t n = (size_t)m->nRows * gc;
+      if ((rc = dev_alloc(m, n, &dd)) < 0) return rc;
+      m->indexBytes += n * sizeof(double);
+      if (hg.devSrcDevice == m->device || hg.devSrcDevice < 0)
+        CLA_CUDA(cudaMemcpyAsync(dd, hg.devDense, n * sizeof(double), cudaMemcpyDeviceToDevice, m->stream));
+      else
+        CLA_CUDA(cudaMemcpyPeerAsync(dd, m->device, hg.devDense, hg.devSrcDevice, n * sizeof(double), m->stream));
+      g.dense = dd;
+    } else if (hg.type == GT_UNC) {
       if ((rc = upload(m, hg.dense.data(), hg.dense.size(), &g.dense, true)) < 0) return rc;
     } else {
       g.valOff = valOff;
@@ -577,7 +607,13 @@ int64_t finalize_device(Matrix* m) {
   CLA_CUDA(cudaStreamSynchronize(m->stream));
   int32_t herr = 0;
   CLA_CUDA(cudaMemcpy(&herr, m->dErr, sizeof(herr), cudaMemcpyDeviceToHost));
-  if (herr) return fail(CLA_ERR_DEVICE_CHECK, herr == 1 ? "RLE run past the last row" : "OLE offset past the last row");
+  if (herr) {
+    cudaMemset(m->dErr, 0, sizeof(int32_t));
+    return fail(herr == 3 ? CLA_ERR_BAD_ARG : CLA_ERR_DEVICE_CHECK,
+                herr == 1 ? "RLE run past the last row"
+                          : (herr == 3 ? "device-resident map holds an id at or above the number of dictionary tuples"
+                                       : "OLE offset past the last row"));
+  }
   const DevGroup* dg = nullptr;
   int64_t rc;
   if ((rc = upload(m, m->groups.data(), m->groups.size(), &dg, false)) < 0) return rc;

@@ -73,6 +73,26 @@ class AMapToData:
         return f"MapTo{MAP_NAMES[self.type]}(size={self.size}, unique={self.unique})"
 
 
+class DeviceMap(AMapToData):
+    """A map whose cells already live in device memory, in the same storage layout (MapToBit words, bytes, u16 or
+    i32). ``dptr`` is the device address, ``owner`` whatever keeps that memory alive (a tensor). Registered with
+    ``cla_add_group_ddc_dev``; the native library copies it device to device when the block is finalized."""
+
+    def __init__(self, mtype: int, size: int, unique: int, dptr: int, nbytes: int, owner=None):
+        super().__init__(mtype, size, unique)
+        if mtype not in (MAP_BIT, MAP_UBYTE, MAP_BYTE, MAP_CHAR, MAP_INT):
+            raise ValueError("device-resident maps: MapToBit, MapToUByte, MapToByte, MapToChar or MapToInt")
+        self.dptr = int(dptr)
+        self._nbytes = int(nbytes)
+        self.owner = owner
+
+    def decode(self):
+        raise RuntimeError("a device-resident map has no host copy; decode it through cla_group_decode")
+
+    def nbytes(self) -> int:
+        return self._nbytes
+
+
 class MapToFactory:
     @staticmethod
     def type_for(size: int, unique: int) -> int:

@@ -45,6 +45,8 @@ SIGNATURES = {
     "cla_add_group_rle": [_I64, _P, _I32, _P, _I32, _P, _P, _I64],
     "cla_add_group_ole": [_I64, _P, _I32, _P, _I32, _P, _P, _I64],
     "cla_add_group_uncompressed": [_I64, _P, _I32, _P],
+    "cla_add_group_ddc_dev": [_I64, _P, _I32, _P, _I32, _I32, _P, _I64],
+    "cla_add_group_uncompressed_dev": [_I64, _P, _I32, _P],
     "cla_add_group_const": [_I64, _P, _I32, _P],
     "cla_add_group_empty": [_I64, _P, _I32],
     "cla_rmm": [_I64, _P, _I32, _I32, _P],

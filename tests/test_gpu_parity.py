@@ -506,9 +506,12 @@ def test_decompress_keeps_registered_values_under_a_large_default(single):
         groups.append(cg.sdc_from_row_ids([c], rng.standard_normal((card, 1)) * 1e-3, ids, np.array([1e6 + c])))
     cmb = CompressedMatrixBlock(nRows, 3, groups).to_device()
     assert np.array_equal(np.array(CLALibDecompress.decompress(cmb)), dense_of(cmb))
+    # the products see the same cells as (d - default) + default, like the reference after extractCommon: their
+    # error is relative to those two terms, not to the small cell
     v = rng.standard_normal(3)
     X = dense_of(cmb)
-    assert rel_err(CLALibRightMultBy.rightMultByMatrix(cmb, v).ravel(), X @ v, np.abs(X) @ np.abs(v)) < TOL
+    defs = np.array([1e6, 1e6 + 1, 1e6 + 2])
+    assert rel_err(CLALibRightMultBy.rightMultByMatrix(cmb, v).ravel(), X @ v, (np.abs(X - defs) + np.abs(defs)) @ np.abs(v)) < TOL
     cmb.free()
 
 
@@ -659,3 +662,48 @@ def test_sum_aggregates():
     assert rel_err(CLALibCompAgg.rowSums(cmb), X.sum(axis=1, keepdims=True), np.abs(X).sum(axis=1, keepdims=True) + 1e-300) < TOL
     assert abs(CLALibCompAgg.sum(cmb) - X.sum()) <= TOL * np.abs(X).sum()
     cmb.free()
+
+
+def test_groups_registered_from_device_memory(oracle):
+    """cla_add_group_ddc_dev / cla_add_group_uncompressed_dev: a block whose maps and dense values are handed over as
+    device buffers gives the same bits as the same block registered from host arrays, for every map class the call
+    takes; an id outside the dictionary is refused when the block is finalized."""
+    import torch
+    from systemds_b200.mapping import DeviceMap, MAP_BIT, MAP_BYTE, MAP_CHAR, MAP_INT, MAP_UBYTE
+    rng = np.random.default_rng(77)
+    nRows = 70001
+    dev = torch.device("cuda", 0)
+    host_groups, dev_groups, keep = [], [], []
+    specs = [(2, MAP_BIT), (100, MAP_UBYTE), (250, MAP_BYTE), (900, MAP_CHAR), (70000, MAP_INT)]
+    for c, (card, mt) in enumerate(specs):
+        ids = rng.integers(0, card, nRows)
+        d = rng.standard_normal((card, 1))
+        m = MapToFactory.create_from(ids, card, force_type=mt)
+        host_groups.append(cg.ColGroupDDC([c], d, m))
+        t = torch.from_numpy(m.data.view(np.uint8).copy()).to(dev)
+        keep.append(t)
+        dev_groups.append(cg.ColGroupDDC([c], d, DeviceMap(mt, nRows, card, t.data_ptr(), t.numel(), owner=t)))
+    dense = rng.standard_normal((nRows, 3))
+    td = torch.from_numpy(dense).to(dev)
+    nc = len(specs)
+    host_groups.append(cg.ColGroupUncompressed([nc, nc + 1, nc + 2], dense))
+    dev_groups.append(cg.ColGroupUncompressedDev([nc, nc + 1, nc + 2], nRows, td.data_ptr(), owner=td))
+    a = CompressedMatrixBlock(nRows, nc + 3, host_groups).to_device()
+    b = CompressedMatrixBlock(nRows, nc + 3, dev_groups).to_device()
+    v = rng.standard_normal(nc + 3)
+    V = rng.standard_normal((nc + 3, 16))
+    y = rng.standard_normal((1, nRows))
+    for f in (lambda m: CLALibRightMultBy.rightMultByMatrix(m, v), lambda m: CLALibRightMultBy.rightMultByMatrix(m, V),
+              lambda m: CLALibDecompress.decompress(m)):
+        assert np.array_equal(np.array(f(a)), np.array(f(b)))
+    X = dense_of(a)
+    assert rel_err(CLALibLeftMultBy.leftMultByMatrix(b, y), y @ X, np.abs(y) @ np.abs(X)) < TOL
+    assert rel_err(CLALibTSMM.leftMultByTransposeSelf(b), oracle.dense_tsmm_ld(X), np.abs(X).T @ np.abs(X)) < TOL
+    for gi in range(nc):
+        assert np.array_equal(b.group_row_ids(gi), a.group_row_ids(gi))
+    a.free()
+    b.free()
+    bad = torch.full((nRows,), 7, dtype=torch.uint8, device=dev)
+    g = cg.ColGroupDDC([0], rng.standard_normal((5, 1)), DeviceMap(MAP_UBYTE, nRows, 5, bad.data_ptr(), nRows, owner=bad))
+    with pytest.raises(CLAError):
+        CompressedMatrixBlock(nRows, 1, [g]).to_device()
