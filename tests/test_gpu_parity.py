@@ -232,7 +232,7 @@ def test_empty_and_errors():
 
 
 def test_full_size_checksum_config2(oracle):
-    """BASELINE-size t(y) %*% X (10M x 200): with y = 1 the product equals counts . dictionary, a checksum built
+    """Full-size t(y) %*% X (10M x 200): with y = 1 the product equals counts . dictionary, a checksum built
     from the bit-exact device histograms; linearity ties a random y to it."""
     cmb, y = datagen.config2(nRows=10_000_000, nCols=200)
     cmb.to_device()
