@@ -166,7 +166,12 @@ struct Matrix {
   int32_t* dSparseIdx = nullptr;  // device group indices of the SDC groups with listed rows and RLE groups with runs, list order
   int nSparse = 0;
   bool sparseListBuilt = false;
-  bool denseQuad = false;        // some stage of the tensor-core RMM takes the quad-column decode
+  // row-major work lists of the SDC / RLE groups for the tensor-core right product (cla_rmm_dmma.cu), built on first use
+  void* dStepItems = nullptr;
+  uint32_t* dStepPtr = nullptr;
+  void* dWinItems = nullptr;
+  uint32_t* dWinPtr = nullptr;
+  bool spListsTried = false, spListsOk = false;
   int32_t* dColSrc = nullptr;    // [nCols][2]: dense-map / uncompressed group holding the column and the position in it (-1: none)
   bool colSrcValid = false;      // false when some column is held by more than one such group (overlapping input)
   bool hasConst = false;
@@ -221,6 +226,7 @@ int64_t ensure_scratch(Matrix* m, size_t bytes);
 int64_t ensure_scratch2(Matrix* m, size_t bytes);
 int64_t ensure_io(Matrix* m, size_t bytes);
 int64_t ensure_small(Matrix* m, size_t bytes);
+int64_t ensure_sparse_list(Matrix* m);  // Matrix::dSparseIdx (cla_generic.cu)
 
 // launchers implemented in the kernel translation units; all enqueue on `s` and return CLA_OK or an error.
 int64_t launch_rmm(Matrix* m, const double* dV, int vCols, double* dOut, cudaStream_t s, bool afterFast = false);

@@ -157,7 +157,7 @@ k_rmm_vec_general(const DevGroup* __restrict__ groups, int nGroups, const int32_
 }
 
 // SDC groups with listed rows and RLE groups with runs, in list order (built once per handle)
-static int64_t ensure_sparse_list(Matrix* m) {
+int64_t ensure_sparse_list(Matrix* m) {
   if (m->sparseListBuilt) return CLA_OK;
   std::vector<int32_t> idx;
   for (int gi = 0; gi < m->nDev; gi++) {

@@ -12,8 +12,10 @@
 //      one per-tile base vector, only runs that start or end inside the tile touch individual rows;
 //   4. adds constV * V and stores.
 #include "cla_common.cuh"
+#include <cub/cub.cuh>
 #include <algorithm>
 #include <climits>
+#include <cstdlib>
 
 namespace cla {
 
@@ -176,16 +178,23 @@ k_rmm_dmma(const DevGroup* __restrict__ groups, int nGroups, const DenseCol* __r
 }
 
 // --------------------------------------------------------------------------------------------------
-// Second generation of the same kernel. Differences:
-//  * a CTA owns a block of 1024 rows (the granularity of the skip indexes) and walks it as eight 128-row tiles,
-//    so the decode state of every sparse group survives from tile to tile: one lane per SDC group keeps
-//    (next listed row, its element index, stream position), one lane per RLE group keeps its current run;
-//  * the lanes do not add anything themselves: they push work items {first row, last row, table row} into one
-//    queue per warp (a warp owns 16 rows of the tile), and each warp then applies its own queue to its own rows
-//    with plain read-modify-writes (no atomics on doubles), eight items in flight at a time;
-//  * runs that cover a whole tile go to a base queue that every warp folds into two registers per lane;
-//  * dense-operand columns come from a flat descriptor array (map, dictionary column, V row).
-// Limits: at most 256 SDC and 256 RLE groups (8 warps x 32 lanes); larger inputs use k_rmm_dmma.
+// Second generation. The CTAs are persistent (one per SM) and hold the rows of V that belong to the dense-operand
+// columns in shared memory for their whole life, so nothing in the main loop needs a CTA-wide barrier: every warp
+// works on its own 512-row units, 16 rows at a time, independently of the others. For its 16 rows a warp
+//   1. decodes 32 dense-operand columns at a time (lane = column: one 128-bit map load and 16 dictionary reads,
+//      or 16 values of an uncompressed column) into its private stage and multiplies it with the resident rows of
+//      V by DMMA m8n8k4, accumulators in registers; the map word of the stage after next and the dictionary reads
+//      of the next stage are in flight meanwhile, and while one warp waits the other seven keep the tensor pipe busy;
+//   2. moves the accumulators to its private result tile and adds the SDC and RLE groups from their
+//      pre-aggregated tables P_g = D_g * V[cols_g, :], walking the work lists built once per matrix by
+//      build_sparse_lists (below): per 16-row step the pieces {first row, end row, table row} of every listed SDC
+//      row and of every RLE run that starts or ends inside a 64-row window, sorted by group, so that each output
+//      row receives its terms in the groups' list order without any queue or atomic; and per 64-row window the
+//      table rows of the RLE runs that cover the window entirely, which are summed once per window into a vector
+//      held in registers. Sixteen table rows are in flight at a time;
+//   3. adds constV * V and writes the 16 rows out, 512 contiguous bytes per row.
+// Dense-operand columns beyond what fits shared memory next to the warps' tiles are handled by further launches
+// that add to the result.
 // --------------------------------------------------------------------------------------------------
 struct DenseDesc {
   const void* map;     // map (dense-map groups) or null
@@ -197,431 +206,343 @@ struct DenseDesc {
   int32_t pad;
 };
 
-constexpr int Q_CAP = 512;            // items per warp queue (a power of two: sorted in place)
-constexpr int QB_CAP = 512;           // base queue
-constexpr int QD_CAP = 32;            // per-warp queue of run boundaries
-constexpr int GM_SUB = SKIP_ROWS / GM_TR;  // tiles per block
+constexpr int G3_UNIT = 512;         // rows per warp work unit: 64 steps of 8 rows, 8 windows of 64
+constexpr int G3_STEP = 8;           // rows per step of the sparse work lists (one DMMA row tile)
+constexpr int G3_WIN = 64;
 
-struct WorkItem {    // read as one little-endian 64-bit key, the table row is the most significant part
-  uint16_t ra, rb;   // rows [ra, rb) of the tile
-  uint32_t prow;     // row of the table arena P
-};
-struct DeltaItem {   // rows [row, end) of the tile (inside one warp's 16-row slice) hold table row P[prow] of an RLE group
-  int16_t row;
-  int16_t end;
+// One piece of work of the sparse phase: rows [ra, rb) of an 8-row step (or a whole 64-row window) receive table row prow.
+struct SpItem {
   uint32_t prow;
+  uint32_t rows;  // ra | rb << 8
 };
-static_assert(sizeof(WorkItem) == 8 && sizeof(DeltaItem) == 8, "queue items are sorted as 64-bit keys");
 
-// Queue slots are handed out in arrival order, which depends on warp timing; the queues are sorted by table row
-// before they are applied (a group's table rows lie behind those of every earlier group, and one group never has
-// two items on the same output row), so every output row receives its groups' terms in list order.
-// A full queue drops the item: the count keeps growing and the tile then takes sparse_rows_in_order instead.
-__device__ __forceinline__ void push_item(WorkItem* q, int* qn, int w, int ra, int rb, uint32_t prow) {
-  const int slot = atomicAdd(&qn[w], 1);
-  if (slot < Q_CAP) {
-    WorkItem it;
-    it.ra = (uint16_t)ra;
-    it.rb = (uint16_t)rb;
-    it.prow = prow;
-    q[w * Q_CAP + slot] = it;
-  }
-}
+// NT = 8-column tiles per CTA (8: 64 output columns, two per lane in the sparse phase; 4: 32 columns, one per lane),
+// WARPS = warps per CTA. Sixteen warps of at most 128 registers: with eight, the SM issued 0.9 instructions per clock
+// (two warps per scheduler, every instruction waiting out the latency of the one before) and neither the tensor
+// pipe nor the L1 data pipe was busy; the per-warp buffers are sized so that sixteen fit next to V.
+template <int NT, int WARPS>
+struct G3 {
+  static constexpr int TN = NT * 8;
+  static constexpr int LDB = TN + 4;    // = 4 mod 16: conflict-free fragment loads
+  static constexpr int LDC = TN + 2;    // row stride of a warp's result tile (8 rows at a time)
+  static constexpr int WBUF = 16 * GM_LDAR > G3_STEP * LDC ? 16 * GM_LDAR : G3_STEP * LDC;  // doubles per warp: stage [16][GM_LDAR], then the tile
+  static constexpr int THREADS = WARPS * 32;
+  static constexpr int CPL = TN / 32;   // output columns per lane in the sparse phase
+  static constexpr int KMAX = ((227 * 1024 - 1024 - WARPS * WBUF * 8) / (LDB * 8)) / GM_KC * GM_KC;  // resident rows of V
+};
 
-// Bitonic sort of n 64-bit keys in shared memory by one warp; the array must have room for the next power of two.
-__device__ __forceinline__ void warp_sort_u64(unsigned long long* a, int n) {
-  const int lane = threadIdx.x & 31;
-  int np = 1;
-  while (np < n) np <<= 1;
-  for (int i = n + lane; i < np; i += 32) a[i] = ~0ull;
-  __syncwarp();
-  for (int k = 2; k <= np; k <<= 1)
-    for (int j = k >> 1; j > 0; j >>= 1) {
-      for (int t = lane; t < (np >> 1); t += 32) {
-        const int i = ((t & ~(j - 1)) << 1) | (t & (j - 1));  // lower index of the t-th pair at distance j
-        const int l = i | j;
-        const unsigned long long x = a[i], y = a[l];
-        const bool up = (i & k) == 0;
-        if ((x > y) == up) {
-          a[i] = y;
-          a[l] = x;
-        }
-      }
-      __syncwarp();
-    }
-}
-__device__ __forceinline__ void warp_sort_u32(uint32_t* a, int n) {
-  const int lane = threadIdx.x & 31;
-  int np = 1;
-  while (np < n) np <<= 1;
-  for (int i = n + lane; i < np; i += 32) a[i] = ~0u;
-  __syncwarp();
-  for (int k = 2; k <= np; k <<= 1)
-    for (int j = k >> 1; j > 0; j >>= 1) {
-      for (int t = lane; t < (np >> 1); t += 32) {
-        const int i = ((t & ~(j - 1)) << 1) | (t & (j - 1));
-        const int l = i | j;
-        const uint32_t x = a[i], y = a[l];
-        const bool up = (i & k) == 0;
-        if ((x > y) == up) {
-          a[i] = y;
-          a[l] = x;
-        }
-      }
-      __syncwarp();
-    }
-}
-
-template <bool QUAD>  // QUAD: the quad-column decode is compiled in (it costs registers the other stages then spill)
-__global__ void __launch_bounds__(GM_THREADS, 2)
-k_rmm_dmma2(const DevGroup* __restrict__ groups, const DenseDesc* __restrict__ dd, int nDense,
-            const int32_t* __restrict__ sdcIdx, int nSdc, const int32_t* __restrict__ rleIdx, int nRle, int nRows,
-            const double* __restrict__ V, int vCols, const double* __restrict__ P, const double* __restrict__ constRow,
-            double* __restrict__ out) {
+template <int NT, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 1)
+k_rmm_dmma3(const DenseDesc* __restrict__ dd, int nDense, const SpItem* __restrict__ stepItems,
+            const uint32_t* __restrict__ stepPtr, const SpItem* __restrict__ winItems,
+            const uint32_t* __restrict__ winPtr, int nRows, const double* __restrict__ V, int vCols,
+            const double* __restrict__ P, const double* __restrict__ constRow, double* __restrict__ out, int accumulate) {
+  typedef G3<NT, WARPS> C;
+  constexpr int TN = C::TN, LDB = C::LDB, LDC = C::LDC, CPL = C::CPL;
   extern __shared__ __align__(16) double sm[];
-  double* As = sm;                      // [GM_TR][GM_LDAR] row-major stage of the dense operand
-  double* Bs = sm + GM_TR * GM_LDAR;    // [GM_KC][GM_LDB]
-  double* Cs = sm;                      // [GM_TR][GM_LDC] (aliases the stage)
-  WorkItem* q = (WorkItem*)(sm + GM_TR * GM_LDC);      // [8][Q_CAP]
-  uint32_t* qb = (uint32_t*)(q + 8 * Q_CAP);           // [QB_CAP] table rows of tile-covering runs
-  DeltaItem* qd = (DeltaItem*)(qb + QB_CAP);           // [8][QD_CAP] run boundaries per warp
-  int* qn = (int*)(qd + 8 * QD_CAP);                   // [8] queue lengths, [8] base queue, [9..16] boundary queues
-  double* basep = (double*)(qn + 32);                  // [4][GM_TN] partial base vectors
-  double* basev = basep + 4 * GM_TN;                   // [GM_TN] base vector of the tile
+  const int nSt = (nDense + GM_KC - 1) / GM_KC;  // stages of 32 dense-operand columns
+  const int kPad = nSt * GM_KC;
+  double* Vs = sm;                                   // [kPad][LDB]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int blk0 = blockIdx.x * SKIP_ROWS;
-  const int j0 = blockIdx.y * GM_TN, vc = min(GM_TN, vCols - j0);
+  double* W = sm + (size_t)kPad * LDB + warp * C::WBUF;  // this warp's stage / result tile
+  const int j0 = blockIdx.y * TN, vc = min(TN, vCols - j0);
+  for (int e = tid; e < kPad * TN; e += C::THREADS) {
+    const int kc = e / TN, n = e - kc * TN;
+    Vs[kc * LDB + n] = (kc < nDense && n < vc) ? V[(size_t)dd[kc].vrow * vCols + j0 + n] : 0.0;
+  }
+  __syncthreads();
   const int am = lane >> 2, ak = lane & 3;
-  const bool sparse = (nSdc + nRle) > 0;
+  const int n0 = CPL * lane;  // this lane's output column(s) in the result tile
+  const bool c0ok = n0 < vc, c1ok = CPL == 2 && n0 + 1 < vc;
+  const bool vec2 = CPL == 2 && ((vCols | j0) & 1) == 0 && c1ok;  // rows of P and out start 16-byte aligned, both columns exist
+  const char* Pb = (const char*)(P + j0 + n0);   // this lane's columns of table row 0
+  const uint32_t rowBytes = (uint32_t)vCols * 8u;  // the launcher checks that the whole table stays below 4 GB
+  char* Wb = (char*)(W + n0);                     // this lane's columns of row 0 of the result tile
+  const double2 cst = make_double2((constRow && c0ok) ? constRow[j0 + n0] : 0.0, (constRow && c1ok) ? constRow[j0 + n0 + 1] : 0.0);
 
-  // ---- per-lane decode state for the whole block ----
-  const int sgi = warp * 32 + lane;
-  const bool hasS = sgi < nSdc, hasR = sgi < nRle;
-  int sRow = INT_MAX, sElem = 0;
-  int64_t sPos = 0;
-  int64_t rRun = 0;
-  DevGroup gs, gr;  // copies of this lane's groups (registers / local)
-  if (hasS) {
-    gs = groups[sdcIdx[sgi]];
-    if (gs.nOff > 0) {
-      if (gs.offType == CLA_OFF_BYTE || gs.offType == CLA_OFF_CHAR) {
-        const SdcSkip sk = gs.skip[blockIdx.x];
-        if (sk.elem < gs.nOff) {
-          sRow = sk.row;
-          sElem = sk.elem;
-          sPos = sk.pos;
+  // Decode of one stage for 16 rows, split so that the map word of stage t + 2 and the dictionary reads of stage
+  // t + 1 are in flight while stage t multiplies: map word first (byte maps, full 16 rows) ...
+  auto stage_map = [&](int r0, int r1, int k0) -> uint4 {
+    const int kc = k0 + lane;
+    if (kc < nDense && r0 + 16 <= r1) {
+      const int mt = dd[kc].mapType;
+      if (mt == CLA_MAP_UBYTE || mt == CLA_MAP_BYTE) return __ldg((const uint4*)((const uint8_t*)dd[kc].map + r0));
+    }
+    return make_uint4(0, 0, 0, 0);
+  };
+  // ... then the values
+  auto stage_values = [&](int r0, int r1, int k0, const uint4& w, double (&v)[16]) {
+    const int kc = k0 + lane;
+#pragma unroll
+    for (int i = 0; i < 16; i++) v[i] = 0.0;
+    if (kc >= nDense) return;
+    const DenseDesc d = dd[kc];
+    if (d.mapType < 0) {
+#pragma unroll
+      for (int i = 0; i < 16; i++)
+        if (r0 + i < r1) v[i] = d.src[(size_t)(r0 + i) * d.gCols];
+    } else if ((d.mapType == CLA_MAP_UBYTE || d.mapType == CLA_MAP_BYTE) && r0 + 16 <= r1) {
+      const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int i = 0; i < 16; i++) v[i] = d.src[(size_t)((ww[i >> 2] >> (8 * (i & 3))) & 0xFF) * d.gCols];
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; i++)
+        if (r0 + i < r1) v[i] = d.src[(size_t)map_get(d.mapType, d.map, d.mapHi, r0 + i) * d.gCols];
+    }
+  };
+
+  const int nUnits = (nRows + G3_UNIT - 1) / G3_UNIT;
+  for (int unit = blockIdx.x * WARPS + warp; unit < nUnits; unit += gridDim.x * WARPS) {
+    const int U0 = unit * G3_UNIT, U1 = min(nRows, U0 + G3_UNIT);
+    // list bounds of the unit's 64 steps and 8 windows: lane l holds the starts of steps l and 32 + l (window l); the
+    // end of the last one is the start of the next unit's first
+    uint32_t sp0 = 0, sp1 = 0, spEnd = 0, wp = 0, wpEnd = 0;
+    if (stepPtr) {
+      sp0 = stepPtr[unit * (G3_UNIT / G3_STEP) + lane];
+      sp1 = stepPtr[unit * (G3_UNIT / G3_STEP) + 32 + lane];
+      spEnd = stepPtr[(unit + 1) * (G3_UNIT / G3_STEP)];
+      wp = winPtr[unit * (G3_UNIT / G3_WIN) + (lane & 7)];
+      wpEnd = winPtr[(unit + 1) * (G3_UNIT / G3_WIN)];
+    }
+    const int nSub = (U1 - U0 + 15) / 16;
+    uint4 wq = nSt > 0 ? stage_map(U0, U1, 0) : make_uint4(0, 0, 0, 0);  // the map word is fetched one stage ahead
+    double baseWin[CPL];
+#pragma unroll
+    for (int q = 0; q < CPL; q++) baseWin[q] = 0.0;
+    for (int sub = 0; sub < nSub; sub++) {
+      const int r0 = U0 + sub * 16, r1 = min(U1, r0 + 16);
+      double c[2][NT][2];
+      if (accumulate) {
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+          for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+              const int row = r0 + mt * 8 + am, n = nt * 8 + ak * 2 + u;
+              c[mt][nt][u] = (row < r1 && n < vc) ? out[(size_t)row * vCols + j0 + n] : 0.0;
+            }
+      } else {
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+          for (int nt = 0; nt < NT; nt++) c[mt][nt][0] = c[mt][nt][1] = 0.0;
+      }
+      for (int st = 0; st < nSt; st++) {
+        const int k0 = st * GM_KC;
+        {
+          double v[16];
+          stage_values(r0, r1, k0, wq, v);
+          __syncwarp();  // the previous stage's fragment loads (or the previous step's stores) are done
+#pragma unroll
+          for (int i = 0; i < 16; i++) W[i * GM_LDAR + lane] = v[i];
         }
-      } else {  // OffsetSingle / OffsetTwo
-        if (gs.first >= blk0) sRow = gs.first;
-        else if (gs.offType == CLA_OFF_TWO && gs.last >= blk0) {
-          sRow = gs.last;
-          sElem = 1;
+        {  // map word of the next stage
+          const bool lastSt = st + 1 == nSt;
+          const int nr0 = lastSt ? r0 + 16 : r0, nk0 = lastSt ? 0 : k0 + GM_KC;
+          if (nr0 < U1) wq = stage_map(nr0, U1 < nr0 + 16 ? U1 : nr0 + 16, nk0);
+        }
+        __syncwarp();
+#pragma unroll
+        for (int ks = 0; ks < GM_KC; ks += 4) {
+          double a[2];
+#pragma unroll
+          for (int mt = 0; mt < 2; mt++) a[mt] = W[(mt * 8 + am) * GM_LDAR + ks + ak];
+#pragma unroll
+          for (int nt = 0; nt < NT; nt++) {
+            const double b = Vs[(k0 + ks + ak) * LDB + nt * 8 + am];
+#pragma unroll
+            for (int mt = 0; mt < 2; mt++) dmma884(c[mt][nt][0], c[mt][nt][1], a[mt], b);
+          }
+        }
+      }
+      // ---- the two 8-row halves: accumulators -> result tile, sparse groups from the work lists, constants, store.
+      //      One copy of this code (no unrolling over the halves or the two lists): with sixteen warps at different
+      //      places of the kernel, instruction fetch was the largest stall of the fully unrolled form. ----
+#pragma unroll 1
+      for (int h = 0; h < 2; h++) {
+        const int h0 = r0 + h * G3_STEP, h1 = min(r1, h0 + G3_STEP);
+        if (h0 >= h1) break;
+        __syncwarp();
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+          *(double2*)&W[am * LDC + nt * 8 + ak * 2] =
+              make_double2(h ? c[1][nt][0] : c[0][nt][0], h ? c[1][nt][1] : c[0][nt][1]);
+        __syncwarp();
+        double base[CPL];
+#pragma unroll
+        for (int q = 0; q < CPL; q++) base[q] = 0.0;
+        if (stepPtr) {
+          const bool whole = h1 - h0 == G3_STEP;
+          const int step = sub * 2 + h;
+          const bool newWin = (step & 7) == 0;  // a new 64-row window: first the runs that cover it entirely
+          if (newWin) {
+#pragma unroll
+            for (int q = 0; q < CPL; q++) baseWin[q] = 0.0;
+          }
+          const int w = step >> 3;
+          const uint32_t q0 = __shfl_sync(0xffffffffu, wp, w), q1n = __shfl_sync(0xffffffffu, wp, (w + 1) & 7);
+          const uint32_t pa = __shfl_sync(0xffffffffu, step < 32 ? sp0 : sp1, step & 31);
+          const uint32_t pbn = __shfl_sync(0xffffffffu, step + 1 < 32 ? sp0 : sp1, (step + 1) & 31);
+#pragma unroll 1
+          for (int pass = newWin ? 0 : 1; pass < 2; pass++) {
+            const bool toWin = pass == 0;
+            const SpItem* __restrict__ items = toWin ? winItems : stepItems;
+            const uint32_t p0 = toWin ? q0 : pa, p1 = toWin ? (w == 7 ? wpEnd : q1n) : (step == 63 ? spEnd : pbn);
+            // items [p0, p1): 32 per coalesced load; every lane turns its own item into the byte offset of the table
+            // row and a word {offset of the first row in the tile, number of rows, "add to the base vector"} once,
+            // so that the serial part per item is two shuffles, one load and one read-modify-write. Eight table
+            // rows are in flight at a time; items are applied in list order.
+#pragma unroll 1
+            for (uint32_t i0 = p0; i0 < p1; i0 += 32) {
+              const int cnt = (int)min(32u, p1 - i0);
+              uint32_t offP = 0, wrd = 0;
+              if (lane < cnt) {
+                const SpItem e = items[i0 + lane];
+                const uint32_t ra = e.rows & 0xFF, nr = ((e.rows >> 8) & 0xFF) - ra;
+                offP = e.prow * rowBytes;
+                wrd = (ra * (uint32_t)(LDC * 8)) | (nr << 16) | ((toWin || (whole && nr == G3_STEP)) ? 0x80000000u : 0u);
+              }
+#pragma unroll 1
+              for (int b0 = 0; b0 < cnt; b0 += 8) {
+                double2 t[8];
+                uint32_t rw[8];
+                const int nb = min(8, cnt - b0);
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                  const uint32_t po = __shfl_sync(0xffffffffu, offP, (b0 + j) & 31);
+                  rw[j] = __shfl_sync(0xffffffffu, wrd, (b0 + j) & 31);
+                  if (j < nb) {
+                    const char* pp = Pb + po;
+                    if (vec2) t[j] = *(const double2*)pp;
+                    else t[j] = make_double2(c0ok ? ((const double*)pp)[0] : 0.0, c1ok ? ((const double*)pp)[1] : 0.0);
+                  }
+                }
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                  if (j < nb) {
+                    if (rw[j] & 0x80000000u) {  // covers the whole step (or window): one add to a vector in registers
+                      if (toWin) {
+                        baseWin[0] += t[j].x;
+                        if (CPL == 2) baseWin[CPL - 1] += t[j].y;
+                      } else {
+                        base[0] += t[j].x;
+                        if (CPL == 2) base[CPL - 1] += t[j].y;
+                      }
+                    } else {
+                      char* cp = Wb + (rw[j] & 0xFFFFu);
+                      int nr = (int)((rw[j] >> 16) & 0xFF);
+                      do {
+                        if (CPL == 2) {
+                          double2 cv = *(double2*)cp;
+                          cv.x += t[j].x;
+                          cv.y += t[j].y;
+                          *(double2*)cp = cv;
+                        } else
+                          *(double*)cp += t[j].x;
+                        cp += LDC * 8;
+                      } while (--nr > 0);
+                    }
+                  }
+                }
+              }
+            }
+          }
+        }
+        __syncwarp();
+#pragma unroll 1
+        for (int r = 0; r < h1 - h0; r++) {
+          double* o = out + (size_t)(h0 + r) * vCols + j0 + n0;
+          if (CPL == 2) {
+            const double2 cv = *(const double2*)&W[r * LDC + n0];
+            const double x = ((cv.x + base[0]) + baseWin[0]) + cst.x, y = ((cv.y + base[CPL - 1]) + baseWin[CPL - 1]) + cst.y;
+            if (vec2) *(double2*)o = make_double2(x, y);
+            else {
+              if (c0ok) o[0] = x;
+              if (c1ok) o[1] = y;
+            }
+          } else if (c0ok)
+            o[0] = ((W[r * LDC + n0] + base[0]) + baseWin[0]) + cst.x;
         }
       }
     }
   }
-  if (hasR) {
-    gr = groups[rleIdx[sgi]];
-    rRun = gr.runSkip[blockIdx.x];
+}
+
+// --------------------------------------------------------------------------------------------------
+// Work lists of the sparse phase, built once per matrix (first wide right product): the SDC and RLE groups turned
+// from per-group index structures into per-row-range lists. A warp per (group, 1024-row block) decodes the block
+// (offset stream from its skip entry, runs from the merged run list) and emits
+//   * per 8-row step: {rows [ra, rb) of the step, table row} for every listed SDC row and for every piece of an RLE
+//     run that lies in a 64-row window the run does not cover entirely;
+//   * per 64-row window: {table row} for every RLE run that covers the window entirely.
+// Both lists are sorted by (step or window, table row); table rows grow with the group index, so within a step the
+// items are in the groups' list order. The ptr arrays hold the start of every step / window (padded to whole units).
+// --------------------------------------------------------------------------------------------------
+__global__ void k_sparse_emit(const DevGroup* __restrict__ groups, const int32_t* __restrict__ sparseIdx, int nSparse,
+                              int nRows, unsigned long long* __restrict__ stepKeys, uint32_t* __restrict__ stepVals,
+                              unsigned long long* __restrict__ winKeys, unsigned long long* __restrict__ counters) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warpId = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+  const int nBlocks = (nRows + SKIP_ROWS - 1) / SKIP_ROWS;
+  const int gi = (int)(warpId / nBlocks), blk = (int)(warpId % nBlocks);
+  if (gi >= nSparse) return;
+  const DevGroup& g = groups[sparseIdx[gi]];
+  const int b0 = blk * SKIP_ROWS, b1 = min(nRows, b0 + SKIP_ROWS);
+  auto emit_step = [&](int row0, int row1, uint32_t prow) {  // rows [row0, row1) inside one step
+    const unsigned long long slot = atomicAdd(&counters[0], 1ull);
+    if (stepKeys) {
+      stepKeys[slot] = ((unsigned long long)(row0 / G3_STEP) << 32) | prow;
+      stepVals[slot] = (uint32_t)(row0 % G3_STEP) | ((uint32_t)(row1 - row0 / G3_STEP * G3_STEP) << 8);
+    }
+  };
+  if (g.type == GT_SDC) {
+    sdc_walk_block(g, b0, b1, [&](int row, int e) {
+      const int id = g.single ? 0 : map_get(g.mapType, g.map, g.mapHi, e);
+      emit_step(row, row + 1, (uint32_t)(g.valOff + id));
+    });
+  } else if (g.type == GT_RLE) {
+    for (int64_t ri = g.runSkip[blk] + lane; ri < g.nRuns; ri += 32) {
+      const RleRun R = g.runs[ri];
+      if (R.start >= b1) break;
+      const int a = max(R.start, b0), b = min(R.start + (int)R.len, b1);
+      const uint32_t prow = (uint32_t)(g.valOff + R.k);
+      for (int w0 = a & ~(G3_WIN - 1); w0 < b; w0 += G3_WIN) {
+        const int wa = max(a, w0), wb = min(b, w0 + G3_WIN);
+        if (wa >= wb) continue;
+        if (wb - wa == G3_WIN) {
+          const unsigned long long slot = atomicAdd(&counters[1], 1ull);
+          if (winKeys) winKeys[slot] = ((unsigned long long)(w0 / G3_WIN) << 32) | prow;
+        } else {
+          for (int s0 = wa / G3_STEP * G3_STEP; s0 < wb; s0 += G3_STEP) {
+            const int sa = max(wa, s0), sb = min(wb, s0 + G3_STEP);
+            if (sa < sb) emit_step(sa, sb, prow);
+          }
+        }
+      }
+    }
   }
-
-  for (int sub = 0; sub < GM_SUB; sub++) {
-    const int r0 = blk0 + sub * GM_TR;
-    if (r0 >= nRows) break;
-    const int r1 = min(nRows, r0 + GM_TR);
-    double c[2][8][2];
-#pragma unroll
-    for (int mt = 0; mt < 2; mt++)
-#pragma unroll
-      for (int nt = 0; nt < 8; nt++) c[mt][nt][0] = c[mt][nt][1] = 0.0;
-
-    for (int k0 = 0; k0 < nDense; k0 += GM_KC) {
-      const int rbase = warp * 16;
-      if (QUAD && dd[k0].pad && r0 + GM_TR <= nRows) {
-        // stage, all 32 columns single-column byte-map groups: a load instruction covers 8 rows x 4 adjacent
-        // columns (lane = 4 * row + column). The four dictionaries of such a quad lie next to each other in the
-        // packed copy, so a gather touches one or two cache lines where a lane-per-column gather touches 32 (the
-        // L1 tag stage, one line per cycle, was the limit of this loop); the stores hit 16 distinct banks.
-        const int kk = lane & 3, r8 = lane >> 2;
-        const int rowA = r0 + rbase + r8;
-#pragma unroll
-        for (int half = 0; half < 2; half++) {
-          const uint8_t* mp[4];
-          const double* sp[4];
-#pragma unroll
-          for (int g4 = 0; g4 < 4; g4++) {
-            const int col = k0 + (half * 4 + g4) * 4 + kk;
-            mp[g4] = nullptr;
-            sp[g4] = nullptr;
-            if (col < nDense) {
-              mp[g4] = (const uint8_t*)dd[col].map;
-              sp[g4] = dd[col].src;
-            }
-          }
-          uint32_t id[4][2];
-#pragma unroll
-          for (int g4 = 0; g4 < 4; g4++)
-#pragma unroll
-            for (int h = 0; h < 2; h++) id[g4][h] = mp[g4] ? (uint32_t)__ldg(mp[g4] + rowA + 8 * h) : 0u;
-          double vv[4][2];
-#pragma unroll
-          for (int g4 = 0; g4 < 4; g4++)
-#pragma unroll
-            for (int h = 0; h < 2; h++) vv[g4][h] = sp[g4] ? sp[g4][id[g4][h]] : 0.0;
-#pragma unroll
-          for (int g4 = 0; g4 < 4; g4++)
-#pragma unroll
-            for (int h = 0; h < 2; h++) As[(rbase + r8 + 8 * h) * GM_LDAR + (half * 4 + g4) * 4 + kk] = vv[g4][h];
-        }
-      } else {  // stage: warp = 16 rows of the tile, lane = one of the 32 dense columns. A dense-map column costs its lane
-         // one 128-bit map load (16 ids) and 16 dictionary reads; an uncompressed column is read row by row, the
-         // warp covering 32 consecutive values of a dense row. A warp-wide store is one row of the stage.
-        const int kc = k0 + lane;
-        double v[16];
-#pragma unroll
-        for (int i = 0; i < 16; i++) v[i] = 0.0;
-        if (kc < nDense) {
-          const DenseDesc d = dd[kc];
-          const int row0 = r0 + rbase;
-          if (d.mapType < 0) {
-#pragma unroll
-            for (int i = 0; i < 16; i++)
-              if (row0 + i < nRows) v[i] = d.src[(size_t)(row0 + i) * d.gCols];
-          } else if ((d.mapType == CLA_MAP_UBYTE || d.mapType == CLA_MAP_BYTE) && row0 + 16 <= nRows) {
-            const uint4 w = __ldg((const uint4*)((const uint8_t*)d.map + row0));  // row0 is a multiple of 16
-            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-            for (int i = 0; i < 16; i++) v[i] = d.src[(size_t)((ww[i >> 2] >> (8 * (i & 3))) & 0xFF) * d.gCols];
-          } else {
-#pragma unroll
-            for (int i = 0; i < 16; i++)
-              if (row0 + i < nRows) v[i] = d.src[(size_t)map_get(d.mapType, d.map, d.mapHi, row0 + i) * d.gCols];
-          }
-        }
-#pragma unroll
-        for (int i = 0; i < 16; i++) As[(rbase + i) * GM_LDAR + lane] = v[i];
-      }
-      {
-        for (int e = tid; e < GM_KC * GM_TN; e += GM_THREADS) {
-          const int kk = e >> 6, n = e & 63;
-          double x = 0.0;
-          if (k0 + kk < nDense && n < vc) x = V[(size_t)dd[k0 + kk].vrow * vCols + j0 + n];
-          Bs[kk * GM_LDB + n] = x;
-        }
-      }
-      __syncthreads();
-#pragma unroll
-      for (int ks = 0; ks < GM_KC; ks += 4) {
-        double a[2];
-#pragma unroll
-        for (int mt = 0; mt < 2; mt++) a[mt] = As[(warp * 16 + mt * 8 + am) * GM_LDAR + ks + ak];
-#pragma unroll
-        for (int nt = 0; nt < 8; nt++) {
-          const double b = Bs[(ks + ak) * GM_LDB + nt * 8 + am];
-#pragma unroll
-          for (int mt = 0; mt < 2; mt++) dmma884(c[mt][nt][0], c[mt][nt][1], a[mt], b);
-        }
-      }
-      __syncthreads();
+}
+// items[i] = {table row, rows}; ptr[u] = first item whose step / window is >= u
+__global__ void k_sparse_pack(const unsigned long long* __restrict__ keys, const uint32_t* __restrict__ vals, int64_t n,
+                              SpItem* __restrict__ items) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    SpItem it;
+    it.prow = (uint32_t)keys[i];
+    it.rows = vals ? vals[i] : 0u;
+    items[i] = it;
+  }
+}
+__global__ void k_sparse_ptr(const unsigned long long* __restrict__ keys, int64_t n, uint32_t* __restrict__ ptr, int64_t nPtr) {
+  for (int64_t u = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; u < nPtr; u += (int64_t)gridDim.x * blockDim.x) {
+    int64_t lo = 0, hi = n;  // first key with (key >> 32) >= u
+    while (lo < hi) {
+      const int64_t mid = (lo + hi) >> 1;
+      if ((int64_t)(keys[mid] >> 32) < u) lo = mid + 1;
+      else hi = mid;
     }
-
-    if (!sparse) {  // straight from the fragments
-#pragma unroll
-      for (int mt = 0; mt < 2; mt++) {
-        const int row = r0 + warp * 16 + mt * 8 + (lane >> 2);
-        if (row >= r1) continue;
-#pragma unroll
-        for (int nt = 0; nt < 8; nt++)
-#pragma unroll
-          for (int u = 0; u < 2; u++) {
-            const int n = nt * 8 + (lane & 3) * 2 + u;
-            if (n < vc) out[(size_t)row * vCols + j0 + n] = c[mt][nt][u] + (constRow ? constRow[j0 + n] : 0.0);
-          }
-      }
-      continue;
-    }
-#pragma unroll
-    for (int mt = 0; mt < 2; mt++)
-#pragma unroll
-      for (int nt = 0; nt < 8; nt++)
-#pragma unroll
-        for (int u = 0; u < 2; u++)
-          Cs[(warp * 16 + mt * 8 + (lane >> 2)) * GM_LDC + nt * 8 + (lane & 3) * 2 + u] = c[mt][nt][u];
-    if (tid < 17) qn[tid] = 0;
-    __syncthreads();
-
-    // ---- decode: every lane advances its groups through [r0, r1) and queues the work ----
-    if (hasS) {
-      const int maxV = gs.offType == CLA_OFF_BYTE ? 255 : 65535;
-      while (sRow < r1) {
-        if (sRow >= r0) {
-          const int id = gs.single ? 0 : map_get(gs.mapType, gs.map, gs.mapHi, sElem);
-          const int rl = sRow - r0;
-          push_item(q, qn, rl >> 4, rl, rl + 1, (uint32_t)(gs.valOff + id));
-        }
-        if (sElem + 1 >= gs.nOff) {
-          sRow = INT_MAX;
-          break;
-        }
-        if (gs.offType == CLA_OFF_BYTE) {
-          const uint8_t* dp = (const uint8_t*)gs.offData;
-          int d = dp[sPos++];
-          while (d == 0) {
-            sRow += maxV;
-            d = dp[sPos++];
-          }
-          sRow += d;
-        } else if (gs.offType == CLA_OFF_CHAR) {
-          const uint16_t* dp = (const uint16_t*)gs.offData;
-          int d = dp[sPos++];
-          while (d == 0) {
-            sRow += maxV;
-            d = dp[sPos++];
-          }
-          sRow += d;
-        } else
-          sRow = gs.last;  // OffsetTwo
-        sElem++;
-      }
-    }
-    if (hasR) {
-      while (rRun < gr.nRuns) {
-        const RleRun run = gr.runs[rRun];
-        if (run.start >= r1) break;
-        const int end = run.start + (int)run.len;
-        const int a = max(run.start, r0), b = min(end, r1);
-        if (a < b) {
-          const uint32_t prow = (uint32_t)(gr.valOff + run.k);
-          if (a == r0 && b == r0 + GM_TR) {
-            const int slot = atomicAdd(&qn[8], 1);
-            if (slot < QB_CAP) qb[slot] = prow;
-            else
-              for (int w = 0; w < 8; w++) push_item(q, qn, w, w * 16, w * 16 + 16, prow);
-          } else {
-            // a run that starts or ends inside the tile: every warp whose 16 rows it touches gets the piece of
-            // the run that lies in its slice
-            for (int w = (a - r0) >> 4; w <= (b - 1 - r0) >> 4; w++) {
-              const int aw = max(a - r0, w * 16), bw = min(b - r0, w * 16 + 16);
-              const int slot = atomicAdd(&qn[9 + w], 1);
-              if (slot < QD_CAP) qd[w * QD_CAP + slot] = DeltaItem{(int16_t)aw, (int16_t)bw, prow};
-              else
-                push_item(q, qn, w, aw, bw, prow);
-            }
-          }
-        }
-        if (end <= r1) rRun++;
-        else break;
-      }
-    }
-    __syncthreads();
-
-    // ---- fix the summation order: sort every queue by table row. A tile with an overflowed work queue drops its
-    //      queues and takes the slow in-order walk below instead ----
-    bool ovf = false;
-#pragma unroll
-    for (int w = 0; w < 8; w++) ovf |= qn[w] > Q_CAP;
-    if (!ovf) {
-      warp_sort_u64((unsigned long long*)(q + warp * Q_CAP), qn[warp]);
-      warp_sort_u64((unsigned long long*)(qd + warp * QD_CAP), min(qn[9 + warp], QD_CAP));
-      if (warp == 0) warp_sort_u32(qb, min(qn[8], QB_CAP));
-    }
-    __syncthreads();
-
-    // ---- base vector: constV * V plus the table rows of all runs that cover the whole tile. Thread = (one of four
-    //      item slices, column): every thread's loads are independent, so the whole sum costs one or two latencies ----
-    {
-      const int n = tid & 63, sl = tid >> 6;
-      const int nbq = ovf ? 0 : min(qn[8], QB_CAP);
-      double sacc = 0.0;
-      if (n < vc)
-        for (int i = sl; i < nbq; i += 4) sacc += P[(size_t)qb[i] * vCols + j0 + n];
-      basep[sl * GM_TN + n] = sacc;
-      __syncthreads();
-      if (tid < GM_TN)
-        basev[tid] = basep[tid] + basep[GM_TN + tid] + basep[2 * GM_TN + tid] + basep[3 * GM_TN + tid] +
-                     ((constRow && tid < vc) ? constRow[j0 + tid] : 0.0);
-      __syncthreads();
-    }
-    // ---- apply: warp w owns rows [16 w, 16 w + 16); lane owns the adjacent columns 2 lane and 2 lane + 1 ----
-    {
-      const int n0 = 2 * lane;
-      const bool c0ok = n0 < vc, c1ok = n0 + 1 < vc;
-      const bool vec2 = ((vCols | j0) & 1) == 0 && c1ok;  // table rows start 16-byte aligned and both columns exist
-      auto ldp = [&](uint32_t prow) -> double2 {              // two adjacent values of a table row
-        const double* p = P + (size_t)prow * vCols + j0 + n0;
-        if (vec2) return *(const double2*)p;
-        return make_double2(c0ok ? p[0] : 0.0, c1ok ? p[1] : 0.0);
-      };
-      const double2 bsum = make_double2(c0ok ? basev[n0] : 0.0, c1ok ? basev[n0 + 1] : 0.0);
-      if (ovf) {
-        sparse_rows_in_order(groups, nSdc, sdcIdx, P, vCols, j0, vc, Cs, r0, r1, blockIdx.x);
-        sparse_rows_in_order(groups, nRle, rleIdx, P, vCols, j0, vc, Cs, r0, r1, blockIdx.x);
-      }
-      const int nq = ovf ? 0 : qn[warp];
-      const WorkItem* myq = q + warp * Q_CAP;
-      for (int i0 = 0; i0 < nq; i0 += 8) {
-        double2 t[8];
-        WorkItem it[8];
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-          it[i] = myq[min(i0 + i, nq - 1)];
-          t[i] = i0 + i < nq ? ldp(it[i].prow) : make_double2(0.0, 0.0);
-        }
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-          if (i0 + i < nq)
-            for (int r = it[i].ra; r < it[i].rb; r++) {
-              double2* cp = (double2*)&Cs[r * GM_LDC + n0];
-              double2 cv = *cp;
-              cv.x += t[i].x;
-              cv.y += t[i].y;
-              *cp = cv;
-            }
-        }
-      }
-      // run pieces: eight at a time, their table rows are fetched first; then every row of the slice adds the
-      // table rows of the pieces that cover it. (Walking the slice with a running sum, +P at a start and -P at an
-      // end, is cheaper but leaves rounding residue of earlier, possibly much larger, values in later rows; the
-      // reference adds a row's own values and nothing else.)
-      const int nd = ovf ? 0 : min(qn[9 + warp], QD_CAP);
-      const DeltaItem* myd = qd + warp * QD_CAP;
-      for (int i0 = 0; i0 < nd; i0 += 8) {
-        double2 t[8];
-        int da[8], db[8];
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-          const DeltaItem d = myd[min(i0 + i, nd - 1)];
-          da[i] = i0 + i < nd ? d.row : 0;
-          db[i] = i0 + i < nd ? d.end : 0;
-          t[i] = i0 + i < nd ? ldp(d.prow) : make_double2(0.0, 0.0);
-        }
-        for (int r = warp * 16; r < warp * 16 + 16; r++) {
-          double2 add = make_double2(0.0, 0.0);
-          bool any = false;
-#pragma unroll
-          for (int i = 0; i < 8; i++)
-            if (da[i] <= r && r < db[i]) {
-              add.x += t[i].x;
-              add.y += t[i].y;
-              any = true;
-            }
-          if (any) {
-            double2* cp = (double2*)&Cs[r * GM_LDC + n0];
-            double2 cv = *cp;
-            cv.x += add.x;
-            cv.y += add.y;
-            *cp = cv;
-          }
-        }
-      }
-      for (int r = warp * 16; r < warp * 16 + 16; r++) {
-        if (r0 + r >= r1) break;
-        const double2 cv = *(const double2*)&Cs[r * GM_LDC + n0];
-        if (c0ok) out[(size_t)(r0 + r) * vCols + j0 + n0] = cv.x + bsum.x;
-        if (c1ok) out[(size_t)(r0 + r) * vCols + j0 + n0 + 1] = cv.y + bsum.y;
-      }
-    }
-    __syncthreads();  // the stage of the next tile overwrites Cs
+    ptr[u] = (uint32_t)lo;
   }
 }
 
@@ -694,21 +615,6 @@ static int64_t ensure_dense_cols(Matrix* m) {
       dd.push_back(d);
     }
   }
-  // pad of a stage's first column: 1 if the stage takes the quad-column decode: all its columns single-column
-  // byte-map groups, and deep dictionaries (measured: 256 values 4.3 -> 3.2 ms on 2M x 200 x 16, but with 4 values
-  // the extra byte loads and descriptor reads cost more than the saved cache-line lookups, 1.33 -> 1.59 ms per
-  // 1M x 200 x 64)
-  for (size_t k0 = 0; k0 < dd.size(); k0 += GM_KC) {
-    bool all = true;
-    int64_t vals = 0;
-    const size_t k1 = std::min(dd.size(), k0 + GM_KC);
-    for (size_t k = k0; k < k1; k++) {
-      all &= (dd[k].mapType == CLA_MAP_UBYTE || dd[k].mapType == CLA_MAP_BYTE) && dd[k].gCols == 1;
-      vals += m->groups[dc[k].group].nVals;
-    }
-    dd[k0].pad = (all && vals >= 64 * (int64_t)(k1 - k0)) ? 1 : 0;
-    m->denseQuad |= dd[k0].pad != 0;
-  }
   auto up = [&](const void* src, size_t bytes, void** dst) -> int64_t {
     *dst = nullptr;
     if (!bytes) return CLA_OK;
@@ -727,6 +633,85 @@ static int64_t ensure_dense_cols(Matrix* m) {
   m->nSdcGroups = (int)sdc.size();
   m->nRleGroups = (int)rle.size();
   m->denseColsBuilt = true;
+  return CLA_OK;
+}
+
+// Builds the work lists (see k_sparse_emit). Returns CLA_OK with m->spListsOk = false when the lists would not fit
+// 32-bit positions or device memory; the caller then takes the first-generation kernel.
+static int64_t build_sparse_lists(Matrix* m, cudaStream_t s) {
+  if (m->spListsTried) return CLA_OK;
+  m->spListsTried = true;
+  int64_t rc;
+  if ((rc = ensure_sparse_list(m)) < 0) return rc;
+  if (m->nSparse == 0 || m->nRows == 0) {
+    m->spListsOk = true;  // nothing to add: the kernel is told so by null lists
+    return CLA_OK;
+  }
+  if (m->totalVals >= (1ll << 32)) return CLA_OK;
+  const int nBlocks = (m->nRows + SKIP_ROWS - 1) / SKIP_ROWS;
+  const int64_t warps = (int64_t)m->nSparse * nBlocks;
+  const unsigned grid = (unsigned)((warps * 32 + 255) / 256);
+  unsigned long long* dCnt = nullptr;
+  CLA_CUDA(cudaMalloc((void**)&dCnt, 2 * sizeof(unsigned long long)));
+  auto fail_free = [&](std::vector<void*> ps, int64_t code, const std::string& msg) {
+    for (void* p : ps)
+      if (p) cudaFree(p);
+    cudaFree(dCnt);
+    return code == CLA_OK ? CLA_OK : fail(code, msg);
+  };
+  CLA_CUDA(cudaMemsetAsync(dCnt, 0, 2 * sizeof(unsigned long long), s));
+  k_sparse_emit<<<grid, 256, 0, s>>>(m->dGroups, m->dSparseIdx, m->nSparse, m->nRows, nullptr, nullptr, nullptr, dCnt);  // count
+  unsigned long long cnt[2] = {0, 0};
+  CLA_CUDA(cudaMemcpyAsync(cnt, dCnt, sizeof(cnt), cudaMemcpyDeviceToHost, s));
+  CLA_CUDA(cudaStreamSynchronize(s));
+  const int64_t nStep = (int64_t)cnt[0], nWin = (int64_t)cnt[1];
+  if (nStep >= (1ll << 31) || nWin >= (1ll << 31)) return fail_free({}, CLA_OK, "");
+  const int nUnits = (m->nRows + G3_UNIT - 1) / G3_UNIT;
+  const int64_t nStepPtr = (int64_t)nUnits * (G3_UNIT / G3_STEP) + 1, nWinPtr = (int64_t)nUnits * (G3_UNIT / G3_WIN) + 1;
+  // sort buffers (freed below), then the final lists
+  unsigned long long *k0 = nullptr, *k1 = nullptr, *wk0 = nullptr, *wk1 = nullptr;
+  uint32_t *v0 = nullptr, *v1 = nullptr;
+  void* tmp = nullptr;
+  auto A = [&](void** p, size_t bytes) { return cudaMalloc(p, std::max<size_t>(bytes, 16)) == cudaSuccess; };
+  if (!A((void**)&k0, nStep * 8) || !A((void**)&k1, nStep * 8) || !A((void**)&v0, nStep * 4) || !A((void**)&v1, nStep * 4) ||
+      !A((void**)&wk0, nWin * 8) || !A((void**)&wk1, nWin * 8)) {
+    cudaGetLastError();
+    return fail_free({k0, k1, v0, v1, wk0, wk1}, CLA_OK, "");
+  }
+  CLA_CUDA(cudaMemsetAsync(dCnt, 0, 2 * sizeof(unsigned long long), s));
+  k_sparse_emit<<<grid, 256, 0, s>>>(m->dGroups, m->dSparseIdx, m->nSparse, m->nRows, k0, v0, wk0, dCnt);
+  size_t tb1 = 0, tb2 = 0;
+  cub::DeviceRadixSort::SortPairs(nullptr, tb1, k0, k1, v0, v1, (int)nStep, 0, 64, s);
+  cub::DeviceRadixSort::SortKeys(nullptr, tb2, wk0, wk1, (int)nWin, 0, 64, s);
+  if (!A(&tmp, std::max(tb1, tb2))) {
+    cudaGetLastError();
+    return fail_free({k0, k1, v0, v1, wk0, wk1}, CLA_OK, "");
+  }
+  if (nStep) cub::DeviceRadixSort::SortPairs(tmp, tb1, k0, k1, v0, v1, (int)nStep, 0, 64, s);
+  if (nWin) cub::DeviceRadixSort::SortKeys(tmp, tb2, wk0, wk1, (int)nWin, 0, 64, s);
+  void *stepItems = nullptr, *winItems = nullptr, *stepPtr = nullptr, *winPtr = nullptr;
+  if (!A(&stepItems, nStep * sizeof(SpItem)) || !A(&winItems, nWin * sizeof(SpItem)) || !A(&stepPtr, nStepPtr * 4) ||
+      !A(&winPtr, nWinPtr * 4)) {
+    cudaGetLastError();
+    return fail_free({k0, k1, v0, v1, wk0, wk1, tmp, stepItems, winItems, stepPtr, winPtr}, CLA_OK, "");
+  }
+  const unsigned long long* sk = nStep ? k1 : k0;
+  const unsigned long long* wk = nWin ? wk1 : wk0;
+  k_sparse_pack<<<1184, 256, 0, s>>>(sk, nStep ? v1 : v0, nStep, (SpItem*)stepItems);
+  k_sparse_pack<<<1184, 256, 0, s>>>(wk, nullptr, nWin, (SpItem*)winItems);
+  k_sparse_ptr<<<(unsigned)((nStepPtr + 255) / 256), 256, 0, s>>>(sk, nStep, (uint32_t*)stepPtr, nStepPtr);
+  k_sparse_ptr<<<(unsigned)((nWinPtr + 255) / 256), 256, 0, s>>>(wk, nWin, (uint32_t*)winPtr, nWinPtr);
+  CLA_CUDA(cudaStreamSynchronize(s));
+  CLA_CUDA(cudaGetLastError());
+  for (void* p : {(void*)k0, (void*)k1, (void*)v0, (void*)v1, (void*)wk0, (void*)wk1, tmp, (void*)dCnt}) cudaFree(p);
+  for (void* p : {stepItems, winItems, stepPtr, winPtr}) m->allocs.push_back(p);
+  m->dStepItems = stepItems;
+  m->dWinItems = winItems;
+  m->dStepPtr = (uint32_t*)stepPtr;
+  m->dWinPtr = (uint32_t*)winPtr;
+  m->deviceBytes += (nStep + nWin) * (int64_t)sizeof(SpItem) + (nStepPtr + nWinPtr) * 4;
+  m->stats.device_bytes = m->deviceBytes;
+  m->spListsOk = true;
   return CLA_OK;
 }
 
@@ -756,23 +741,39 @@ int64_t launch_rmm_dmma(Matrix* m, const double* dV, int vCols, double* dOut, cu
     m->stats.kernel_launches++;
   }
   const size_t smem = std::max((size_t)(GM_KC * GM_LDA + GM_KC * GM_LDB), (size_t)(GM_TR * GM_LDC + GM_TN)) * sizeof(double);
-  const size_t smem2 = (size_t)GM_TR * GM_LDC * sizeof(double) + 8 * Q_CAP * sizeof(WorkItem) + QB_CAP * 4 +
-                       8 * QD_CAP * sizeof(DeltaItem) + 32 * 4 + 5 * GM_TN * sizeof(double);
+  if ((rc = build_sparse_lists(m, s)) < 0) return rc;
   static bool attrSet[64] = {};  // per device: function attributes belong to the device's context
   bool& attr = attrSet[m->device & 63];
   if (!attr) {
     CLA_CUDA(cudaFuncSetAttribute(k_rmm_dmma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    CLA_CUDA(cudaFuncSetAttribute(k_rmm_dmma2<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2));
-    CLA_CUDA(cudaFuncSetAttribute(k_rmm_dmma2<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2));
+    CLA_CUDA(cudaFuncSetAttribute(k_rmm_dmma3<8, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+    CLA_CUDA(cudaFuncSetAttribute(k_rmm_dmma3<4, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
     attr = true;
   }
   prof_begin(m, s);
-  if (m->nSdcGroups <= 256 && m->nRleGroups <= 256 && m->totalVals < (1ll << 32)) {
-    dim3 grid((m->nRows + SKIP_ROWS - 1) / SKIP_ROWS, (vCols + GM_TN - 1) / GM_TN);
-    auto kern = m->denseQuad ? k_rmm_dmma2<true> : k_rmm_dmma2<false>;
-    kern<<<grid, GM_THREADS, smem2, s>>>(m->dGroups, (const DenseDesc*)m->dDenseDesc, m->nDenseCols,
-                                               (const int32_t*)m->dSdcIdx, m->nSdcGroups, (const int32_t*)m->dRleIdx,
-                                               m->nRleGroups, m->nRows, dV, vCols, P, constRow, dOut);
+  if (m->spListsOk && (m->nSparse == 0 || (int64_t)m->totalVals * vCols * 8 < (1ll << 32))) {  // table-row offsets are 32-bit
+    static const int wideEnv = getenv("CLA_RMM_WIDE_TILES") ? atoi(getenv("CLA_RMM_WIDE_TILES")) : -1;  // tuning aid
+    const bool wide = wideEnv >= 0 ? wideEnv != 0 : vCols > 32;  // 64 output columns per CTA, or 32
+    const int TN = wide ? 64 : 32, W = 16;
+    const int kMax = wide ? G3<8, 16>::KMAX : G3<4, 16>::KMAX;
+    const int ldb = TN + 4, wbuf = wide ? G3<8, 16>::WBUF : G3<4, 16>::WBUF;
+    const int nUnits = (m->nRows + G3_UNIT - 1) / G3_UNIT;
+    const int gridY = (vCols + TN - 1) / TN;
+    dim3 grid((unsigned)std::max(1, std::min(std::max(1, m->smCount / gridY), (nUnits + W - 1) / W)), gridY);
+    const DenseDesc* dd = (const DenseDesc*)m->dDenseDesc;
+    int k0 = 0;
+    do {  // dense-operand columns in slices that fit shared memory; the first launch also adds the sparse groups
+      const int nk = std::min(kMax, m->nDenseCols - k0);
+      const bool first = k0 == 0;
+      const size_t smem3 = ((size_t)((nk + GM_KC - 1) / GM_KC * GM_KC) * ldb + (size_t)W * wbuf) * sizeof(double);
+      auto kern = wide ? k_rmm_dmma3<8, 16> : k_rmm_dmma3<4, 16>;
+      kern<<<grid, W * 32, smem3, s>>>(dd + k0, nk, first ? (const SpItem*)m->dStepItems : nullptr,
+                                       first ? m->dStepPtr : nullptr, (const SpItem*)m->dWinItems, m->dWinPtr, m->nRows, dV,
+                                       vCols, P, first ? constRow : nullptr, dOut, first ? 0 : 1);
+      m->stats.kernel_launches++;
+      k0 += nk;
+    } while (k0 < m->nDenseCols);
+    m->stats.kernel_launches--;  // counted once more below
   } else {
     dim3 grid((m->nRows + GM_TR - 1) / GM_TR, (vCols + GM_TN - 1) / GM_TN);
     k_rmm_dmma<<<grid, GM_THREADS, smem, s>>>(m->dGroups, m->nDev, (const DenseCol*)m->dDenseCols, m->nDenseCols, m->nRows,
