@@ -8,6 +8,7 @@
 // Constant columns are part of the decompressed chunk, so no correction layer is needed.
 #include "cla_common.cuh"
 #include <algorithm>
+#include <cstdlib>
 
 namespace cla {
 
@@ -20,6 +21,16 @@ __device__ __forceinline__ void dmma884(double& c0, double& c1, double a, double
   asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};"
                : "+d"(c0), "+d"(c1)
                : "d"(a), "d"(b));
+}
+
+// m16n8k8: eight times the flops of m8n8k4 per instruction and, per flop, half the B-fragment bytes (a 16-row tile
+// reuses each B value for twice the rows). Fragments (PTX ISA, mma.m16n8k8 .f64): a0 (g, t), a1 (g + 8, t),
+// a2 (g, t + 4), a3 (g + 8, t + 4); b0 (k = t, n = g), b1 (k = t + 4, n = g); c0 (g, 2t), c1 (g, 2t + 1),
+// c2 (g + 8, 2t), c3 (g + 8, 2t + 1), with g = lane >> 2, t = lane & 3.
+__device__ __forceinline__ void dmma1688(double (&c)[4], double a0, double a1, double a2, double a3, double b0, double b1) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f64.f64.f64.f64 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+d"(c[0]), "+d"(c[1]), "+d"(c[2]), "+d"(c[3])
+               : "d"(a0), "d"(a1), "d"(a2), "d"(a3), "d"(b0), "d"(b1));
 }
 
 // Loads pinned where they are written: volatile asm is not moved across the (volatile) DMMAs, so a load issued
@@ -122,14 +133,13 @@ k_gemm_tn_dmma(const double* __restrict__ A, int aCols, const double* __restrict
 }
 
 // --------------------------------------------------------------------------------------------------
-// Up to 128 columns: one CTA holds the whole upper triangle of the result as 8x8 DMMA tiles, so nothing of the
+// Up to 128 columns: one CTA holds the whole upper triangle of the result as 16x8 DMMA tiles, so nothing of the
 // product is computed twice and only the triangle's tiles are computed at all. Rows are split across CTAs; each
 // adds its partial triangle to the result with atomics at the end.
 // FUSED: the 32-row stage is decoded straight from the maps and dictionaries (dense-map and uncompressed groups
 // only), so the dense form of X never exists, not even in L2. Otherwise the stage is read from a decompressed chunk.
 // --------------------------------------------------------------------------------------------------
 constexpr int TT_KT = 32;             // rows per stage
-constexpr int TT_LD = TT_KT + 4;      // stride of the transposed stage Xt[col][row]: = 4 mod 16
 
 // What the staging loop needs to know about one matrix column, kept in shared memory.
 struct TsmmCol {
@@ -159,15 +169,60 @@ constexpr int T16_MAXC = 8;   // columns decoded per warp and stage at 128 colum
 // pointers (map, dictionary) instead of the full record, whose reads were 40 % of the kernel's shared-memory load
 // instructions. SIMPLE = 1: single-column groups and no constant part; SIMPLE = 2: also the group width (co-coded
 // columns) and the constant part of the column.
+// The MMAs of one 32-row stage on 16 x 8 tiles for a warp that owns N of its TPW tile slots. N is a template
+// parameter, not a predicate on each MMA: a predicated-off MMA still takes its turn in the tensor pipe.
+// The fragments of k-step ks + 8 are loaded before the MMAs of k-step ks are issued.
+template <int N, int TPW, int LD>
+__device__ __forceinline__ void tsmm_stage_1688(const double* __restrict__ Xt, const int (&offA)[TPW], const int (&offB)[TPW],
+                                                uint32_t aMask, double (&c)[TPW][4]) {
+  double2 bC[N], aC0 = *(const double2*)&Xt[offA[0]], aC1 = *(const double2*)&Xt[offA[0] + 8 * LD];
+#pragma unroll
+  for (int sl = 0; sl < N; sl++) bC[sl] = *(const double2*)&Xt[offB[sl]];
+#pragma unroll
+  for (int ks = 0; ks < 32; ks += 8) {
+    double2 bN[N], aN0 = make_double2(0.0, 0.0), aN1 = make_double2(0.0, 0.0);
+    if (ks + 8 < 32) {
+      aN0 = *(const double2*)&Xt[offA[0] + ks + 8];
+      aN1 = *(const double2*)&Xt[offA[0] + 8 * LD + ks + 8];
+#pragma unroll
+      for (int sl = 0; sl < N; sl++) bN[sl] = *(const double2*)&Xt[offB[sl] + ks + 8];
+    }
+    double2 a0 = aC0, a1 = aC1;
+#pragma unroll
+    for (int sl = 0; sl < N; sl++) {
+      if (sl > 0 && ((aMask >> sl) & 1u)) {
+        a0 = *(const double2*)&Xt[offA[sl] + ks];
+        a1 = *(const double2*)&Xt[offA[sl] + 8 * LD + ks];
+      }
+      dmma1688(c[sl], a0.x, a1.x, a0.y, a1.y, bC[sl].x, bC[sl].y);
+    }
+    if (ks + 8 < 32) {
+      aC0 = aN0;
+      aC1 = aN1;
+#pragma unroll
+      for (int sl = 0; sl < N; sl++) bC[sl] = bN[sl];
+    }
+  }
+}
+
+// The triangle is cut into 16 x 8 tiles for m16n8k8 (8 x 8 tiles on m8n8k4 needed twice the B-fragment bytes per
+// flop and four times the instructions; measured 10.6 -> 10.3 ms on 20M x 100). The stage keeps its rows (the k dimension) in the
+// order 0, 4, 1, 5, 2, 6, 3, 7 within every group of eight, so that the two k values a lane needs of an A or B
+// fragment are adjacent: one 128-bit load per fragment half; its stride TT_LDB = 8 mod 16 makes those loads
+// conflict free (a quarter-warp reads 64 contiguous bytes of two columns).
+constexpr int TT_LDB = TT_KT + 8;
 template <bool FUSED, int MT, int TPW, int SIMPLE>
 __global__ void __launch_bounds__(T16_THREADS, 1)
 k_tsmm_tri16(const DevGroup* __restrict__ groups, const int32_t* __restrict__ colSrc, const double* __restrict__ constV,
              const double* __restrict__ X, int rowBegin, int rowEnd, int nCols, double* __restrict__ C, int32_t* err) {
-  extern __shared__ __align__(16) double XtAll[];  // four stages of [NT * 8][TT_LD], the column records, four mbarriers
+  extern __shared__ __align__(16) double XtAll[];  // four stages of [nColsPad][TT_LDB], the column records, four mbarriers
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int NT = (nCols + 7) >> 3;
-  const int nColsPad = NT * 8;
-  const int stageDoubles = nColsPad * TT_LD;
+  constexpr int LD = TT_LDB;
+  constexpr int CW = 4;                             // accumulator doubles per tile slot
+  const int NT = (nCols + 7) >> 3;                  // 8-column tiles
+  const int NI = (nCols + 15) >> 4;                 // tile rows (16 matrix columns each)
+  const int nColsPad = NI * 16;                     // columns of the stage (zero beyond nCols)
+  const int stageDoubles = nColsPad * LD;
   TsmmCol* cols = (TsmmCol*)(XtAll + 4 * stageDoubles);
   uint64_t* bars = (uint64_t*)(cols + nColsPad);
   if (tid == 0) {
@@ -218,7 +273,10 @@ k_tsmm_tri16(const DevGroup* __restrict__ groups, const int32_t* __restrict__ co
     __syncthreads();
   }
   // this warp's tiles: [t0, t1) of the row-major order of the upper triangle
-  const int nTiles = NT * (NT + 1) / 2;
+  // tile row I holds the tiles (I, J) with J >= firstJ(I): every 8-column tile that reaches the diagonal or lies above it
+  auto rowLen = [&](int I) { return NT - 2 * I; };
+  auto firstJ = [&](int I) { return 2 * I; };
+  const int nTiles = NI * NT - NI * (NI - 1);
   const int t0 = nTiles * warp / T16_WARPS, t1 = nTiles * (warp + 1) / T16_WARPS;
   const int am = lane >> 2, ak = lane & 3;
   // Fragment offsets of each of the TPW tile slots. A slot the warp does not own points at tile (0, 0) and its
@@ -227,31 +285,34 @@ k_tsmm_tri16(const DevGroup* __restrict__ groups, const int32_t* __restrict__ co
   int offA[TPW], offB[TPW];
   uint32_t aMask = 1;
   {
-    int I = 0, base = 0;  // base = linear index of tile (I, I)
-    while (I < NT && base + (NT - I) <= t0) {
-      base += NT - I;
+    int I = 0, base = 0;  // base = linear index of the first tile of row I
+    while (I < NI && base + rowLen(I) <= t0) {
+      base += rowLen(I);
       I++;
     }
-    int J = I + (t0 - base);
+    int J = firstJ(I) + (t0 - base);
 #pragma unroll
     for (int sl = 0; sl < TPW; sl++) {
       if (t0 + sl < t1) {
-        offA[sl] = (I * 8 + am) * TT_LD + ak;
-        offB[sl] = (J * 8 + am) * TT_LD + ak;
-        if (J == I) aMask |= 1u << sl;
+        offA[sl] = (I * 16 + am) * LD + 2 * ak;
+        offB[sl] = (J * 8 + am) * LD + 2 * ak;
+        if (J == firstJ(I)) aMask |= 1u << sl;
         if (++J == NT) {
           I++;
-          J = I;
+          J = firstJ(I);
         }
       } else {
-        offA[sl] = offB[sl] = am * TT_LD + ak;
+        offA[sl] = offB[sl] = am * LD + 2 * ak;
         aMask |= 1u << sl;
       }
     }
   }
-  double c[TPW][2];
+  const int nMine = t1 - t0;
+  double c[TPW][CW];
 #pragma unroll
-  for (int i = 0; i < TPW; i++) c[i][0] = c[i][1] = 0.0;
+  for (int i = 0; i < TPW; i++)
+#pragma unroll
+    for (int u = 0; u < CW; u++) c[i][u] = 0.0;
 
   const int64_t nStages = ((int64_t)(rowEnd - rowBegin) + TT_KT - 1) / TT_KT;
   const int64_t sa = nStages * blockIdx.x / gridDim.x, sb = nStages * (blockIdx.x + 1) / gridDim.x;
@@ -308,7 +369,8 @@ k_tsmm_tri16(const DevGroup* __restrict__ groups, const int32_t* __restrict__ co
     for (int b = 0; b < T16_MAXC; b++) {
       const int cc = warp + T16_WARPS * b;
       if (cc < nColsPad)
-        Xt[cc * TT_LD + lane] = vals[b] + ((FUSED && inRange && SIMPLE != 1) ? (SIMPLE == 2 ? cstArr[cc] : cols[cc].cst) : 0.0);
+        Xt[cc * LD + ((lane & ~7) | ((lane & 3) << 1) | ((lane >> 2) & 1))] =
+            vals[b] + ((FUSED && inRange && SIMPLE != 1) ? (SIMPLE == 2 ? cstArr[cc] : cols[cc].cst) : 0.0);
     }
   };
   // Four stage buffers, each with an mbarrier that counts the 512 threads' "my part of this stage is stored". A warp
@@ -355,50 +417,34 @@ k_tsmm_tri16(const DevGroup* __restrict__ groups, const int32_t* __restrict__ co
     // the one before it; no branch in the loop body (the A reload is a predicated load)
     // (the fragments of k-step ks + 4 are loaded into registers before the DMMAs of k-step ks are issued, so the
     // shared-memory latency is covered by the warp's own DMMAs rather than by the three other warps of its scheduler)
-    double bC[TPW], aC = Xt[offA[0]];
-#pragma unroll
-    for (int sl = 0; sl < TPW; sl++) bC[sl] = Xt[offB[sl]];
-#pragma unroll
-    for (int ks = 0; ks < TT_KT; ks += 4) {
-      double bN[TPW], aN = 0.0;
-      if (ks + 4 < TT_KT) {
-        aN = Xt[offA[0] + ks + 4];
-#pragma unroll
-        for (int sl = 0; sl < TPW; sl++) bN[sl] = Xt[offB[sl] + ks + 4];
-      }
-      double a = aC;
-#pragma unroll
-      for (int sl = 0; sl < TPW; sl++) {
-        if (sl > 0 && ((aMask >> sl) & 1u)) a = Xt[offA[sl] + ks];
-        dmma884(c[sl][0], c[sl][1], a, bC[sl]);
-      }
-      if (ks + 4 < TT_KT) {
-        aC = aN;
-#pragma unroll
-        for (int sl = 0; sl < TPW; sl++) bC[sl] = bN[sl];
-      }
+    {
+      static_assert(TT_KT == 32, "tsmm_stage_1688 walks 32 rows");
+      if (nMine == TPW) tsmm_stage_1688<TPW, TPW, LD>(Xt, offA, offB, aMask, c);
+      else if (nMine == TPW - 1) tsmm_stage_1688<(TPW > 1 ? TPW - 1 : 1), TPW, LD>(Xt, offA, offB, aMask, c);
+      else if (nMine == TPW - 2) tsmm_stage_1688<(TPW > 2 ? TPW - 2 : 1), TPW, LD>(Xt, offA, offB, aMask, c);
+      else if (nMine > 0) tsmm_stage_1688<1, TPW, LD>(Xt, offA, offB, aMask, c);
     }
   }
   // ---- add the partial tiles ----
   {
     int I = 0, base = 0;
-    while (I < NT && base + (NT - I) <= t0) {
-      base += NT - I;
+    while (I < NI && base + rowLen(I) <= t0) {
+      base += rowLen(I);
       I++;
     }
-    int J = I + (t0 - base);
+    int J = firstJ(I) + (t0 - base);
 #pragma unroll
     for (int sl = 0; sl < TPW; sl++) {
       if (t0 + sl < t1) {
-        const int gi = I * 8 + (lane >> 2);
 #pragma unroll
-        for (int u = 0; u < 2; u++) {
-          const int gj = J * 8 + (lane & 3) * 2 + u;
+        for (int u = 0; u < CW; u++) {
+          const int gi = I * 16 + (lane >> 2) + 8 * (u >> 1);
+          const int gj = J * 8 + (lane & 3) * 2 + (u & 1);
           if (gi < nCols && gj < nCols && gi <= gj && c[sl][u] != 0.0) atomicAdd(&C[(size_t)gi * nCols + gj], c[sl][u]);
         }
         if (++J == NT) {
           I++;
-          J = I;
+          J = firstJ(I);
         }
       }
     }
@@ -480,8 +526,9 @@ int64_t measure_fp64_peaks(int device, double* dmmaTflops, double* dfmaTflops) {
   return CLA_OK;
 }
 
-// The 16-warp kernel is instantiated for 3, 6 and 9 tile slots per warp (up to 48, 104 and 128 columns) and for
-// the map widths the decode specialises on.
+// The 16-warp kernel is instantiated for the map widths the decode specialises on and, by tile slots per warp, for
+// 3, 6 and 9 slots of 8 x 8 tiles (up to 48, 104 and 128 columns; rows read from a decompressed chunk) and for 2 and 5
+// slots of 16 x 8 tiles (up to 64 and 128 columns; decoded on the fly).
 template <int TPW>
 static void tri16_go(bool fused, int mt, int simple, int grid, size_t smem, cudaStream_t s, const DevGroup* groups,
                      const int32_t* colSrc, const double* constV, const double* X, int rows, int n, double* dOut, int32_t* err) {
@@ -498,10 +545,10 @@ static void tri16_go(bool fused, int mt, int simple, int grid, size_t smem, cuda
 }
 static void launch_tri16(bool fused, int mt, int simple, int n, int grid, size_t smem, cudaStream_t s, const DevGroup* groups,
                          const int32_t* colSrc, const double* constV, const double* X, int rows, double* dOut, int32_t* err) {
-  const int NT = (n + 7) / 8, perWarp = (NT * (NT + 1) / 2 + T16_WARPS - 1) / T16_WARPS;
-  if (perWarp <= 3) tri16_go<3>(fused, mt, simple, grid, smem, s, groups, colSrc, constV, X, rows, n, dOut, err);
-  else if (perWarp <= 6) tri16_go<6>(fused, mt, simple, grid, smem, s, groups, colSrc, constV, X, rows, n, dOut, err);
-  else tri16_go<9>(fused, mt, simple, grid, smem, s, groups, colSrc, constV, X, rows, n, dOut, err);
+  const int NT = (n + 7) / 8, NI = (n + 15) / 16, perWarp = (NI * NT - NI * (NI - 1) + T16_WARPS - 1) / T16_WARPS;
+  if (perWarp <= 2) tri16_go<2>(fused, mt, simple, grid, smem, s, groups, colSrc, constV, X, rows, n, dOut, err);
+  else if (perWarp <= 4) tri16_go<4>(fused, mt, simple, grid, smem, s, groups, colSrc, constV, X, rows, n, dOut, err);
+  else tri16_go<5>(fused, mt, simple, grid, smem, s, groups, colSrc, constV, X, rows, n, dOut, err);
 }
 template <int TPW>
 static int64_t tri16_set_smem_t(int bytes) {
@@ -520,9 +567,9 @@ static int64_t tri16_set_smem_t(int bytes) {
 }
 static int64_t tri16_set_smem(int bytes) {
   int64_t rc;
-  if ((rc = tri16_set_smem_t<3>(bytes)) < 0) return rc;
-  if ((rc = tri16_set_smem_t<6>(bytes)) < 0) return rc;
-  return tri16_set_smem_t<9>(bytes);
+  if ((rc = tri16_set_smem_t<2>(bytes)) < 0) return rc;
+  if ((rc = tri16_set_smem_t<4>(bytes)) < 0) return rc;
+  return tri16_set_smem_t<5>(bytes);
 }
 
 int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s) {
@@ -534,11 +581,11 @@ int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s) {
   const bool tri = n <= 128;
   bool denseOnly = m->colSrcValid;
   for (auto& g : m->groups) denseOnly &= (g.type == GT_DDC || g.type == GT_UNC);
-  const size_t tri16Smem = (size_t)((n + 7) / 8 * 8) * (4 * TT_LD * sizeof(double) + sizeof(TsmmCol) + 28) + 4 * sizeof(uint64_t);
+  const size_t tri16Smem = (size_t)((n + 15) / 16 * 16) * (4 * TT_LDB * sizeof(double) + sizeof(TsmmCol) + 28) + 4 * sizeof(uint64_t);
   static bool attrSet[64] = {};  // per device: function attributes belong to the device's context
   bool& attr = attrSet[m->device & 63];
   if (!attr) {
-    if ((rc = tri16_set_smem(128 * (4 * TT_LD * 8 + (int)sizeof(TsmmCol) + 28) + 32)) < 0) return rc;
+    if ((rc = tri16_set_smem(128 * (4 * TT_LDB * 8 + (int)sizeof(TsmmCol) + 28) + 32)) < 0) return rc;
     attr = true;
   }
   if (tri && denseOnly) {  // one launch over all rows, decoding as it goes
