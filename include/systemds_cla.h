@@ -157,6 +157,16 @@ int64_t cla_add_group_empty(cla_handle h, const int32_t* colIdx, int32_t gCols);
  * cla_mmchain  replaces lib/CLALibMMChain.java:92  mmChain(x, v, w, out, ctype, k): out[nCols] = t(X) (w * (X v))
  * cla_decompress replaces lib/CLALibDecompress.java:56  decompress(cmb, k): out[nRows x nCols] */
 int64_t cla_rmm(cla_handle h, const double* V, int32_t vRows, int32_t vCols, double* out);
+/* X * V kept compressed: replaces lib/CLALibRightMultBy.java:51 rightMultByMatrix(m1, m2, ret, k, allowOverlap = true),
+ * i.e. RMMOverlapping (:157-201). Returns the handle (> 0, finalized, same device) of an overlapping block
+ * [nRows x vCols] whose groups share the index structures of h and hold the dictionaries D_g * V[cols_g, :]; cost is
+ * proportional to the dictionaries, not to the rows (uncompressed groups excepted: their product is materialised).
+ * The new block takes every call a registered block takes (products, decompress, aggregates; t(h) %*% result through
+ * cla_tmm is the reference's overlapping-intermediate form of the matrix-multiply chain, lib/CLALibMMChain.java:109-122).
+ * It may outlive h: destroying h first only retires the handle, its device memory is released with the last such
+ * result. The _dev form takes V in device memory and enqueues on `stream` (it still synchronises that stream). */
+cla_handle cla_rmm_overlapping(cla_handle h, const double* V, int32_t vRows, int32_t vCols);
+cla_handle cla_rmm_overlapping_dev(cla_handle h, const double* dV, int32_t vRows, int32_t vCols, void* stream);
 int64_t cla_lmm(cla_handle h, const double* Yt, int32_t yRows, double* out);
 int64_t cla_tsmm(cla_handle h, double* out);
 int64_t cla_mmchain(cla_handle h, const double* v, const double* w, int32_t ctype, double* out);

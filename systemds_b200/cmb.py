@@ -269,12 +269,21 @@ class CLALibMatrixMult:
 
 class CLALibRightMultBy:
     @staticmethod
-    def rightMultByMatrix(m1: CompressedMatrixBlock, m2) -> np.ndarray:
+    def rightMultByMatrix(m1: CompressedMatrixBlock, m2, allowOverlap: bool = False):
+        """``m1 %*% m2``. With ``allowOverlap`` the result stays compressed (CLALibRightMultBy.java:51,157-201): an
+        overlapping ``CompressedMatrixBlock`` on the device that shares ``m1``'s index structures."""
         V = _f64(m2)
         if V.ndim == 1:
             V = V.reshape(-1, 1)
         if V.shape[0] != m1.clen:
             raise native.CLAError(-4, "rightMultByMatrix: inner dimensions do not match")
+        if allowOverlap:
+            h = check(native.lib().cla_rmm_overlapping(m1.handle(), ptr(V), V.shape[0], V.shape[1]))
+            st = native.cla_stats()
+            check(native.lib().cla_stats_get(h, C.byref(st)))
+            ret = CompressedMatrixBlock(m1.rlen, V.shape[1], overlapping=True)
+            ret._handle, ret.device, ret._reg_index = h, m1.device, list(range(st.n_groups))
+            return ret
         out = np.empty((m1.rlen, V.shape[1]), np.float64)
         nnz = check(native.lib().cla_rmm(m1.handle(), ptr(V), V.shape[0], V.shape[1], ptr(out)))
         return _wrap(out, nnz)
@@ -319,10 +328,18 @@ class CLALibTSMM:
 
 class CLALibMMChain:
     @staticmethod
-    def mmChain(x: CompressedMatrixBlock, v, w=None, ctype: int = CHAIN_XtXv) -> np.ndarray:
+    def mmChain(x: CompressedMatrixBlock, v, w=None, ctype: int = CHAIN_XtXv, allowOverlap: bool = False) -> np.ndarray:
+        """``t(x) %*% (w * (x %*% v))``. ``allowOverlap`` (XtXv only) keeps the intermediate ``x %*% v`` compressed and
+        multiplies the two compressed blocks (CLALibMMChain.java:109-122,128-131)."""
         v = _f64(v).reshape(-1)
         if v.shape[0] != x.clen:
             raise native.CLAError(-4, "mmChain: v must have nCols entries")
+        if allowOverlap and ctype == CHAIN_XtXv:
+            tmp = CLALibRightMultBy.rightMultByMatrix(x, v, allowOverlap=True)
+            try:
+                return CLALibLeftMultBy.leftMultByMatrixTransposed(tmp, x)
+            finally:
+                tmp.free()
         wv = None
         if ctype == CHAIN_XtwXv:
             if w is None:

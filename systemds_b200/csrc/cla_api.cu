@@ -107,8 +107,26 @@ cla_handle cla_create(int32_t nRows, int32_t nCols, int32_t overlapping) {
 int64_t cla_destroy(cla_handle h) {
   std::shared_ptr<Matrix> mp;
   if (!table_erase(h, &mp)) return fail(CLA_ERR_BAD_HANDLE, "unknown or destroyed handle");
-  std::lock_guard<std::mutex> lk(mp->mu);
-  release(mp.get());
+  std::shared_ptr<Matrix> parent;
+  {
+    std::lock_guard<std::mutex> lk(mp->mu);
+    if (mp->children > 0) {  // blocks from cla_rmm_overlapping still read this one's index structures
+      mp->zombie = true;
+      return CLA_OK;
+    }
+    release(mp.get());
+    parent = std::move(mp->parent);
+  }
+  while (parent) {  // the last child of a destroyed parent frees it too
+    std::shared_ptr<Matrix> next;
+    {
+      std::lock_guard<std::mutex> lk(parent->mu);
+      if (--parent->children > 0 || !parent->zombie) break;
+      release(parent.get());
+      next = std::move(parent->parent);
+    }
+    parent = std::move(next);
+  }
   return CLA_OK;
 }
 
@@ -649,6 +667,46 @@ int64_t cla_tmm_dev(cla_handle left, cla_handle right, double* dOut, void* strea
   rc = tmm_dev(l, r, dOut, s);
   const int64_t e1 = order_end(l, s), e2 = r != l ? order_end(r, s) : CLA_OK;
   return rc < 0 ? rc : (e1 < 0 ? e1 : (e2 < 0 ? e2 : rc));
+}
+
+// X %*% V as an overlapping compressed block (see make_overlapping)
+static cla_handle rmm_overlapping(cla_handle h, const double* V, bool vOnDevice, int32_t vRows, int32_t vCols, cudaStream_t userStream) {
+  std::shared_ptr<Matrix> mp = lookup(h);
+  if (!mp) return fail(CLA_ERR_BAD_HANDLE, "unknown or destroyed handle");
+  Matrix* m = mp.get();
+  std::lock_guard<std::mutex> lk(m->mu);
+  if (!m->finalized) return fail(CLA_ERR_STATE, "cla_finalize has not been called on this handle");
+  if (vRows != m->nCols || vCols < 0) return fail(CLA_ERR_SHAPE, "rmm: V must be [nCols x vCols]");
+  if (!V && (size_t)vRows * vCols) return fail(CLA_ERR_BAD_ARG, "rmm: null buffer");
+  CLA_CUDA(cudaSetDevice(m->device));
+  cudaStream_t s = vOnDevice ? userStream : m->stream;
+  int64_t rc;
+  if ((rc = order_begin(m, s)) < 0) return rc;
+  const double* dV = V;
+  if (!vOnDevice) {
+    const size_t bytes = (size_t)vRows * vCols * sizeof(double);
+    if ((rc = ensure_io(m, bytes + 256)) < 0) return rc;
+    if (bytes) CLA_CUDA(cudaMemcpyAsync(m->io, V, bytes, cudaMemcpyHostToDevice, s));
+    dV = (const double*)m->io;
+  }
+  auto child = std::make_shared<Matrix>();
+  m->stats.calls_rmm++;
+  rc = make_overlapping(m, child.get(), dV, vCols, s);  // synchronises s
+  m->lastValid = false;
+  if (rc < 0) {
+    release(child.get());
+    return rc;
+  }
+  child->parent = mp;
+  m->children++;
+  return table_insert(child);
+}
+
+cla_handle cla_rmm_overlapping(cla_handle h, const double* V, int32_t vRows, int32_t vCols) {
+  return rmm_overlapping(h, V, false, vRows, vCols, nullptr);
+}
+cla_handle cla_rmm_overlapping_dev(cla_handle h, const double* dV, int32_t vRows, int32_t vCols, void* stream) {
+  return rmm_overlapping(h, dV, true, vRows, vCols, (cudaStream_t)stream);
 }
 
 int64_t cla_rmm(cla_handle h, const double* V, int32_t vRows, int32_t vCols, double* out) {

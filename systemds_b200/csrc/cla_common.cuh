@@ -3,6 +3,7 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <memory>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -140,7 +141,14 @@ struct HostGroup {
 
 struct FastPlan;  // plans of the specialised DDC kernels (cla_fast.cu)
 
+struct Matrix;
 struct Matrix {
+  // A block returned by cla_rmm_overlapping shares the index structures of the block it was computed from; it
+  // keeps that block alive (parent), and a parent destroyed before its children only leaves the handle table: its
+  // device memory is released with the last child (children, zombie; both guarded by the parent's mutex).
+  std::shared_ptr<Matrix> parent;
+  int children = 0;
+  bool zombie = false;
   int32_t nRows = 0, nCols = 0;
   bool overlapping = false;
   bool finalized = false;
@@ -237,7 +245,13 @@ int64_t col_minmax(Matrix* m, std::vector<double>& lo, std::vector<double>& hi, 
 int64_t row_minmax(Matrix* m, int wantMax, double* dOut, cudaStream_t s);
 int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s);
 int64_t launch_tmm(Matrix* left, Matrix* right, double* dOut, cudaStream_t s);  // t(left) %*% right, both compressed
+// products on the dictionaries of two all-dense-map operands (cla_pairs.cu)
+bool pairs_eligible(const Matrix* L, const Matrix* R, bool self);
+int64_t launch_pairs(Matrix* L, Matrix* R, bool self, double* dOut, cudaStream_t s);
 int64_t launch_decompress(Matrix* m, double* dOut, cudaStream_t s);
+// X %*% V kept compressed: fills `child` (fresh Matrix) with groups that alias m's index structures (cla_generic.cu)
+int64_t make_overlapping(Matrix* m, Matrix* child, const double* dV, int vCols, cudaStream_t s);
+int64_t init_device_state(Matrix* m);  // stream, events, error word of a Matrix whose device is set (cla_finalize.cu)
 int64_t launch_decompress_range(Matrix* m, int r0, int r1, double* dOut, cudaStream_t s);
 int64_t launch_group_decode(Matrix* m, int devGroup, int32_t* dIds, cudaStream_t s);
 int64_t launch_group_counts(Matrix* m, int devGroup, unsigned long long* dCounts, cudaStream_t s);

@@ -402,7 +402,7 @@ static int64_t build_sdc_skip(const HostGroup& hg, int nRows, std::vector<SdcSki
   return CLA_OK;
 }
 
-int64_t finalize_device(Matrix* m) {
+int64_t init_device_state(Matrix* m) {
   CLA_CUDA(cudaSetDevice(m->device));
   cudaDeviceProp prop;
   CLA_CUDA(cudaGetDeviceProperties(&prop, m->device));
@@ -415,6 +415,12 @@ int64_t finalize_device(Matrix* m) {
   CLA_CUDA(cudaMalloc(&errp, 64));
   CLA_CUDA(cudaMemset(errp, 0, 64));
   m->dErr = (int32_t*)errp;
+  return CLA_OK;
+}
+
+int64_t finalize_device(Matrix* m) {
+  int64_t rc0 = init_device_state(m);
+  if (rc0 < 0) return rc0;
 
   m->constV.assign(m->nCols, 0.0);
   m->regToDev.assign(m->hg.size(), -1);

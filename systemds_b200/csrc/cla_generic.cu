@@ -220,6 +220,118 @@ int64_t launch_rmm(Matrix* m, const double* dV, int vCols, double* dOut, cudaStr
 }
 
 // --------------------------------------------------------------------------------------------------
+// X %*% V kept compressed (CLALibRightMultBy.RMMOverlapping, lib/CLALibRightMultBy.java:157-201): every dictionary
+// group of X becomes a group over all vCols result columns that keeps its index structure (the maps, offset
+// streams and run lists are shared with X, not copied) and gets the dictionary P_g = D_g * V[cols_g, :]
+// (ADictBasedColGroup.rightMultByMatrix, colgroup/ADictBasedColGroup.java:246-275); an uncompressed group becomes the
+// uncompressed product of its block (colgroup/ColGroupUncompressed.java, rightMultByMatrix); the constants become
+// constV * V (addConstant, :203-206). The result is an overlapping block: its cells are the sums over the groups.
+// --------------------------------------------------------------------------------------------------
+__global__ void k_unc_times_v(const double* __restrict__ dense, int gCols, const int32_t* __restrict__ cols, int64_t nRows,
+                              const double* __restrict__ V, int vCols, double* __restrict__ out) {
+  const int64_t n = nRows * vCols;
+  for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < n; e += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = e / vCols;
+    const int j = (int)(e - r * vCols);
+    double s = 0;
+    for (int c = 0; c < gCols; c++) s += dense[r * gCols + c] * V[(size_t)cols[c] * vCols + j];
+    out[e] = s;
+  }
+}
+__global__ void k_iota_cols(int32_t* p, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) p[i] = i;
+}
+
+int64_t make_overlapping(Matrix* m, Matrix* child, const double* dV, int vCols, cudaStream_t s) {
+  auto dalloc = [&](void** p, size_t bytes) -> int64_t {
+    *p = nullptr;
+    cudaError_t e = cudaMalloc(p, std::max<size_t>(bytes, 16));
+    if (e != cudaSuccess) return fail(CLA_ERR_NOMEM, std::string("cudaMalloc overlapping result: ") + cudaGetErrorString(e));
+    child->allocs.push_back(*p);
+    child->deviceBytes += (int64_t)bytes;
+    return CLA_OK;
+  };
+  int64_t rc;
+  child->nRows = m->nRows;
+  child->nCols = vCols;
+  child->overlapping = true;
+  child->multiCover = true;
+  child->colSrcValid = false;
+  child->device = m->device;
+  if ((rc = init_device_state(child)) < 0) return rc;
+  void *P = nullptr, *iota = nullptr, *cst = nullptr;
+  if ((rc = dalloc(&P, (size_t)std::max<int64_t>(m->totalVals, 1) * vCols * sizeof(double))) < 0) return rc;
+  if ((rc = dalloc(&iota, (size_t)std::max(vCols, 1) * sizeof(int32_t))) < 0) return rc;
+  if ((rc = dalloc(&cst, (size_t)std::max(vCols, 1) * sizeof(double))) < 0) return rc;
+  if (vCols > 0) k_iota_cols<<<(vCols + 255) / 256, 256, 0, s>>>((int32_t*)iota, vCols);
+  if (m->nDev > 0 && vCols > 0) {
+    int64_t maxE = 1;
+    for (auto& g : m->groups) maxE = std::max<int64_t>(maxE, (int64_t)g.nVals * vCols);
+    dim3 grid(m->nDev, (unsigned)std::max<int64_t>(1, std::min<int64_t>(64, (maxE + 255) / 256)));
+    k_dict_times_v<<<grid, 256, 0, s>>>(m->dGroups, dV, vCols, (double*)P, 0);
+  }
+  child->constV.assign(vCols, 0.0);
+  if (m->hasConst && vCols > 0) {
+    k_const_times_v<<<(vCols + 127) / 128, 128, 0, s>>>(m->dConstV, m->nCols, dV, vCols, (double*)cst);
+    CLA_CUDA(cudaMemcpyAsync(child->constV.data(), cst, (size_t)vCols * sizeof(double), cudaMemcpyDeviceToHost, s));
+  } else
+    CLA_CUDA(cudaMemsetAsync(cst, 0, (size_t)std::max(vCols, 1) * sizeof(double), s));
+  child->dConstV = (double*)cst;
+  // the groups: same index structures, new dictionaries / dense blocks, every group over all result columns
+  child->groups.clear();
+  child->hg.clear();
+  child->regToDev.clear();
+  for (int gi = 0; gi < m->nDev; gi++) {
+    DevGroup g = m->groups[gi];
+    HostGroup hg;  // the record kept after finalize: type, width, number of tuples
+    hg.type = g.origType;
+    hg.cols.resize(vCols);
+    for (int j = 0; j < vCols; j++) hg.cols[j] = j;
+    hg.nVals = g.origType == GT_OLE ? g.nVals - 1 : g.nVals;
+    if (g.type == GT_UNC) {
+      void* d = nullptr;
+      if ((rc = dalloc(&d, (size_t)m->nRows * vCols * sizeof(double))) < 0) return rc;
+      if ((int64_t)m->nRows * vCols > 0)
+        k_unc_times_v<<<grid_for((int64_t)m->nRows * vCols, 256), 256, 0, s>>>(g.dense, g.gCols, g.cols, m->nRows, dV, vCols, (double*)d);
+      g.dense = (const double*)d;
+    } else {
+      g.dict = g.dictRaw = (const double*)P + (size_t)g.valOff * vCols;
+    }
+    g.gCols = vCols;
+    g.cols = (const int32_t*)iota;
+    g.inFast = 0;
+    child->regToDev.push_back((int)child->groups.size());
+    child->groups.push_back(g);
+    child->hg.push_back(std::move(hg));
+  }
+  child->nDev = (int)child->groups.size();
+  child->totalVals = m->totalVals;
+  void* dg = nullptr;
+  if ((rc = dalloc(&dg, std::max<size_t>(child->groups.size(), 1) * sizeof(DevGroup))) < 0) return rc;
+  if (!child->groups.empty())
+    CLA_CUDA(cudaMemcpyAsync(dg, child->groups.data(), child->groups.size() * sizeof(DevGroup), cudaMemcpyHostToDevice, s));
+  child->dGroups = (DevGroup*)dg;
+  void* cs = nullptr;  // column -> group table: unused for overlapping blocks, but allocated like everywhere else
+  if ((rc = dalloc(&cs, (size_t)std::max(vCols, 1) * 2 * sizeof(int32_t))) < 0) return rc;
+  CLA_CUDA(cudaMemsetAsync(cs, 0xFF, (size_t)std::max(vCols, 1) * 2 * sizeof(int32_t), s));
+  child->dColSrc = (int32_t*)cs;
+  CLA_CUDA(cudaStreamSynchronize(s));
+  CLA_CUDA(cudaGetLastError());
+  child->hasConst = false;
+  for (double x : child->constV) child->hasConst |= (x != 0.0);
+  child->colMin.assign(vCols, 0.0);  // extrema of an overlapping block are taken from decompressed rows
+  child->colMax.assign(vCols, 0.0);
+  child->indexBytes = (int64_t)std::max<int64_t>(m->totalVals, 1) * vCols * 8;
+  child->stats.n_cols = vCols;
+  child->stats.n_groups = (int64_t)child->hg.size();
+  child->stats.device_bytes = child->deviceBytes;
+  child->stats.index_bytes = child->indexBytes;
+  child->finalized = true;
+  return CLA_OK;
+}
+
+// --------------------------------------------------------------------------------------------------
 // decompress = RMM with V = I restricted to the group's own columns: out[r, cols_g] += D_g[id_g(r), :]
 // One launch per group keeps the reference's "groups in list order" summation
 // (lib/CLALibDecompress.java:427-434) without atomics.

@@ -575,6 +575,15 @@ static int64_t tri16_set_smem(int bytes) {
 int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s) {
   const int n = m->nCols;
   if (n == 0) return CLA_OK;
+  if (m->nRows > 0 && pairs_eligible(m, m, true)) {  // few co-coded groups: on the dictionaries
+    const int64_t rc = launch_pairs(m, m, true, dOut, s);
+    if (rc < 0) return rc;
+    // overlapping groups add to a cell from several pairs, in no fixed order: copy the upper triangle down
+    k_mirror<<<std::max(1, std::min(1024, (int)(((int64_t)n * n + 255) / 256))), 256, 0, s>>>(dOut, n);
+    m->stats.kernel_launches++;
+    CLA_CUDA(cudaGetLastError());
+    return CLA_OK;
+  }
   CLA_CUDA(cudaMemsetAsync(dOut, 0, sizeof(double) * (size_t)n * n, s));
   if (m->nRows == 0) return CLA_OK;
   int64_t rc;
@@ -655,6 +664,7 @@ int64_t launch_tsmm(Matrix* m, double* dOut, cudaStream_t s) {
 int64_t launch_tmm(Matrix* L, Matrix* R, double* dOut, cudaStream_t s) {
   const int a = L->nCols, b = R->nCols;
   if ((int64_t)a * b == 0) return CLA_OK;
+  if (L->nRows > 0 && pairs_eligible(L, R, false)) return launch_pairs(L, R, false, dOut, s);  // pair pre-aggregation
   CLA_CUDA(cudaMemsetAsync(dOut, 0, sizeof(double) * (size_t)a * b, s));
   if (L->nRows == 0) return CLA_OK;
   int64_t rc;

@@ -50,6 +50,8 @@ SIGNATURES = {
     "cla_add_group_const": [_I64, _P, _I32, _P],
     "cla_add_group_empty": [_I64, _P, _I32],
     "cla_rmm": [_I64, _P, _I32, _I32, _P],
+    "cla_rmm_overlapping": [_I64, _P, _I32, _I32],
+    "cla_rmm_overlapping_dev": [_I64, _P, _I32, _I32, _P],
     "cla_lmm": [_I64, _P, _I32, _P],
     "cla_read_block": [_P, _I64, _P, _P],
     "cla_tsmm": [_I64, _P],

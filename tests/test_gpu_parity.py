@@ -465,6 +465,47 @@ def test_compressed_times_compressed(oracle, case, nRows):
     B.free()
 
 
+PAIR_CASES = [
+    (("ddc2", "ddc2", "ddc2"), ("ddc2", "ddc2"), False),
+    (("ddc2", "ddcfor", "ddc2", "const"), ("ddc2", "ddc_bit", "ddc2", "ddcfor"), False),
+    (("ddc2", "ole", "ddc2"), ("ddc2", "ddc2", "empty"), False),
+    (("ddc2", "ddc2", "ddc2", "const"), ("ddc2", "ddc2", "ddc2"), True),
+]
+
+
+@pytest.mark.parametrize("case", range(len(PAIR_CASES)))
+@pytest.mark.parametrize("nRows", [1, 1000, 70001])
+def test_products_on_the_dictionaries(oracle, case, nRows):
+    """t(A) %*% B and t(X) %*% X when every group is a dense-map group and there are few co-coded groups: the joint
+    count tables of the group pairs (integer histograms) times the dictionaries, instead of decompressing
+    (APreAgg.leftMultByAColGroup, AColGroupCompressed.tsmm, APreAgg.tsmmAColGroup). Checked against the oracle's pair
+    pre-aggregation and the dense product; the self-product is bit-symmetric; the integer case is exact."""
+    ka, kb, overlap = PAIR_CASES[case]
+    A = datagen.random_cmb(700 + case, nRows, ka, overlap).to_device()
+    B = datagen.random_cmb(800 + case, nRows, kb, overlap).to_device()
+    XA, XB = dense_of(A), dense_of(B)
+    aA, aB = abs_dense_of(A), abs_dense_of(B)
+    scale = aA.T @ aB + 1e-300
+    k0 = A.stats()["kernel_launches"]
+    got = CLALibLeftMultBy.leftMultByMatrixTransposed(B, A)
+    # the pair path launches a handful of kernels, never one decompress + GEMM per row chunk
+    assert A.stats()["kernel_launches"] - k0 <= 9
+    assert rel_err(got, XA.T @ XB, scale) < TOL
+    if not overlap:
+        assert rel_err(got, oracle.OracleMatrix(A).tmm(oracle.OracleMatrix(B)), scale) < TOL
+    self_ = CLALibTSMM.leftMultByTransposeSelf(A)
+    assert rel_err(self_, oracle.dense_tsmm_ld(XA), aA.T @ aA + 1e-300) < TOL
+    assert np.array_equal(self_, self_.T)
+    A.free()
+    B.free()
+    # integer dictionaries: exact (lib/CLALibMMChainTest's 0-ULP bar for the self-product)
+    if not overlap and not any("for" in k for k in ka):  # the generator draws frame-of-reference tuples as reals
+        Ai = datagen.random_cmb(900 + case, nRows, ka, integer=True).to_device()
+        Xi = dense_of(Ai)
+        assert np.array_equal(np.array(CLALibTSMM.leftMultByTransposeSelf(Ai)), Xi.T @ Xi)
+        Ai.free()
+
+
 @pytest.mark.parametrize("name,kinds,overlap", CASES)
 @pytest.mark.parametrize("nRows", [1, 37, 5000, 70001])
 def test_min_max_aggregates(oracle, name, kinds, overlap, nRows):
@@ -707,3 +748,39 @@ def test_groups_registered_from_device_memory(oracle):
     g = cg.ColGroupDDC([0], rng.standard_normal((5, 1)), DeviceMap(MAP_UBYTE, nRows, 5, bad.data_ptr(), nRows, owner=bad))
     with pytest.raises(CLAError):
         CompressedMatrixBlock(nRows, 1, [g]).to_device()
+
+
+@pytest.mark.parametrize("kinds,overlap", [(("ddc", "ddc2", "sdc", "rle", "unc", "const", "ole"), False),
+                                           (("ddc2", "ddc2", "ddc_bit"), False), (("ddc", "sdc", "rle", "ddc2"), True)])
+@pytest.mark.parametrize("nRows", [1, 1000, 70001])
+def test_right_product_kept_compressed(oracle, kinds, overlap, nRows):
+    """rightMultByMatrix(..., allowOverlap=True) (RMMOverlapping, lib/CLALibRightMultBy.java:157-201): the result is an
+    overlapping block on the device that shares the operand's index structures. Its decompressed form equals the dense
+    product, it takes further products, it survives its parent, and t(X) %*% (X %*% v) through it equals mmChain."""
+    rng = np.random.default_rng(nRows)
+    X_ = datagen.random_cmb(1200 + nRows, nRows, kinds, overlap).to_device()
+    X = dense_of(X_)
+    aX = abs_dense_of(X_)
+    for vc in (1, 5):
+        V = rng.standard_normal((X_.clen, vc))
+        R = CLALibRightMultBy.rightMultByMatrix(X_, V, allowOverlap=True)
+        assert isinstance(R, CompressedMatrixBlock) and R.isOverlapping() and (R.rlen, R.clen) == (nRows, vc)
+        sc = aX @ np.abs(V) + 1e-300
+        assert rel_err(CLALibDecompress.decompress(R), X @ V, sc) < TOL
+        assert rel_err(CLALibDecompress.decompress(R), CLALibRightMultBy.rightMultByMatrix(X_, V), sc) < TOL
+        W = rng.standard_normal((vc, 3))
+        assert rel_err(CLALibRightMultBy.rightMultByMatrix(R, W), (X @ V) @ W, sc @ np.abs(W) + 1e-300) < TOL
+        y = rng.standard_normal((2, nRows))
+        assert rel_err(CLALibLeftMultBy.leftMultByMatrix(R, y), y @ (X @ V), np.abs(y) @ sc + 1e-300) < TOL
+        # t(X) %*% (X %*% V): two compressed blocks
+        got = CLALibLeftMultBy.leftMultByMatrixTransposed(R, X_)
+        assert rel_err(got, X.T @ (X @ V), aX.T @ sc + 1e-300) < 10 * TOL
+        R.free()
+    v = rng.standard_normal(X_.clen)
+    s = aX.T @ (aX @ np.abs(v)) + 1e-300
+    assert rel_err(CLALibMMChain.mmChain(X_, v, allowOverlap=True).ravel(), CLALibMMChain.mmChain(X_, v).ravel(), s) < 10 * TOL
+    # the result outlives the block it came from
+    R = CLALibRightMultBy.rightMultByMatrix(X_, v, allowOverlap=True)
+    X_.free()
+    assert rel_err(CLALibDecompress.decompress(R).ravel(), X @ v, aX @ np.abs(v) + 1e-300) < TOL
+    R.free()
