@@ -569,42 +569,51 @@ __device__ __forceinline__ void rmm_f_chunk(const LmmChunk& ch, const FusedUnit*
       mul[u] = 1u << units[(ch.unit0 + u) * 16 + slot].sh;
     }
   }
-  for (int64_t st = s0 + warp; st < s1; st += LMM_W) {
-    const int64_t r0 = st * LMM_STEP + half * 32;
+  // The ids of the next 16 rows are loaded before the current 16 are looked up (two register buffers): with a few
+  // steps per warp on a short matrix, waiting for each load before issuing the next was most of the run time.
+  auto load_ids = [&](int64_t st, int sub, uint4 (&ma)[NU], uint4 (&mb)[NU]) {
+    const int64_t rb = ((st * LMM_STEP + half * 32) >> 4) + sub;
 #pragma unroll
-    for (int sub = 0; sub < 2; sub++) {
-      uint4 ma[NU], mb[NU];
-#pragma unroll
-      for (int u = 0; u < NU; u++) {
-        const uint8_t* src = mp[u] + ((r0 >> 4) + sub) * 512;
-        ma[u] = __ldg((const uint4*)src);
-        mb[u] = __ldg((const uint4*)(src + 16));
-      }
-      double acc[16];
-#pragma unroll
-      for (int i = 0; i < 16; i++) acc[i] = 0.0;
-#pragma unroll
-      for (int u = 0; u < NU; u++) {
-        // ids stay below 256 after the shift, so the four bytes of a word never carry into each other
-        const uint32_t ww[4] = {ma[u].x * mul[u] + mb[u].x, ma[u].y * mul[u] + mb[u].y, ma[u].z * mul[u] + mb[u].z,
-                                ma[u].w * mul[u] + mb[u].w};
-        const unsigned char* T = tbase[u];
-#pragma unroll
-        for (int i = 0; i < 16; i++) acc[i] += *(const double*)(T + byte_x128(ww[i >> 2], i & 3));
-      }
-#pragma unroll
-      for (int d = 8; d >= 1; d >>= 1) {
-        const bool up = (slot & d) != 0;
-#pragma unroll
-        for (int i = 0; i < d; i++) {
-          const double lo = acc[i], hi = acc[i + d];
-          const double recv = __shfl_xor_sync(0xffffffffu, up ? lo : hi, d);
-          acc[i] = (up ? hi : lo) + recv;
-        }
-      }
-      const int64_t row = r0 + sub * 16 + slot;
-      if (row < nRows) out[row] = first ? acc[0] + init : out[row] + acc[0];
+    for (int u = 0; u < NU; u++) {
+      const uint8_t* src = mp[u] + rb * 512;
+      ma[u] = __ldg((const uint4*)src);
+      mb[u] = __ldg((const uint4*)(src + 16));
     }
+  };
+  auto lookup_rows = [&](int64_t st, int sub, const uint4 (&ma)[NU], const uint4 (&mb)[NU]) {
+    double acc[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) acc[i] = 0.0;
+#pragma unroll
+    for (int u = 0; u < NU; u++) {
+      // ids stay below 256 after the shift, so the four bytes of a word never carry into each other
+      const uint32_t ww[4] = {ma[u].x * mul[u] + mb[u].x, ma[u].y * mul[u] + mb[u].y, ma[u].z * mul[u] + mb[u].z,
+                              ma[u].w * mul[u] + mb[u].w};
+      const unsigned char* T = tbase[u];
+#pragma unroll
+      for (int i = 0; i < 16; i++) acc[i] += *(const double*)(T + byte_x128(ww[i >> 2], i & 3));
+    }
+#pragma unroll
+    for (int d = 8; d >= 1; d >>= 1) {
+      const bool up = (slot & d) != 0;
+#pragma unroll
+      for (int i = 0; i < d; i++) {
+        const double lo = acc[i], hi = acc[i + d];
+        const double recv = __shfl_xor_sync(0xffffffffu, up ? lo : hi, d);
+        acc[i] = (up ? hi : lo) + recv;
+      }
+    }
+    const int64_t row = st * LMM_STEP + half * 32 + sub * 16 + slot;
+    if (row < nRows) out[row] = first ? acc[0] + init : out[row] + acc[0];
+  };
+  uint4 a0[NU], b0[NU], a1[NU], b1[NU];
+  int64_t st = s0 + warp;
+  if (st < s1) load_ids(st, 0, a0, b0);
+  for (; st < s1; st += LMM_W) {
+    load_ids(st, 1, a1, b1);
+    lookup_rows(st, 0, a0, b0);
+    if (st + LMM_W < s1) load_ids(st + LMM_W, 0, a0, b0);
+    lookup_rows(st, 1, a1, b1);
   }
 }
 

@@ -377,17 +377,21 @@ __global__ void k_decomp_rle(DevGroup g, double* __restrict__ out, int r0, int r
 }
 
 // Decompress of a block whose columns each belong to at most one group, every group type, one pass: a CTA owns
-// 256 rows x 8 columns and builds them in shared memory, one warp per
-// column with lanes along the rows -- a dense-map column reads 32 consecutive ids per load, an SDC column fills its
-// constant and then scatters the listed rows (warp-scan decode from the skip entry), an RLE column fills its runs --
-// and then writes the tile out with lanes along the columns (64-byte segments of 4 output rows per instruction).
+// 128 rows x 32 columns and builds them in shared memory, a warp per column (four columns each) with lanes along the
+// rows -- a dense-map column reads four consecutive ids per lane (one 128-byte line per warp for byte maps), an SDC
+// column fills its constant and then scatters the listed rows (warp-scan decode from the skip entry), an RLE column
+// fills its runs -- and then writes the tile out a row per warp instruction, 256 contiguous bytes per row.
 // Uncompressed columns skip the tile: adjacent columns are adjacent in memory, so the write-out loop reads them.
-// Every output cell is written exactly once; nothing is read back.
-constexpr int DB_COLS = 8;
-constexpr int DB_ROWS = 256;         // a quarter of a skip-index block: 16 KB of tile, eight CTAs per SM (an SDC / RLE walk
-                                     // starts at the block's skip entry and passes over the quarters before its own);
-                                     // measured 1M x 200: 1024 rows 1.15 ms, 512 rows 0.90 ms, 256 rows 0.82 ms
-constexpr int DB_LD = DB_ROWS + 2;   // column stride of the tile: 2 w + row spreads a write-out instruction over the banks
+// Every output cell is written exactly once; nothing is read back. (Measured alternatives, both slower: a 256 x 8
+// tile, whose 64-byte output pieces lie 4 KB apart; persistent CTAs that keep their columns' dictionaries in shared
+// memory -- the kernel is bound by the latency of its load -> lookup -> store chain, which many small CTAs hide
+// better than few large ones.)
+constexpr int DB_COLS = 32;
+constexpr int DB_ROWS = 128;
+constexpr int DB_LD = DB_ROWS + 1;   // column stride of the tile (odd: the row-wise read of the write-out is conflict free)
+// position of tile row r inside its column: the four rows of a lane go to four different 32-row groups, so a warp's
+// store of one of them is contiguous
+__device__ __forceinline__ int db_pos(int r) { return (r & 3) * 32 + (r >> 2); }
 __global__ void __launch_bounds__(256)
 k_decomp_block(const DevGroup* __restrict__ groups, const int32_t* __restrict__ colSrc, const double* __restrict__ constV,
                double* __restrict__ out, int r0, int r1, int nCols, int exactSdc) {
@@ -409,66 +413,67 @@ k_decomp_block(const DevGroup* __restrict__ groups, const int32_t* __restrict__ 
       }
     }
   }
-  if (warp < nc) {
-    const int c = c0 + warp;
+  for (int cw = warp; cw < nc; cw += 8) {
+    const int c = c0 + cw;
     const int gi = colSrc[2 * c];
     const double cst = constV ? constV[c] : 0.0;
-    double* col = dtile + warp * DB_LD;
+    double* col = dtile + cw * DB_LD;
     if (gi < 0) {
-      for (int rr = lane; rr < nr; rr += 32) col[rr] = cst;
+      for (int rr = lane; rr < nr; rr += 32) col[db_pos(rr)] = cst;
     } else {
       const DevGroup& g = groups[gi];
       const int j = colSrc[2 * c + 1], gc = g.gCols;
       const double* dict = g.dict + j;
       if (g.type == GT_DDC) {
         const int mt = g.mapType;
-        // eight rows per lane in flight: all ids are loaded before the first dictionary read that needs one
-        for (int base = 0; base < nr; base += 256) {
-          int id[8];
+        // four consecutive rows per lane; all ids are loaded before the first dictionary read that needs one
+        int id[4];
+        const int rr0 = lane * 4;
+        if ((mt == CLA_MAP_UBYTE || mt == CLA_MAP_BYTE) && nr == DB_ROWS) {
+          const uint32_t w = __ldg((const uint32_t*)((const uint8_t*)g.map + rb) + lane);  // rb is a multiple of 128
 #pragma unroll
-          for (int u = 0; u < 8; u++) {
-            const int rr = base + u * 32 + lane;
-            id[u] = rr < nr ? map_get(mt, g.map, g.mapHi, rb + rr) : 0;
-          }
-          double v[8];
+          for (int u = 0; u < 4; u++) id[u] = (w >> (8 * u)) & 0xFF;
+        } else {
 #pragma unroll
-          for (int u = 0; u < 8; u++) v[u] = dict[(size_t)id[u] * gc];
-#pragma unroll
-          for (int u = 0; u < 8; u++) {
-            const int rr = base + u * 32 + lane;
-            if (rr < nr) col[rr] = cst + v[u];
-          }
+          for (int u = 0; u < 4; u++) id[u] = rr0 + u < nr ? map_get(mt, g.map, g.mapHi, rb + rr0 + u) : 0;
         }
+        double v[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) v[u] = dict[(size_t)id[u] * gc];
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+          if (rr0 + u < nr) col[u * 32 + lane] = cst + v[u];  // = db_pos(rr0 + u)
       } else if (g.type == GT_SDC) {
-        for (int rr = lane; rr < nr; rr += 32) col[rr] = cst;
+        for (int rr = lane; rr < nr; rr += 32) col[db_pos(rr)] = cst;
         __syncwarp();
         // exactSdc: the column belongs to this group alone, so its constant is exactly the group's default tuple and
         // a listed row holds the registered value itself (the reference writes d, lib/CLALibDecompress.java:310-357)
         const double* raw = g.dictRaw + j;
         sdc_walk_block(g, rb, re, [&](int row, int e) {
           const int id = g.single ? 0 : map_get(g.mapType, g.map, g.mapHi, e);
-          col[row - rb] = exactSdc ? raw[(size_t)id * gc] : cst + dict[(size_t)id * gc];
+          col[db_pos(row - rb)] = exactSdc ? raw[(size_t)id * gc] : cst + dict[(size_t)id * gc];
         });
       } else if (g.type == GT_RLE) {
-        for (int rr = lane; rr < nr; rr += 32) col[rr] = cst;
+        for (int rr = lane; rr < nr; rr += 32) col[db_pos(rr)] = cst;
         __syncwarp();
         for (int64_t ri = g.runSkip[rb / SKIP_ROWS]; ri < g.nRuns; ri++) {
           const RleRun run = g.runs[ri];
           if (run.start >= re) break;
           const int a = max(run.start, rb), b = min(run.start + (int)run.len, re);
           const double v = cst + dict[(size_t)run.k * gc];
-          for (int i = a + lane; i < b; i += 32) col[i - rb] = v;
+          for (int i = a + lane; i < b; i += 32) col[db_pos(i - rb)] = v;
         }
       }
     }
   }
   __syncthreads();
-  for (int e = tid; e < nr * DB_COLS; e += 256) {
-    const int rr = e / DB_COLS, cc = e - rr * DB_COLS;
-    if (cc >= nc) continue;
-    const double* us = uncSrc[cc];
-    const double v = us ? uncCst[cc] + us[(size_t)(rb + rr) * uncStride[cc]] : dtile[cc * DB_LD + rr];
-    out[(size_t)(rb - r0 + rr) * nCols + c0 + cc] = v;
+  // a row per warp instruction: lane = column of the tile
+  for (int rr = warp; rr < nr; rr += 8) {
+    if (lane < nc) {
+      const double* us = uncSrc[lane];
+      const double v = us ? uncCst[lane] + us[(size_t)(rb + rr) * uncStride[lane]] : dtile[lane * DB_LD + db_pos(rr)];
+      out[(size_t)(rb - r0 + rr) * nCols + c0 + lane] = v;
+    }
   }
 }
 
