@@ -56,7 +56,7 @@ DESCS = {
 }
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, per matrix row, from ncu captures of
 # scaled-down cases (traffic grows in proportion to the rows); None = not captured
-TRAFFIC_PER_ROW = {0: 103.1, 1: 242.55, 2: 1097.9, 3: 202.55, 4: 2220.5}
+TRAFFIC_PER_ROW = {0: 134.1, 1: 223.45, 2: 1934.0, 3: 202.95, 4: 2170.5}
 
 
 def measured_peaks():
@@ -297,11 +297,11 @@ class Workload:
         """(bound, work per launch, unit scale, peak, unit, kernel): bytes for the HBM-bound products, flops for TSMM."""
         n, ib = self.n, self.index_bytes
         if self.idx == 0:
-            return "hbm", ib + n * 8 + 100 * 8, "k_rmm_vec_f / k_rmm_vec_u8"
+            return "hbm", ib + n * 8 + 100 * 8, "k_rmm_vec_f"
         if self.idx == 1:
             return "hbm", ib + n * 8 + 200 * 8, "k_lmm_vec_u8"
         if self.idx == 2:
-            return "hbm", ib + n * 64 * 8 + 500 * 64 * 8, "k_rmm_dmma2"
+            return "hbm", ib + n * 64 * 8 + 500 * 64 * 8, "k_rmm_dmma3"
         if self.idx == 3:
             return "tensor", 2.0 * n * 100 * 101 / 2, "k_tsmm_tri16"
         return "hbm", 2 * ib + 2 * n * 8 + 2 * 1000 * 8, "k_rmm_vec_b + k_lmm_vec_u8"

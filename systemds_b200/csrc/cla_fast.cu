@@ -85,7 +85,7 @@ struct FastPlan {
   std::vector<LmmChunk> fchunks;
   LmmChunk* dFChunks = nullptr;
   struct FusedUnit* dFUnits = nullptr;  // [slots]
-  uint8_t* dFMaps = nullptr;            // [slab16][16-row block][slot][2 x 16 ids]
+  uint8_t* dFMaps = nullptr;            // [slab16][16-row block][a | b][slot][16 ids]
   size_t fImageDoubles = 0;
   std::vector<void*> allocs;
 };
@@ -387,20 +387,142 @@ k_lmm_vec_u8(const LmmChunk* __restrict__ chunks, int nChunks, const uint8_t* __
 #undef LMM_CASE
 }
 
-// out[col] += sum over the chunk's CTAs of partial[cta][slot], in CTA order (deterministic per column)
+// out[col] += sum over the chunk's CTAs of partial[cta][slot]. A warp per column slot: lane l adds the partial sums of
+// CTAs l, l + 32, ... (row ranges that were launched separately one after the other), then a shuffle tree adds the
+// 32 lanes -- a fixed order for a given launch geometry, so the result is reproducible, and the 80 or so partial
+// sums of a column are no longer one chain of dependent loads.
 __global__ void k_lmm_vec_final(const LmmChunk* __restrict__ chunks, int nChunks, const int* __restrict__ slotCol,
                                 const double* __restrict__ partial, double* __restrict__ out, int nParts, int gridPerPart) {
   const int c = blockIdx.x;
   if (c >= nChunks) return;
   const LmmChunk ch = chunks[c];
-  for (int u = threadIdx.x; u < ch.nUnits * 16; u += blockDim.x) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nWarps = blockDim.x >> 5;
+  const int n = nParts * ch.nCta;
+  for (int u = warp; u < ch.nUnits * 16; u += nWarps) {
     const int col = slotCol[ch.unit0 * 16 + u];
     if (col < 0) continue;
     double s = 0;
-    for (int part = 0; part < nParts; part++)  // row ranges that were launched separately, in row order
-      for (int b = 0; b < ch.nCta; b++)
-        s += partial[((size_t)part * gridPerPart + ch.cta0 + b) * LMM_PART + u];
-    atomicAdd(&out[col], s);
+    for (int i = lane; i < n; i += 32) {
+      const int part = i / ch.nCta, b = i - part * ch.nCta;
+      s += partial[((size_t)part * gridPerPart + ch.cta0 + b) * LMM_PART + u];
+    }
+#pragma unroll
+    for (int d = 16; d; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
+    if (lane == 0) atomicAdd(&out[col], s);
+  }
+}
+
+// --------------------------------------------------------------------------------------------------
+// Decompress from the column-per-lane layout.
+//
+// Same chunks, interleaved maps and table images as k_lmm_vec_u8: lane s of a half-warp owns column slot s of a
+// unit, loads 16 rows of its ids with one 128-bit load, reads each value from its own bank pair of the unit's
+// table and stores it. The 16 slots of a unit are 16 neighbouring output columns (the plan orders the slots by
+// column), so a warp store writes two full 128-byte pieces of two rows: no transposition through shared memory,
+// no bank conflicts, no gathers from global memory. Per 32 cells the L1 data pipe sees 2 wavefronts of lookups,
+// 2 of stores and 1/4 of map loads (the tile kernel in cla_generic.cu needs about 20, most of them for the gather
+// of dictionary values through L1), which puts the bound on the output stream. Every cell is written exactly once
+// with the same operation as the tile kernel (column constant + dictionary value).
+// --------------------------------------------------------------------------------------------------
+constexpr int DEC_W = 16;
+constexpr int DEC_T = DEC_W * 32;
+
+__device__ __forceinline__ void dec_rows16(const uint4 w, const unsigned char* T, double cst, double* o, size_t ld) {
+  const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+  for (int i = 0; i < 16; i++) __stcs(o + (size_t)i * ld, cst + *(const double*)(T + byte_x128(ww[i >> 2], i & 3)));
+}
+
+__global__ void __launch_bounds__(DEC_T, 1)
+k_decomp_fast(const LmmChunk* __restrict__ chunks, int nChunks, const uint8_t* __restrict__ imaps, int64_t nRB,
+              const double* __restrict__ tablesImg, const int* __restrict__ slotCol, const double* __restrict__ constV,
+              double* __restrict__ out, int nCols, int r0, int r1, int32_t* err) {
+  extern __shared__ __align__(128) unsigned char smraw[];
+  __shared__ __align__(8) uint64_t mbar;
+  __shared__ LmmChunk ch;
+  __shared__ int unitOff[LMM_MAX_UNITS];
+  __shared__ int sCol[LMM_MAX_UNITS * 16];
+  __shared__ double sCst[LMM_MAX_UNITS * 16];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int slot = lane & 15, half = lane >> 4;
+  if (tid == 0) {
+    int c = 0;
+    while (c + 1 < nChunks && (int)blockIdx.x >= chunks[c].cta0 + chunks[c].nCta) c++;
+    ch = chunks[c];
+    int off = 0;
+    for (int u = 0; u < ch.nUnits; u++) {
+      unitOff[u] = off;
+      off += ch.nk[u] * 128;
+    }
+  }
+  __syncthreads();
+  if (tid < ch.nUnits * 16) {
+    const int col = slotCol[ch.unit0 * 16 + tid];
+    sCol[tid] = col;
+    sCst[tid] = (constV && col >= 0) ? constV[col] : 0.0;
+  }
+  const int NU = ch.nUnits;
+  const int ctaInChunk = blockIdx.x - ch.cta0;
+  const int64_t stepBegin = r0 / LMM_STEP, stepEnd = ((int64_t)r1 + LMM_STEP - 1) / LMM_STEP;  // r0 is a multiple of LMM_STEP
+  const int64_t nSteps = stepEnd - stepBegin;
+  const int64_t s0 = stepBegin + nSteps * ctaInChunk / ch.nCta, s1 = stepBegin + nSteps * (ctaInChunk + 1) / ch.nCta;
+  const size_t ld = (size_t)nCols;
+  if (!tma_load_to_smem(smraw, tablesImg + ch.tblOff, (uint32_t)ch.tblDoubles * 8u, &mbar)) {
+    // the tables never arrived: flag it, and make the failure visible in this CTA's cells as well (a device-buffer
+    // caller only sees the error word at its next cla_stats_get)
+    if (tid == 0) atomicExch(err, 102);
+    const int64_t rb = s0 * LMM_STEP, re = min((int64_t)r1, s1 * LMM_STEP);
+    const int w = NU * 16;
+    for (int64_t i = tid; i < (re - rb) * w; i += DEC_T) {
+      const int col = sCol[(int)(i % w)];
+      if (col >= 0) out[(size_t)(rb + i / w - r0) * ld + col] = __longlong_as_double(0x7ff8000000000000ll);
+    }
+    return;
+  }
+  const uint8_t* mbase = imaps + (size_t)ch.unit0 * nRB * 256 + slot * 16;
+  auto ids_at = [&](int64_t st, int u) { return mbase + ((size_t)u * nRB + ((st * LMM_STEP + half * 32) >> 4)) * 256; };
+  int64_t st = s0 + warp;
+  int u = 0;
+  uint4 a = make_uint4(0, 0, 0, 0), b = a;
+  if (st < s1) {
+    const uint8_t* src = ids_at(st, 0);
+    a = __ldg((const uint4*)src);
+    b = __ldg((const uint4*)(src + 256));
+  }
+  while (st < s1) {
+    // ids of the next (step, unit) of this warp, one iteration ahead
+    int64_t nst = st;
+    int nu = u + 1;
+    if (nu == NU) {
+      nu = 0;
+      nst = st + DEC_W;
+    }
+    uint4 na = a, nb = b;
+    if (nst < s1) {
+      const uint8_t* src = ids_at(nst, nu);
+      na = __ldg((const uint4*)src);
+      nb = __ldg((const uint4*)(src + 256));
+    }
+    const int col = sCol[u * 16 + slot];
+    if (col >= 0) {
+      const double cst = sCst[u * 16 + slot];
+      const unsigned char* T = smraw + unitOff[u] + slot * 8;
+      const int64_t row0 = st * LMM_STEP + half * 32;
+      double* o = out + (size_t)(row0 - r0) * ld + col;
+      if (row0 + 32 <= r1) {
+        dec_rows16(a, T, cst, o, ld);
+        dec_rows16(b, T, cst, o + 16 * ld, ld);
+      } else {
+        const uint32_t ww[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int i = 0; i < 32; i++)
+          if (row0 + i < r1) o[(size_t)i * ld] = cst + *(const double*)(T + byte_x128(ww[i >> 2], i & 3));
+      }
+    }
+    a = na;
+    b = nb;
+    st = nst;
+    u = nu;
   }
 }
 
@@ -516,8 +638,8 @@ k_rmm_vec_b(const LmmChunk* __restrict__ chunks, int nChunks, const uint8_t* __r
 // RMM with two groups per dictionary read. When dictionaries are small, two groups g and h share one column
 // slot: the slot's table holds P_g[a] + P_h[b] at entry (a << sh) | b (at most 256 entries), so one 8-byte read
 // serves two cells -- the lookup bound of 16 reads per clock per SM then allows 32 cells per clock. The maps stay
-// as registered; the kernel reads both groups' ids ([slab16][16-row block][slot][a ids | b ids], 32 contiguous
-// bytes per lane) and combines them with one multiply-add per four rows. Otherwise identical to k_rmm_vec_b.
+// as registered; the kernel reads both groups' ids ([slab16][16-row block][a | b][slot][16 ids], one 128-bit load
+// each) and combines them with one multiply-add per four rows. Otherwise identical to k_rmm_vec_b.
 // --------------------------------------------------------------------------------------------------
 __global__ void k_rmm_f_tables(const DevGroup* __restrict__ groups, const LmmChunk* __restrict__ chunks,
                                const FusedUnit* __restrict__ units, const double* __restrict__ v,
@@ -565,7 +687,7 @@ __device__ __forceinline__ void rmm_f_chunk(const LmmChunk& ch, const FusedUnit*
     for (int u = 0; u < NU; u++) {
       tbase[u] = smraw + off + slot * 8;
       off += (size_t)ch.nk[u] * 128;
-      mp[u] = fmaps + (size_t)(ch.unit0 + u) * nRB * 512 + slot * 32;
+      mp[u] = fmaps + (size_t)(ch.unit0 + u) * nRB * 512 + slot * 16;
       mul[u] = 1u << units[(ch.unit0 + u) * 16 + slot].sh;
     }
   }
@@ -576,8 +698,8 @@ __device__ __forceinline__ void rmm_f_chunk(const LmmChunk& ch, const FusedUnit*
 #pragma unroll
     for (int u = 0; u < NU; u++) {
       const uint8_t* src = mp[u] + rb * 512;
-      ma[u] = __ldg((const uint4*)src);
-      mb[u] = __ldg((const uint4*)(src + 16));
+      ma[u] = __ldg((const uint4*)src);          // 16 lanes x 16 bytes: two full 128-byte lines per half-warp
+      mb[u] = __ldg((const uint4*)(src + 256));
     }
   };
   auto lookup_rows = [&](int64_t st, int sub, const uint4 (&ma)[NU], const uint4 (&mb)[NU]) {
@@ -645,13 +767,13 @@ k_rmm_vec_f(const LmmChunk* __restrict__ chunks, int nChunks, const FusedUnit* _
   }
 }
 
-// [slab16][16-row block][slot][a ids (16) | b ids (16)]
+// [slab16][16-row block][a | b][slot][16 ids]: a half-warp's load of the a ids (and of the b ids) is 256 contiguous bytes
 __global__ void k_rmm_f_interleave(const uint8_t* const* __restrict__ mapA, const uint8_t* const* __restrict__ mapB,
                                    int nSlots, int nRows, int64_t nRB, uint8_t* __restrict__ out) {
   const int64_t total = (int64_t)nSlots * nRB * 2;
   for (int64_t g = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; g < total; g += (int64_t)gridDim.x * blockDim.x) {
-    const int which = (int)(g & 1);
-    const int slot = (int)((g >> 1) & 15);
+    const int slot = (int)(g & 15);
+    const int which = (int)((g >> 4) & 1);
     const int64_t rb = (g >> 5) % nRB;
     const int64_t slab = (g >> 5) / nRB;
     const int unit = (int)slab * 16 + slot;
@@ -799,12 +921,17 @@ int64_t fast_plan_build(Matrix* m) {
   if ((rc = plan_upload(fp, groupOf, &fp->dGroupOf)) < 0) return rc;
   if ((rc = plan_upload(fp, imgOff, &fp->dImgOff)) < 0) return rc;
 
-  // ---- LMM: one column slot per (group, column), ordered by table depth; 16 slots per unit ----
-  struct Unit { int g, j, nv; };
+  // ---- LMM: one column slot per (group, column), in output-column order; 16 slots per unit ----
+  // (A chunk holds at most LMM_MAX_UNITS units and their tables fit at any depth, so nothing is gained by packing
+  // shallow tables together; in column order the 16 slots of a unit are neighbours in a decompressed row.)
+  struct Unit { int g, j, nv, col; };
   std::vector<Unit> units;
-  for (int gi = 0; gi < nG; gi++)
-    for (int j = 0; j < G[gi].gCols; j++) units.push_back({gi, j, G[gi].nVals});
-  std::stable_sort(units.begin(), units.end(), [](const Unit& a, const Unit& b) { return a.nv > b.nv; });
+  for (int gi = 0; gi < nG; gi++) {
+    std::vector<int32_t> cols(G[gi].gCols);
+    CLA_CUDA(cudaMemcpy(cols.data(), G[gi].cols, cols.size() * 4, cudaMemcpyDeviceToHost));
+    for (int j = 0; j < G[gi].gCols; j++) units.push_back({gi, j, G[gi].nVals, cols[j]});
+  }
+  std::stable_sort(units.begin(), units.end(), [](const Unit& a, const Unit& b) { return a.col < b.col; });
   fp->nUnits = (int)units.size();
   const int nU16 = (fp->nUnits + 15) / 16;
   fp->nSlots = nU16 * 16;
@@ -860,15 +987,7 @@ int64_t fast_plan_build(Matrix* m) {
   flush();
   for (int u = 0; u < fp->nUnits; u++) {
     slotMap[u] = gmap[units[u].g];
-    slotCol[u] = 0;  // filled below from the device column lists
-  }
-  {  // output column of every slot
-    for (int gi = 0; gi < nG; gi++) {
-      std::vector<int32_t> cols(G[gi].gCols);
-      CLA_CUDA(cudaMemcpy(cols.data(), G[gi].cols, cols.size() * 4, cudaMemcpyDeviceToHost));
-      for (int u = 0; u < fp->nUnits; u++)
-        if (units[u].g == gi) slotCol[u] = cols[units[u].j];
-    }
+    slotCol[u] = units[u].col;
   }
   // CTAs per chunk in proportion to its cost, one CTA per SM in total. Cost per 64-row warp step in
   // L1 data-pipe wavefronts: 64 per unit for the dictionary reads, 8 per unit for the map loads and
@@ -916,6 +1035,7 @@ int64_t fast_plan_build(Matrix* m) {
   m->deviceBytes += (int64_t)image.size() * 8;
   CLA_CUDA(cudaFuncSetAttribute(k_lmm_vec_u8, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_MAX - 1024));
   CLA_CUDA(cudaFuncSetAttribute(k_rmm_vec_b, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_MAX - 1024));
+  CLA_CUDA(cudaFuncSetAttribute(k_decomp_fast, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_MAX - 2048));
   CLA_CUDA(cudaFuncSetAttribute(k_rmm_vec_u8<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
   CLA_CUDA(cudaFuncSetAttribute(k_rmm_vec_u8<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
   CLA_CUDA(cudaFuncSetAttribute(k_rmm_vec_u8<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
@@ -1081,6 +1201,23 @@ static int64_t fast_rmm_vec_f(Matrix* m, FastPlan* fp, const double* dV, double*
 bool fast_plan_ok(const Matrix* m) { return m->fast && m->fast->ok; }
 bool fast_plan_partial(const Matrix* m) { return m->fast && m->fast->ok && m->fast->partial; }
 
+// Rows [r0, r1) of the decompressed matrix into dOut (row r0 first) when every column is a slot of the plan and no
+// column belongs to two groups; 0 = not covered (the caller takes the tile kernel).
+int64_t fast_decompress(Matrix* m, int r0, int r1, double* dOut, cudaStream_t s) {
+  FastPlan* fp = m->fast;
+  if (!fp || !fp->ok || fp->partial || !fp->dLmmMaps || !m->colSrcValid || fp->nUnits != m->nCols || (r0 % LMM_STEP)) return 0;
+  static const bool off = getenv("CLA_DECOMP_TILES") != nullptr;
+  if (off) return 0;
+  size_t smem = 0;
+  for (auto& c : fp->lchunks) smem = std::max(smem, (size_t)c.tblDoubles * 8);
+  k_decomp_fast<<<fp->lmmGrid, DEC_T, smem, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dLmmMaps, fp->nRB, fp->dLmmTables,
+                                                fp->dSlotCol, m->hasConst ? m->dConstV : nullptr, dOut, m->nCols, r0, r1,
+                                                m->dErr);
+  m->stats.kernel_launches++;
+  CLA_CUDA(cudaGetLastError());
+  return 1;
+}
+
 int64_t fast_rmm_vec(Matrix* m, const double* dV, double* dOut, cudaStream_t s) {
   FastPlan* fp = m->fast;
   if (!fp || !fp->ok || ((uintptr_t)dOut & 15)) return 0;  // 128-bit stores need an aligned output
@@ -1140,7 +1277,7 @@ int64_t fast_lmm_vec(Matrix* m, const double* dY, double* dOut, cudaStream_t s) 
   k_lmm_vec_u8<<<fp->lmmGrid, LMM_T, smem, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dLmmMaps, fp->nRB, fp->dLmmTables, dY,
                                                m->nRows, 0, nSteps, partial, m->dErr);
   prof_end(m, s);
-  k_lmm_vec_final<<<(unsigned)fp->lchunks.size(), 128, 0, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dSlotCol,
+  k_lmm_vec_final<<<(unsigned)fp->lchunks.size(), 512, 0, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dSlotCol,
                                                               partial, dOut, 1, fp->lmmGrid);
   m->stats.kernel_launches += 2;
   if (m->hasConst)
@@ -1185,7 +1322,7 @@ int64_t fast_lmm_vec_host(Matrix* m, const double* hostY, double* dY, double* dO
     if (i == LMM_PIPE - 1) prof_end(m, s);
     m->stats.kernel_launches++;
   }
-  k_lmm_vec_final<<<(unsigned)fp->lchunks.size(), 128, 0, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dSlotCol, partial,
+  k_lmm_vec_final<<<(unsigned)fp->lchunks.size(), 512, 0, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dSlotCol, partial,
                                                               dOut, LMM_PIPE, fp->lmmGrid);
   m->stats.kernel_launches++;
   if (m->hasConst)
@@ -1246,7 +1383,7 @@ int64_t fast_lmm_vec_noalloc(Matrix* m, const double* dY, double* dOut, cudaStre
   const int64_t nSteps = ((int64_t)m->nRows + LMM_STEP - 1) / LMM_STEP;
   k_lmm_vec_u8<<<fp->lmmGrid, LMM_T, smem, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dLmmMaps, fp->nRB, fp->dLmmTables,
                                                dY, m->nRows, 0, nSteps, partial, m->dErr);
-  k_lmm_vec_final<<<(unsigned)fp->lchunks.size(), 128, 0, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dSlotCol,
+  k_lmm_vec_final<<<(unsigned)fp->lchunks.size(), 512, 0, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dSlotCol,
                                                               partial, dOut, 1, fp->lmmGrid);
   m->stats.kernel_launches += 2;
   if (m->hasConst)

@@ -482,6 +482,8 @@ int64_t launch_decompress_range(Matrix* m, int r0, int r1, double* dOut, cudaStr
   const int64_t n = (int64_t)(r1 - r0) * m->nCols;
   if (n <= 0) return CLA_OK;
   if (m->colSrcValid) {  // no column held by two groups: one pass, every cell written once
+    const int64_t rf = fast_decompress(m, r0, r1, dOut, s);  // byte-map matrices: straight from the column-per-lane layout
+    if (rf != 0) return rf < 0 ? rf : CLA_OK;
     const size_t smem = (size_t)DB_COLS * DB_LD * sizeof(double);
     static bool attrSet[64] = {};  // per device: function attributes belong to the device's context
     bool& attr = attrSet[m->device & 63];

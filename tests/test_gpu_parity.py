@@ -128,6 +128,9 @@ def test_fast_vector_paths(oracle, nRows, shape):
     assert rel_err(CLALibLeftMultBy.leftMultByMatrix(cmb, Y), om.lmm(Y), np.abs(Y) @ aX + 1e-300) < TOL
     st = cmb.stats()
     assert st["kernel_launches"] > 0 and st["calls_rmm"] >= 2 and st["calls_lmm"] >= 2
+    # decompress straight from the column-per-lane layout (every column a slot) or by the tile kernel (const column):
+    # a cell is one dictionary value (plus the column constant), so both are exact (lib/CLALibDecompress.java:427-434)
+    assert np.array_equal(np.array(CLALibDecompress.decompress(cmb)), X)
     cmb.free()
 
 
