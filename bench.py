@@ -20,7 +20,8 @@ Prints one JSON line: value = rows/s with inputs resident in HBM (max over ranks
 e2e = the same product through the host-buffer C-ABI call (operands copied host->device and the result
 device->host inside the timed region), roofline = algorithmic bytes (or flops) of the dominant kernel over its
 CUDA-event duration against the measured peak, cpu_baseline = the CPU restatement of the reference algorithm on the
-host cores. `--impl reference` times that CPU path alone.
+host cores. `--impl reference` times that CPU path alone. `--decompress` adds the time of cla_decompress_dev of the
+main workload's matrix into a device buffer (bytes written per second against the copy bandwidth).
 """
 from __future__ import annotations
 
@@ -443,6 +444,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-also", action="store_true", help="skip the other four workloads")
     ap.add_argument("--also-steps", type=int, default=5)
+    ap.add_argument("--decompress", action="store_true",
+                    help="also time cla_decompress_dev of the main workload's matrix into a device buffer (one GPU)")
     ap.add_argument("--also-rows-scale", type=float, default=1.0, help="scale the rows of the 'also' workloads (profiling aid)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -545,6 +548,27 @@ def main():
         result["cpu_baseline"] = {"value": rate, "unit": UNIT, "cores": cores, "kind": "port",
                                   "sample": (f"the full workload, {rows} rows" if rows == n else f"{rows} rows of the same workload")
                                             + f", mean of 3 runs ({ms:.0f} ms each)"}
+    # ---- decompress of the same matrix into a device buffer (the output stream is the bound: 8 bytes per cell) ----
+    if args.decompress and world == 1:
+        cols = main.cmb.clen
+        dense = torch.empty((n, cols), dtype=torch.float64, device=dev)
+        dec = lambda: check(L.cla_decompress_dev(main.h, C.c_void_p(dense.data_ptr()), main.sptr))  # noqa: E731
+        for _ in range(3):
+            dec()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.also_steps):
+            dec()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.also_steps
+        wr = n * cols * 8
+        result["decompress"] = {"ms": ms, "rows": n, "cols": cols, "written_GBs": wr / (ms * 1e-3) / 1e9,
+                                "frac": wr / (ms * 1e-3) / 1e9 / hbm_peak, "peak_source": f"of {peak_kind}",
+                                "algorithmic_bytes": wr + main.index_bytes,
+                                "note": "cla_decompress_dev into a device buffer; frac = bytes written / time / copy bandwidth"}
+        del dense
     main.free()
 
     # ---- the other workloads, every rank, same sharding ----

@@ -12,6 +12,12 @@
  * number of non-zeros of the result (>= 0) so the caller can setNonZeros(), or a negative
  * CLA_ERR_* code. There is no CPU fallback: without a usable CUDA device every call fails.
  *
+ * Host buffers may be ordinary (pageable) memory, as the arrays a JVM hands over are: transfers of
+ * 4 MB and more from or to memory that is neither pinned nor registered go through a ring of pinned
+ * slices owned by the handle (32 MB, allocated at the first such call), moved by a few host threads
+ * of the calling process for the duration of the call (environment: CLA_STAGE_THREADS, 0 = plain
+ * cudaMemcpyAsync). Pinned and registered buffers are copied asynchronously as they are.
+ *
  * Threading: calls on one handle are serialised by an internal mutex; different handles may be
  * used concurrently. The thread budget "k" of the reference's calls has no meaning here.
  * Device-buffer calls (cla_*_dev) return once their work is enqueued on the caller's stream; all

@@ -591,13 +591,24 @@ static int64_t host_call(Matrix* m, const double* in1, size_t n1, const double* 
   unsigned long long* dCnt = (unsigned long long*)(base + oCnt);
   cudaStream_t s = m->stream;
   if ((rc = order_begin(m, s)) < 0) return rc;
-  if (n1 && !deferIn1) CLA_CUDA(cudaMemcpyAsync(d1, in1, n1 * 8, cudaMemcpyHostToDevice, s));  // deferred: run() uploads it
-  if (n2) CLA_CUDA(cudaMemcpyAsync(d2, in2, n2 * 8, cudaMemcpyHostToDevice, s));
+  // large operands in pageable memory go through the handle's pinned ring (cla_hostcopy.cu)
+  auto upload = [&](double* d, const double* h, size_t n) -> int64_t {
+    if (host_copy_staged(m, h, n * 8)) return host_to_device_staged(m, d, h, n * 8, s, nullptr);
+    CLA_CUDA(cudaMemcpyAsync(d, h, n * 8, cudaMemcpyHostToDevice, s));
+    return CLA_OK;
+  };
+  if (n1 && !deferIn1 && (rc = upload(d1, in1, n1)) < 0) return rc;  // deferred: run() uploads it
+  if (n2 && (rc = upload(d2, in2, n2)) < 0) return rc;
   CLA_CUDA(cudaEventRecord(m->ev0, s));
   if ((rc = run(d1, n2 ? d2 : nullptr, dOut, s)) < 0) return rc;
   CLA_CUDA(cudaEventRecord(m->ev1, s));
   if ((rc = launch_count_nnz(m, dOut, (int64_t)nOut, dCnt, s)) < 0) return rc;
-  if (nOut) CLA_CUDA(cudaMemcpyAsync(out, dOut, nOut * 8, cudaMemcpyDeviceToHost, s));
+  if (nOut) {
+    if (host_copy_staged(m, out, nOut * 8)) {
+      if ((rc = device_to_host_staged(m, out, dOut, nOut * 8, s)) < 0) return rc;
+    } else
+      CLA_CUDA(cudaMemcpyAsync(out, dOut, nOut * 8, cudaMemcpyDeviceToHost, s));
+  }
   unsigned long long nnz = 0;
   CLA_CUDA(cudaMemcpyAsync(&nnz, dCnt, sizeof(nnz), cudaMemcpyDeviceToHost, s));
   CLA_CUDA(cudaStreamSynchronize(s));

@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <memory>
+#include <functional>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -140,6 +141,7 @@ struct HostGroup {
 };
 
 struct FastPlan;  // plans of the specialised DDC kernels (cla_fast.cu)
+struct HostStage; // pinned ring for operands in pageable host memory (cla_hostcopy.cu)
 
 struct Matrix;
 struct Matrix {
@@ -197,7 +199,7 @@ struct Matrix {
   int32_t* dErr = nullptr;  // device self-check word
   cudaStream_t stream = nullptr;
   cudaStream_t copyStream = nullptr;  // uploads overlapped with kernels in the host-buffer left product
-  cudaEvent_t copyDone[4] = {nullptr, nullptr, nullptr, nullptr};
+  cudaEvent_t copyDone[8] = {};  // one per row range of the pipelined host-buffer left product
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   // Every product call uses the handle's one set of scratch buffers. A call that arrives on another stream than
   // the previous one first waits for `lastDone` (recorded when the previous call had enqueued its work), so two
@@ -206,6 +208,7 @@ struct Matrix {
   cudaStream_t lastStream = nullptr;
   bool lastValid = false;
   FastPlan* fast = nullptr;
+  HostStage* hostStage = nullptr;
   bool profile = false;
   std::vector<std::pair<cudaEvent_t, cudaEvent_t>> profEvents;  // ring of event pairs
   size_t profUsed = 0;
@@ -234,6 +237,13 @@ int64_t ensure_scratch(Matrix* m, size_t bytes);
 int64_t ensure_scratch2(Matrix* m, size_t bytes);
 int64_t ensure_io(Matrix* m, size_t bytes);
 int64_t ensure_small(Matrix* m, size_t bytes);
+// Transfers between pageable host memory and the device through the handle's pinned ring (cla_hostcopy.cu).
+// host_copy_staged: whether a transfer of `bytes` at `host` should take them (large, pageable, ring available).
+bool host_copy_staged(Matrix* m, const void* host, size_t bytes);
+int64_t host_to_device_staged(Matrix* m, void* dDst, const void* host, size_t bytes, cudaStream_t cs,
+                              const std::function<int64_t(size_t)>& enqueued);
+int64_t device_to_host_staged(Matrix* m, void* host, const void* dSrc, size_t bytes, cudaStream_t s);
+void host_stage_free(Matrix* m);
 int64_t ensure_sparse_list(Matrix* m);  // Matrix::dSparseIdx (cla_generic.cu)
 
 // launchers implemented in the kernel translation units; all enqueue on `s` and return CLA_OK or an error.

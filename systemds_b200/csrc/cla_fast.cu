@@ -426,12 +426,7 @@ __global__ void k_lmm_vec_final(const LmmChunk* __restrict__ chunks, int nChunks
 // --------------------------------------------------------------------------------------------------
 constexpr int DEC_W = 16;
 constexpr int DEC_T = DEC_W * 32;
-
-__device__ __forceinline__ void dec_rows16(const uint4 w, const unsigned char* T, double cst, double* o, size_t ld) {
-  const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-  for (int i = 0; i < 16; i++) __stcs(o + (size_t)i * ld, cst + *(const double*)(T + byte_x128(ww[i >> 2], i & 3)));
-}
+constexpr int DEC_NP = (LMM_MAX_UNITS + 1) / 2;  // unit pairs of a chunk: a warp store covers 32 neighbouring columns
 
 __global__ void __launch_bounds__(DEC_T, 1)
 k_decomp_fast(const LmmChunk* __restrict__ chunks, int nChunks, const uint8_t* __restrict__ imaps, int64_t nRB,
@@ -479,50 +474,62 @@ k_decomp_fast(const LmmChunk* __restrict__ chunks, int nChunks, const uint8_t* _
     }
     return;
   }
-  const uint8_t* mbase = imaps + (size_t)ch.unit0 * nRB * 256 + slot * 16;
-  auto ids_at = [&](int64_t st, int u) { return mbase + ((size_t)u * nRB + ((st * LMM_STEP + half * 32) >> 4)) * 256; };
-  int64_t st = s0 + warp;
-  int u = 0;
-  uint4 a = make_uint4(0, 0, 0, 0), b = a;
-  if (st < s1) {
-    const uint8_t* src = ids_at(st, 0);
-    a = __ldg((const uint4*)src);
-    b = __ldg((const uint4*)(src + 256));
-  }
-  while (st < s1) {
-    // ids of the next (step, unit) of this warp, one iteration ahead
-    int64_t nst = st;
-    int nu = u + 1;
-    if (nu == NU) {
-      nu = 0;
-      nst = st + DEC_W;
-    }
-    uint4 na = a, nb = b;
-    if (nst < s1) {
-      const uint8_t* src = ids_at(nst, nu);
-      na = __ldg((const uint4*)src);
-      nb = __ldg((const uint4*)(src + 256));
-    }
-    const int col = sCol[u * 16 + slot];
-    if (col >= 0) {
-      const double cst = sCst[u * 16 + slot];
-      const unsigned char* T = smraw + unitOff[u] + slot * 8;
-      const int64_t row0 = st * LMM_STEP + half * 32;
-      double* o = out + (size_t)(row0 - r0) * ld + col;
-      if (row0 + 32 <= r1) {
-        dec_rows16(a, T, cst, o, ld);
-        dec_rows16(b, T, cst, o + 16 * ld, ld);
-      } else {
-        const uint32_t ww[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+  // This lane's column of every unit pair: unit 2p + half, slot lane & 15
+  int toff[DEC_NP];   // byte offset of the lane's table column in shared memory
+  double cst[DEC_NP];
+  int colOf[DEC_NP];
 #pragma unroll
-        for (int i = 0; i < 32; i++)
-          if (row0 + i < r1) o[(size_t)i * ld] = cst + *(const double*)(T + byte_x128(ww[i >> 2], i & 3));
+  for (int p = 0; p < DEC_NP; p++) {
+    const int u = 2 * p + half;
+    const bool ok = u < NU;
+    colOf[p] = ok ? sCol[u * 16 + slot] : -1;
+    cst[p] = ok ? sCst[u * 16 + slot] : 0.0;
+    toff[p] = (ok ? unitOff[u] : 0) + slot * 8;
+  }
+  // ids of this lane's column of pair p, 16-row block b: units lie nRB * 256 bytes apart, a missing last unit reads unit 0's
+  const uint8_t* mbase = imaps + (size_t)ch.unit0 * nRB * 256 + slot * 16;
+  const size_t pairStride = (size_t)2 * nRB * 256, halfOff = (size_t)half * nRB * 256;
+  auto ids_at = [&](int p, int64_t b) {
+    const size_t uo = (2 * p + half < NU) ? p * pairStride + halfOff : 0;
+    return __ldg((const uint4*)(mbase + uo + b * 256));
+  };
+  // A warp owns 16-row blocks; it writes them a row at a time, 256 contiguous bytes per store and the chunk's columns
+  // of a row one after the other: runs of consecutive addresses are what the memory system turns into full-rate
+  // writes (the same cells written as 128-byte pieces of many rows reach about 0.9 of this order's rate). The ids of
+  // the next block are loaded before the current one is looked up.
+  const int64_t b0 = s0 * (LMM_STEP / 16), b1 = s1 * (LMM_STEP / 16);
+  uint4 w[DEC_NP], nw[DEC_NP];
+  int64_t blk = b0 + warp;
+  if (blk < b1) {
+#pragma unroll
+    for (int p = 0; p < DEC_NP; p++) w[p] = ids_at(p, blk);
+  }
+  for (; blk < b1; blk += DEC_W) {
+    if (blk + DEC_W < b1) {
+#pragma unroll
+      for (int p = 0; p < DEC_NP; p++) nw[p] = ids_at(p, blk + DEC_W);
+    }
+    const int64_t row0 = blk * 16;
+    double* o = out + (size_t)(row0 - r0) * ld;
+    const bool whole = row0 + 16 <= r1;
+#pragma unroll 1
+    for (int j = 0; j < 4; j++) {  // four rows per round (one id word per unit pair): 4 x DEC_NP lookups in flight
+      uint32_t word[DEC_NP];
+#pragma unroll
+      for (int p = 0; p < DEC_NP; p++) word[p] = j == 0 ? w[p].x : (j == 1 ? w[p].y : (j == 2 ? w[p].z : w[p].w));
+      double* orow = o + (size_t)(4 * j) * ld;
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        if (whole || row0 + 4 * j + i < r1) {
+#pragma unroll
+          for (int p = 0; p < DEC_NP; p++)
+            if (colOf[p] >= 0) orow[colOf[p]] = cst[p] + *(const double*)(smraw + toff[p] + byte_x128(word[p], i));
+        }
+        orow += ld;
       }
     }
-    a = na;
-    b = nb;
-    st = nst;
-    u = nu;
+#pragma unroll
+    for (int p = 0; p < DEC_NP; p++) w[p] = nw[p];
   }
 }
 
@@ -1287,19 +1294,28 @@ int64_t fast_lmm_vec(Matrix* m, const double* dY, double* dOut, cudaStream_t s) 
 }
 
 
-// Host-buffer t(y) %*% X with the upload of y overlapped with the product: y is copied in LMM_PIPE row ranges
+// Host-buffer t(y) %*% X with the upload of y overlapped with the product: y is copied in up to LMM_PIPE_MAX row ranges
 // on a second stream, and the kernel for a range starts as soon as its slice has arrived. Returns 0 if the
 // specialised kernel does not cover the matrix (the caller then copies y whole and takes the normal path).
-constexpr int LMM_PIPE = 4;
+constexpr int LMM_PIPE_MAX = 8;  // = the handle's copyDone events
+static int lmm_pipe_depth() {
+  static const int d = [] {
+    const char* e = getenv("CLA_LMM_PIPE");
+    const int v = e ? atoi(e) : 8;
+    return v < 1 ? 1 : (v > LMM_PIPE_MAX ? LMM_PIPE_MAX : v);
+  }();
+  return d;
+}
 int64_t fast_lmm_vec_host(Matrix* m, const double* hostY, double* dY, double* dOut, cudaStream_t s) {
   FastPlan* fp = m->fast;
   if (!fp || !fp->ok || fp->partial || ((uintptr_t)dY & 15) || m->nRows < (1 << 20)) return 0;
   int64_t rc;
+  const int LMM_PIPE = lmm_pipe_depth();
   const size_t partBytes = (size_t)LMM_PIPE * fp->lmmGrid * LMM_PART * 8;
   if ((rc = ensure_scratch(m, partBytes + 256)) < 0) return rc;
   if (!m->copyStream) {
     CLA_CUDA(cudaStreamCreateWithFlags(&m->copyStream, cudaStreamNonBlocking));
-    for (int i = 0; i < LMM_PIPE; i++) CLA_CUDA(cudaEventCreateWithFlags(&m->copyDone[i], cudaEventDisableTiming));
+    for (int i = 0; i < LMM_PIPE_MAX; i++) CLA_CUDA(cudaEventCreateWithFlags(&m->copyDone[i], cudaEventDisableTiming));
   }
   double* partial = (double*)m->scratch;
   CLA_CUDA(cudaMemsetAsync(dOut, 0, sizeof(double) * (size_t)m->nCols, s));
@@ -1309,10 +1325,14 @@ int64_t fast_lmm_vec_host(Matrix* m, const double* hostY, double* dY, double* dO
   // the copy stream must not run ahead of work already queued on s that still reads dY
   CLA_CUDA(cudaEventRecord(m->ev1, s));
   CLA_CUDA(cudaStreamWaitEvent(m->copyStream, m->ev1, 0));
-  for (int i = 0; i < LMM_PIPE; i++) {
-    const int64_t sb = nSteps * i / LMM_PIPE, se = nSteps * (i + 1) / LMM_PIPE;
-    const int64_t rb = sb * LMM_STEP, re = std::min<int64_t>(m->nRows, se * LMM_STEP);
-    if (re > rb) CLA_CUDA(cudaMemcpyAsync(dY + rb, hostY + rb, (size_t)(re - rb) * 8, cudaMemcpyHostToDevice, m->copyStream));
+  auto range_rows = [&](int i, int64_t& sb, int64_t& se, int64_t& rb, int64_t& re) {
+    sb = nSteps * i / LMM_PIPE, se = nSteps * (i + 1) / LMM_PIPE;
+    rb = sb * LMM_STEP, re = std::min<int64_t>(m->nRows, se * LMM_STEP);
+  };
+  // the kernel of row range i, once that range of y is on the copy stream
+  auto launch_range = [&](int i) -> int64_t {
+    int64_t sb, se, rb, re;
+    range_rows(i, sb, se, rb, re);
     CLA_CUDA(cudaEventRecord(m->copyDone[i], m->copyStream));
     CLA_CUDA(cudaStreamWaitEvent(s, m->copyDone[i], 0));
     if (i == 0) prof_begin(m, s);
@@ -1321,6 +1341,32 @@ int64_t fast_lmm_vec_host(Matrix* m, const double* hostY, double* dY, double* dO
                                                  m->dErr);
     if (i == LMM_PIPE - 1) prof_end(m, s);
     m->stats.kernel_launches++;
+    return CLA_OK;
+  };
+  if (host_copy_staged(m, hostY, (size_t)m->nRows * 8)) {
+    // y lives in pageable memory: host threads move it through the pinned ring, and every row range starts as soon
+    // as its last slice is on the copy stream
+    int nextRange = 0;
+    rc = host_to_device_staged(m, dY, hostY, (size_t)m->nRows * 8, m->copyStream, [&](size_t bytesQueued) -> int64_t {
+      while (nextRange < LMM_PIPE) {
+        int64_t sb, se, rb, re;
+        range_rows(nextRange, sb, se, rb, re);
+        if ((size_t)re * 8 > bytesQueued) break;
+        const int64_t r = launch_range(nextRange++);
+        if (r < 0) return r;
+      }
+      return CLA_OK;
+    });
+    if (rc < 0) return rc;
+    while (nextRange < LMM_PIPE)
+      if ((rc = launch_range(nextRange++)) < 0) return rc;
+  } else {
+    for (int i = 0; i < LMM_PIPE; i++) {
+      int64_t sb, se, rb, re;
+      range_rows(i, sb, se, rb, re);
+      if (re > rb) CLA_CUDA(cudaMemcpyAsync(dY + rb, hostY + rb, (size_t)(re - rb) * 8, cudaMemcpyHostToDevice, m->copyStream));
+      if ((rc = launch_range(i)) < 0) return rc;
+    }
   }
   k_lmm_vec_final<<<(unsigned)fp->lchunks.size(), 512, 0, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dSlotCol, partial,
                                                               dOut, LMM_PIPE, fp->lmmGrid);

@@ -690,6 +690,7 @@ void release(Matrix* m) {
     }
   if (m->copyStream) cudaStreamDestroy(m->copyStream);
   m->copyStream = nullptr;
+  host_stage_free(m);
   if (m->stream) cudaStreamDestroy(m->stream);
   m->scratch = m->scratch2 = m->io = nullptr;
   m->dErr = nullptr;

@@ -468,12 +468,14 @@ k_decomp_block(const DevGroup* __restrict__ groups, const int32_t* __restrict__ 
   }
   __syncthreads();
   // a row per warp instruction: lane = column of the tile
-  for (int rr = warp; rr < nr; rr += 8) {
-    if (lane < nc) {
-      const double* us = uncSrc[lane];
-      const double v = us ? uncCst[lane] + us[(size_t)(rb + rr) * uncStride[lane]] : dtile[lane * DB_LD + db_pos(rr)];
-      out[(size_t)(rb - r0 + rr) * nCols + c0 + lane] = v;
-    }
+  if (lane < nc) {
+    const double* us = uncSrc[lane];  // this lane's column: read once, not per row
+    const size_t ustride = us ? (size_t)uncStride[lane] : 0;
+    const double ucst = us ? uncCst[lane] : 0.0;
+    const double* tcol = dtile + lane * DB_LD;
+    double* o = out + (size_t)(rb - r0) * nCols + c0 + lane;
+    for (int rr = warp; rr < nr; rr += 8)
+      o[(size_t)rr * nCols] = us ? ucst + us[(size_t)(rb + rr) * ustride] : tcol[db_pos(rr)];
   }
 }
 

@@ -34,6 +34,15 @@ __device__ __forceinline__ void dmma884(double& c0, double& c1, double a, double
                : "d"(a), "d"(b));
 }
 
+// m16n8k8 (PTX ISA fragment layout, g = lane >> 2, t = lane & 3): a0 (g, t), a1 (g + 8, t), a2 (g, t + 4),
+// a3 (g + 8, t + 4); b0 (k = t, n = g), b1 (k = t + 4, n = g); c0 (g, 2t), c1 (g, 2t + 1), c2 (g + 8, 2t), c3 (g + 8, 2t + 1)
+__device__ __forceinline__ void dmma1688(double& c0, double& c1, double& c2, double& c3, double a0, double a1, double a2,
+                                         double a3, double b0, double b1) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f64.f64.f64.f64 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+d"(c0), "+d"(c1), "+d"(c2), "+d"(c3)
+               : "d"(a0), "d"(a1), "d"(a2), "d"(a3), "d"(b0), "d"(b1));
+}
+
 struct DenseCol {
   int32_t group;  // device group index
   int32_t j;      // column inside the group
@@ -344,16 +353,16 @@ k_rmm_dmma3(const DenseDesc* __restrict__ dd, int nDense, const SpItem* __restri
           if (nr0 < U1) wq = stage_map(nr0, U1 < nr0 + 16 ? U1 : nr0 + 16, nk0);
         }
         __syncwarp();
+        // m16n8k8: the 16 staged rows are one A tile, so a quarter of the tensor instructions of the m8n8k4 form for
+        // the same fragment loads (both shapes run at the same rate; the kernel is short of issue slots, not of math)
 #pragma unroll
-        for (int ks = 0; ks < GM_KC; ks += 4) {
-          double a[2];
-#pragma unroll
-          for (int mt = 0; mt < 2; mt++) a[mt] = W[(mt * 8 + am) * GM_LDAR + ks + ak];
+        for (int ks = 0; ks < GM_KC; ks += 8) {
+          const double a0 = W[am * GM_LDAR + ks + ak], a1 = W[(8 + am) * GM_LDAR + ks + ak];
+          const double a2 = W[am * GM_LDAR + ks + 4 + ak], a3 = W[(8 + am) * GM_LDAR + ks + 4 + ak];
 #pragma unroll
           for (int nt = 0; nt < NT; nt++) {
-            const double b = Vs[(k0 + ks + ak) * LDB + nt * 8 + am];
-#pragma unroll
-            for (int mt = 0; mt < 2; mt++) dmma884(c[mt][nt][0], c[mt][nt][1], a[mt], b);
+            const double b0 = Vs[(k0 + ks + ak) * LDB + nt * 8 + am], b1 = Vs[(k0 + ks + 4 + ak) * LDB + nt * 8 + am];
+            dmma1688(c[0][nt][0], c[0][nt][1], c[1][nt][0], c[1][nt][1], a0, a1, a2, a3, b0, b1);
           }
         }
       }

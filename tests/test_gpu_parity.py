@@ -257,6 +257,31 @@ def test_full_size_checksum_config2(oracle):
     cmb.free()
 
 
+def test_pageable_operands_through_the_pinned_ring():
+    """Host operands in ordinary (pageable) memory, as a JVM heap array is, are moved through the handle's pinned
+    ring by host threads; pinned operands take plain asynchronous copies. Both must give the same bits: t(y) %*% X
+    (upload of y in slices, the product of a row range starting when its last slice is queued), X %*% v (download of
+    the result) and decompress (a download of many ring rounds)."""
+    import torch
+    nRows = (1 << 20) + 777
+    cmb = _ddc_matrix(nRows, [256] * 24, 11)
+    cmb.to_device()
+    rng = np.random.default_rng(5)
+    y = rng.standard_normal((1, nRows))                       # pageable
+    y_pin = torch.from_numpy(y.copy()).pin_memory().numpy()   # pinned
+    a = np.array(CLALibLeftMultBy.leftMultByMatrix(cmb, y))
+    b = np.array(CLALibLeftMultBy.leftMultByMatrix(cmb, y_pin))
+    assert np.array_equal(a, b)
+    X = dense_of(cmb)
+    assert rel_err(a, y @ X, np.abs(y) @ np.abs(X) + 1e-300) < TOL
+    v = rng.standard_normal(cmb.clen)
+    u = np.array(CLALibRightMultBy.rightMultByMatrix(cmb, v)).ravel()    # 8 MB result into a pageable array
+    assert rel_err(u, X @ v, np.abs(X) @ np.abs(v) + 1e-300) < TOL
+    assert np.array_equal(np.array(CLALibRightMultBy.rightMultByMatrix(cmb, v)).ravel(), u)
+    assert np.array_equal(np.array(CLALibDecompress.decompress(cmb)), X)  # 200 MB: the ring is reused many times
+    cmb.free()
+
+
 def test_benchmark_shapes_against_oracle(oracle):
     """The five benchmark configurations at sizes the oracle finishes in seconds, each through its own operation."""
     # configs[0] at full size: X %*% v, 1M x 100, 16 values per column
