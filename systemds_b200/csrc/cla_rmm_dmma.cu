@@ -226,7 +226,7 @@ struct SpItem {
 };
 
 // NT = 8-column tiles per CTA (8: 64 output columns, two per lane in the sparse phase; 4: 32 columns, one per lane),
-// WARPS = warps per CTA. Sixteen warps of at most 128 registers: with eight, the SM issued 0.9 instructions per clock
+// WARPS = warps per CTA, IB = table rows in flight per warp in the sparse phase. Sixteen warps of at most 128 registers: with eight, the SM issued 0.9 instructions per clock
 // (two warps per scheduler, every instruction waiting out the latency of the one before) and neither the tensor
 // pipe nor the L1 data pipe was busy; the per-warp buffers are sized so that sixteen fit next to V.
 template <int NT, int WARPS>
@@ -240,7 +240,7 @@ struct G3 {
   static constexpr int KMAX = ((227 * 1024 - 1024 - WARPS * WBUF * 8) / (LDB * 8)) / GM_KC * GM_KC;  // resident rows of V
 };
 
-template <int NT, int WARPS>
+template <int NT, int WARPS, int IB>
 __global__ void __launch_bounds__(WARPS * 32, 1)
 k_rmm_dmma3(const DenseDesc* __restrict__ dd, int nDense, const SpItem* __restrict__ stepItems,
             const uint32_t* __restrict__ stepPtr, const SpItem* __restrict__ winItems,
@@ -401,7 +401,7 @@ k_rmm_dmma3(const DenseDesc* __restrict__ dd, int nDense, const SpItem* __restri
             const uint32_t p0 = toWin ? q0 : pa, p1 = toWin ? (w == 7 ? wpEnd : q1n) : (step == 63 ? spEnd : pbn);
             // items [p0, p1): 32 per coalesced load; every lane turns its own item into the byte offset of the table
             // row and a word {offset of the first row in the tile, number of rows, "add to the base vector"} once,
-            // so that the serial part per item is two shuffles, one load and one read-modify-write. Eight table
+            // so that the serial part per item is two shuffles, one load and one read-modify-write. IB table
             // rows are in flight at a time; items are applied in list order.
 #pragma unroll 1
             for (uint32_t i0 = p0; i0 < p1; i0 += 32) {
@@ -414,12 +414,12 @@ k_rmm_dmma3(const DenseDesc* __restrict__ dd, int nDense, const SpItem* __restri
                 wrd = (ra * (uint32_t)(LDC * 8)) | (nr << 16) | ((toWin || (whole && nr == G3_STEP)) ? 0x80000000u : 0u);
               }
 #pragma unroll 1
-              for (int b0 = 0; b0 < cnt; b0 += 8) {
-                double2 t[8];
-                uint32_t rw[8];
-                const int nb = min(8, cnt - b0);
+              for (int b0 = 0; b0 < cnt; b0 += IB) {
+                double2 t[IB];
+                uint32_t rw[IB];
+                const int nb = min(IB, cnt - b0);
 #pragma unroll
-                for (int j = 0; j < 8; j++) {
+                for (int j = 0; j < IB; j++) {
                   const uint32_t po = __shfl_sync(0xffffffffu, offP, (b0 + j) & 31);
                   rw[j] = __shfl_sync(0xffffffffu, wrd, (b0 + j) & 31);
                   if (j < nb) {
@@ -429,7 +429,7 @@ k_rmm_dmma3(const DenseDesc* __restrict__ dd, int nDense, const SpItem* __restri
                   }
                 }
 #pragma unroll
-                for (int j = 0; j < 8; j++) {
+                for (int j = 0; j < IB; j++) {
                   if (j < nb) {
                     if (rw[j] & 0x80000000u) {  // covers the whole step (or window): one add to a vector in registers
                       if (toWin) {
@@ -755,8 +755,8 @@ int64_t launch_rmm_dmma(Matrix* m, const double* dV, int vCols, double* dOut, cu
   bool& attr = attrSet[m->device & 63];
   if (!attr) {
     CLA_CUDA(cudaFuncSetAttribute(k_rmm_dmma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    CLA_CUDA(cudaFuncSetAttribute(k_rmm_dmma3<8, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-    CLA_CUDA(cudaFuncSetAttribute(k_rmm_dmma3<4, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+    CLA_CUDA(cudaFuncSetAttribute(k_rmm_dmma3<8, 16, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+    CLA_CUDA(cudaFuncSetAttribute(k_rmm_dmma3<4, 16, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
     attr = true;
   }
   prof_begin(m, s);
@@ -775,7 +775,9 @@ int64_t launch_rmm_dmma(Matrix* m, const double* dV, int vCols, double* dOut, cu
       const int nk = std::min(kMax, m->nDenseCols - k0);
       const bool first = k0 == 0;
       const size_t smem3 = ((size_t)((nk + GM_KC - 1) / GM_KC * GM_KC) * ldb + (size_t)W * wbuf) * sizeof(double);
-      auto kern = wide ? k_rmm_dmma3<8, 16> : k_rmm_dmma3<4, 16>;
+      // table rows in flight per warp in the sparse phase: 4 with the 64-column tile (8 cost more in spilled
+      // registers than the extra loads in flight gain: 10.1 vs 9.76 ms on 4M rows of the mixed benchmark matrix)
+      auto kern = wide ? k_rmm_dmma3<8, 16, 4> : k_rmm_dmma3<4, 16, 8>;
       kern<<<grid, W * 32, smem3, s>>>(dd + k0, nk, first ? (const SpItem*)m->dStepItems : nullptr,
                                        first ? m->dStepPtr : nullptr, (const SpItem*)m->dWinItems, m->dWinPtr, m->nRows, dV,
                                        vCols, P, first ? constRow : nullptr, dOut, first ? 0 : 1);
