@@ -220,6 +220,71 @@ class Workload:
     def P(self, t):
         return C.c_void_p(t.data_ptr())
 
+    comm = None          # shared by all workloads of this process (one buffer of 10,000 doubles per rank)
+    comm_note = "nccl"
+
+    @classmethod
+    def setup_allreduce(cls, rank, local_rank, world, dev, kind):
+        """The exchange that ends a step on N > 1 GPUs: the library's kernel over peer memory (checked once against
+        NCCL on a random vector), or NCCL when that is asked for or the peer setup fails."""
+        import torch
+        import torch.distributed as dist
+        if world == 1 or kind == "nccl":
+            return
+        from systemds_b200.comm import HANDLE_BYTES, PeerAllReduce, torch_exchange
+
+        def all_ok(flag):  # every stage is agreed on by all ranks, so no rank waits in a collective the others skipped
+            f = torch.tensor([int(flag)], device=dev)
+            dist.all_reduce(f, op=dist.ReduceOp.MIN)
+            return int(f[0]) == 1
+
+        c, err = None, None
+        try:
+            c = PeerAllReduce(rank, world, local_rank, 10000, connect=False)
+        except Exception as e:  # noqa: BLE001
+            err = e
+        handles = torch_exchange(dev)(c.handle_bytes if c is not None else bytes(HANDLE_BYTES))
+        stage = all_ok(c is not None)
+        if stage:
+            try:
+                c.connect(handles=handles)
+            except Exception as e:  # noqa: BLE001
+                err = e
+            stage = all_ok(err is None)
+        ok = 0
+        if stage:
+            g = torch.Generator(device=dev)
+            g.manual_seed(1234 + rank)
+            x = torch.randn(10000, dtype=torch.float64, device=dev, generator=g)
+            y = x.clone()
+            dist.all_reduce(y)
+            try:
+                c(x.data_ptr(), 10000, torch.cuda.current_stream().cuda_stream)
+                c.status()
+                ok = int(bool(((x - y).abs() <= 1e-12 * (x.abs() + y.abs()) + 1e-15).all()))
+            except Exception as e:  # noqa: BLE001
+                err = e
+        if err is not None:
+            cls.comm_note = f"nccl (peer setup failed: {type(err).__name__}: {str(err)[:80]})"
+        cls.comm = c
+        t = torch.tensor([ok], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        if int(t[0]) == 1:
+            cls.comm_note = "cla_allreduce_dev: one kernel per rank over NVLink peer memory (stores + flags, rank-ordered sum)"
+        else:
+            if cls.comm is not None:
+                cls.comm.close()
+            cls.comm = None
+            if cls.comm_note == "nccl":
+                cls.comm_note = "nccl (peer result did not match)"
+
+    def allreduce(self, t):
+        import torch.distributed as dist
+        if Workload.comm is not None:
+            Workload.comm(t.data_ptr(), t.numel(), self.sptr.value or 0)
+        else:
+            dist.all_reduce(t)
+
     def build(self):
         import torch
         from systemds_b200 import datagen, datagen_dev
@@ -269,7 +334,6 @@ class Workload:
 
     # one product with device-resident operands, on the current stream
     def step(self):
-        import torch.distributed as dist
         from systemds_b200.native import check
         L, h, P, s = self.L, self.h, self.P, self.sptr
         if self.idx == 0:
@@ -277,17 +341,17 @@ class Workload:
         elif self.idx == 1:
             check(L.cla_lmm_dev(h, P(self.y), 1, P(self.out), s))
             if self.world > 1:
-                dist.all_reduce(self.out)
+                self.allreduce(self.out)
         elif self.idx == 2:
             check(L.cla_rmm_dev(h, P(self.V), 500, 64, P(self.out), s))
         elif self.idx == 3:
             check(L.cla_tsmm_dev(h, P(self.out), s))
             if self.world > 1:
-                dist.all_reduce(self.out)
+                self.allreduce(self.out)
         else:
             check(L.cla_mmchain_dev(h, P(self.v), None, 0, P(self.out), P(self.u), s))
             if self.world > 1:
-                dist.all_reduce(self.out)
+                self.allreduce(self.out)
             self.out.add_(self.v, alpha=1e-3)  # after the reduce, once (scripts/builtin/lmCG.dml: q = t(X) %*% (X %*% p) + lambda * p)
 
     @property
@@ -347,7 +411,7 @@ class Workload:
             check(L.cla_mmchain(h, a(self.e_in), None, 0, a(self.e_out)))
         if self.world > 1 and self.idx in (1, 3, 4):  # the partial results of the shards add up
             t = torch.from_numpy(self.e_out).to(self.dev)
-            dist.all_reduce(t)
+            self.allreduce(t)
             self.e_out[...] = t.cpu().numpy()
         if self.idx == 4:
             self.e_out += 1e-3 * self.e_in
@@ -405,7 +469,10 @@ def time_steps(wl: Workload, steps: int, warmup: int, world: int):
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     k_ms = (st1["main_kernel_ms"] - st0["main_kernel_ms"]) / steps
-    return float(t[0]) / steps, k_ms, int(st1["kernel_launches"] - st0["kernel_launches"])
+    launches = int(st1["kernel_launches"] - st0["kernel_launches"])
+    if Workload.comm is not None and wl.idx in (1, 3, 4):
+        launches += steps  # k_peer_allreduce, once per step
+    return float(t[0]) / steps, k_ms, launches
 
 
 def roofline_of(wl: Workload, k_ms: float, hbm_peak: float, peak_kind: str, dmma_peak: float):
@@ -444,6 +511,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-also", action="store_true", help="skip the other four workloads")
     ap.add_argument("--also-steps", type=int, default=5)
+    ap.add_argument("--allreduce", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: the library's exchange over peer memory (default) or NCCL")
     ap.add_argument("--decompress", action="store_true",
                     help="also time cla_decompress_dev of the main workload's matrix into a device buffer (one GPU)")
     ap.add_argument("--also-rows-scale", type=float, default=1.0, help="scale the rows of the 'also' workloads (profiling aid)")
@@ -475,6 +544,7 @@ def main():
     check(L.cla_measure_fp64_peaks(local_rank, C.byref(dm), C.byref(df)))
     dmma_peak = dm.value
 
+    Workload.setup_allreduce(rank, local_rank, world, dev, args.allreduce)
     w = args.workload
     n = args.rows or DEFAULT_ROWS[w]
     # the main workload keeps host-generated arrays when the CPU baseline will read them (workload 1 on one GPU)
@@ -512,6 +582,7 @@ def main():
         "data": "synthetic",
         "config": {"workload": DESCS[w], "rows_per_gpu": n,
                    "parallelism": f"row-sharded x{world}" if world > 1 else "single GPU",
+                   "allreduce": Workload.comm_note if world > 1 else None,
                    "l2": ("256 MB buffer written between timed steps (inputs are below the 126 MB L2)" if main.needs_l2_flush
                           else f"inputs ({main.index_bytes / 1e9:.2f} GB per step) larger than L2; no flush needed"),
                    "host": {"numa_node": numa_node, "cpus": len(os.sched_getaffinity(0))}},
@@ -589,6 +660,9 @@ def main():
         result["also"] = also
     if rank == 0:
         print(json.dumps(result))
+    if Workload.comm is not None:
+        Workload.comm.status()
+        Workload.comm.close()
     if world > 1:
         dist.destroy_process_group()
 

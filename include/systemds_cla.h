@@ -234,6 +234,24 @@ int64_t cla_mmchain_dev(cla_handle h, const double* dV, const double* dW, int32_
  * stream first), so two calls whose kernels overlap on the GPU -- different streams or handles -- race. */
 int64_t cla_lmm_vec_noalloc_dev(cla_handle h, const double* dY, double* dOut, void* stream);
 
+/* ---- The sum over the ranks that ends a product on a row-sharded block (one process per GPU, one node) ----
+ * It has no counterpart in the reference, whose compressed products run in one JVM. Each rank holds the rows of its
+ * shard; t(y) %*% X, t(X) %*% X and the chain give per-rank partial results that add up. cla_allreduce_dev sums n
+ * doubles in place over all ranks with one kernel per rank over NVLink peer memory (stores into every peer's
+ * buffer, a flag, a bounded wait, the sum in rank order: all ranks end with identical bits). Setup: every rank
+ * calls cla_comm_create, the host passes the 64-byte handles of all ranks (rank order) to cla_comm_connect.
+ * All ranks must call cla_allreduce_dev the same number of times in the same order. A rank that does not arrive
+ * within the time limit (default 2 s) makes the others fill their result with NaN; cla_comm_status (which
+ * synchronises the device) then returns CLA_ERR_DEVICE_CHECK naming the missing rank, and the comm stays usable.
+ * cla_comm_connect(comm, NULL) maps every rank to the caller's own buffer (single-process checks). */
+#define CLA_COMM_HANDLE_BYTES 64
+int64_t cla_comm_create(int32_t device, int32_t rank, int32_t world, int64_t maxDoubles, void* ipcHandleOut);
+int64_t cla_comm_connect(int64_t comm, const void* allHandles);
+int64_t cla_comm_set_timeout_ms(int64_t comm, int64_t ms);
+int64_t cla_allreduce_dev(int64_t comm, double* dBuf, int64_t n, void* stream);
+int64_t cla_comm_status(int64_t comm);
+int64_t cla_comm_destroy(int64_t comm);
+
 /* ---- decoded index structures (for bit-exact checks and for f2-style consumers) -------------
  * ids[nRows]: dictionary id of every row of group g, -1 where the row holds the default (or zero)
  * tuple; for an uncompressed group the row number. Computed by the device decode kernels.

@@ -10,7 +10,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libsystemds_cla.so")
-SOURCES = ["cla_finalize.cu", "cla_generic.cu", "cla_fast.cu", "cla_tsmm.cu", "cla_pairs.cu", "cla_rmm_dmma.cu", "cla_agg.cu", "cla_api.cu", "cla_wire.cu", "cla_hostcopy.cu"]
+SOURCES = ["cla_finalize.cu", "cla_generic.cu", "cla_fast.cu", "cla_tsmm.cu", "cla_pairs.cu", "cla_rmm_dmma.cu", "cla_agg.cu", "cla_api.cu", "cla_wire.cu", "cla_hostcopy.cu", "cla_comm.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--extended-lambda",
               "-Xcompiler", "-fPIC", "-Wno-deprecated-gpu-targets"]
 

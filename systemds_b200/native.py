@@ -66,6 +66,12 @@ SIGNATURES = {
     "cla_decompress_dev": [_I64, _P, _P],
     "cla_tmm_dev": [_I64, _I64, _P, _P],
     "cla_mmchain_dev": [_I64, _P, _P, _I32, _P, _P, _P],
+    "cla_comm_create": [_I32, _I32, _I32, _I64, _P],
+    "cla_comm_connect": [_I64, _P],
+    "cla_comm_set_timeout_ms": [_I64, _I64],
+    "cla_allreduce_dev": [_I64, _P, _I64, _P],
+    "cla_comm_status": [_I64],
+    "cla_comm_destroy": [_I64],
     "cla_group_decode": [_I64, _I32, _P],
     "cla_group_counts": [_I64, _I32, _P],
 }

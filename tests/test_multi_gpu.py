@@ -1,6 +1,6 @@
 """Row-sharded products on two GPUs: one process per GPU, each holding a row shard on its device; the partial
-results of t(y) X, t(X) X and t(X)(X v) are all-reduced with NCCL (the path's only exchange step) and checked against
-the dense product; X v stays row partitioned. Skipped where fewer than two GPUs are visible."""
+results of t(y) X, t(X) X and t(X)(X v) are all-reduced (the path's only exchange step) with NCCL and with the library's
+own kernel over peer memory, and checked against the dense product; X v stays row partitioned. Skipped where fewer than two GPUs are visible."""
 import ctypes as C
 import os
 import socket
@@ -45,12 +45,36 @@ def _rank(rank, world, port, q):
     check(L.cla_tsmm_dev(h, P(tsmm), s))
     check(L.cla_mmchain_dev(h, P(vd), None, 0, P(chain), None, s))
     check(L.cla_rmm_dev(h, P(vd), n, 1, P(u), s))
+    # the same sums through the library's own exchange over peer memory (cla_allreduce_dev), before NCCL touches them
+    from systemds_b200.comm import PeerAllReduce, torch_exchange
+    comm = PeerAllReduce(rank, world, rank, n * n, torch_exchange(dev))
+    peer = [t.clone() for t in (lmm, tsmm, chain)]
+    for _ in range(3):  # repeated calls walk both slot parities
+        again = [t.clone() for t in (lmm, tsmm, chain)]
+        for t in again:
+            comm(t.data_ptr(), t.numel(), s.value)
+    for t in peer:
+        comm(t.data_ptr(), t.numel(), s.value)
+    comm.status()
+    same = all(torch.equal(a_, b_) for a_, b_ in zip(peer, again))
     for t in (lmm, tsmm, chain):
         dist.all_reduce(t)
     torch.cuda.synchronize()
+    # every rank holds identical bits of the peer sums (rank-ordered addition), and they agree with NCCL's to rounding
+    bits = [torch.zeros_like(t) for t in peer]
+    for b_, t in zip(bits, peer):
+        b_.copy_(t)
+        dist.broadcast(b_, 0)
+    same = same and all(torch.equal(a_, b_) for a_, b_ in zip(peer, bits))
+    close = all(bool(((a_ - b_).abs() <= 1e-12 * (a_.abs() + b_.abs()) + 1e-300).all()) or
+                float((a_ - b_).abs().max()) <= 1e-9 * float(b_.abs().max()) for a_, b_ in zip(peer, (lmm, tsmm, chain)))
+    ok = torch.tensor([int(same), int(close)], device=dev)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    comm.close()
     st = part.stats()
     if rank == 0:
-        q.put([lmm.cpu().numpy(), tsmm.cpu().numpy(), chain.cpu().numpy(), u.cpu().numpy(), st["kernel_launches"]])
+        q.put([lmm.cpu().numpy(), tsmm.cpu().numpy(), chain.cpu().numpy(), u.cpu().numpy(), st["kernel_launches"],
+               ok.cpu().tolist()])
     dist.barrier()
     part.free()
     dist.destroy_process_group()
@@ -69,11 +93,12 @@ def test_two_gpu_partials_add_up(oracle):
     procs = [ctx.Process(target=_rank, args=(r, 2, port, q)) for r in range(2)]
     for p in procs:
         p.start()
-    lmm, tsmm, chain, u0, launches = q.get(timeout=300)
+    lmm, tsmm, chain, u0, launches, peer_ok = q.get(timeout=300)
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
     assert launches > 0
+    assert peer_ok == [1, 1], "peer-memory all-reduce: [identical on all ranks and between calls, agrees with NCCL]"
     cmb = datagen.random_cmb(44, NROWS, KINDS)
     X = dense_of(cmb)
     aX = np.abs(X)
