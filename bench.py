@@ -511,6 +511,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-also", action="store_true", help="skip the other four workloads")
     ap.add_argument("--also-steps", type=int, default=5)
+    ap.add_argument("--strong", action="store_true",
+                    help="strong scaling: the workload's rows are split over the N GPUs instead of each GPU holding all of them")
     ap.add_argument("--allreduce", default="peer", choices=["peer", "nccl"],
                     help="N > 1: the library's exchange over peer memory (default) or NCCL")
     ap.add_argument("--decompress", action="store_true",
@@ -547,6 +549,8 @@ def main():
     Workload.setup_allreduce(rank, local_rank, world, dev, args.allreduce)
     w = args.workload
     n = args.rows or DEFAULT_ROWS[w]
+    if args.strong:
+        n = max(4096, n // world)
     # the main workload keeps host-generated arrays when the CPU baseline will read them (workload 1 on one GPU)
     main = Workload(w, n, rank, local_rank, world, dev, L, host_gen=(w == 1)).build()
 
@@ -578,7 +582,7 @@ def main():
 
     result = {
         "metric": METRICS[w], "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64",
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if args.strong else "weak", "vs_baseline": None, "dtype": "f64",
         "data": "synthetic",
         "config": {"workload": DESCS[w], "rows_per_gpu": n,
                    "parallelism": f"row-sharded x{world}" if world > 1 else "single GPU",
@@ -648,7 +652,7 @@ def main():
         for i in range(5):
             if i == w:
                 continue
-            rows = max(4096, int(DEFAULT_ROWS[i] * args.also_rows_scale))
+            rows = max(4096, int(DEFAULT_ROWS[i] * args.also_rows_scale) // (world if args.strong else 1))
             wl = Workload(i, rows, rank, local_rank, world, dev, L).build()
             ms_i, k_i, launches_i = time_steps(wl, args.also_steps, 3, world)
             also[f"workload{i}"] = {"metric": METRICS[i], "workload": DESCS[i], "rows_per_gpu": rows,

@@ -140,6 +140,17 @@ struct HostGroup {
   int devSrcDevice = -1;
 };
 
+// Row-major work lists of the SDC / RLE groups (built by ensure_sparse_lists, cla_rmm_dmma.cu): rows are cut into
+// steps of 8 and windows of 64, a warp work unit of the tensor-core right product is 512 rows.
+constexpr int G3_UNIT = 512;
+constexpr int G3_STEP = 8;
+constexpr int G3_WIN = 64;
+// One piece of work: rows [ra, rb) of an 8-row step (or a whole 64-row window) receive table row prow.
+struct SpItem {
+  uint32_t prow;
+  uint32_t rows;  // ra | rb << 8
+};
+
 struct FastPlan;  // plans of the specialised DDC kernels (cla_fast.cu)
 struct HostStage; // pinned ring for operands in pageable host memory (cla_hostcopy.cu)
 
@@ -175,6 +186,11 @@ struct Matrix {
   bool denseColsBuilt = false;
   int32_t* dSparseIdx = nullptr;  // device group indices of the SDC groups with listed rows and RLE groups with runs, list order
   int nSparse = 0;
+  // the other groups by kind, list order: dense-map groups (all, then those the specialised kernels do not take), uncompressed
+  int32_t* dDdcIdx = nullptr;
+  int32_t* dDdcRestIdx = nullptr;
+  int32_t* dUncIdx = nullptr;
+  int nDdc = 0, nDdcRest = 0, nUnc = 0;
   bool sparseListBuilt = false;
   // row-major work lists of the SDC / RLE groups for the tensor-core right product (cla_rmm_dmma.cu), built on first use
   void* dStepItems = nullptr;
@@ -182,6 +198,7 @@ struct Matrix {
   void* dWinItems = nullptr;
   uint32_t* dWinPtr = nullptr;
   bool spListsTried = false, spListsOk = false;
+  int64_t nStepPtr = 0, nWinPtr = 0;  // entries of dStepPtr / dWinPtr (the last one = number of items)
   int32_t* dColSrc = nullptr;    // [nCols][2]: dense-map / uncompressed group holding the column and the position in it (-1: none)
   bool colSrcValid = false;      // false when some column is held by more than one such group (overlapping input)
   bool hasConst = false;
@@ -244,7 +261,8 @@ int64_t host_to_device_staged(Matrix* m, void* dDst, const void* host, size_t by
                               const std::function<int64_t(size_t)>& enqueued);
 int64_t device_to_host_staged(Matrix* m, void* host, const void* dSrc, size_t bytes, cudaStream_t s);
 void host_stage_free(Matrix* m);
-int64_t ensure_sparse_list(Matrix* m);  // Matrix::dSparseIdx (cla_generic.cu)
+int64_t ensure_sparse_list(Matrix* m);
+int64_t ensure_sparse_lists(Matrix* m, cudaStream_t s);  // the row-major work lists; m->spListsOk tells whether they exist  // Matrix::dSparseIdx (cla_generic.cu)
 
 // launchers implemented in the kernel translation units; all enqueue on `s` and return CLA_OK or an error.
 int64_t launch_rmm(Matrix* m, const double* dV, int vCols, double* dOut, cudaStream_t s, bool afterFast = false);

@@ -548,7 +548,7 @@ __global__ void k_rmm_b_tables(const LmmChunk* __restrict__ chunks, const int* _
   int base = 0;
   for (int u = 0; u < ch.nUnits; u++) {
     const int n = ch.nk[u] * 16;
-    for (int e = threadIdx.x; e < n; e += blockDim.x) {
+    for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < n; e += gridDim.y * blockDim.x) {  // gridDim.y CTAs per chunk
       const int col = slotCol[(ch.unit0 + u) * 16 + (e & 15)];
       P[ch.tblOff + base + e] = col >= 0 ? T[ch.tblOff + base + e] * v[col] : 0.0;
     }
@@ -655,7 +655,7 @@ __global__ void k_rmm_f_tables(const DevGroup* __restrict__ groups, const LmmChu
   int base = 0;
   for (int q = 0; q < ch.nUnits; q++) {
     const int n = ch.nk[q] * 16;
-    for (int e = threadIdx.x; e < n; e += blockDim.x) {
+    for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < n; e += gridDim.y * blockDim.x) {  // gridDim.y CTAs per chunk
       const FusedUnit u = units[(ch.unit0 + q) * 16 + (e & 15)];
       const int k = e >> 4;
       double val = 0.0;
@@ -1159,7 +1159,7 @@ static int64_t fast_rmm_vec_b(Matrix* m, FastPlan* fp, const double* dV, double*
   if ((rc = ensure_scratch(m, pBytes + 256)) < 0) return rc;
   double* P = (double*)m->scratch;
   double* constRow = nullptr;
-  k_rmm_b_tables<<<(unsigned)fp->lchunks.size(), 256, 0, s>>>(fp->dLChunks, fp->dSlotCol, fp->dLmmTables, dV, P);
+  k_rmm_b_tables<<<dim3((unsigned)fp->lchunks.size(), 16), 256, 0, s>>>(fp->dLChunks, fp->dSlotCol, fp->dLmmTables, dV, P);
   m->stats.kernel_launches++;
   if (m->hasConst) {
     constRow = (double*)((char*)m->scratch + pBytes);
@@ -1185,7 +1185,7 @@ static int64_t fast_rmm_vec_f(Matrix* m, FastPlan* fp, const double* dV, double*
   if ((rc = ensure_scratch(m, pBytes + 256)) < 0) return rc;
   double* P = (double*)m->scratch;
   double* constRow = nullptr;
-  k_rmm_f_tables<<<(unsigned)fp->fchunks.size(), 256, 0, s>>>(m->dGroups, fp->dFChunks, fp->dFUnits, dV, P);
+  k_rmm_f_tables<<<dim3((unsigned)fp->fchunks.size(), 16), 256, 0, s>>>(m->dGroups, fp->dFChunks, fp->dFUnits, dV, P);
   m->stats.kernel_launches++;
   if (m->hasConst) {
     constRow = (double*)((char*)m->scratch + pBytes);

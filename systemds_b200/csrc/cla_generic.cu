@@ -69,42 +69,98 @@ __global__ void k_const_times_v(const double* __restrict__ constV, int nCols, co
 constexpr int RV_THREADS = 256;
 constexpr int RV_WARPS = RV_THREADS / 32;
 constexpr size_t RV_SMEM = (size_t)(RV_WARPS + 1) * SKIP_ROWS * sizeof(double);
+// LISTS: the SDC / RLE contributions come from the row-major work lists (8-row steps, 64-row windows) instead of the
+// rounds of step 3: a thread owns one step of the block and applies its items in list order to its own eight sums,
+// a thread per window sums the runs that cover the window. No staging tile, two shared-memory updates per listed
+// row instead of sixteen per row and round.
+constexpr size_t RV_SMEM_LISTS = (size_t)(2 * SKIP_ROWS + 16) * sizeof(double);
+template <bool LISTS>
 __global__ void __launch_bounds__(RV_THREADS)
-k_rmm_vec_general(const DevGroup* __restrict__ groups, int nGroups, const int32_t* __restrict__ sparseIdx, int nSparse,
-                  int nRows, const double* __restrict__ P, const double* __restrict__ v,
-                  const double* __restrict__ constRow, double* __restrict__ out, int afterFast) {
+k_rmm_vec_general(const DevGroup* __restrict__ groups, const int32_t* __restrict__ ddcIdx, int nDdc,
+                  const int32_t* __restrict__ uncIdx, int nUnc, const int32_t* __restrict__ sparseIdx, int nSparse, int nRows, const double* __restrict__ P, const double* __restrict__ v,
+                  const double* __restrict__ constRow, double* __restrict__ out, int afterFast,
+                  const SpItem* __restrict__ stepItems, const uint32_t* __restrict__ stepPtr, int64_t nStepPtr,
+                  const SpItem* __restrict__ winItems, const uint32_t* __restrict__ winPtr, int64_t nWinPtr) {
   extern __shared__ __align__(16) double rvsm[];
   double* acc = rvsm;                  // [SKIP_ROWS]
-  double* stage = rvsm + SKIP_ROWS;    // [RV_WARPS][SKIP_ROWS]
+  double* stage = rvsm + SKIP_ROWS;    // [RV_WARPS][SKIP_ROWS]; LISTS: sums of the steps [8][128], then 16 window sums
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int r0 = blockIdx.x * SKIP_ROWS, r1 = min(nRows, r0 + SKIP_ROWS);
   for (int i = tid; i < SKIP_ROWS; i += RV_THREADS) acc[i] = 0.0;
   __syncthreads();
-  bool anyUnc = false;
-  // dense-map groups: a thread owns rows tid, tid + 256, ... of the block
-  for (int gi = 0; gi < nGroups; gi++) {
-    const DevGroup& g = groups[gi];
-    if (afterFast && g.inFast) continue;
-    if (g.type == GT_DDC) {
-      const double* Pg = P + g.valOff;
-      for (int r = r0 + tid; r < r1; r += RV_THREADS) acc[r - r0] += Pg[map_get(g.mapType, g.map, g.mapHi, r)];
-    } else if (g.type == GT_UNC)
-      anyUnc = true;
+  // dense-map groups (list order; after the specialised kernels only those they left): a thread owns rows tid, tid + 256, ...
+  for (int i = 0; i < nDdc; i++) {
+    const DevGroup& g = groups[ddcIdx[i]];
+    const double* Pg = P + g.valOff;
+    for (int r = r0 + tid; r < r1; r += RV_THREADS) acc[r - r0] += Pg[map_get(g.mapType, g.map, g.mapHi, r)];
   }
   __syncthreads();
-  // uncompressed groups: a warp owns rows warp, warp + 8, ...
-  if (anyUnc) {
-    for (int gi = 0; gi < nGroups; gi++) {
-      const DevGroup& g = groups[gi];
-      if (g.type != GT_UNC) continue;
-      for (int r = r0 + warp; r < r1; r += RV_WARPS) {
-        double s = 0;
-        for (int c = lane; c < g.gCols; c += 32) s += g.dense[(size_t)r * g.gCols + c] * v[g.cols[c]];
-        for (int d = 16; d; d >>= 1) s += __shfl_down_sync(0xffffffffu, s, d);
-        if (lane == 0) acc[r - r0] += s;
+  // uncompressed groups: a warp owns rows warp, warp + 8, ...; lanes along the dense row, two columns each per pass,
+  // four rows in flight (their loads are issued before the first of the four shuffle reductions)
+  for (int i = 0; i < nUnc; i++) {
+    const DevGroup& g = groups[uncIdx[i]];
+    const int gc = g.gCols;
+    const double* __restrict__ dense = g.dense;
+    for (int cb = 0; cb < gc; cb += 64) {
+      const int ca = cb + lane, cc = cb + 32 + lane;
+      const double va = ca < gc ? v[g.cols[ca]] : 0.0, vb = cc < gc ? v[g.cols[cc]] : 0.0;
+      for (int rb = r0 + warp * 4; rb < r1; rb += RV_WARPS * 4) {
+        double sum[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          const int r = rb + q;
+          const double* row = dense + (size_t)r * gc;
+          const double xa = (r < r1 && ca < gc) ? row[ca] : 0.0, xb = (r < r1 && cc < gc) ? row[cc] : 0.0;
+          sum[q] = xa * va + xb * vb;
+        }
+#pragma unroll
+        for (int q = 0; q < 4; q++)
+          for (int d = 16; d; d >>= 1) sum[q] += __shfl_down_sync(0xffffffffu, sum[q], d);
+        if (lane == 0) {
+#pragma unroll
+          for (int q = 0; q < 4; q++)
+            if (rb + q < r1) acc[rb + q - r0] += sum[q];
+        }
+      }
+    }
+  }
+  if (nUnc) __syncthreads();
+  if (LISTS) {
+    constexpr int NSTEP = SKIP_ROWS / G3_STEP, NWIN = SKIP_ROWS / G3_WIN;  // 128 steps, 16 windows per block
+    double* sacc = stage;                 // row i of step t at [i * NSTEP + t]: neighbouring threads, neighbouring words
+    double* wbase = stage + SKIP_ROWS;    // [NWIN]
+    for (int i = tid; i < SKIP_ROWS; i += RV_THREADS) sacc[i] = 0.0;
+    __syncthreads();
+    if (tid < NWIN) {  // runs that cover a whole window
+      const int64_t w = (int64_t)blockIdx.x * NWIN + tid;
+      const uint32_t p0 = winPtr[min(w, nWinPtr - 1)], p1 = winPtr[min(w + 1, nWinPtr - 1)];
+      double sum = 0.0;
+      for (uint32_t i = p0; i < p1; i++) sum += P[winItems[i].prow];
+      wbase[tid] = sum;
+    } else if (tid >= RV_THREADS - NSTEP) {  // listed rows and run pieces of one 8-row step, in list order
+      const int t = tid - (RV_THREADS - NSTEP);
+      const int64_t st = (int64_t)blockIdx.x * NSTEP + t;
+      const uint32_t p0 = stepPtr[min(st, nStepPtr - 1)], p1 = stepPtr[min(st + 1, nStepPtr - 1)];
+      SpItem e = p0 < p1 ? stepItems[p0] : SpItem{0, 0};
+      for (uint32_t i = p0; i < p1; i++) {
+        const SpItem nxt = i + 1 < p1 ? stepItems[i + 1] : SpItem{0, 0};  // next item in flight during this one's table read
+        const double p = P[e.prow];
+        const int ra = e.rows & 0xFF, rb = (e.rows >> 8) & 0xFF;
+        for (int r = ra; r < rb; r++) sacc[r * NSTEP + t] += p;
+        e = nxt;
       }
     }
     __syncthreads();
+    const double c0 = (constRow != nullptr && !afterFast) ? constRow[0] : 0.0;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const int rr = tid * 4 + i, r = r0 + rr;
+      if (r < r1) {
+        const double val = ((acc[rr] + sacc[(rr & 7) * NSTEP + (rr >> 3)]) + wbase[rr >> 6]) + c0;
+        out[r] = afterFast ? out[r] + val : val;
+      }
+    }
+    return;
   }
   // SDC / RLE groups, eight per round. From here on thread t owns rows 4 t .. 4 t + 3.
   double a4[4];
@@ -159,20 +215,34 @@ k_rmm_vec_general(const DevGroup* __restrict__ groups, int nGroups, const int32_
 // SDC groups with listed rows and RLE groups with runs, in list order (built once per handle)
 int64_t ensure_sparse_list(Matrix* m) {
   if (m->sparseListBuilt) return CLA_OK;
-  std::vector<int32_t> idx;
+  std::vector<int32_t> sparse, ddc, ddcRest, unc;
   for (int gi = 0; gi < m->nDev; gi++) {
     const DevGroup& g = m->groups[gi];
-    if ((g.type == GT_SDC && g.nOff > 0) || (g.type == GT_RLE && g.nRuns > 0)) idx.push_back(gi);
+    if ((g.type == GT_SDC && g.nOff > 0) || (g.type == GT_RLE && g.nRuns > 0)) sparse.push_back(gi);
+    if (g.type == GT_DDC) {
+      ddc.push_back(gi);
+      if (!g.inFast) ddcRest.push_back(gi);
+    }
+    if (g.type == GT_UNC) unc.push_back(gi);
   }
-  if (!idx.empty()) {
+  auto up = [&](const std::vector<int32_t>& idx, int32_t** d) -> int64_t {
+    if (idx.empty()) return CLA_OK;
     void* p = nullptr;
     cudaError_t e = cudaMalloc(&p, idx.size() * sizeof(int32_t));
-    if (e != cudaSuccess) return fail(CLA_ERR_NOMEM, std::string("cudaMalloc sparse group list: ") + cudaGetErrorString(e));
+    if (e != cudaSuccess) return fail(CLA_ERR_NOMEM, std::string("cudaMalloc group list: ") + cudaGetErrorString(e));
     m->allocs.push_back(p);
     CLA_CUDA(cudaMemcpy(p, idx.data(), idx.size() * sizeof(int32_t), cudaMemcpyHostToDevice));
-    m->dSparseIdx = (int32_t*)p;
-  }
-  m->nSparse = (int)idx.size();
+    *d = (int32_t*)p;
+    return CLA_OK;
+  };
+  int64_t rc;
+  if ((rc = up(sparse, &m->dSparseIdx)) < 0 || (rc = up(ddc, &m->dDdcIdx)) < 0 || (rc = up(ddcRest, &m->dDdcRestIdx)) < 0 ||
+      (rc = up(unc, &m->dUncIdx)) < 0)
+    return rc;
+  m->nSparse = (int)sparse.size();
+  m->nDdc = (int)ddc.size();
+  m->nDdcRest = (int)ddcRest.size();
+  m->nUnc = (int)unc.size();
   m->sparseListBuilt = true;
   return CLA_OK;
 }
@@ -207,12 +277,27 @@ int64_t launch_rmm(Matrix* m, const double* dV, int vCols, double* dOut, cudaStr
   static bool attrSet[64] = {};  // per device: function attributes belong to the device's context
   bool& attr = attrSet[m->device & 63];
   if (!attr) {
-    CLA_CUDA(cudaFuncSetAttribute(k_rmm_vec_general, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RV_SMEM));
+    CLA_CUDA(cudaFuncSetAttribute(k_rmm_vec_general<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RV_SMEM));
     attr = true;
   }
+  // matrices with many listed rows: the row-major work lists (shared with the tensor-core right product), built once
+  bool lists = false;
+  if (m->nSparse > 0 && m->nRows >= 4 * SKIP_ROWS) {
+    if ((rc = ensure_sparse_lists(m, s)) < 0) return rc;
+    lists = m->spListsOk && m->dStepPtr != nullptr;
+  }
+  const int32_t* ddcIdx = afterFast ? m->dDdcRestIdx : m->dDdcIdx;
+  const int nDdc = afterFast ? m->nDdcRest : m->nDdc;
   prof_begin(m, s);
-  k_rmm_vec_general<<<(m->nRows + SKIP_ROWS - 1) / SKIP_ROWS, RV_THREADS, RV_SMEM, s>>>(
-      m->dGroups, m->nDev, m->dSparseIdx, m->nSparse, m->nRows, P, dV, constRow, dOut, afterFast ? 1 : 0);
+  const unsigned grid = (unsigned)((m->nRows + SKIP_ROWS - 1) / SKIP_ROWS);
+  if (lists)
+    k_rmm_vec_general<true><<<grid, RV_THREADS, RV_SMEM_LISTS, s>>>(
+        m->dGroups, ddcIdx, nDdc, m->dUncIdx, m->nUnc, m->dSparseIdx, m->nSparse, m->nRows, P, dV, constRow, dOut, afterFast ? 1 : 0,
+        (const SpItem*)m->dStepItems, m->dStepPtr, m->nStepPtr, (const SpItem*)m->dWinItems, m->dWinPtr, m->nWinPtr);
+  else
+    k_rmm_vec_general<false><<<grid, RV_THREADS, RV_SMEM, s>>>(m->dGroups, ddcIdx, nDdc, m->dUncIdx, m->nUnc, m->dSparseIdx, m->nSparse, m->nRows, P, dV,
+                                                             constRow, dOut, afterFast ? 1 : 0, nullptr, nullptr, 0, nullptr,
+                                                             nullptr, 0);
   prof_end(m, s);
   m->stats.kernel_launches++;
   CLA_CUDA(cudaGetLastError());
@@ -433,6 +518,12 @@ k_decomp_block(const DevGroup* __restrict__ groups, const int32_t* __restrict__ 
           const uint32_t w = __ldg((const uint32_t*)((const uint8_t*)g.map + rb) + lane);  // rb is a multiple of 128
 #pragma unroll
           for (int u = 0; u < 4; u++) id[u] = (w >> (8 * u)) & 0xFF;
+        } else if (mt == CLA_MAP_CHAR && nr == DB_ROWS) {
+          const uint2 w = __ldg((const uint2*)((const uint16_t*)g.map + rb) + lane);  // four 16-bit ids per lane
+          id[0] = w.x & 0xFFFF;
+          id[1] = w.x >> 16;
+          id[2] = w.y & 0xFFFF;
+          id[3] = w.y >> 16;
         } else {
 #pragma unroll
           for (int u = 0; u < 4; u++) id[u] = rr0 + u < nr ? map_get(mt, g.map, g.mapHi, rb + rr0 + u) : 0;

@@ -215,15 +215,6 @@ struct DenseDesc {
   int32_t pad;
 };
 
-constexpr int G3_UNIT = 512;         // rows per warp work unit: 64 steps of 8 rows, 8 windows of 64
-constexpr int G3_STEP = 8;           // rows per step of the sparse work lists (one DMMA row tile)
-constexpr int G3_WIN = 64;
-
-// One piece of work of the sparse phase: rows [ra, rb) of an 8-row step (or a whole 64-row window) receive table row prow.
-struct SpItem {
-  uint32_t prow;
-  uint32_t rows;  // ra | rb << 8
-};
 
 // NT = 8-column tiles per CTA (8: 64 output columns, two per lane in the sparse phase; 4: 32 columns, one per lane),
 // WARPS = warps per CTA, IB = table rows in flight per warp in the sparse phase. Sixteen warps of at most 128 registers: with eight, the SM issued 0.9 instructions per clock
@@ -647,7 +638,7 @@ static int64_t ensure_dense_cols(Matrix* m) {
 
 // Builds the work lists (see k_sparse_emit). Returns CLA_OK with m->spListsOk = false when the lists would not fit
 // 32-bit positions or device memory; the caller then takes the first-generation kernel.
-static int64_t build_sparse_lists(Matrix* m, cudaStream_t s) {
+int64_t ensure_sparse_lists(Matrix* m, cudaStream_t s) {
   if (m->spListsTried) return CLA_OK;
   m->spListsTried = true;
   int64_t rc;
@@ -718,6 +709,8 @@ static int64_t build_sparse_lists(Matrix* m, cudaStream_t s) {
   m->dWinItems = winItems;
   m->dStepPtr = (uint32_t*)stepPtr;
   m->dWinPtr = (uint32_t*)winPtr;
+  m->nStepPtr = nStepPtr;
+  m->nWinPtr = nWinPtr;
   m->deviceBytes += (nStep + nWin) * (int64_t)sizeof(SpItem) + (nStepPtr + nWinPtr) * 4;
   m->stats.device_bytes = m->deviceBytes;
   m->spListsOk = true;
@@ -750,7 +743,7 @@ int64_t launch_rmm_dmma(Matrix* m, const double* dV, int vCols, double* dOut, cu
     m->stats.kernel_launches++;
   }
   const size_t smem = std::max((size_t)(GM_KC * GM_LDA + GM_KC * GM_LDB), (size_t)(GM_TR * GM_LDC + GM_TN)) * sizeof(double);
-  if ((rc = build_sparse_lists(m, s)) < 0) return rc;
+  if ((rc = ensure_sparse_lists(m, s)) < 0) return rc;
   static bool attrSet[64] = {};  // per device: function attributes belong to the device's context
   bool& attr = attrSet[m->device & 63];
   if (!attr) {
