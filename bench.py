@@ -21,7 +21,9 @@ e2e = the same product through the host-buffer C-ABI call (operands copied host-
 device->host inside the timed region), roofline = algorithmic bytes (or flops) of the dominant kernel over its
 CUDA-event duration against the measured peak, cpu_baseline = the CPU restatement of the reference algorithm on the
 host cores. `--impl reference` times that CPU path alone. `--decompress` adds the time of cla_decompress_dev of the
-main workload's matrix into a device buffer (bytes written per second against the copy bandwidth).
+main workload's matrix into a device buffer (bytes written per second against the copy bandwidth). With N > 1 the sums
+over the ranks run through the library's kernel over peer memory (`--allreduce nccl` switches to NCCL); `--strong` splits
+the workload's rows over the N GPUs instead of giving each GPU all of them.
 """
 from __future__ import annotations
 
