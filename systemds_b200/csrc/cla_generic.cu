@@ -622,10 +622,11 @@ constexpr int LMM_HIST_MAX = 6144;        // doubles of shared histogram (48 KB)
 // grid: (row chunks, dictionary groups, q tiles). A: [totalVals x q]
 __global__ void __launch_bounds__(LMM_THREADS)
 k_lmm_preagg(const DevGroup* __restrict__ groups, int nRows, int rowsPerChunk, const double* __restrict__ Yt, int q,
-             double* __restrict__ A, int skipFast) {
+             double* __restrict__ A, int skipFast, int skipSparse) {
   __shared__ double hist[LMM_HIST_MAX];
   const DevGroup& g = groups[blockIdx.y];
   if (g.type == GT_UNC || (skipFast && g.inFast)) return;
+  if (skipSparse && (g.type == GT_SDC || g.type == GT_RLE)) return;  // taken from the row-major work lists (k_lmm_lists)
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int ra = blockIdx.x * rowsPerChunk, rb = min(nRows, ra + rowsPerChunk);
   if (ra >= rb) return;
@@ -744,6 +745,56 @@ __global__ void k_lmm_const(const double* __restrict__ sums, const double* __res
     out[e] += sums[e / nCols] * constV[e % nCols];
 }
 
+// Pre-aggregation of the SDC / RLE groups for one left row from the row-major work lists: A[table row] += the left
+// values of the rows an item covers. A CTA walks 1024-row blocks (left values staged in shared memory); a thread per
+// 8-row step applies the step's items, a thread per 64-row window the runs that cover the window, into a table in
+// shared memory that is added to A once per CTA. (The per-group form walks every offset stream and, for RLE, reads
+// the whole left row once per group.)
+constexpr int LL_THREADS = 256;
+__global__ void __launch_bounds__(LL_THREADS)
+k_lmm_lists(const SpItem* __restrict__ stepItems, const uint32_t* __restrict__ stepPtr, int64_t nStepPtr,
+            const SpItem* __restrict__ winItems, const uint32_t* __restrict__ winPtr, int64_t nWinPtr, int nRows,
+            const double* __restrict__ y, int nVals, double* __restrict__ A) {
+  extern __shared__ __align__(16) double llsm[];
+  double* ys = llsm;                 // [SKIP_ROWS]
+  double* hist = llsm + SKIP_ROWS;   // [nVals]
+  constexpr int NSTEP = SKIP_ROWS / G3_STEP, NWIN = SKIP_ROWS / G3_WIN;
+  const int tid = threadIdx.x;
+  for (int i = tid; i < nVals; i += LL_THREADS) hist[i] = 0.0;
+  const int nBlocks = (nRows + SKIP_ROWS - 1) / SKIP_ROWS;
+  for (int b = blockIdx.x; b < nBlocks; b += gridDim.x) {
+    __syncthreads();  // the previous block's readers of ys are done (and hist is cleared before the first block)
+    const int r0 = b * SKIP_ROWS;
+    for (int i = tid; i < SKIP_ROWS; i += LL_THREADS) ys[i] = r0 + i < nRows ? y[r0 + i] : 0.0;
+    __syncthreads();
+    if (tid < NWIN) {
+      const int64_t w = (int64_t)b * NWIN + tid;
+      const uint32_t p0 = winPtr[min(w, nWinPtr - 1)], p1 = winPtr[min(w + 1, nWinPtr - 1)];
+      if (p0 < p1) {
+        double sum = 0.0;
+        for (int i = 0; i < G3_WIN; i++) sum += ys[tid * G3_WIN + i];
+        for (uint32_t i = p0; i < p1; i++) atomicAdd(&hist[winItems[i].prow], sum);
+      }
+    } else if (tid >= LL_THREADS - NSTEP) {
+      const int t = tid - (LL_THREADS - NSTEP);
+      const int64_t st = (int64_t)b * NSTEP + t;
+      const uint32_t p0 = stepPtr[min(st, nStepPtr - 1)], p1 = stepPtr[min(st + 1, nStepPtr - 1)];
+      for (uint32_t i = p0; i < p1; i++) {
+        const SpItem e = stepItems[i];
+        const int ra = e.rows & 0xFF, rb = (e.rows >> 8) & 0xFF;
+        double sum = 0.0;
+        for (int r = ra; r < rb; r++) sum += ys[t * G3_STEP + r];
+        atomicAdd(&hist[e.prow], sum);
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < nVals; i += LL_THREADS) {
+    const double v = hist[i];
+    if (v != 0.0) atomicAdd(&A[i], v);
+  }
+}
+
 int64_t launch_lmm(Matrix* m, const double* dYt, int q, double* dOut, cudaStream_t s, bool afterFast) {
   if (q == 0 || m->nCols == 0) return CLA_OK;
   if (!afterFast) CLA_CUDA(cudaMemsetAsync(dOut, 0, sizeof(double) * (size_t)q * m->nCols, s));
@@ -761,8 +812,30 @@ int64_t launch_lmm(Matrix* m, const double* dYt, int q, double* dOut, cudaStream
     rowsPerChunk = std::max(SKIP_ROWS * 4, ((rowsPerChunk + SKIP_ROWS - 1) / SKIP_ROWS) * SKIP_ROWS);
     const int chunks = (m->nRows + rowsPerChunk - 1) / rowsPerChunk;
     dim3 grid(chunks, m->nDev, (q + LMM_QT - 1) / LMM_QT);
+    // one left row on a tall matrix with SDC / RLE groups: those come from the row-major work lists
+    bool lists = false;
+    const size_t llSmem = (size_t)(SKIP_ROWS + std::max<int64_t>(m->totalVals, 1)) * sizeof(double);
+    if (q == 1 && m->nRows >= 4 * SKIP_ROWS && llSmem <= 160 * 1024) {
+      if ((rc = ensure_sparse_list(m)) < 0) return rc;
+      if (m->nSparse > 0) {
+        if ((rc = ensure_sparse_lists(m, s)) < 0) return rc;
+        lists = m->spListsOk && m->dStepPtr != nullptr;
+      }
+    }
     prof_begin(m, s);
-    k_lmm_preagg<<<grid, LMM_THREADS, 0, s>>>(m->dGroups, m->nRows, rowsPerChunk, dYt, q, A, afterFast ? 1 : 0);
+    k_lmm_preagg<<<grid, LMM_THREADS, 0, s>>>(m->dGroups, m->nRows, rowsPerChunk, dYt, q, A, afterFast ? 1 : 0, lists ? 1 : 0);
+    if (lists) {
+      static bool llAttr[64] = {};
+      if (!llAttr[m->device & 63]) {
+        CLA_CUDA(cudaFuncSetAttribute(k_lmm_lists, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        llAttr[m->device & 63] = true;
+      }
+      const int nBlocks = (m->nRows + SKIP_ROWS - 1) / SKIP_ROWS;
+      k_lmm_lists<<<std::min(nBlocks, 2 * m->smCount), LL_THREADS, llSmem, s>>>(
+          (const SpItem*)m->dStepItems, m->dStepPtr, m->nStepPtr, (const SpItem*)m->dWinItems, m->dWinPtr, m->nWinPtr, m->nRows,
+          dYt, (int)m->totalVals, A);
+      m->stats.kernel_launches++;
+    }
     prof_end(m, s);
     k_lmm_post<<<m->nDev, 128, 0, s>>>(m->dGroups, A, q, m->nCols, dOut, afterFast ? 1 : 0);
     m->stats.kernel_launches += 2;
