@@ -148,7 +148,7 @@ constexpr int G3_WIN = 64;
 // One piece of work: rows [ra, rb) of an 8-row step (or a whole 64-row window) receive table row prow.
 struct SpItem {
   uint32_t prow;
-  uint32_t rows;  // ra | rb << 8
+  uint32_t rows;  // ra | rb << 8 | (index of the step or window inside its 1024-row block) << 16
 };
 
 struct FastPlan;  // plans of the specialised DDC kernels (cla_fast.cu)

@@ -746,19 +746,21 @@ __global__ void k_lmm_const(const double* __restrict__ sums, const double* __res
 }
 
 // Pre-aggregation of the SDC / RLE groups for one left row from the row-major work lists: A[table row] += the left
-// values of the rows an item covers. A CTA walks 1024-row blocks (left values staged in shared memory); a thread per
-// 8-row step applies the step's items, a thread per 64-row window the runs that cover the window, into a table in
-// shared memory that is added to A once per CTA. (The per-group form walks every offset stream and, for RLE, reads
-// the whole left row once per group.)
+// values of the rows an item covers. A CTA walks 1024-row blocks (left values staged in shared memory, with their
+// sums per 64-row window); the block's items are read coalesced, a thread per item (an item names its step or window
+// inside the block), and added to a table in shared memory that goes to A once per CTA. (The per-group form walks
+// every offset stream and, for RLE, reads the whole left row once per group.) Like the general left product this
+// combines partial sums with atomics.
 constexpr int LL_THREADS = 256;
 __global__ void __launch_bounds__(LL_THREADS)
 k_lmm_lists(const SpItem* __restrict__ stepItems, const uint32_t* __restrict__ stepPtr, int64_t nStepPtr,
             const SpItem* __restrict__ winItems, const uint32_t* __restrict__ winPtr, int64_t nWinPtr, int nRows,
             const double* __restrict__ y, int nVals, double* __restrict__ A) {
   extern __shared__ __align__(16) double llsm[];
-  double* ys = llsm;                 // [SKIP_ROWS]
-  double* hist = llsm + SKIP_ROWS;   // [nVals]
   constexpr int NSTEP = SKIP_ROWS / G3_STEP, NWIN = SKIP_ROWS / G3_WIN;
+  double* ys = llsm;                        // [SKIP_ROWS]
+  double* ywin = llsm + SKIP_ROWS;          // [NWIN]
+  double* hist = llsm + SKIP_ROWS + NWIN;   // [nVals]
   const int tid = threadIdx.x;
   for (int i = tid; i < nVals; i += LL_THREADS) hist[i] = 0.0;
   const int nBlocks = (nRows + SKIP_ROWS - 1) / SKIP_ROWS;
@@ -768,24 +770,25 @@ k_lmm_lists(const SpItem* __restrict__ stepItems, const uint32_t* __restrict__ s
     for (int i = tid; i < SKIP_ROWS; i += LL_THREADS) ys[i] = r0 + i < nRows ? y[r0 + i] : 0.0;
     __syncthreads();
     if (tid < NWIN) {
-      const int64_t w = (int64_t)b * NWIN + tid;
-      const uint32_t p0 = winPtr[min(w, nWinPtr - 1)], p1 = winPtr[min(w + 1, nWinPtr - 1)];
-      if (p0 < p1) {
-        double sum = 0.0;
-        for (int i = 0; i < G3_WIN; i++) sum += ys[tid * G3_WIN + i];
-        for (uint32_t i = p0; i < p1; i++) atomicAdd(&hist[winItems[i].prow], sum);
-      }
-    } else if (tid >= LL_THREADS - NSTEP) {
-      const int t = tid - (LL_THREADS - NSTEP);
-      const int64_t st = (int64_t)b * NSTEP + t;
-      const uint32_t p0 = stepPtr[min(st, nStepPtr - 1)], p1 = stepPtr[min(st + 1, nStepPtr - 1)];
-      for (uint32_t i = p0; i < p1; i++) {
-        const SpItem e = stepItems[i];
-        const int ra = e.rows & 0xFF, rb = (e.rows >> 8) & 0xFF;
-        double sum = 0.0;
-        for (int r = ra; r < rb; r++) sum += ys[t * G3_STEP + r];
-        atomicAdd(&hist[e.prow], sum);
-      }
+      double sum = 0.0;
+      for (int i = 0; i < G3_WIN; i++) sum += ys[tid * G3_WIN + i];
+      ywin[tid] = sum;
+    }
+    __syncthreads();
+    const int64_t w0 = (int64_t)b * NWIN, s0 = (int64_t)b * NSTEP;
+    const uint32_t wa = winPtr[min(w0, nWinPtr - 1)], wb = winPtr[min(w0 + NWIN, nWinPtr - 1)];
+    for (uint32_t i = wa + tid; i < wb; i += LL_THREADS) {
+      const SpItem e = winItems[i];
+      atomicAdd(&hist[e.prow], ywin[(e.rows >> 16) & (NWIN - 1)]);
+    }
+    const uint32_t sa = stepPtr[min(s0, nStepPtr - 1)], sb = stepPtr[min(s0 + NSTEP, nStepPtr - 1)];
+    for (uint32_t i = sa + tid; i < sb; i += LL_THREADS) {
+      const SpItem e = stepItems[i];
+      const int ra = e.rows & 0xFF, rb = (e.rows >> 8) & 0xFF;
+      const double* yr = ys + ((e.rows >> 16) & (NSTEP - 1)) * G3_STEP;
+      double sum = 0.0;
+      for (int r = ra; r < rb; r++) sum += yr[r];
+      atomicAdd(&hist[e.prow], sum);
     }
   }
   __syncthreads();
@@ -814,7 +817,7 @@ int64_t launch_lmm(Matrix* m, const double* dYt, int q, double* dOut, cudaStream
     dim3 grid(chunks, m->nDev, (q + LMM_QT - 1) / LMM_QT);
     // one left row on a tall matrix with SDC / RLE groups: those come from the row-major work lists
     bool lists = false;
-    const size_t llSmem = (size_t)(SKIP_ROWS + std::max<int64_t>(m->totalVals, 1)) * sizeof(double);
+    const size_t llSmem = (size_t)(SKIP_ROWS + SKIP_ROWS / G3_WIN + std::max<int64_t>(m->totalVals, 1)) * sizeof(double);
     if (q == 1 && m->nRows >= 4 * SKIP_ROWS && llSmem <= 160 * 1024) {
       if ((rc = ensure_sparse_list(m)) < 0) return rc;
       if (m->nSparse > 0) {

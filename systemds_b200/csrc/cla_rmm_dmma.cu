@@ -494,7 +494,8 @@ __global__ void k_sparse_emit(const DevGroup* __restrict__ groups, const int32_t
     const unsigned long long slot = atomicAdd(&counters[0], 1ull);
     if (stepKeys) {
       stepKeys[slot] = ((unsigned long long)(row0 / G3_STEP) << 32) | prow;
-      stepVals[slot] = (uint32_t)(row0 % G3_STEP) | ((uint32_t)(row1 - row0 / G3_STEP * G3_STEP) << 8);
+      stepVals[slot] = (uint32_t)(row0 % G3_STEP) | ((uint32_t)(row1 - row0 / G3_STEP * G3_STEP) << 8) |
+                       ((uint32_t)((row0 / G3_STEP) % (SKIP_ROWS / G3_STEP)) << 16);  // + the step's place in its 1024-row block
     }
   };
   if (g.type == GT_SDC) {
@@ -530,7 +531,8 @@ __global__ void k_sparse_pack(const unsigned long long* __restrict__ keys, const
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
     SpItem it;
     it.prow = (uint32_t)keys[i];
-    it.rows = vals ? vals[i] : 0u;
+    // window items carry the window's place in its 1024-row block where step items carry the step's
+    it.rows = vals ? vals[i] : (uint32_t)((keys[i] >> 32) % (SKIP_ROWS / G3_WIN)) << 16;
     items[i] = it;
   }
 }
