@@ -396,9 +396,9 @@ __global__ void k_lmm_vec_final(const LmmChunk* __restrict__ chunks, int nChunks
   const int c = blockIdx.x;
   if (c >= nChunks) return;
   const LmmChunk ch = chunks[c];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nWarps = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nWarps = (blockDim.x >> 5) * gridDim.y;
   const int n = nParts * ch.nCta;
-  for (int u = warp; u < ch.nUnits * 16; u += nWarps) {
+  for (int u = blockIdx.y * (blockDim.x >> 5) + warp; u < ch.nUnits * 16; u += nWarps) {  // gridDim.y CTAs per chunk
     const int col = slotCol[ch.unit0 * 16 + u];
     if (col < 0) continue;
     double s = 0;
@@ -1284,7 +1284,7 @@ int64_t fast_lmm_vec(Matrix* m, const double* dY, double* dOut, cudaStream_t s) 
   k_lmm_vec_u8<<<fp->lmmGrid, LMM_T, smem, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dLmmMaps, fp->nRB, fp->dLmmTables, dY,
                                                m->nRows, 0, nSteps, partial, m->dErr);
   prof_end(m, s);
-  k_lmm_vec_final<<<(unsigned)fp->lchunks.size(), 512, 0, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dSlotCol,
+  k_lmm_vec_final<<<dim3((unsigned)fp->lchunks.size(), LMM_MAX_UNITS), 512, 0, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dSlotCol,
                                                               partial, dOut, 1, fp->lmmGrid);
   m->stats.kernel_launches += 2;
   if (m->hasConst)
@@ -1368,7 +1368,7 @@ int64_t fast_lmm_vec_host(Matrix* m, const double* hostY, double* dY, double* dO
       if ((rc = launch_range(i)) < 0) return rc;
     }
   }
-  k_lmm_vec_final<<<(unsigned)fp->lchunks.size(), 512, 0, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dSlotCol, partial,
+  k_lmm_vec_final<<<dim3((unsigned)fp->lchunks.size(), LMM_MAX_UNITS), 512, 0, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dSlotCol, partial,
                                                               dOut, LMM_PIPE, fp->lmmGrid);
   m->stats.kernel_launches++;
   if (m->hasConst)
@@ -1429,7 +1429,7 @@ int64_t fast_lmm_vec_noalloc(Matrix* m, const double* dY, double* dOut, cudaStre
   const int64_t nSteps = ((int64_t)m->nRows + LMM_STEP - 1) / LMM_STEP;
   k_lmm_vec_u8<<<fp->lmmGrid, LMM_T, smem, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dLmmMaps, fp->nRB, fp->dLmmTables,
                                                dY, m->nRows, 0, nSteps, partial, m->dErr);
-  k_lmm_vec_final<<<(unsigned)fp->lchunks.size(), 512, 0, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dSlotCol,
+  k_lmm_vec_final<<<dim3((unsigned)fp->lchunks.size(), LMM_MAX_UNITS), 512, 0, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dSlotCol,
                                                               partial, dOut, 1, fp->lmmGrid);
   m->stats.kernel_launches += 2;
   if (m->hasConst)
