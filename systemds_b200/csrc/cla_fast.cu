@@ -1245,9 +1245,10 @@ int64_t fast_rmm_vec(Matrix* m, const double* dV, double* dOut, cudaStream_t s) 
     k_const_dot<<<1, 256, 0, s>>>(m->dConstV, dV, m->nCols, constRow);
     m->stats.kernel_launches++;
   }
-  // rows per thread: the widest map load that still leaves >= 32 resident warps per SM
-  const double warpsPerSm16 = (double)m->nRows / (16.0 * 32.0 * m->smCount);
-  int R = warpsPerSm16 >= 32 ? 16 : (warpsPerSm16 * 2 >= 32 ? 8 : 4);
+  // rows per thread: 128-bit map loads from about two million rows on, 32-bit ones below (measured on 100 groups of
+  // 16 values, ms per product for 4 / 8 / 16 rows per thread: 1M rows 0.052 / 0.071 / 0.057, 3M rows 0.127 / 0.142 /
+  // 0.127, 10M rows 0.358 / 0.449 / 0.322; eight rows per thread lose at every size)
+  int R = m->nRows >= (2 << 20) - 200000 ? 16 : 4;
   if (const char* e = getenv("CLA_RMM_ROWS_PER_THREAD")) {  // tuning aid
     const int v = atoi(e);
     if (v == 4 || v == 8 || v == 16) R = v;
@@ -1256,10 +1257,16 @@ int64_t fast_rmm_vec(Matrix* m, const double* dV, double* dOut, cudaStream_t s) 
   for (size_t c = 0; c < fp->rchunks.size(); c++) {
     const RmmChunk& ch = fp->rchunks[c];
     const size_t smem = (size_t)ch.tblDoubles * 8 + (size_t)(ch.g1 - ch.g0) * 12 + 16;
-    const int perSm = std::max(1, std::min(8, (int)((200 * 1024) / std::max<size_t>(smem, 1))));
+    auto kern = R == 16 ? k_rmm_vec_u8<16> : (R == 8 ? k_rmm_vec_u8<8> : k_rmm_vec_u8<4>);
+    // as many CTAs as are resident at once (registers and shared memory decide): the tile loop does the rest, and
+    // no partial second wave is left over
+    int perSm = 1;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, kern, RMM_T, smem) != cudaSuccess || perSm < 1) {
+      cudaGetLastError();
+      perSm = 1;
+    }
     const int grid = std::min(nTiles, m->smCount * perSm);
     if (c == 0) prof_begin(m, s);
-    auto kern = R == 16 ? k_rmm_vec_u8<16> : (R == 8 ? k_rmm_vec_u8<8> : k_rmm_vec_u8<4>);
     kern<<<grid, RMM_T, smem, s>>>(fp->dMaps, fp->dTblOff, ch.g0, ch.g1, P + ch.tblOff, ch.tblDoubles, m->nRows, constRow,
                                    dOut, c > 0 ? 1 : 0, m->dErr);
     if (c + 1 == fp->rchunks.size()) prof_end(m, s);
