@@ -424,7 +424,7 @@ __global__ void k_lmm_vec_final(const LmmChunk* __restrict__ chunks, int nChunks
 // of dictionary values through L1), which puts the bound on the output stream. Every cell is written exactly once
 // with the same operation as the tile kernel (column constant + dictionary value).
 // --------------------------------------------------------------------------------------------------
-constexpr int DEC_W = 16;
+constexpr int DEC_W = 12;  // warps per CTA (measured 8 / 10 / 12 / 14 / 16 / 20 / 24: 12 writes the most, 4.2-4.5 TB/s)
 constexpr int DEC_T = DEC_W * 32;
 constexpr int DEC_NP = (LMM_MAX_UNITS + 1) / 2;  // unit pairs of a chunk: a warp store covers 32 neighbouring columns
 
