@@ -37,8 +37,12 @@ constexpr int RMM_ROWS_PT = 16;       // rows per thread
 constexpr int RMM_TILE = RMM_T * RMM_ROWS_PT;
 
 // ---- LMM plan ----
-constexpr int LMM_W = 12;             // warps per CTA
+// Warps per CTA (one CTA per SM). Measured on the benchmark workloads for 10 / 12 / 14 / 16 warps: t(y) X 10M x 200
+// 0.718 / 0.675 / 0.682 / 0.654 ms (sixteen warps fit 128 registers with 20 bytes of spills), the fused X v 1M x 100
+// 0.0699 / 0.0686 / 0.0688 / 0.0665 ms per step; k_rmm_vec_b is the exception (lmCG step 9.32 / 8.52 / 8.51 / 8.56 ms).
+constexpr int LMM_W = 16;
 constexpr int LMM_T = LMM_W * 32;
+constexpr int RB_W = 12;              // k_rmm_vec_b
 constexpr int LMM_MAX_UNITS = 7;      // 16-column table units per CTA (7 x 32 KB at 256 tuples)
 constexpr int LMM_PART = LMM_MAX_UNITS * 16;  // partial sums a CTA writes
 constexpr int LMM_STEP = 64;          // rows per warp step (32 per half-warp)
@@ -573,7 +577,7 @@ __device__ __forceinline__ void rmm_b_chunk(const LmmChunk& ch, const uint8_t* _
       mp[u] = imaps + (size_t)(ch.unit0 + u) * nRB * 256 + slot * 16;
     }
   }
-  for (int64_t st = s0 + warp; st < s1; st += LMM_W) {
+  for (int64_t st = s0 + warp; st < s1; st += RB_W) {
     const int64_t r0 = st * LMM_STEP + half * 32;
     uint4 m[NU][2];
 #pragma unroll
@@ -613,7 +617,7 @@ __device__ __forceinline__ void rmm_b_chunk(const LmmChunk& ch, const uint8_t* _
   }
 }
 
-__global__ void __launch_bounds__(LMM_T, 1)
+__global__ void __launch_bounds__(RB_W * 32, 1)
 k_rmm_vec_b(const LmmChunk* __restrict__ chunks, int nChunks, const uint8_t* __restrict__ imaps, int64_t nRB,
             const double* __restrict__ P, int nRows, const double* __restrict__ constRow, double* __restrict__ out,
             int32_t* err) {
@@ -1171,7 +1175,7 @@ static int64_t fast_rmm_vec_b(Matrix* m, FastPlan* fp, const double* dV, double*
   const int64_t nSteps = ((int64_t)m->nRows + LMM_STEP - 1) / LMM_STEP;
   const int grid = (int)std::min<int64_t>(m->smCount, nSteps);
   prof_begin(m, s);
-  k_rmm_vec_b<<<grid, LMM_T, smem, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dLmmMaps, fp->nRB, P, m->nRows, constRow,
+  k_rmm_vec_b<<<grid, RB_W * 32, smem, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dLmmMaps, fp->nRB, P, m->nRows, constRow,
                                         dOut, m->dErr);
   prof_end(m, s);
   m->stats.kernel_launches++;
