@@ -216,7 +216,7 @@ struct Matrix {
   int32_t* dErr = nullptr;  // device self-check word
   cudaStream_t stream = nullptr;
   cudaStream_t copyStream = nullptr;  // uploads overlapped with kernels in the host-buffer left product
-  cudaEvent_t copyDone[8] = {};  // one per row range of the pipelined host-buffer left product
+  cudaEvent_t copyDone[16] = {};  // one per row range of the pipelined host-buffer left product
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   // Every product call uses the handle's one set of scratch buffers. A call that arrives on another stream than
   // the previous one first waits for `lastDone` (recorded when the previous call had enqueued its work), so two

@@ -1308,7 +1308,7 @@ int64_t fast_lmm_vec(Matrix* m, const double* dY, double* dOut, cudaStream_t s) 
 // Host-buffer t(y) %*% X with the upload of y overlapped with the product: y is copied in up to LMM_PIPE_MAX row ranges
 // on a second stream, and the kernel for a range starts as soon as its slice has arrived. Returns 0 if the
 // specialised kernel does not cover the matrix (the caller then copies y whole and takes the normal path).
-constexpr int LMM_PIPE_MAX = 8;  // = the handle's copyDone events
+constexpr int LMM_PIPE_MAX = 16;  // = the handle's copyDone events
 static int lmm_pipe_depth() {
   static const int d = [] {
     const char* e = getenv("CLA_LMM_PIPE");
@@ -1336,8 +1336,13 @@ int64_t fast_lmm_vec_host(Matrix* m, const double* hostY, double* dY, double* dO
   // the copy stream must not run ahead of work already queued on s that still reads dY
   CLA_CUDA(cudaEventRecord(m->ev1, s));
   CLA_CUDA(cudaStreamWaitEvent(m->copyStream, m->ev1, 0));
+  // Row ranges of decreasing size (weights n, n - 1, ..., 1): the copy engine is the slower side, so every kernel has
+  // finished before the next range has arrived, and what is left after the last byte has landed is the product over
+  // the smallest range only.
+  const int64_t wSum = (int64_t)LMM_PIPE * (LMM_PIPE + 1) / 2;
+  auto range_start = [&](int i) { return nSteps * ((int64_t)i * (2 * LMM_PIPE - i + 1) / 2) / wSum; };  // i ranges: n + ... + (n - i + 1)
   auto range_rows = [&](int i, int64_t& sb, int64_t& se, int64_t& rb, int64_t& re) {
-    sb = nSteps * i / LMM_PIPE, se = nSteps * (i + 1) / LMM_PIPE;
+    sb = range_start(i), se = i + 1 == LMM_PIPE ? nSteps : range_start(i + 1);
     rb = sb * LMM_STEP, re = std::min<int64_t>(m->nRows, se * LMM_STEP);
   };
   // the kernel of row range i, once that range of y is on the copy stream
