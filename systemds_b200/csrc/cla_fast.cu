@@ -1074,7 +1074,8 @@ int64_t fast_plan_build(Matrix* m) {
       fu.push_back(FusedUnit{a, -1, 0, G[a].nVals, 1});
       hi--;
     }
-    if (paired * 2 >= nG && !fp->partial) {
+    // (fast_rmm_vec takes this kernel below 4M rows only: no second copy of the maps for taller matrices)
+    if (paired * 2 >= nG && !fp->partial && m->nRows < (4 << 20)) {
       std::stable_sort(fu.begin(), fu.end(), [](const FusedUnit& x, const FusedUnit& y) { return (x.nva << x.sh) > (y.nva << y.sh); });
       fp->nFused = (int)fu.size();
       const int nU16F = (fp->nFused + 15) / 16;
