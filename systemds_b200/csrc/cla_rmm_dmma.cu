@@ -217,9 +217,10 @@ struct DenseDesc {
 
 
 // NT = 8-column tiles per CTA (8: 64 output columns, two per lane in the sparse phase; 4: 32 columns, one per lane),
-// WARPS = warps per CTA, IB = table rows in flight per warp in the sparse phase. Sixteen warps of at most 128 registers: with eight, the SM issued 0.9 instructions per clock
-// (two warps per scheduler, every instruction waiting out the latency of the one before) and neither the tensor
-// pipe nor the L1 data pipe was busy; the per-warp buffers are sized so that sixteen fit next to V.
+// WARPS = warps per CTA, IB = table rows in flight per warp in the sparse phase. With eight warps the SM issued 0.9
+// instructions per clock (two warps per scheduler, every instruction waiting out the latency of the one before) and
+// neither the tensor pipe nor the L1 data pipe was busy; sixteen warps must fit 128 registers and spill; twelve is
+// the measured optimum for the 64-column tile. The per-warp buffers are sized so that sixteen fit next to V.
 template <int NT, int WARPS>
 struct G3 {
   static constexpr int TN = NT * 8;
@@ -750,7 +751,7 @@ int64_t launch_rmm_dmma(Matrix* m, const double* dV, int vCols, double* dOut, cu
   bool& attr = attrSet[m->device & 63];
   if (!attr) {
     CLA_CUDA(cudaFuncSetAttribute(k_rmm_dmma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    CLA_CUDA(cudaFuncSetAttribute(k_rmm_dmma3<8, 16, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+    CLA_CUDA(cudaFuncSetAttribute(k_rmm_dmma3<8, 12, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
     CLA_CUDA(cudaFuncSetAttribute(k_rmm_dmma3<4, 16, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
     attr = true;
   }
@@ -758,9 +759,9 @@ int64_t launch_rmm_dmma(Matrix* m, const double* dV, int vCols, double* dOut, cu
   if (m->spListsOk && (m->nSparse == 0 || (int64_t)m->totalVals * vCols * 8 < (1ll << 32))) {  // table-row offsets are 32-bit
     static const int wideEnv = getenv("CLA_RMM_WIDE_TILES") ? atoi(getenv("CLA_RMM_WIDE_TILES")) : -1;  // tuning aid
     const bool wide = wideEnv >= 0 ? wideEnv != 0 : vCols > 32;  // 64 output columns per CTA, or 32
-    const int TN = wide ? 64 : 32, W = 16;
-    const int kMax = wide ? G3<8, 16>::KMAX : G3<4, 16>::KMAX;
-    const int ldb = TN + 4, wbuf = wide ? G3<8, 16>::WBUF : G3<4, 16>::WBUF;
+    const int TN = wide ? 64 : 32, W = wide ? 12 : 16;
+    const int kMax = wide ? G3<8, 12>::KMAX : G3<4, 16>::KMAX;
+    const int ldb = TN + 4, wbuf = wide ? G3<8, 12>::WBUF : G3<4, 16>::WBUF;
     const int nUnits = (m->nRows + G3_UNIT - 1) / G3_UNIT;
     const int gridY = (vCols + TN - 1) / TN;
     dim3 grid((unsigned)std::max(1, std::min(std::max(1, m->smCount / gridY), (nUnits + W - 1) / W)), gridY);
@@ -770,9 +771,10 @@ int64_t launch_rmm_dmma(Matrix* m, const double* dV, int vCols, double* dOut, cu
       const int nk = std::min(kMax, m->nDenseCols - k0);
       const bool first = k0 == 0;
       const size_t smem3 = ((size_t)((nk + GM_KC - 1) / GM_KC * GM_KC) * ldb + (size_t)W * wbuf) * sizeof(double);
-      // table rows in flight per warp in the sparse phase: 4 with the 64-column tile (8 cost more in spilled
-      // registers than the extra loads in flight gain: 10.1 vs 9.76 ms on 4M rows of the mixed benchmark matrix)
-      auto kern = wide ? k_rmm_dmma3<8, 16, 4> : k_rmm_dmma3<4, 16, 8>;
+      // 64-column tile: 12 warps of up to 170 registers (no spills; 16 warps of 128 registers spilled 320 bytes) and 8
+      // table rows in flight in the sparse phase. Measured on 4M rows of the mixed benchmark matrix, ms per product:
+      // 8 / 10 / 12 / 14 / 16 warps 10.8 / 10.5 / 8.9 / 9.4 / 9.8; with 12 warps 2 / 4 / 8 table rows 10.0 / 9.0 / 8.9.
+      auto kern = wide ? k_rmm_dmma3<8, 12, 8> : k_rmm_dmma3<4, 16, 8>;
       kern<<<grid, W * 32, smem3, s>>>(dd + k0, nk, first ? (const SpItem*)m->dStepItems : nullptr,
                                        first ? m->dStepPtr : nullptr, (const SpItem*)m->dWinItems, m->dWinPtr, m->nRows, dV,
                                        vCols, P, first ? constRow : nullptr, dOut, first ? 0 : 1);
