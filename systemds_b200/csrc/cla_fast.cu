@@ -32,7 +32,7 @@ constexpr int FAST_MIN_ROWS = 4096;
 constexpr int SMEM_MAX = 227 * 1024;
 
 // ---- RMM plan ----
-constexpr int RMM_T = 256;            // threads
+constexpr int RMM_T = 128;            // threads (128 / 256 / 512 measured on 10M x 100, 16 values: 0.313 / 0.320 / 0.496 ms)
 constexpr int RMM_ROWS_PT = 16;       // rows per thread
 constexpr int RMM_TILE = RMM_T * RMM_ROWS_PT;
 
