@@ -105,6 +105,11 @@ JFN(jlong, rmm)(JNIEnv* env, jclass, jlong h, jdoubleArray V, jint vRows, jint v
   Out o(env, out);
   return cla_rmm(h, (const double*)v.p, vRows, vCols, (double*)o.p);
 }
+// X %*% V kept compressed (CLALibRightMultBy.rightMultByMatrix with allowOverlap): returns the handle of the new block
+JFN(jlong, rmmOverlapping)(JNIEnv* env, jclass, jlong h, jdoubleArray V, jint vRows, jint vCols) {
+  In v(env, V);
+  return cla_rmm_overlapping(h, (const double*)v.p, vRows, vCols);
+}
 JFN(jlong, lmm)(JNIEnv* env, jclass, jlong h, jdoubleArray Yt, jint yRows, jdoubleArray out) {
   In y(env, Yt);
   Out o(env, out);
