@@ -300,6 +300,12 @@ class CompressedMatrixBlock {
     b->handle_ = h;
     return b;
   }
+  // wraps a handle the library returned (an overlapping product): already on the device, no host-side groups
+  static std::unique_ptr<CompressedMatrixBlock> adopt(cla_handle h, int rows, int cols) {
+    std::unique_ptr<CompressedMatrixBlock> b(new CompressedMatrixBlock(rows, cols, true));
+    b->handle_ = h;
+    return b;
+  }
   // uploads the groups on first use (cla_create .. cla_finalize)
   cla_handle nativeHandle(int device = 0) {
     if (!handle_) {
@@ -327,6 +333,13 @@ struct CLALibRightMultBy {  // lib/CLALibRightMultBy.java:57
       throw DMLCompressionException(e.code, std::string("Failed Right MM: ") + e.what());  // :99-101
     }
     return ret;
+  }
+  // allowOverlap = true (lib/CLALibRightMultBy.java:61-64, RMMOverlapping :127-161): the product stays compressed, an
+  // overlapping block on the device that shares m1's index structures (m1 must outlive it or be destroyed first:
+  // the library keeps what the result still needs)
+  static std::unique_ptr<CompressedMatrixBlock> rightMultByMatrixOverlapping(CompressedMatrixBlock& m1, const MatrixBlock& m2) {
+    cla_handle h = check(cla_rmm_overlapping(m1.nativeHandle(), m2.values.data(), m2.rlen, m2.clen), "cla_rmm_overlapping");
+    return CompressedMatrixBlock::adopt(h, m1.getNumRows(), m2.clen);
   }
 };
 struct CLALibLeftMultBy {  // lib/CLALibLeftMultBy.java:126; left is [q x nRows]
@@ -394,6 +407,34 @@ struct CLALibDecompress {  // lib/CLALibDecompress.java:56
     return ret;
   }
 };
+
+// The sum over row shards on the GPUs of one node (one process per GPU), over NVLink peer memory; no counterpart in
+// the reference. exchange(mine, all) must fill `all` with the CLA_COMM_HANDLE_BYTES-byte handles of all ranks in rank
+// order (MPI_Allgather or whatever the host uses).
+class PeerAllReduce {
+  int64_t comm_ = 0;
+
+ public:
+  template <class Exchange>
+  PeerAllReduce(int device, int rank, int world, int64_t maxDoubles, Exchange&& exchange) {
+    std::vector<char> mine(CLA_COMM_HANDLE_BYTES), all((size_t)world * CLA_COMM_HANDLE_BYTES);
+    comm_ = check(cla_comm_create(device, rank, world, maxDoubles, mine.data()), "cla_comm_create");
+    try {
+      exchange(mine.data(), all.data());
+      check(cla_comm_connect(comm_, all.data()), "cla_comm_connect");
+    } catch (...) {
+      cla_comm_destroy(comm_);
+      throw;
+    }
+  }
+  PeerAllReduce(const PeerAllReduce&) = delete;
+  PeerAllReduce& operator=(const PeerAllReduce&) = delete;
+  ~PeerAllReduce() { if (comm_) cla_comm_destroy(comm_); }
+  // in place on a device buffer, enqueued on `stream`; every rank ends with identical bits
+  void operator()(double* dBuf, int64_t n, void* stream) { check(cla_allreduce_dev(comm_, dBuf, n, stream), "cla_allreduce_dev"); }
+  void status() { check(cla_comm_status(comm_), "cla_comm_status"); }  // throws if a rank failed to arrive earlier
+};
+
 
 }  // namespace cla
 }  // namespace sysds

@@ -96,6 +96,10 @@ int main() {
       int64_t nnz = 0;
       for (double x : R.values) nnz += x != 0.0;
       if (nnz != R.getNonZeros()) { std::printf("nnz %lld != %lld\n", (long long)R.getNonZeros(), (long long)nnz); bad++; }
+      // the same product kept compressed (allowOverlap): its decompressed form is the dense product
+      std::unique_ptr<CompressedMatrixBlock> RO = CLALibRightMultBy::rightMultByMatrixOverlapping(cmb, V);
+      MatrixBlock D = CLALibDecompress::decompress(*RO);
+      report("rmm overlapping", relErr(D.values, ref, sc), 1e-12);
     }
     {  // Yt %*% X
       MatrixBlock L = CLALibLeftMultBy::leftMultByMatrix(cmb, Yt);
