@@ -512,7 +512,7 @@ def main():
     ap.add_argument("--rows", type=int, default=None, help="rows per GPU (default: the workload's benchmark size)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-also", action="store_true", help="skip the other four workloads")
-    ap.add_argument("--also-steps", type=int, default=5)
+    ap.add_argument("--also-steps", type=int, default=20)
     ap.add_argument("--strong", action="store_true",
                     help="strong scaling: the workload's rows are split over the N GPUs instead of each GPU holding all of them")
     ap.add_argument("--allreduce", default="peer", choices=["peer", "nccl"],
@@ -656,7 +656,7 @@ def main():
                 continue
             rows = max(4096, int(DEFAULT_ROWS[i] * args.also_rows_scale) // (world if args.strong else 1))
             wl = Workload(i, rows, rank, local_rank, world, dev, L).build()
-            ms_i, k_i, launches_i = time_steps(wl, args.also_steps, 3, world)
+            ms_i, k_i, launches_i = time_steps(wl, args.also_steps, 5, world)
             also[f"workload{i}"] = {"metric": METRICS[i], "workload": DESCS[i], "rows_per_gpu": rows,
                                     "value": rows * world / (ms_i * 1e-3), "unit": UNIT, "ms_per_step": ms_i,
                                     "steps": args.also_steps, "gpu_launches": launches_i,
