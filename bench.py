@@ -484,7 +484,8 @@ def roofline_of(wl: Workload, k_ms: float, hbm_peak: float, peak_kind: str, dmma
     if bound == "hbm":
         ach = work / (k_ms * 1e-3) / 1e9
         r = {"bound": "hbm", "kernel": kernel, "achieved": ach, "peak": hbm_peak, "unit": "GB/s", "frac": ach / hbm_peak,
-             "peak_source": f"of {peak_kind}", "kernel_ms": k_ms, "algorithmic_bytes": work}
+             "peak_source": f"of {peak_kind}", "frac_of_nominal_8000_GBs": ach / 8000.0, "kernel_ms": k_ms,
+             "algorithmic_bytes": work}
         if wl.idx == 2:  # this product is bound by the FP64 tensor pipe long before HBM: say so next to the HBM figure
             fl = 2.0 * wl.n * 250 * 64
             r["dmma"] = {"algorithmic_TFLOPs": fl / (k_ms * 1e-3) / 1e12, "peak_TFLOPs": dmma_peak,
