@@ -468,9 +468,9 @@ static int64_t lmm_dev(Matrix* m, const double* dYt, int32_t yRows, double* dOut
     if (rc == 1) return CLA_OK;
     if (rc == 2) return launch_lmm(m, dYt, yRows, dOut, s, true);
   }
-  // Several left rows: one pass of the one-vector kernel per row for the groups it covers (measured 0.17 ms per
-  // row on 2M x 200 against 1.5 ms per row in the general pre-aggregation kernel), the general kernels for the
-  // rest. Rows of an odd-length Yt are not 16-byte aligned, so they are copied to a padded pitch first.
+  // Several left rows: passes of the column-per-lane kernels over four, two or one row at a time for the groups they
+  // cover (measured 0.17 ms per row on 2M x 200 for the one-row kernel against 1.5 ms per row in the general
+  // pre-aggregation kernel), the general kernels for the rest. Rows of an odd-length Yt are not 16-byte aligned, so they are copied to a padded pitch first.
   static const int lmmLoopMax = loop_limit("CLA_LMM_LOOP_MAX", 1 << 30);  // tuning aid
   if (yRows >= 2 && yRows <= lmmLoopMax && fast_plan_ok(m) && m->nRows > 0) {
     const double* rows = dYt;
@@ -484,9 +484,12 @@ static int64_t lmm_dev(Matrix* m, const double* dYt, int32_t yRows, double* dOut
       rows = (const double*)m->scratch2;
     }
     int64_t rc = 0;
-    for (int i = 0; i < yRows; i++) {
-      rc = fast_lmm_vec(m, rows + pitch * i, dOut + (size_t)i * m->nCols, s);
+    for (int i = 0; i < yRows;) {  // four rows per pass over the maps, then two, then one
+      const int q = yRows - i >= 4 ? 4 : (yRows - i >= 2 ? 2 : 1);
+      rc = q == 1 ? fast_lmm_vec(m, rows + pitch * i, dOut + (size_t)i * m->nCols, s)
+                  : fast_lmm_rows(m, rows + pitch * i, pitch, q, dOut + (size_t)i * m->nCols, s);
       if (rc <= 0) break;
+      i += q;
     }
     if (rc < 0) return rc;
     if (rc == 1) return CLA_OK;

@@ -296,6 +296,7 @@ bool fast_plan_ok(const Matrix* m);       // some or all groups are covered by t
 bool fast_plan_partial(const Matrix* m);  // ... some but not all
 int64_t fast_rmm_vec(Matrix* m, const double* dV, double* dOut, cudaStream_t s);
 int64_t fast_lmm_vec(Matrix* m, const double* dY, double* dOut, cudaStream_t s);
+int64_t fast_lmm_rows(Matrix* m, const double* dY, size_t pitch, int q, double* dOut, cudaStream_t s);  // q = 2 or 4 left rows at once
 int64_t fast_decompress(Matrix* m, int r0, int r1, double* dOut, cudaStream_t s);  // 1 = done, 0 = not covered
 int64_t fast_lmm_vec_host(Matrix* m, const double* hostY, double* dY, double* dOut, cudaStream_t s);
 int64_t fast_lmm_vec_noalloc(Matrix* m, const double* dY, double* dOut, cudaStream_t s);

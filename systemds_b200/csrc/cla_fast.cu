@@ -417,6 +417,140 @@ __global__ void k_lmm_vec_final(const LmmChunk* __restrict__ chunks, int nChunks
 }
 
 // --------------------------------------------------------------------------------------------------
+// LMM with Q left rows at once (Q = 2 or 4; the reference's left-multiply blocks four rows too,
+// lib/CLALibLeftMultBy.java:731-819). Same layout and lookups as k_lmm_vec_u8, but a dictionary value fetched for a
+// cell multiplies the cell's Q left values: one pass over the maps and one lookup per cell serve Q rows, where Q
+// passes of the one-row kernel would fetch each value Q times. partial: [gridDim.x][Q][LMM_PART].
+// --------------------------------------------------------------------------------------------------
+constexpr int LQ_W = 12;              // warps per CTA (Q x NU accumulators per lane: up to 170 registers)
+constexpr int LQ_T = LQ_W * 32;
+
+template <int NU, int Q>
+__device__ __forceinline__ void lmmq_body(const LmmChunk& ch, const uint8_t* __restrict__ imaps, int64_t nRB,
+                                          const double* __restrict__ tablesImg, const double* __restrict__ y, size_t pitch,
+                                          int nRows, double* __restrict__ partial, unsigned char* smraw, uint64_t* mbar,
+                                          int32_t* err) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int slot = lane & 15, half = lane >> 4;
+  if (!tma_load_to_smem(smraw, tablesImg + ch.tblOff, (uint32_t)ch.tblDoubles * 8u, mbar)) {
+    if (tid == 0) atomicExch(err, 105);
+    for (int u = tid; u < Q * LMM_PART; u += LQ_T) partial[(size_t)blockIdx.x * Q * LMM_PART + u] = __longlong_as_double(0x7ff8000000000000ll);
+    return;
+  }
+  const unsigned char* tbase[NU];
+  const uint8_t* mp[NU];
+  {
+    size_t off = 0;
+#pragma unroll
+    for (int u = 0; u < NU; u++) {
+      tbase[u] = smraw + off + slot * 8;
+      off += (size_t)ch.nk[u] * 128;
+      mp[u] = imaps + (size_t)(ch.unit0 + u) * nRB * 256 + slot * 16;
+    }
+  }
+  double acc[NU][Q];
+#pragma unroll
+  for (int u = 0; u < NU; u++)
+#pragma unroll
+    for (int q = 0; q < Q; q++) acc[u][q] = 0.0;
+  const int ctaInChunk = blockIdx.x - ch.cta0;
+  const int64_t nSteps = ((int64_t)nRows + LMM_STEP - 1) / LMM_STEP;
+  const int64_t s0 = nSteps * ctaInChunk / ch.nCta, s1 = nSteps * (ctaInChunk + 1) / ch.nCta;
+  for (int64_t st = s0 + warp; st < s1; st += LQ_W) {
+    const int64_t r0 = st * LMM_STEP + half * 32;
+    if (st * LMM_STEP + LMM_STEP <= nRows) {
+#pragma unroll 1
+      for (int sub = 0; sub < 2; sub++) {
+        uint4 m[NU];
+#pragma unroll
+        for (int u = 0; u < NU; u++) m[u] = __ldg((const uint4*)(mp[u] + ((r0 >> 4) + sub) * 256));
+        const double* yr = y + r0 + sub * 16;
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) {  // two rows per 128-bit load of every left row
+          double2 yq[Q];
+#pragma unroll
+          for (int q = 0; q < Q; q++) yq[q] = __ldg((const double2*)(yr + q * pitch + i));
+#pragma unroll
+          for (int u = 0; u < NU; u++) {
+            const uint32_t w = (i >> 2) == 0 ? m[u].x : ((i >> 2) == 1 ? m[u].y : ((i >> 2) == 2 ? m[u].z : m[u].w));
+            const double t0 = *(const double*)(tbase[u] + byte_x128(w, i & 3));
+            const double t1 = *(const double*)(tbase[u] + byte_x128(w, (i & 3) + 1));
+#pragma unroll
+            for (int q = 0; q < Q; q++) acc[u][q] = fma(yq[q].y, t1, fma(yq[q].x, t0, acc[u][q]));
+          }
+        }
+      }
+    } else {  // ragged last step
+      for (int64_t r = r0; r < min((int64_t)nRows, r0 + 32); r++) {
+#pragma unroll
+        for (int u = 0; u < NU; u++) {
+          const double t = *(const double*)(tbase[u] + 128 * (int)mp[u][(r >> 4) * 256 + (r & 15)]);
+#pragma unroll
+          for (int q = 0; q < Q; q++) acc[u][q] = fma(y[q * pitch + r], t, acc[u][q]);
+        }
+      }
+    }
+  }
+  __syncthreads();  // tables no longer needed
+  double* red = (double*)smraw;  // [LQ_W][Q][NU*16]
+#pragma unroll
+  for (int u = 0; u < NU; u++)
+#pragma unroll
+    for (int q = 0; q < Q; q++) {
+      double a = acc[u][q];
+      a += __shfl_xor_sync(0xffffffffu, a, 16);
+      if (half == 0) red[(warp * Q + q) * (NU * 16) + u * 16 + slot] = a;
+    }
+  __syncthreads();
+  for (int e = tid; e < Q * NU * 16; e += LQ_T) {
+    const int q = e / (NU * 16), u = e - q * (NU * 16);
+    double s = 0;
+    for (int w = 0; w < LQ_W; w++) s += red[(w * Q + q) * (NU * 16) + u];
+    partial[((size_t)blockIdx.x * Q + q) * LMM_PART + u] = s;
+  }
+}
+
+template <int Q>
+__global__ void __launch_bounds__(LQ_T, 1)
+k_lmm_vecq_u8(const LmmChunk* __restrict__ chunks, int nChunks, const uint8_t* __restrict__ imaps, int64_t nRB,
+              const double* __restrict__ tablesImg, const double* __restrict__ y, size_t pitch, int nRows,
+              double* __restrict__ partial, int32_t* err) {
+  extern __shared__ __align__(128) unsigned char smraw[];
+  __shared__ __align__(8) uint64_t mbar;
+  __shared__ LmmChunk ch;
+  if (threadIdx.x == 0) {
+    int c = 0;
+    while (c + 1 < nChunks && (int)blockIdx.x >= chunks[c].cta0 + chunks[c].nCta) c++;
+    ch = chunks[c];
+  }
+  __syncthreads();
+#define LQ_CASE(N) case N: lmmq_body<N, Q>(ch, imaps, nRB, tablesImg, y, pitch, nRows, partial, smraw, &mbar, err); break;
+  switch (ch.nUnits) {
+    LQ_CASE(1) LQ_CASE(2) LQ_CASE(3) LQ_CASE(4) LQ_CASE(5) LQ_CASE(6)
+    default: lmmq_body<7, Q>(ch, imaps, nRB, tablesImg, y, pitch, nRows, partial, smraw, &mbar, err); break;
+  }
+#undef LQ_CASE
+}
+
+// out[q][col] += sum over the chunk's CTAs of partial[cta][q][slot]; blockIdx.z = q
+__global__ void k_lmm_vecq_final(const LmmChunk* __restrict__ chunks, int nChunks, const int* __restrict__ slotCol,
+                                 const double* __restrict__ partial, double* __restrict__ out, int Q, int nCols) {
+  const int c = blockIdx.x, q = blockIdx.z;
+  if (c >= nChunks) return;
+  const LmmChunk ch = chunks[c];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nWarps = (blockDim.x >> 5) * gridDim.y;
+  for (int u = blockIdx.y * (blockDim.x >> 5) + warp; u < ch.nUnits * 16; u += nWarps) {
+    const int col = slotCol[ch.unit0 * 16 + u];
+    if (col < 0) continue;
+    double s = 0;
+    for (int i = lane; i < ch.nCta; i += 32) s += partial[((size_t)(ch.cta0 + i) * Q + q) * LMM_PART + u];
+#pragma unroll
+    for (int d = 16; d; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
+    if (lane == 0) atomicAdd(&out[(size_t)q * nCols + col], s);
+  }
+}
+
+// --------------------------------------------------------------------------------------------------
 // Decompress from the column-per-lane layout.
 //
 // Same chunks, interleaved maps and table images as k_lmm_vec_u8: lane s of a half-warp owns column slot s of a
@@ -1305,6 +1439,42 @@ int64_t fast_lmm_vec(Matrix* m, const double* dY, double* dOut, cudaStream_t s) 
   return fp->partial ? 2 : 1;
 }
 
+
+// Q = 2 or 4 left rows (rows q of y at y + q * pitch, 16-byte aligned) in one pass; same return values as fast_lmm_vec.
+template <int Q>
+static int64_t fast_lmm_rows_t(Matrix* m, FastPlan* fp, const double* dY, size_t pitch, double* dOut, cudaStream_t s) {
+  int64_t rc;
+  const size_t partBytes = (size_t)fp->lmmGrid * Q * LMM_PART * 8;
+  if ((rc = ensure_scratch(m, partBytes + 256)) < 0) return rc;
+  double* partial = (double*)m->scratch;
+  CLA_CUDA(cudaMemsetAsync(dOut, 0, sizeof(double) * (size_t)Q * m->nCols, s));
+  size_t smem = (size_t)LQ_W * Q * LMM_PART * 8;
+  for (auto& c : fp->lchunks) smem = std::max(smem, (size_t)c.tblDoubles * 8);
+  static bool attr[64] = {};
+  if (!attr[m->device & 63]) {
+    CLA_CUDA(cudaFuncSetAttribute(k_lmm_vecq_u8<Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_MAX - 1024));
+    attr[m->device & 63] = true;
+  }
+  prof_begin(m, s);
+  k_lmm_vecq_u8<Q><<<fp->lmmGrid, LQ_T, smem, s>>>(fp->dLChunks, (int)fp->lchunks.size(), fp->dLmmMaps, fp->nRB, fp->dLmmTables, dY,
+                                                  pitch, m->nRows, partial, m->dErr);
+  prof_end(m, s);
+  k_lmm_vecq_final<<<dim3((unsigned)fp->lchunks.size(), LMM_MAX_UNITS, Q), 512, 0, s>>>(fp->dLChunks, (int)fp->lchunks.size(),
+                                                                                       fp->dSlotCol, partial, dOut, Q, m->nCols);
+  m->stats.kernel_launches += 2;
+  if (m->hasConst)
+    for (int q = 0; q < Q; q++)
+      if ((rc = launch_lmm_const(m, dY + q * pitch, 1, dOut + (size_t)q * m->nCols, s)) < 0) return rc;
+  CLA_CUDA(cudaGetLastError());
+  return fp->partial ? 2 : 1;
+}
+int64_t fast_lmm_rows(Matrix* m, const double* dY, size_t pitch, int q, double* dOut, cudaStream_t s) {
+  FastPlan* fp = m->fast;
+  if (!fp || !fp->ok || ((uintptr_t)dY & 15) || (pitch & 1)) return 0;
+  if (q == 4) return fast_lmm_rows_t<4>(m, fp, dY, pitch, dOut, s);
+  if (q == 2) return fast_lmm_rows_t<2>(m, fp, dY, pitch, dOut, s);
+  return fail(CLA_ERR_BAD_ARG, "fast_lmm_rows: 2 or 4 rows");
+}
 
 // Host-buffer t(y) %*% X with the upload of y overlapped with the product: y is copied in up to LMM_PIPE_MAX row ranges
 // on a second stream, and the kernel for a range starts as soon as its slice has arrived. Returns 0 if the

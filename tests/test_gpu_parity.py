@@ -121,9 +121,9 @@ def test_fast_vector_paths(oracle, nRows, shape):
     assert rel_err(CLALibLeftMultBy.leftMultByMatrix(cmb, y), om.lmm(y), np.abs(y) @ aX + 1e-300) < TOL
     s = aX.T @ (aX @ np.abs(v)) + 1e-300
     assert rel_err(CLALibMMChain.mmChain(cmb, v).ravel(), om.mmchain(v).ravel(), s) < 10 * TOL
-    # a few vectors at once: served by the same kernels, one pass per vector
+    # a few vectors at once: served by the same kernels; left rows go four, two and one at a time (7 = 4 + 2 + 1)
     V = rng.standard_normal((cmb.clen, 4))
-    Y = rng.standard_normal((3, nRows))
+    Y = rng.standard_normal((7, nRows))
     assert rel_err(CLALibRightMultBy.rightMultByMatrix(cmb, V), om.rmm(V), aX @ np.abs(V) + 1e-300) < TOL
     assert rel_err(CLALibLeftMultBy.leftMultByMatrix(cmb, Y), om.lmm(Y), np.abs(Y) @ aX + 1e-300) < TOL
     st = cmb.stats()
