@@ -451,10 +451,10 @@ static int64_t rmm_dev(Matrix* m, const double* dV, int32_t vRows, int32_t vCols
   }
   // A pass of the one-column kernels per column beats the tensor-core kernel (whose time hardly depends on
   // the width up to 64 columns) for a few columns; measured crossover: about 16 columns when every group is
-  // a byte-map DDC group (2M x 200: 0.26 ms per column against 4.3 ms), about 5 when SDC / RLE groups take
-  // the general pass as well (1M x 500, 451 groups: 0.64 ms per column against 3.25 ms).
+  // a byte-map DDC group (2M x 200: 0.26 ms per column against 4.3 ms), about 7 when SDC / RLE groups take
+  // the general pass as well (1M x 500, 451 groups: 0.25 ms per column against 1.9 ms).
   static const int loopEnv = loop_limit("CLA_RMM_LOOP_MAX", -1);  // tuning aid
-  const int loopMax = loopEnv >= 0 ? loopEnv : (fast_plan_partial(m) ? 4 : 12);
+  const int loopMax = loopEnv >= 0 ? loopEnv : (fast_plan_partial(m) ? 7 : 12);
   if (vCols >= 2 && vCols <= loopMax && fast_plan_ok(m) && m->nRows > 0) return rmm_by_vectors(m, dV, vCols, dOut, s);
   return launch_rmm_dmma(m, dV, vCols, dOut, s);  // FP64 tensor cores
 }
