@@ -463,6 +463,9 @@ TMM_CASES = [
     (("unc", "ddc", "sdcs"), ("unc", "rle", "ddc_char", "sdc", "empty")),
     (("ddc",) * 70, ("ddc",) * 3),
     (("ddcfor", "sdcfor", "ddc_bit"), ("sdcsz", "ddc", "ddc")),
+    # mixed left sides against a right side of byte-map dense-map groups only
+    (("ddc", "sdc", "rle", "unc", "ddc2", "sdcz", "const"), ("ddc",) * 5),
+    (("sdc", "ddc_char", "rle"), ("ddc", "ddc2", "ddc_bit", "ddc")),
 ]
 
 
