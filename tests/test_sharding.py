@@ -75,3 +75,33 @@ def test_two_rank_gloo_partials_add_up(oracle):
     assert rel_err(chain.ravel(), X.T @ (X @ v), aX.T @ (aX @ np.abs(v))) < 10 * TOL
     a, b = shard.shard_bounds(cmb.rlen, 2)[0]
     assert rel_err(u0.ravel(), (X @ v)[a:b], (aX @ np.abs(v))[a:b] + 1e-300) < TOL
+
+
+def _exchange_rank(rank, world, port, q):
+    import torch.distributed as dist
+    from systemds_b200.comm import HANDLE_BYTES, torch_exchange
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    got = torch_exchange(None)(bytes([rank + 1]) * HANDLE_BYTES)  # what the ranks do with their 64-byte IPC handles
+    q.put((rank, [g[0] for g in got], [len(g) for g in got]))
+    dist.destroy_process_group()
+
+
+def test_handle_exchange_over_gloo():
+    """The host-side half of the peer-memory all-reduce setup: every rank ends up with all ranks' handles, in rank
+    order (the device half needs GPUs and is covered by the gpu tests)."""
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_exchange_rank, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, firsts, lens in res:
+        assert firsts == [1, 2] and lens == [64, 64]
