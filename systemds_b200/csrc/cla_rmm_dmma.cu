@@ -752,6 +752,7 @@ int64_t launch_rmm_dmma(Matrix* m, const double* dV, int vCols, double* dOut, cu
   if (!attr) {
     CLA_CUDA(cudaFuncSetAttribute(k_rmm_dmma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     CLA_CUDA(cudaFuncSetAttribute(k_rmm_dmma3<8, 12, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+    CLA_CUDA(cudaFuncSetAttribute(k_rmm_dmma3<8, 16, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
     CLA_CUDA(cudaFuncSetAttribute(k_rmm_dmma3<4, 16, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
     attr = true;
   }
@@ -759,10 +760,14 @@ int64_t launch_rmm_dmma(Matrix* m, const double* dV, int vCols, double* dOut, cu
   if (m->spListsOk && (m->nSparse == 0 || (int64_t)m->totalVals * vCols * 8 < (1ll << 32))) {  // table-row offsets are 32-bit
     static const int wideEnv = getenv("CLA_RMM_WIDE_TILES") ? atoi(getenv("CLA_RMM_WIDE_TILES")) : -1;  // tuning aid
     const bool wide = wideEnv >= 0 ? wideEnv != 0 : vCols > 32;  // 64 output columns per CTA, or 32
-    const int TN = wide ? 64 : 32, W = wide ? 12 : 16;
-    const int kMax = wide ? G3<8, 12>::KMAX : G3<4, 16>::KMAX;
-    const int ldb = TN + 4, wbuf = wide ? G3<8, 12>::WBUF : G3<4, 16>::WBUF;
     const int nUnits = (m->nRows + G3_UNIT - 1) / G3_UNIT;
+    // 64-column tile: 12 warps of 166 registers are 9 % faster per row than 16 warps of 128 (which spill), but a warp
+    // works on whole 512-row units, so below two units per warp the 16-warp CTA finishes in fewer rounds (1M rows:
+    // 2.6 ms against 3.5 ms under the profiler; 4M rows: 9.8 against 8.9 ms)
+    const bool w12 = wide && nUnits >= 2 * 12 * std::max(1, m->smCount / ((vCols + 63) / 64));  // CTAs along the rows
+    const int TN = wide ? 64 : 32, W = w12 ? 12 : 16;
+    const int kMax = wide ? (w12 ? G3<8, 12>::KMAX : G3<8, 16>::KMAX) : G3<4, 16>::KMAX;
+    const int ldb = TN + 4, wbuf = wide ? (w12 ? G3<8, 12>::WBUF : G3<8, 16>::WBUF) : G3<4, 16>::WBUF;
     const int gridY = (vCols + TN - 1) / TN;
     dim3 grid((unsigned)std::max(1, std::min(std::max(1, m->smCount / gridY), (nUnits + W - 1) / W)), gridY);
     const DenseDesc* dd = (const DenseDesc*)m->dDenseDesc;
@@ -774,7 +779,7 @@ int64_t launch_rmm_dmma(Matrix* m, const double* dV, int vCols, double* dOut, cu
       // 64-column tile: 12 warps of up to 170 registers (no spills; 16 warps of 128 registers spilled 320 bytes) and 8
       // table rows in flight in the sparse phase. Measured on 4M rows of the mixed benchmark matrix, ms per product:
       // 8 / 10 / 12 / 14 / 16 warps 10.8 / 10.5 / 8.9 / 9.4 / 9.8; with 12 warps 2 / 4 / 8 table rows 10.0 / 9.0 / 8.9.
-      auto kern = wide ? k_rmm_dmma3<8, 12, 8> : k_rmm_dmma3<4, 16, 8>;
+      auto kern = wide ? (w12 ? k_rmm_dmma3<8, 12, 8> : k_rmm_dmma3<8, 16, 4>) : k_rmm_dmma3<4, 16, 8>;
       kern<<<grid, W * 32, smem3, s>>>(dd + k0, nk, first ? (const SpItem*)m->dStepItems : nullptr,
                                        first ? m->dStepPtr : nullptr, (const SpItem*)m->dWinItems, m->dWinPtr, m->nRows, dV,
                                        vCols, P, first ? constRow : nullptr, dOut, first ? 0 : 1);
